@@ -1,0 +1,158 @@
+/*
+ * race_b200.h -- C ABI of the B200 (sm_100a) RACE-attention prefix-path library.
+ *
+ * Plain pointers and sizes only; no torch types.  Every entry point enqueues work on the
+ * caller's stream and returns without synchronising (the *_host entry points are the one
+ * exception and say so).  Buffers are caller-owned.  Return value of every int function:
+ *   0                      success
+ *   < 0                    argument error (RACE_ERR_* below); nothing was launched
+ *   > 0                    the first cudaError_t the launcher met
+ * The pattern (raw pointers + shape struct + stream, first error returned, unsupported
+ * shapes rejected with an error code instead of an exception) follows the reference's
+ * plain-C++ launcher layer, src/causal_v2/kernels/race_causal_fwd.h:44-66,126-130.
+ *
+ * Tensor layouts (row-major, contiguous, 16-byte aligned base pointers):
+ *   probsQ, probsK : [N, T, L, R]   bucket probabilities, element type = shape.dtype
+ *   V, out         : [N, T, d_k]    element type = shape.dtype
+ *   state          : [N, S*(d_k+1)] fp32, S = L*R; for one stream B[s][c] at s*d_k + c and
+ *                    A[s] at S*d_k + s  (A = sum of key probabilities, B = sum of pK (x) v)
+ * N = M*B*H independent streams (the reference's BatchedACE flattens [M,B,T,H,d_k] to
+ * [N,T,d_k], src/race_baseline.py:35-40).
+ */
+#ifndef RACE_B200_H_
+#define RACE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { RACE_DTYPE_F32 = 0, RACE_DTYPE_BF16 = 1 };
+
+/* kernel families: AUTO picks TENSOR when the shape is supported by it, else SIMT */
+enum { RACE_VARIANT_AUTO = 0, RACE_VARIANT_SIMT = 1, RACE_VARIANT_TENSOR = 2 };
+
+enum {
+    RACE_OK = 0,
+    RACE_ERR_NULL = -1,        /* a required pointer is NULL */
+    RACE_ERR_SHAPE = -2,       /* shape outside the supported range */
+    RACE_ERR_ALIGN = -3,       /* pointer or row not 16-byte aligned */
+    RACE_ERR_WORKSPACE = -4,   /* workspace_bytes smaller than required */
+    RACE_ERR_TILE = -5,        /* tile_tokens not a positive multiple of the chunk length */
+    RACE_ERR_VARIANT = -6,     /* variant unknown or not available for this shape */
+    RACE_ERR_DEVICE_WAIT = -7  /* a bounded device-side wait ran out (read from status word) */
+};
+
+typedef struct RaceShape {
+    int64_t n_streams; /* N = M*B*H */
+    int64_t seq_len;   /* T (may be 0: returns without launching) */
+    int32_t n_tables;  /* L */
+    int32_t n_buckets; /* R = 2^K buckets per table */
+    int32_t head_dim;  /* d_k */
+    int32_t dtype;     /* RACE_DTYPE_* of probsQ/probsK/V/out */
+    float eps;         /* added to A before the divide; the reference uses 1e-6 */
+    int32_t reserved;  /* must be 0 */
+} RaceShape;
+
+/* Library / ABI version (major*1000 + minor). */
+int race_b200_version(void);
+
+/* Static, NUL-terminated description of a return code of this library. */
+const char* race_b200_error_string(int code);
+
+/* 1 if the shape can run with the given variant, else 0.
+ * Replaces race::causal::is_supported (src/causal_v2/kernels/race_causal_fwd.h:72). */
+int race_b200_is_supported(const RaceShape* shape, int variant);
+
+/* Floats in a state / carry buffer: N * L*R * (d_k + 1).
+ * Replaces final_state_floats (src/causal_v2/kernels/race_causal_fwd.h:101). */
+size_t race_b200_state_floats(const RaceShape* shape);
+
+/* Tokens per state tile the launcher would pick for this shape on the current device.
+ * Replaces race_causal_select_tile_tokens (src/causal_v2/kernels/race_causal_fwd.h:89-90). */
+int race_b200_select_tile_tokens(const RaceShape* shape, int variant, int* tile_tokens);
+
+/* Bytes of workspace race_b200_causal_fwd / race_b200_tile_totals need for this tile length
+ * (tile_tokens = 0: the automatic one).  Replaces workspace_floats (:99). */
+size_t race_b200_causal_workspace_bytes(const RaceShape* shape, int tile_tokens, int variant);
+
+/*
+ * Causal per-bucket prefix forward:
+ *   out[n,t,:] = sum_s pQ[n,t,s] * B_t[n,s,:] / (A_t[n,s] + eps),
+ *   A_t = carry_A + sum_{j<=t} pK[n,j,:],  B_t = carry_B + sum_{j<=t} pK[n,j,:] (x) V[n,j,:].
+ * This is BatchedACE.forward's cumsum / divide / bmm (src/race_baseline.py:45-51) and, with
+ * carry_in, one chunk step of chunked_forward (src/race_chunked.py:54-63), without ever
+ * materialising a T axis.  Replaces race_causal_forward
+ * (src/causal_v2/kernels/race_causal_fwd.h:126-130) at the probabilities boundary.
+ *   carry_in   nullable; state layout; sums over tokens that precede this call's first token
+ *   state_out  nullable; state layout; carry_in + sums over all T tokens of this call
+ *   workspace  >= race_b200_causal_workspace_bytes(); contents undefined on entry
+ *   status     nullable device int32; set non-zero by a kernel whose bounded wait ran out
+ */
+int race_b200_causal_fwd(const void* probs_q, const void* probs_k, const void* v, void* out,
+                         const float* carry_in, float* state_out, void* workspace,
+                         size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
+                         int variant, void* stream, int* status);
+
+/*
+ * Totals of a token range: totals[n] = (sum_t pK (x) V, sum_t pK) in state layout.  Pass 1 of
+ * the sequence-sharded driver and the reduction of the non-causal forward
+ * (the `pref[:, -1:]` carry of src/race_chunked.py:62-63 without forming prefixes;
+ * role of race_causal_tile_sums + the scan's final_state, race_causal_fwd.h:104-113).
+ */
+int race_b200_tile_totals(const void* probs_k, const void* v, float* totals, void* workspace,
+                          size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
+                          void* stream);
+
+/*
+ * Non-causal per-bucket forward (upstream scaling/benchmark_time.py:155-162 as quoted in the
+ * reference's analysis/hot-path.md:157-162):
+ *   Bs = pK^T V, A = sum_t pK, E = Bs/(A+eps), out = pQ E.
+ * totals (state layout, required) receives (Bs, A); it is what the backward needs saved
+ * (the reference saves the same reduced sums, src/noncausal/ops.py:29-33).
+ * Replaces race_forward (src/noncausal/kernels/race_fwd.h:66-68) at the probabilities boundary.
+ */
+int race_b200_noncausal_fwd(const void* probs_q, const void* probs_k, const void* v, void* out,
+                            float* totals, void* workspace, size_t workspace_bytes,
+                            const RaceShape* shape, void* stream);
+
+/* Bytes of workspace the non-causal backward needs. */
+size_t race_b200_noncausal_bwd_workspace_bytes(const RaceShape* shape);
+
+/*
+ * Non-causal backward: gradients w.r.t. probsQ, probsK, V given d_out and the forward's
+ * totals.  d_probs_q / d_probs_k / d_v have the layouts and dtype of their primals.
+ * Replaces race_backward (src/noncausal/kernels/race_bwd.h:81-85) for the per-bucket form.
+ */
+int race_b200_noncausal_bwd(const void* probs_q, const void* probs_k, const void* v,
+                            const float* totals, const void* d_out, void* d_probs_q,
+                            void* d_probs_k, void* d_v, void* workspace, size_t workspace_bytes,
+                            const RaceShape* shape, void* stream);
+
+/*
+ * Bucket-probability producer (src/race_baseline.py:41-44):
+ *   probs[row, l, :] = softmax_r( (tanh(x[row] . planes[l,k]) / sqrt(d_k)) . corner_r ),
+ * corner r has +1 on plane k iff bit (K-1-k) of r is set.  x [rows, d_k] (dtype_x),
+ * planes [L*K, d_k] fp32 (row-major: planes_T transposed), probs [rows, L, 2^K] (dtype_probs).
+ */
+int race_b200_bucket_probs(const void* x, const float* planes, void* probs, int64_t rows,
+                           int32_t d_k, int32_t n_tables, int32_t n_bits, int32_t dtype_x,
+                           int32_t dtype_probs, void* stream);
+
+/*
+ * Host-buffer causal forward: same arithmetic as race_b200_causal_fwd with every tensor in
+ * HOST memory (pinned for full copy bandwidth).  Allocates device staging buffers, streams
+ * the sequence through them in segments (copy-in, kernel and copy-out overlapped on three
+ * streams, the carry staying on the device between segments) and SYNCHRONISES before
+ * returning.  segment_tokens = 0 picks a default.  device = CUDA ordinal to run on.
+ */
+int race_b200_causal_fwd_host(const void* probs_q, const void* probs_k, const void* v, void* out,
+                              const float* carry_in, float* state_out, const RaceShape* shape,
+                              int64_t segment_tokens, int variant, int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RACE_B200_H_ */

@@ -1,0 +1,13 @@
+"""B200-native (sm_100a) RACE-attention prefix path.
+
+Public surface:
+  BatchedACE                      drop-in operator (signature of src/race_baseline.py:21-52)
+  race_causal_prefix              probabilities-level causal forward (the hot path)
+  race_tile_totals                per-stream totals (A, B) of a token range
+  race_noncausal                  non-causal forward with autograd
+  bucket_probs                    bucket-probability producer
+"""
+from .operator import BatchedACE  # noqa: F401
+from .ops import (bucket_probs, is_supported, pack_state, race_causal_prefix,  # noqa: F401
+                  race_causal_prefix_host, race_noncausal, race_tile_totals, select_tile_tokens,
+                  unpack_state)

@@ -1,0 +1,270 @@
+// extern "C" entry points: argument validation, workspace bookkeeping and dispatch to the
+// kernel families.  Nothing here synchronises or allocates, except the *_host entry point.
+#include <cstdio>
+#include <cstring>
+
+#include "launch.h"
+
+using namespace race;
+
+namespace {
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int elt_bytes(int dtype) { return dtype == RACE_DTYPE_BF16 ? 2 : 4; }
+
+// Shape checks shared by every entry point.  Rows of probs ([S] elements) and of V ([d_k]
+// elements) must be multiples of 16 bytes: all tile loads are 16-byte vector or TMA loads.
+int check_shape(const RaceShape* sh, Dims* dm) {
+    if (!sh) return RACE_ERR_NULL;
+    if (sh->dtype != RACE_DTYPE_F32 && sh->dtype != RACE_DTYPE_BF16) return RACE_ERR_SHAPE;
+    if (sh->reserved != 0) return RACE_ERR_SHAPE;
+    if (sh->n_streams < 0 || sh->seq_len < 0) return RACE_ERR_SHAPE;
+    if (sh->n_tables <= 0 || sh->n_buckets <= 0 || sh->head_dim <= 0) return RACE_ERR_SHAPE;
+    if ((int64_t)sh->n_tables * sh->n_buckets > 4096) return RACE_ERR_SHAPE;
+    if (!(sh->eps >= 0.f)) return RACE_ERR_SHAPE;
+    dm->N = sh->n_streams;
+    dm->T = sh->seq_len;
+    dm->S = sh->n_tables * sh->n_buckets;
+    dm->D = sh->head_dim;
+    dm->eps = sh->eps;
+    const int eb = elt_bytes(sh->dtype);
+    if ((dm->S * eb) % 16 != 0 || (dm->D * eb) % 16 != 0) return RACE_ERR_ALIGN;
+    return RACE_OK;
+}
+
+int sm_count() {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess)
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms > 0 ? sms : 148;
+}
+
+int resolve_variant(const Dims& dm, int dtype, int variant) {
+    if (variant == RACE_VARIANT_AUTO)
+        return tensor_supported(dm, dtype) ? RACE_VARIANT_TENSOR : RACE_VARIANT_SIMT;
+    return variant;
+}
+
+bool variant_supported(const Dims& dm, int dtype, int variant) {
+    if (variant == RACE_VARIANT_SIMT) return simt_supported(dm);
+    if (variant == RACE_VARIANT_TENSOR) return tensor_supported(dm, dtype);
+    return false;
+}
+
+int chunk_of(int variant) { return variant == RACE_VARIANT_TENSOR ? tensor_chunk_tokens() : kSimtChunk; }
+
+int pick_tile(const Dims& dm, int dtype, int variant) {
+    if (variant == RACE_VARIANT_TENSOR) return tensor_default_tile_tokens(dm, dtype, sm_count());
+    return simt_default_tile_tokens(dm, sm_count());
+}
+
+size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile) {
+    if (dm.T == 0 || dm.N == 0) return 0;
+    if (variant == RACE_VARIANT_TENSOR) return tensor_workspace_bytes(dm, dtype, tile);
+    const int64_t tiles = (dm.T + tile - 1) / tile;
+    return (size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
+}
+
+}  // namespace
+
+extern "C" {
+
+int race_b200_version(void) { return 1000; }
+
+const char* race_b200_error_string(int code) {
+    switch (code) {
+        case RACE_OK: return "ok";
+        case RACE_ERR_NULL: return "a required pointer is NULL";
+        case RACE_ERR_SHAPE: return "shape outside the supported range";
+        case RACE_ERR_ALIGN: return "pointer or row not 16-byte aligned";
+        case RACE_ERR_WORKSPACE: return "workspace too small";
+        case RACE_ERR_TILE: return "tile_tokens is not a positive multiple of the chunk length";
+        case RACE_ERR_VARIANT: return "kernel variant unknown or unavailable for this shape";
+        case RACE_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString((cudaError_t)code);
+    return "unknown error";
+}
+
+int race_b200_is_supported(const RaceShape* shape, int variant) {
+    Dims dm;
+    if (check_shape(shape, &dm) != RACE_OK) return 0;
+    const int var = resolve_variant(dm, shape->dtype, variant);
+    return variant_supported(dm, shape->dtype, var) ? 1 : 0;
+}
+
+size_t race_b200_state_floats(const RaceShape* shape) {
+    Dims dm;
+    if (check_shape(shape, &dm) != RACE_OK) return 0;
+    return (size_t)dm.N * state_floats_per_stream(dm.S, dm.D);
+}
+
+int race_b200_select_tile_tokens(const RaceShape* shape, int variant, int* tile_tokens) {
+    Dims dm;
+    if (!tile_tokens) return RACE_ERR_NULL;
+    int rc = check_shape(shape, &dm);
+    if (rc != RACE_OK) return rc;
+    const int var = resolve_variant(dm, shape->dtype, variant);
+    if (!variant_supported(dm, shape->dtype, var)) return RACE_ERR_VARIANT;
+    *tile_tokens = pick_tile(dm, shape->dtype, var);
+    return RACE_OK;
+}
+
+size_t race_b200_causal_workspace_bytes(const RaceShape* shape, int tile_tokens, int variant) {
+    Dims dm;
+    if (check_shape(shape, &dm) != RACE_OK) return 0;
+    const int var = resolve_variant(dm, shape->dtype, variant);
+    if (!variant_supported(dm, shape->dtype, var)) return 0;
+    const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, var);
+    return workspace_bytes_for(dm, shape->dtype, var, tile);
+}
+
+int race_b200_causal_fwd(const void* probs_q, const void* probs_k, const void* v, void* out,
+                         const float* carry_in, float* state_out, void* workspace,
+                         size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
+                         int variant, void* stream, int* status) {
+    Dims dm;
+    int rc = check_shape(shape, &dm);
+    if (rc != RACE_OK) return rc;
+    const int var = resolve_variant(dm, shape->dtype, variant);
+    if (var != RACE_VARIANT_SIMT && var != RACE_VARIANT_TENSOR) return RACE_ERR_VARIANT;
+    if (!variant_supported(dm, shape->dtype, var)) return var == variant ? RACE_ERR_VARIANT : RACE_ERR_SHAPE;
+    if (tile_tokens < 0) return RACE_ERR_TILE;
+    const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, var);
+    if (tile % chunk_of(var) != 0) return RACE_ERR_TILE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t sf = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D);
+    if (dm.N == 0) return RACE_OK;
+    if (dm.T == 0) {
+        // nothing to launch: the state passes through
+        if (state_out) {
+            cudaError_t e = carry_in
+                ? cudaMemcpyAsync(state_out, carry_in, sf * sizeof(float), cudaMemcpyDeviceToDevice, st)
+                : cudaMemsetAsync(state_out, 0, sf * sizeof(float), st);
+            return (int)e;
+        }
+        return RACE_OK;
+    }
+    if (!probs_q || !probs_k || !v || !out || !workspace) return RACE_ERR_NULL;
+    if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(out) ||
+        !aligned16(workspace) || !aligned16(carry_in) || !aligned16(state_out))
+        return RACE_ERR_ALIGN;
+    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, var, tile)) return RACE_ERR_WORKSPACE;
+    if (var == RACE_VARIANT_TENSOR)
+        return (int)causal_fwd_tensor(probs_q, probs_k, v, out, carry_in, state_out, workspace,
+                                      dm, shape->dtype, tile, st, status);
+    return (int)causal_fwd_simt(probs_q, probs_k, v, out, carry_in, state_out, (float*)workspace,
+                                dm, shape->dtype, tile, false, st);
+}
+
+int race_b200_tile_totals(const void* probs_k, const void* v, float* totals, void* workspace,
+                          size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
+                          void* stream) {
+    Dims dm;
+    int rc = check_shape(shape, &dm);
+    if (rc != RACE_OK) return rc;
+    if (!simt_supported(dm)) return RACE_ERR_SHAPE;
+    if (tile_tokens < 0) return RACE_ERR_TILE;
+    const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, RACE_VARIANT_SIMT);
+    if (tile % kSimtChunk != 0) return RACE_ERR_TILE;
+    if (!totals) return RACE_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t sf = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D);
+    if (dm.N == 0) return RACE_OK;
+    if (dm.T == 0) return (int)cudaMemsetAsync(totals, 0, sf * sizeof(float), st);
+    if (!probs_k || !v || !workspace) return RACE_ERR_NULL;
+    if (!aligned16(probs_k) || !aligned16(v) || !aligned16(totals) || !aligned16(workspace))
+        return RACE_ERR_ALIGN;
+    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, RACE_VARIANT_SIMT, tile))
+        return RACE_ERR_WORKSPACE;
+    return (int)causal_fwd_simt(nullptr, probs_k, v, nullptr, nullptr, totals, (float*)workspace, dm,
+                                shape->dtype, tile, true, st);
+}
+
+int race_b200_noncausal_fwd(const void* probs_q, const void* probs_k, const void* v, void* out,
+                            float* totals, void* workspace, size_t workspace_bytes,
+                            const RaceShape* shape, void* stream) {
+    Dims dm;
+    int rc = check_shape(shape, &dm);
+    if (rc != RACE_OK) return rc;
+    if (!simt_supported(dm)) return RACE_ERR_SHAPE;
+    if (dm.N == 0) return RACE_OK;
+    if (!totals) return RACE_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t sf = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D);
+    if (dm.T == 0) return (int)cudaMemsetAsync(totals, 0, sf * sizeof(float), st);
+    if (!probs_q || !probs_k || !v || !out || !workspace) return RACE_ERR_NULL;
+    if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(out) ||
+        !aligned16(totals) || !aligned16(workspace))
+        return RACE_ERR_ALIGN;
+    const int tile = pick_tile(dm, shape->dtype, RACE_VARIANT_SIMT);
+    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, RACE_VARIANT_SIMT, tile))
+        return RACE_ERR_WORKSPACE;
+    cudaError_t e = causal_fwd_simt(nullptr, probs_k, v, nullptr, nullptr, totals, (float*)workspace,
+                                    dm, shape->dtype, tile, true, st);
+    if (e != cudaSuccess) return (int)e;
+    return (int)noncausal_query(probs_q, totals, out, dm, shape->dtype, sm_count(), st);
+}
+
+size_t race_b200_noncausal_bwd_workspace_bytes(const RaceShape* shape) {
+    Dims dm;
+    if (check_shape(shape, &dm) != RACE_OK || !simt_supported(dm)) return 0;
+    const int tile = pick_tile(dm, shape->dtype, RACE_VARIANT_SIMT);
+    const size_t sf = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
+    const size_t tile_ws = workspace_bytes_for(dm, shape->dtype, RACE_VARIANT_SIMT, tile);
+    return (tile_ws + 255) / 256 * 256 + 2 * ((sf + 255) / 256 * 256);
+}
+
+int race_b200_noncausal_bwd(const void* probs_q, const void* probs_k, const void* v,
+                            const float* totals, const void* d_out, void* d_probs_q,
+                            void* d_probs_k, void* d_v, void* workspace, size_t workspace_bytes,
+                            const RaceShape* shape, void* stream) {
+    Dims dm;
+    int rc = check_shape(shape, &dm);
+    if (rc != RACE_OK) return rc;
+    if (!simt_supported(dm)) return RACE_ERR_SHAPE;
+    if (dm.N == 0 || dm.T == 0) return RACE_OK;
+    if (!probs_q || !probs_k || !v || !totals || !d_out || !d_probs_q || !d_probs_k || !d_v ||
+        !workspace)
+        return RACE_ERR_NULL;
+    if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(totals) ||
+        !aligned16(d_out) || !aligned16(d_probs_q) || !aligned16(d_probs_k) || !aligned16(d_v) ||
+        !aligned16(workspace))
+        return RACE_ERR_ALIGN;
+    if (workspace_bytes < race_b200_noncausal_bwd_workspace_bytes(shape)) return RACE_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int tile = pick_tile(dm, shape->dtype, RACE_VARIANT_SIMT);
+    const size_t sfb = ((size_t)dm.N * state_floats_per_stream(dm.S, dm.D) * sizeof(float) + 255) / 256 * 256;
+    const size_t tile_ws = workspace_bytes_for(dm, shape->dtype, RACE_VARIANT_SIMT, tile);
+    // layout: [tile workspace | dE state | (dBs, dA) state], each part 256-byte aligned
+    float* ws_tiles = (float*)workspace;
+    float* dE_state = (float*)((char*)workspace + ((tile_ws + 255) / 256 * 256));
+    float* grads = (float*)((char*)dE_state + sfb);
+    // dE = pQ^T dO : the tile-totals pass with (pQ, dO) in the roles of (pK, V)
+    cudaError_t e = causal_fwd_simt(nullptr, probs_q, d_out, nullptr, nullptr, dE_state, ws_tiles, dm,
+                                    shape->dtype, tile, true, st);
+    if (e != cudaSuccess) return (int)e;
+    e = noncausal_state_grads(totals, dE_state, grads, dm, st);
+    if (e != cudaSuccess) return (int)e;
+    return (int)noncausal_token_grads(probs_k, v, d_out, totals, grads, d_probs_q, d_probs_k, d_v, dm,
+                                      shape->dtype, sm_count(), st);
+}
+
+int race_b200_bucket_probs(const void* x, const float* planes, void* probs, int64_t rows,
+                           int32_t d_k, int32_t n_tables, int32_t n_bits, int32_t dtype_x,
+                           int32_t dtype_probs, void* stream) {
+    if (rows < 0 || d_k <= 0 || d_k > 256 || n_tables <= 0 || n_bits < 1 || n_bits > 6 ||
+        n_tables * n_bits > 64)
+        return RACE_ERR_SHAPE;
+    if ((dtype_x != RACE_DTYPE_F32 && dtype_x != RACE_DTYPE_BF16) ||
+        (dtype_probs != RACE_DTYPE_F32 && dtype_probs != RACE_DTYPE_BF16))
+        return RACE_ERR_SHAPE;
+    if (rows == 0) return RACE_OK;
+    if (!x || !planes || !probs) return RACE_ERR_NULL;
+    return (int)bucket_probs(x, planes, probs, rows, d_k, n_tables, n_bits, dtype_x, dtype_probs,
+                             (cudaStream_t)stream);
+}
+
+}  // extern "C"

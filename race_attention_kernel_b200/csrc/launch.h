@@ -1,0 +1,41 @@
+// Internal launcher interfaces shared by the translation units of the library.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+
+namespace race {
+
+// ---- CUDA-core causal path (causal_simt.cu) -------------------------------------------------
+int simt_groups(int S);
+bool simt_supported(const Dims& dm);
+int simt_default_tile_tokens(const Dims& dm, int sm_count);
+// tile totals -> scan -> outputs; totals_only stops after the scan and writes only state_out.
+cudaError_t causal_fwd_simt(const void* pq, const void* pk, const void* v, void* out,
+                            const float* carry_in, float* state_out, float* ws, const Dims& dm,
+                            int dtype, int tile_tokens, bool totals_only, cudaStream_t stream);
+
+// ---- non-causal path (noncausal_simt.cu) ------------------------------------------------------
+cudaError_t noncausal_query(const void* pq, const float* totals, void* out, const Dims& dm, int dtype,
+                            int sm_count, cudaStream_t stream);
+cudaError_t noncausal_state_grads(const float* totals, const float* dE_state, float* grads,
+                                  const Dims& dm, cudaStream_t stream);
+cudaError_t noncausal_token_grads(const void* pk, const void* v, const void* dout, const float* totals,
+                                  const float* grads, void* dpq, void* dpk, void* dv, const Dims& dm,
+                                  int dtype, int sm_count, cudaStream_t stream);
+
+// ---- bucket-probability producer (bucket_probs.cu) --------------------------------------------
+cudaError_t bucket_probs(const void* x, const float* planes, void* probs, int64_t rows, int d, int L,
+                         int K, int dtype_x, int dtype_probs, cudaStream_t stream);
+
+// ---- tcgen05 tensor-core causal path (causal_tc.cu) ------------------------------------------
+bool tensor_supported(const Dims& dm, int dtype);
+int tensor_chunk_tokens();
+int tensor_default_tile_tokens(const Dims& dm, int dtype, int sm_count);
+size_t tensor_workspace_bytes(const Dims& dm, int dtype, int tile_tokens);
+cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
+                              const float* carry_in, float* state_out, void* ws, const Dims& dm,
+                              int dtype, int tile_tokens, cudaStream_t stream, int* status);
+
+}  // namespace race

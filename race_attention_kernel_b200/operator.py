@@ -1,0 +1,69 @@
+"""Drop-in operator: ``BatchedACE`` with the reference's constructor and call signature.
+
+    ace = BatchedACE(d_k, K, L, M)            # buffers drawn like the reference (CPU RNG)
+    ace = ace.cuda()
+    out = ace(Khf, Vhf, Qhf)                  # argument order K, V, Q; each [M,B,T,H,d_k]
+
+(src/race_baseline.py:21-52).  Buffers keep the reference's names and shapes (``planes_T``
+[d_k, L*K], ``protos_T`` [K, R]) so code that overwrites ``ace.planes_T`` keeps working.
+The forward runs on the GPU only: bucket probabilities come from the producer kernel and the
+cumsum/divide/bmm of the reference is replaced by the prefix kernel.  Host tensors are
+accepted and streamed through the device; there is no CPU compute path.
+"""
+from __future__ import annotations
+
+import itertools
+
+import torch
+from torch import nn
+
+from . import ops
+
+
+class BatchedACE(nn.Module):
+    def __init__(self, d_k, K, L, M, device="cpu", share_planes=True):
+        super().__init__()
+        assert share_planes, "reference config uses shared planes"
+        self.d_k, self.K, self.L, self.M = d_k, K, L, M
+        self.R = 1 << K
+        # drawn exactly like the reference (src/race_baseline.py:27-32) so that a seeded
+        # construction gives the same planes
+        planes = torch.randn(L, K, d_k, device=device)
+        self.register_buffer("planes_T", planes.view(L * K, d_k).T)
+        corners = torch.tensor(list(itertools.product([-1.0, 1.0], repeat=K)), device=device)
+        self.register_buffer("protos_T", corners.T)
+        self.eps = 1e-6
+        self.variant = "auto"
+
+    def _streams(self, x: torch.Tensor) -> torch.Tensor:
+        M, B, T, H, dk = x.shape
+        return x.permute(0, 1, 3, 2, 4).contiguous().view(M * B * H, T, dk)
+
+    def bucket_probs(self, x2: torch.Tensor) -> torch.Tensor:
+        """[N,T,d_k] -> [N,T,L,R] with this module's planes."""
+        planes = self.planes_T.T.contiguous().float()
+        return ops.bucket_probs(x2, planes, self.L, self.K)
+
+    @torch.no_grad()
+    def forward(self, Khf, Vhf, Qhf, *, carry_in=None, return_state=False):
+        if not (Khf.shape == Vhf.shape == Qhf.shape) or Khf.dim() != 5:
+            raise RuntimeError("expected K, V, Q of identical shape [M,B,T,H,d_k]")
+        M, B, T, H, dk = Khf.shape
+        if dk != self.d_k:
+            raise RuntimeError(f"d_k mismatch: module {self.d_k}, input {dk}")
+        host = not Khf.is_cuda
+        dev = self.planes_T.device if self.planes_T.is_cuda else torch.device("cuda", torch.cuda.current_device())
+        if host:
+            Khf, Vhf, Qhf = (t.to(dev, non_blocking=True) for t in (Khf, Vhf, Qhf))
+        if Khf.dtype not in (torch.float32, torch.bfloat16):
+            raise RuntimeError("fp32 or bf16 inputs only")
+        K2, Q2, V2 = self._streams(Khf), self._streams(Qhf), self._streams(Vhf)
+        pK = self.bucket_probs(K2)
+        pQ = self.bucket_probs(Q2)
+        res = ops.race_causal_prefix(pQ, pK, V2, self.eps, carry_in=carry_in,
+                                     return_state=return_state, variant=self.variant)
+        out2 = res[0] if return_state else res
+        out = out2.view(M, B, H, T, dk).permute(0, 1, 3, 2, 4)
+        if host:
+            out = out.cpu()
+        return (out, res[1], res[2]) if return_state else out

@@ -1,0 +1,241 @@
+"""Probabilities-level operators on the C-ABI library.
+
+``race_causal_prefix`` is the hot path: what ``BatchedACE.forward`` does after it has the
+bucket probabilities (src/race_baseline.py:45-51), with an optional carried state
+(src/race_chunked.py:54-63).  ``race_noncausal`` is the full-sequence form with gradients.
+Tensors must be CUDA, contiguous, fp32 or bf16; violations raise ``RuntimeError`` the way the
+reference's binding does (src/causal_v2/kernels/torch_binding.cpp:74-90).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16}
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check_inputs(probsQ, probsK, V, need_q=True):
+    tensors = [("probsK", probsK), ("V", V)] + ([("probsQ", probsQ)] if need_q else [])
+    for name, t in tensors:
+        if not isinstance(t, torch.Tensor):
+            raise RuntimeError(f"{name} must be a tensor")
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor (there is no CPU path)")
+        if t.dtype not in _DTYPES:
+            raise RuntimeError(f"{name}: dtype {t.dtype} not supported (float32 or bfloat16)")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+        if t.device != V.device or t.dtype != V.dtype:
+            raise RuntimeError(f"{name}: device/dtype differ from V")
+    if probsK.dim() != 4 or V.dim() != 3:
+        raise RuntimeError("expected probs [N,T,L,R] and V [N,T,d_k]")
+    if need_q and probsQ.shape != probsK.shape:
+        raise RuntimeError("probsQ and probsK shapes differ")
+    N, T, L, R = probsK.shape
+    if V.shape[0] != N or V.shape[1] != T:
+        raise RuntimeError("V does not match probs in N or T")
+    return N, T, L, R, V.shape[2]
+
+
+def make_shape(N, T, L, R, dk, dtype, eps) -> _lib.RaceShape:
+    return _lib.RaceShape(N, T, L, R, dk, _DTYPES[dtype], float(eps), 0)
+
+
+def pack_state(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    """(A [N,L,R], B [N,L,R,d_k]) -> packed fp32 state [N, S*d_k + S] (B first, then A)."""
+    N = A.shape[0]
+    return torch.cat([B.reshape(N, -1).float(), A.reshape(N, -1).float()], dim=1).contiguous()
+
+
+def unpack_state(state: torch.Tensor, L: int, R: int, dk: int):
+    N = state.shape[0]
+    S = L * R
+    return state[:, S * dk:].reshape(N, L, R), state[:, : S * dk].reshape(N, L, R, dk)
+
+
+def select_tile_tokens(N, T, L, R, dk, dtype=torch.float32, variant="auto") -> int:
+    sh = make_shape(N, T, L, R, dk, dtype, 1e-6)
+    out = ctypes.c_int(0)
+    _lib.check(_lib.lib().race_b200_select_tile_tokens(ctypes.byref(sh), _lib.VARIANTS[variant],
+                                                       ctypes.byref(out)), "select_tile_tokens")
+    return out.value
+
+
+def is_supported(N, T, L, R, dk, dtype=torch.float32, variant="auto") -> bool:
+    sh = make_shape(N, T, L, R, dk, dtype, 1e-6)
+    return bool(_lib.lib().race_b200_is_supported(ctypes.byref(sh), _lib.VARIANTS[variant]))
+
+
+def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
+                       return_state: bool = False, tile_tokens: int = 0, variant: str = "auto",
+                       out: torch.Tensor | None = None):
+    """out[n,t,:] = sum_s pQ[n,t,s] * B_t[n,s,:] / (A_t[n,s] + eps) with inclusive prefixes
+    A_t, B_t (src/race_baseline.py:45-51).
+
+    carry_in: None, a packed state [N, S*d_k+S] or a tuple (A [N,L,R], B [N,L,R,d_k]) holding the
+    sums over tokens before this call's first token.  return_state=True also returns (A, B)
+    after the last token.  tile_tokens / variant are test hooks (0 / "auto" = automatic).
+    """
+    N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
+    if variant not in _lib.VARIANTS:
+        raise RuntimeError(f"unknown variant {variant!r}")
+    L_ = _lib.lib()
+    sh = make_shape(N, T, L, R, dk, V.dtype, eps)
+    var = _lib.VARIANTS[variant]
+    carry = None
+    if carry_in is not None:
+        carry = pack_state(*carry_in) if isinstance(carry_in, (tuple, list)) else carry_in
+        if (not carry.is_cuda or carry.dtype != torch.float32 or not carry.is_contiguous()
+                or carry.numel() != N * L * R * (dk + 1)):
+            raise RuntimeError("carry_in must be a contiguous fp32 CUDA state of N*S*(d_k+1) floats")
+    with torch.cuda.device(V.device):
+        if out is None:
+            out = torch.empty_like(V)
+        state = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device) \
+            if return_state else None
+        ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), tile_tokens, var)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
+        rc = L_.race_b200_causal_fwd(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry),
+                                     _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh),
+                                     tile_tokens, var, _stream(), None)
+    _lib.check(rc, "race_b200_causal_fwd")
+    if return_state:
+        A, B = unpack_state(state, L, R, dk)
+        return out, A, B
+    return out
+
+
+def race_tile_totals(probsK, V, *, tile_tokens: int = 0):
+    """(A [N,L,R], B [N,L,R,d_k]) summed over all T tokens (pass 1 of the sequence-sharded
+    driver; the final carry of src/race_chunked.py:62-63)."""
+    N, T, L, R, dk = _check_inputs(None, probsK, V, need_q=False)
+    L_ = _lib.lib()
+    sh = make_shape(N, T, L, R, dk, V.dtype, 1e-6)
+    with torch.cuda.device(V.device):
+        state = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device)
+        ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), tile_tokens,
+                                                       _lib.VARIANTS["simt"])
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
+        rc = L_.race_b200_tile_totals(_ptr(probsK), _ptr(V), _ptr(state), _ptr(ws), ws_bytes,
+                                      ctypes.byref(sh), tile_tokens, _stream())
+    _lib.check(rc, "race_b200_tile_totals")
+    return unpack_state(state, L, R, dk)
+
+
+def bucket_probs(x: torch.Tensor, planes: torch.Tensor, L: int, K: int,
+                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """x [..., d_k] -> probs [..., L, 2**K]  (src/race_baseline.py:41-44).
+
+    planes: fp32 [L*K, d_k] row-major (``planes_T.T``)."""
+    if not x.is_cuda or x.dtype not in _DTYPES or not x.is_contiguous():
+        raise RuntimeError("x must be a contiguous fp32/bf16 CUDA tensor")
+    dk = x.shape[-1]
+    planes = planes.to(device=x.device, dtype=torch.float32).contiguous()
+    if planes.shape != (L * K, dk):
+        raise RuntimeError(f"planes must be [L*K, d_k] = [{L * K}, {dk}]")
+    out_dtype = out_dtype or x.dtype
+    rows = x.numel() // dk
+    with torch.cuda.device(x.device):
+        probs = torch.empty(*x.shape[:-1], L, 1 << K, dtype=out_dtype, device=x.device)
+        rc = _lib.lib().race_b200_bucket_probs(_ptr(x), _ptr(planes), _ptr(probs), rows, dk, L, K,
+                                               _DTYPES[x.dtype], _DTYPES[out_dtype], _stream())
+    _lib.check(rc, "race_b200_bucket_probs")
+    return probs
+
+
+class _RaceNonCausal(torch.autograd.Function):
+    """out = pQ . (pK^T V / (sum_t pK + eps)) with the hand-written backward kernels.
+
+    Saved for backward: the three inputs and the reduced sums (Bs, A) -- the same choice the
+    reference's autograd wrapper makes (src/noncausal/ops.py:29-33)."""
+
+    @staticmethod
+    def forward(ctx, probsQ, probsK, V, eps):
+        N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
+        L_ = _lib.lib()
+        sh = make_shape(N, T, L, R, dk, V.dtype, eps)
+        with torch.cuda.device(V.device):
+            out = torch.empty_like(V)
+            totals = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device)
+            ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), 0, _lib.VARIANTS["simt"])
+            ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
+            rc = L_.race_b200_noncausal_fwd(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out),
+                                            _ptr(totals), _ptr(ws), ws_bytes, ctypes.byref(sh),
+                                            _stream())
+        _lib.check(rc, "race_b200_noncausal_fwd")
+        ctx.save_for_backward(probsQ, probsK, V, totals)
+        ctx.eps = eps
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_out):
+        probsQ, probsK, V, totals = ctx.saved_tensors
+        if not any(ctx.needs_input_grad[:3]):
+            return None, None, None, None
+        N, T, L, R = probsK.shape
+        dk = V.shape[-1]
+        # autograd may hand over an expanded (stride-0) gradient: the kernels need dense rows
+        grad_out = grad_out.to(V.dtype).contiguous()
+        L_ = _lib.lib()
+        sh = make_shape(N, T, L, R, dk, V.dtype, ctx.eps)
+        with torch.cuda.device(V.device):
+            dpq, dpk, dv = torch.empty_like(probsQ), torch.empty_like(probsK), torch.empty_like(V)
+            ws_bytes = L_.race_b200_noncausal_bwd_workspace_bytes(ctypes.byref(sh))
+            ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
+            rc = L_.race_b200_noncausal_bwd(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(totals),
+                                            _ptr(grad_out), _ptr(dpq), _ptr(dpk), _ptr(dv), _ptr(ws),
+                                            ws_bytes, ctypes.byref(sh), _stream())
+        _lib.check(rc, "race_b200_noncausal_bwd")
+        g = ctx.needs_input_grad
+        return (dpq if g[0] else None, dpk if g[1] else None, dv if g[2] else None, None)
+
+
+def race_noncausal(probsQ, probsK, V, eps: float = 1e-6) -> torch.Tensor:
+    """Non-causal per-bucket RACE attention, differentiable in probsQ, probsK and V
+    (upstream scaling/benchmark_time.py:155-162 as quoted at analysis/hot-path.md:157-162)."""
+    return _RaceNonCausal.apply(probsQ, probsK, V, float(eps))
+
+
+def race_causal_prefix_host(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
+                            return_state: bool = False, segment_tokens: int = 0,
+                            variant: str = "auto", device: int | None = None,
+                            out: torch.Tensor | None = None):
+    """Same result as ``race_causal_prefix`` for tensors in HOST memory (pin them for full copy
+    bandwidth): the library stages the sequence through the device in segments and returns
+    after the last copy back has finished."""
+    for name, t in (("probsQ", probsQ), ("probsK", probsK), ("V", V)):
+        if t.is_cuda or not t.is_contiguous() or t.dtype not in _DTYPES or t.dtype != V.dtype:
+            raise RuntimeError(f"{name} must be a contiguous fp32/bf16 host tensor")
+    N, T, L, R = probsK.shape
+    dk = V.shape[-1]
+    if probsQ.shape != probsK.shape or V.shape[:2] != (N, T):
+        raise RuntimeError("shape mismatch")
+    sh = make_shape(N, T, L, R, dk, V.dtype, eps)
+    carry = None
+    if carry_in is not None:
+        carry = (pack_state(*carry_in) if isinstance(carry_in, (tuple, list)) else carry_in)
+        carry = carry.float().contiguous().cpu()
+    if out is None:
+        out = torch.empty_like(V)
+    state = torch.empty(N, L * R * (dk + 1), dtype=torch.float32) if return_state else None
+    dev = torch.cuda.current_device() if device is None else device
+    rc = _lib.lib().race_b200_causal_fwd_host(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out),
+                                              _ptr(carry), _ptr(state), ctypes.byref(sh),
+                                              segment_tokens, _lib.VARIANTS[variant], dev)
+    _lib.check(rc, "race_b200_causal_fwd_host")
+    if return_state:
+        A, B = unpack_state(state, L, R, dk)
+        return out, A, B
+    return out

@@ -1,0 +1,105 @@
+"""CPU checks of the C-ABI boundary: the library loads, exports every symbol the public header
+declares, and rejects bad arguments with its documented codes (no kernel is launched)."""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+from race_attention_kernel_b200 import _lib
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "race_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(race_b200_\w+)\s*\(", text)))
+
+
+def test_header_symbols_exported():
+    names = _declared()
+    assert len(names) >= 13
+    L = _lib.lib()
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in include/race_b200.h but not exported"
+    assert sorted(_lib.EXPORTS) == names
+
+
+def test_version_and_error_strings():
+    L = _lib.lib()
+    assert L.race_b200_version() >= 1000
+    assert L.race_b200_error_string(0) == b"ok"
+    for code in range(-7, 0):
+        assert L.race_b200_error_string(code) not in (b"", b"unknown error")
+
+
+def _shape(N=8, T=4096, L=4, R=16, dk=64, dtype=0, eps=1e-6, reserved=0):
+    return _lib.RaceShape(N, T, L, R, dk, dtype, eps, reserved)
+
+
+def test_state_floats_and_support():
+    L = _lib.lib()
+    sh = _shape()
+    assert L.race_b200_state_floats(ctypes.byref(sh)) == 8 * 64 * 65
+    assert L.race_b200_is_supported(ctypes.byref(sh), 1) == 1
+    assert L.race_b200_is_supported(ctypes.byref(_shape(dk=96 * 4)), 1) == 0     # d_k > 128
+    assert L.race_b200_is_supported(ctypes.byref(_shape(L=3, R=32)), 1) == 0      # S=96: not /64
+    assert L.race_b200_is_supported(ctypes.byref(_shape(L=8, R=64, dk=128, dtype=1)), 1) == 1
+    assert L.race_b200_is_supported(ctypes.byref(_shape(dtype=7)), 0) == 0
+    assert L.race_b200_is_supported(ctypes.byref(_shape(reserved=1)), 0) == 0
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(dtype=5), -2), (dict(N=-1), -2), (dict(L=0), -2), (dict(eps=-1.0), -2),
+    (dict(reserved=3), -2), (dict(), -1),      # a valid shape then fails on the NULL pointers
+])
+def test_argument_errors_without_launch(kw, code):
+    L = _lib.lib()
+    sh = _shape(**kw)
+    rc = L.race_b200_causal_fwd(None, None, None, None, None, None, None, 0, ctypes.byref(sh), 0, 1,
+                                None, None)
+    assert rc == code
+
+
+def test_misaligned_rows_and_tiles():
+    L = _lib.lib()
+    # S = 6 fp32 = 24-byte rows: not a multiple of 16
+    rc = L.race_b200_causal_fwd(None, None, None, None, None, None, None, 0,
+                                ctypes.byref(_shape(L=1, R=6)), 0, 1, None, None)
+    assert rc == -3
+    # tile that is not a multiple of the 32-token chunk, negative tile
+    for tile in (48, -64):
+        rc = L.race_b200_causal_fwd(None, None, None, None, None, None, None, 0,
+                                    ctypes.byref(_shape()), tile, 1, None, None)
+        assert rc == -5
+    # unknown variant
+    rc = L.race_b200_causal_fwd(None, None, None, None, None, None, None, 0,
+                                ctypes.byref(_shape()), 0, 9, None, None)
+    assert rc == -6
+    # NULL shape
+    assert L.race_b200_causal_fwd(None, None, None, None, None, None, None, 0, None, 0, 1, None, None) == -1
+
+
+def test_workspace_and_tile_selection():
+    L = _lib.lib()
+    sh = _shape(T=1 << 20)
+    tile = ctypes.c_int(0)
+    assert L.race_b200_select_tile_tokens(ctypes.byref(sh), 1, ctypes.byref(tile)) == 0
+    assert tile.value % 32 == 0 and 32 <= tile.value <= 4096
+    ws = L.race_b200_causal_workspace_bytes(ctypes.byref(sh), tile.value, 1)
+    tiles = ((1 << 20) + tile.value - 1) // tile.value
+    assert ws == 8 * tiles * 64 * 65 * 4
+    short = ctypes.c_int(0)
+    L.race_b200_select_tile_tokens(ctypes.byref(_shape(N=1, T=100)), 1, ctypes.byref(short))
+    assert short.value == 32   # a short sequence gets the smallest tile
+
+
+def test_python_binding_rejects_cpu_tensors():
+    import torch
+
+    from race_attention_kernel_b200 import race_causal_prefix
+    pq = torch.rand(1, 8, 2, 4)
+    with pytest.raises(RuntimeError):
+        race_causal_prefix(pq, pq, torch.rand(1, 8, 4))

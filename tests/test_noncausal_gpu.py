@@ -1,0 +1,83 @@
+"""GPU parity of the non-causal forward/backward and of the bucket-probability producer."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import race_oracle as ro
+
+pytestmark = pytest.mark.gpu
+
+
+def _rk():
+    import race_attention_kernel_b200 as rk
+    return rk
+
+
+SHAPES = [(4, 4096, 4, 16, 64), (3, 1, 4, 16, 64), (2, 33, 4, 16, 64), (2, 1000, 2, 4, 64),
+          (2, 300, 1, 32, 64), (2, 200, 2, 8, 32), (2, 300, 4, 16, 128), (2, 300, 8, 64, 128)]
+
+
+@pytest.mark.parametrize("N,T,L,R,dk", SHAPES)
+def test_forward_backward_fp32(N, T, L, R, dk):
+    rk = _rk()
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=T + dk)
+    dO = torch.randn(N, T, dk, generator=torch.Generator().manual_seed(2))
+    ref = ro.noncausal_forward(pQ.double(), pK.double(), V.double())
+    g_ref = ro.noncausal_backward_autograd(pQ.double(), pK.double(), V.double(), dO.double())
+    q, k, v = (t.cuda().requires_grad_(True) for t in (pQ, pK, V))
+    out = rk.race_noncausal(q, k, v)
+    assert ro.rel_l2(out, ref) <= 1e-4
+    out.backward(dO.cuda())
+    for got, want, name in zip((q.grad, k.grad, v.grad), g_ref, ("dPQ", "dPK", "dV")):
+        assert ro.rel_l2(got, want) <= 1e-4, name
+
+
+@pytest.mark.parametrize("N,T,L,R,dk", [(4, 4096, 4, 16, 64), (2, 300, 8, 64, 128)])
+def test_forward_backward_bf16(N, T, L, R, dk):
+    rk = _rk()
+    pQ, pK, V = (t.bfloat16() for t in ro.synthetic_probs(N, T, L, R, dk, seed=3))
+    dO = torch.randn(N, T, dk, generator=torch.Generator().manual_seed(4)).bfloat16()
+    ref = ro.noncausal_forward(pQ.double(), pK.double(), V.double())
+    g_ref = ro.noncausal_backward_autograd(pQ.double(), pK.double(), V.double(), dO.double())
+    q, k, v = (t.cuda().requires_grad_(True) for t in (pQ, pK, V))
+    out = rk.race_noncausal(q, k, v)
+    assert out.dtype == torch.bfloat16 and ro.rel_l2(out, ref) <= 2e-2
+    out.backward(dO.cuda())
+    for got, want in zip((q.grad, k.grad, v.grad), g_ref):
+        assert ro.rel_l2(got, want) <= 2e-2
+
+
+def test_expanded_gradient_and_partial_needs():
+    rk = _rk()
+    pQ, pK, V = (t.cuda() for t in ro.synthetic_probs(2, 100, 4, 16, 64, seed=9))
+    v = V.clone().requires_grad_(True)
+    rk.race_noncausal(pQ, pK, v).sum().backward()      # stride-0 expanded ones as grad
+    _, _, dV = ro.noncausal_backward_autograd(pQ.double().cpu(), pK.double().cpu(), V.double().cpu(),
+                                              torch.ones(2, 100, 64, dtype=torch.float64))
+    assert ro.rel_l2(v.grad, dV) <= 1e-4
+
+
+def test_last_causal_token_equals_noncausal():
+    rk = _rk()
+    pQ, pK, V = (t.cuda() for t in ro.synthetic_probs(3, 500, 4, 16, 64, seed=10))
+    a = rk.race_causal_prefix(pQ, pK, V)[:, -1]
+    b = rk.race_noncausal(pQ, pK, V)[:, -1]
+    assert ro.rel_l2(a, b) <= 1e-5
+
+
+@pytest.mark.parametrize("dk,K,L,rows", [(64, 4, 4, 1000), (64, 2, 2, 77), (64, 5, 1, 64),
+                                         (128, 6, 8, 130), (32, 3, 2, 1), (64, 1, 3, 50)])
+def test_bucket_probs(dk, K, L, rows):
+    rk = _rk()
+    torch.manual_seed(1234)
+    planes_T, protos_T = ro.make_planes(dk, K, L), ro.make_protos(K)
+    x = torch.randn(1, rows, dk, generator=torch.Generator().manual_seed(0))
+    ref = ro.bucket_probs(x.double(), planes_T.double(), protos_T.double(), L, K)
+    got = rk.bucket_probs(x.cuda(), planes_T.T.contiguous().cuda(), L, K)
+    assert got.shape == ref.shape
+    assert ro.rel_l2(got, ref) <= 1e-5
+    assert torch.allclose(got.sum(-1).cpu(), torch.ones(1, rows, L), atol=1e-5)
+    got16 = rk.bucket_probs(x.bfloat16().cuda(), planes_T.T.contiguous().cuda(), L, K)
+    ref16 = ro.bucket_probs(x.bfloat16().double(), planes_T.double(), protos_T.double(), L, K)
+    assert got16.dtype == torch.bfloat16 and ro.rel_l2(got16, ref16) <= 1e-2
