@@ -370,7 +370,7 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
 template <typename Tin, int SPT, int DV>
 cudaError_t launch_simt(const Tin* pq, const Tin* pk, const Tin* v, Tin* out, const float* carry_in,
                         float* state_out, float* ws, const Dims& dm, int tile_tokens, int groups,
-                        bool totals_only, cudaStream_t stream) {
+                        bool totals_only, bool skip_output, cudaStream_t stream) {
     using Ly = SimtLayout<SPT, DV>;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const int sf = state_floats_per_stream(dm.S, dm.D);
@@ -384,7 +384,7 @@ cudaError_t launch_simt(const Tin* pq, const Tin* pk, const Tin* v, Tin* out, co
     dim3 sgrid((unsigned)((sf + 255) / 256), (unsigned)dm.N);
     tile_scan<<<sgrid, 256, 0, stream>>>(ws, carry_in, state_out, tiles, sf, totals_only ? 0 : 1);
     err = cudaGetLastError();
-    if (err != cudaSuccess || totals_only) return err;
+    if (err != cudaSuccess || totals_only || skip_output) return err;
 
     const size_t smem3 = (size_t)(groups > 1 ? Ly::floats_cluster : Ly::floats_single) * sizeof(float);
     auto kern = causal_out_simt<Tin, SPT, DV>;
@@ -408,7 +408,7 @@ cudaError_t launch_simt(const Tin* pq, const Tin* pk, const Tin* v, Tin* out, co
 template <typename Tin>
 cudaError_t dispatch_simt(const void* pq, const void* pk, const void* v, void* out,
                           const float* carry_in, float* state_out, float* ws, const Dims& dm,
-                          int tile_tokens, bool totals_only, cudaStream_t stream) {
+                          int tile_tokens, bool totals_only, bool skip_output, cudaStream_t stream) {
     const int groups = simt_groups(dm.S);
     const int sg = dm.S > kGroupBuckets ? kGroupBuckets : dm.S;
     const int spt = sg <= 16 ? 1 : (sg <= 32 ? 2 : 4);
@@ -417,7 +417,7 @@ cudaError_t dispatch_simt(const void* pq, const void* pk, const void* v, void* o
     if (spt == SPT_ && dv == DV_)                                                                  \
         return launch_simt<Tin, SPT_, DV_>((const Tin*)pq, (const Tin*)pk, (const Tin*)v, (Tin*)out, \
                                            carry_in, state_out, ws, dm, tile_tokens, groups,       \
-                                           totals_only, stream);
+                                           totals_only, skip_output, stream);
     RACE_SIMT_CASE(1, 1) RACE_SIMT_CASE(2, 1) RACE_SIMT_CASE(4, 1)
     RACE_SIMT_CASE(1, 2) RACE_SIMT_CASE(2, 2) RACE_SIMT_CASE(4, 2)
 #undef RACE_SIMT_CASE
@@ -445,12 +445,13 @@ int simt_default_tile_tokens(const Dims& dm, int sm_count) {
 
 cudaError_t causal_fwd_simt(const void* pq, const void* pk, const void* v, void* out,
                             const float* carry_in, float* state_out, float* ws, const Dims& dm,
-                            int dtype, int tile_tokens, bool totals_only, cudaStream_t stream) {
+                            int dtype, int tile_tokens, bool totals_only, cudaStream_t stream,
+                            bool skip_output) {
     if (dtype == RACE_DTYPE_F32)
         return dispatch_simt<float>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens,
-                                    totals_only, stream);
+                                    totals_only, skip_output, stream);
     return dispatch_simt<__nv_bfloat16>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens,
-                                        totals_only, stream);
+                                        totals_only, skip_output, stream);
 }
 
 }  // namespace race

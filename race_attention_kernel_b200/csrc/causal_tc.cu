@@ -1,13 +1,690 @@
-// tcgen05 / TMEM / TMA causal kernel (placeholder until the kernel lands: reports unsupported).
+// tcgen05 / TMEM / TMA output pass of the causal per-bucket prefix path (sm_100a).
+//
+// One CTA owns a (stream, state tile) and walks it in chunks of C = 64 tokens.  Per chunk
+// (S = 64 buckets, D = 64 head dim, carry (A [S], B [S,D]) from the tiles before it):
+//     A_in = A + tril_ones . pK            tcgen05.mma   (inclusive running sum inside the chunk)
+//     W    = pQ / (A_in + eps)             CUDA cores, from TMEM
+//     G    = tril(W . pK^T)                tcgen05.mma, masked on the way TMEM -> shared memory
+//     O    = W . B + G . V                 tcgen05.mma
+//     B   += pK^T . V                      tcgen05.mma, accumulator resident in TMEM
+// which is the chunk identity of the estimator in src/race_baseline.py:45-51
+// (docs/causal_v2_design.md:70-77).  fp32 inputs are split into bf16 hi + lo limbs and every
+// product runs as hi*hi + hi*lo + lo*hi with fp32 accumulation, so operand error is ~2^-17.
+//
+// Warp roles (14 warps): two worker warpgroups take alternate chunks (fp32 -> bf16 operand
+// tiles, W, mask of G, output store); a third warpgroup copies the running B from TMEM to its
+// bf16 operand tile after every update; one warp issues TMA loads into a two-stage ring; one
+// thread issues every tcgen05.mma.  All hand-offs are mbarriers; every wait is bounded and a
+// wait that runs out raises the status word and makes the CTA drain and exit.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
 #include "launch.h"
 
 namespace race {
-bool tensor_supported(const Dims&, int) { return false; }
-int tensor_chunk_tokens() { return 64; }
-int tensor_default_tile_tokens(const Dims&, int, int) { return 1024; }
-size_t tensor_workspace_bytes(const Dims&, int, int) { return 0; }
-cudaError_t causal_fwd_tensor(const void*, const void*, const void*, void*, const float*, float*,
-                              void*, const Dims&, int, int, cudaStream_t, int*) {
-    return cudaErrorNotSupported;
+namespace {
+
+constexpr int C = 64;           // tokens per chunk
+constexpr int S = 64;           // buckets per CTA
+constexpr int D = 64;           // head dim
+constexpr int kThreads = 14 * 32;
+constexpr int kProducerWarp = 12;
+constexpr int kMmaWarp = 13;
+constexpr uint32_t kTmemCols = 512;
+constexpr long long kWaitCycles = 1ll << 31;   // ~1 s: bound of every device-side wait
+
+// ---- shared memory map (bytes from a 1024-aligned base) ---------------------------------------
+constexpr int kTileF32 = C * 64 * 4;        // one staged fp32 tile: 64 tokens x 64 values
+constexpr int kStageBytes = 3 * kTileF32;   // pK | V | pQ
+constexpr int kOpTile = C * 64 * 2;         // one bf16 operand tile (8 KB)
+constexpr int oStage = 0;                               // [2][kStageBytes]
+constexpr int oKt = oStage + 2 * kStageBytes;           // [2 wg][hi|lo]
+constexpr int oVt = oKt + 4 * kOpTile;
+constexpr int oWt = oVt + 4 * kOpTile;                  // W, then reused for masked G
+constexpr int oBt = oWt + 4 * kOpTile;                  // [hi|lo]
+constexpr int oTril = oBt + 2 * kOpTile;
+constexpr int oAcar = oTril + kOpTile;                  // [2][64] fp32
+constexpr int oBars = oAcar + 2 * 64 * 4;
+constexpr int kNumBars = 24;
+constexpr int oMisc = oBars + kNumBars * 8;             // tmem base, abort flag
+constexpr int kSmemBytes = oMisc + 16 + 1024;           // + slack for manual alignment
+
+enum Bar {
+    kFull = 0,      // [2] stage filled by TMA
+    kEmpty = 2,     // [2] stage released by its worker group (8 warp arrivals)
+    kKvReady = 4,   // [2] Kt/Vt operand tiles written
+    kXReady = 6,    // [2] A_loc accumulator complete
+    kWReady = 8,    // [2] W operand tile written
+    kGReady = 10,   // [2] W.B and G accumulators complete
+    kGtReady = 12,  // [2] masked G operand tile written
+    kOReady = 14,   // [2] O accumulator complete
+    kAcar = 16,     // [2] running A of the chunk published
+    kBupdDone = 18, // B accumulator holds the state after chunk c
+    kBaccFree = 19, // B accumulator read out (count 4)
+    kBtReady = 20,  // B operand tile of chunk c written (count 4)
+    kDrain = 21
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+// 16 lanes x 64 columns of fp32: thread t gets rows (t/4, t/4+8), column pairs 8x + 2(t%4) + {0,1}
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st64(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x256b.x8.b32 [%32], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+        ::"r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])),
+          "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// shared-memory matrix descriptor, no swizzle: 8x(16 B) core matrices of 128 contiguous bytes;
+// lbo = byte stride between core matrices along K, sbo = along M/N
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
+}
+// instruction descriptor: bf16 x bf16 -> fp32, M = 64, N = 64
+constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((64u >> 4) << 24);
+constexpr uint32_t kAmn = 1u << 15;  // A operand is M-major
+constexpr uint32_t kBmn = 1u << 16;  // B operand is N-major
+
+// byte offset of element (row, col) in a [64][64] bf16 operand tile of 8x8 core matrices
+__device__ __forceinline__ uint32_t op_off(int row, int col) {
+    return (uint32_t)((((row >> 3) * 8 + (col >> 3)) << 7) + ((row & 7) << 4) + ((col & 7) << 1));
+}
+
+__device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t& lo) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    __nv_bfloat162 l = __floats2bfloat162_rn(a - __low2float(h), b - __high2float(h));
+    hi = *reinterpret_cast<uint32_t*>(&h);
+    lo = *reinterpret_cast<uint32_t*>(&l);
+}
+
+struct Ctx {
+    uint8_t* sm;        // 1024-aligned shared base (generic pointer)
+    uint32_t sm_u32;    // same, shared-window address
+    volatile int* abort_flag;
+    int* status;
+    __device__ __forceinline__ uint32_t bar(int i) const { return sm_u32 + oBars + i * 8; }
+};
+
+// Bounded wait: false if the wait ran out or another role already gave up.
+__device__ __forceinline__ bool wait_bar(const Ctx& cx, int bar, uint32_t parity, int code) {
+    if (mbar_try_wait(cx.bar(bar), parity)) return true;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (!mbar_try_wait(cx.bar(bar), parity)) {
+        if ((++spins & 63) == 0) {
+            if (*cx.abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                *cx.abort_flag = 1;
+                if (cx.status) atomicCAS(cx.status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Warp-uniform flavour: every lane gets the same answer, so .aligned instructions that follow
+// are never reached by a part of the warp only.
+__device__ __forceinline__ bool wait_bar_warp(const Ctx& cx, int bar, uint32_t parity, int code) {
+    return __all_sync(0xffffffffu, wait_bar(cx, bar, parity, code));
+}
+
+// fp32 staged tile (two 128B-swizzled halves of 32 columns) -> bf16 hi/lo operand tiles
+__device__ __forceinline__ void convert_tile(const uint8_t* stage, uint8_t* hi, uint8_t* lo, int tid) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int idx = it * 128 + tid;
+        const int j = idx >> 6, r = idx & 63;            // 8-column group, token row
+        const uint8_t* src = stage + (j >> 2) * 8192 + r * 128;
+        const int jj = j & 3;
+        const float4 a = *reinterpret_cast<const float4*>(src + (((2 * jj) ^ (r & 7)) << 4));
+        const float4 b = *reinterpret_cast<const float4*>(src + (((2 * jj + 1) ^ (r & 7)) << 4));
+        uint4 h, l;
+        split2(a.x, a.y, h.x, l.x);
+        split2(a.z, a.w, h.y, l.y);
+        split2(b.x, b.y, h.z, l.z);
+        split2(b.z, b.w, h.w, l.w);
+        const uint32_t off = (uint32_t)((((r >> 3) * 8 + j) << 7) + ((r & 7) << 4));
+        *reinterpret_cast<uint4*>(hi + off) = h;
+        *reinterpret_cast<uint4*>(lo + off) = l;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+              const __grid_constant__ CUtensorMap map_v, float* __restrict__ out,
+              const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cx;
+    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cx.sm_u32 = smem_u32(cx.sm);
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + oMisc + 4);
+    cx.status = status;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + oMisc);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t tiles = gridDim.x;
+    const int64_t tile = blockIdx.x, n = blockIdx.y;
+    const int64_t t_begin = tile * tile_tokens;
+    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
+    const int nch = (int)((t_end - t_begin + C - 1) / C);
+    const float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+
+    // ---- set-up: barriers, TMEM, the constant lower-triangular ones tile -----------------------
+    if (tid == 0) {
+        *cx.abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(cx.bar(kFull + i), 1);
+            mbar_init(cx.bar(kEmpty + i), 8);
+            mbar_init(cx.bar(kKvReady + i), 4);
+            mbar_init(cx.bar(kXReady + i), 1);
+            mbar_init(cx.bar(kWReady + i), 4);
+            mbar_init(cx.bar(kGReady + i), 1);
+            mbar_init(cx.bar(kGtReady + i), 4);
+            mbar_init(cx.bar(kOReady + i), 1);
+            mbar_init(cx.bar(kAcar + i), 1);
+        }
+        mbar_init(cx.bar(kBupdDone), 1);
+        mbar_init(cx.bar(kBaccFree), 4);
+        mbar_init(cx.bar(kBtReady), 4);
+        mbar_init(cx.bar(kDrain), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(cx.sm_u32 + oMisc), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    for (int i = tid; i < C * 8; i += kThreads) {   // tril[t][j] = (j <= t), 8 columns per item
+        const int t = i >> 3, jg = i & 7;
+        uint32_t w[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int j0 = jg * 8 + 2 * p;
+            w[p] = (j0 <= t ? 0x3F80u : 0u) | (j0 + 1 <= t ? 0x3F800000u : 0u);
+        }
+        *reinterpret_cast<uint4*>(cx.sm + oTril + op_off(t, jg * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmB = tmem;                               // B accumulator, columns [0, 64)
+    auto tmAG = [&](int wg) { return tmem + 64 + wg * 128; };      // A_loc, then G
+    auto tmO = [&](int wg) { return tmem + 64 + wg * 128 + 64; };  // O
+
+    if (warp < 8) {
+        // =========================== worker warpgroups =========================================
+        const int wg = warp >> 2, w = warp & 3, wtid = tid & 127;
+        const int q = lane & 3, rbase = 16 * w + (lane >> 2);
+        const uint32_t lane_base = (uint32_t)(32 * w) << 16;
+        uint8_t* kt_hi = cx.sm + oKt + wg * 2 * kOpTile;
+        uint8_t* kt_lo = kt_hi + kOpTile;
+        uint8_t* vt_hi = cx.sm + oVt + wg * 2 * kOpTile;
+        uint8_t* vt_lo = vt_hi + kOpTile;
+        uint8_t* wt_hi = cx.sm + oWt + wg * 2 * kOpTile;
+        uint8_t* wt_lo = wt_hi + kOpTile;
+        const uint8_t* stage = cx.sm + oStage + wg * kStageBytes;
+        float* out_n = out + n * T * D;
+        uint32_t ph = 0;   // parity of this group's per-chunk barriers (one use per chunk)
+        bool ok = true;
+        for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
+            const int64_t tok0 = t_begin + (int64_t)c * C;
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+            // -- S1: staged pK, V -> operand tiles ------------------------------------------------
+            if (!(ok = wait_bar_warp(cx, kFull + wg, ph, 101))) break;
+            convert_tile(stage, kt_hi, kt_lo, wtid);
+            convert_tile(stage + kTileF32, vt_hi, vt_lo, wtid);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(kKvReady + wg)); mbar_arrive(cx.bar(kEmpty + wg)); }
+
+            // -- S2: W = pQ / (A + A_loc + eps) ----------------------------------------------------
+            if (!(ok = wait_bar_warp(cx, kAcar + wg, ph, 102))) break;
+            float acar[16];
+            {
+                const float* ac = reinterpret_cast<const float*>(cx.sm + oAcar) + wg * 64;
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    const float2 a2 = *reinterpret_cast<const float2*>(ac + 8 * x + 2 * q);
+                    acar[2 * x] = a2.x; acar[2 * x + 1] = a2.y;
+                }
+            }
+            if (!(ok = wait_bar_warp(cx, kXReady + wg, ph, 103))) break;
+            tc_fence_after();
+            float v[32];
+            tmem_ld64(lane_base + tmAG(wg), v);
+            tc_fence_before();
+            {
+                const uint8_t* sq = stage + 2 * kTileF32;
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int row = rbase + 8 * h;
+                        const int chunk = 2 * (x & 3) + (q >> 1);
+                        const float2 pq = *reinterpret_cast<const float2*>(
+                            sq + (x >> 2) * 8192 + row * 128 + ((chunk ^ (row & 7)) << 4) + (q & 1) * 8);
+                        const float a0 = acar[2 * x] + v[4 * x + 2 * h];
+                        const float a1 = acar[2 * x + 1] + v[4 * x + 2 * h + 1];
+                        const float w0 = __fdividef(pq.x, a0 + eps);
+                        const float w1 = __fdividef(pq.y, a1 + eps);
+                        uint32_t hi, lo;
+                        split2(w0, w1, hi, lo);
+                        const uint32_t off = op_off(row, 8 * x + 2 * q);
+                        *reinterpret_cast<uint32_t*>(wt_hi + off) = hi;
+                        *reinterpret_cast<uint32_t*>(wt_lo + off) = lo;
+                        if (h == 1 && w == 3 && (lane >> 2) == 7) {
+                            // row 63: the running A after this chunk, for the other group
+                            float* an = reinterpret_cast<float*>(cx.sm + oAcar) + (wg ^ 1) * 64;
+                            *reinterpret_cast<float2*>(an + 8 * x + 2 * q) = make_float2(a0, a1);
+                        }
+                    }
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(cx.bar(kWReady + wg));
+                mbar_arrive(cx.bar(kEmpty + wg));
+                if (w == 3) mbar_arrive(cx.bar(kAcar + (wg ^ 1)));
+            }
+
+            // -- S3: G -> causal mask -> operand tile (over W's buffer) ----------------------------
+            if (!(ok = wait_bar_warp(cx, kGReady + wg, ph, 104))) break;
+            tc_fence_after();
+            tmem_ld64(lane_base + tmAG(wg), v);
+            tc_fence_before();
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = rbase + 8 * h, col = 8 * x + 2 * q;
+                    const float g0 = col <= row ? v[4 * x + 2 * h] : 0.f;
+                    const float g1 = col + 1 <= row ? v[4 * x + 2 * h + 1] : 0.f;
+                    uint32_t hi, lo;
+                    split2(g0, g1, hi, lo);
+                    const uint32_t off = op_off(row, col);
+                    *reinterpret_cast<uint32_t*>(wt_hi + off) = hi;
+                    *reinterpret_cast<uint32_t*>(wt_lo + off) = lo;
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(kGtReady + wg));
+
+            // -- S4: O -> global -------------------------------------------------------------------
+            if (!(ok = wait_bar_warp(cx, kOReady + wg, ph, 105))) break;
+            tc_fence_after();
+            tmem_ld64(lane_base + tmO(wg), v);
+            tc_fence_before();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                if (row < valid) {
+                    float* orow = out_n + (tok0 + row) * D + 2 * q;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x)
+                        __stcs(reinterpret_cast<float2*>(orow + 8 * x),
+                               make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]));
+                }
+            }
+        }
+    } else if (warp < 12) {
+        // =========================== carry warpgroup ===========================================
+        const int w = warp & 3, q = lane & 3, rbase = 16 * w + (lane >> 2);
+        const uint32_t lane_base = (uint32_t)(32 * w) << 16;
+        uint8_t* bt_hi = cx.sm + oBt;
+        uint8_t* bt_lo = bt_hi + kOpTile;
+        float v[32];
+        // carry-in: B -> TMEM accumulator and operand tile; A -> the first chunk's running A
+#pragma unroll
+        for (int x = 0; x < 8; ++x)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float2 b2 = *reinterpret_cast<const float2*>(
+                    slice + (rbase + 8 * h) * D + 8 * x + 2 * q);
+                v[4 * x + 2 * h] = b2.x; v[4 * x + 2 * h + 1] = b2.y;
+            }
+        tmem_st64(lane_base + tmB, v);
+        tc_fence_before();
+        if (warp == 8) {
+            float* ac = reinterpret_cast<float*>(cx.sm + oAcar);
+            ac[lane] = slice[S * D + lane];
+            ac[lane + 32] = slice[S * D + lane + 32];
+        }
+        bool ok = true;
+        for (int c = -1; c < nch - 1 && ok; ++c) {
+            if (c >= 0) {
+                // state after chunk c: wait for its update, read it out, hand the accumulator back
+                if (!(ok = wait_bar_warp(cx, kBupdDone, c & 1, 201))) break;
+                tc_fence_after();
+                tmem_ld64(lane_base + tmB, v);
+                tc_fence_before();
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(cx.bar(kBaccFree));
+                if (c < 0 && warp == 8) mbar_arrive(cx.bar(kAcar + 0));
+            }
+            // the previous operand tile may be overwritten once W.B of chunk c has completed
+            if (c >= 0 && !(ok = wait_bar_warp(cx, kGReady + (c & 1), (c >> 1) & 1, 202))) break;
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t hi, lo;
+                    split2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1], hi, lo);
+                    const uint32_t off = op_off(rbase + 8 * h, 8 * x + 2 * q);
+                    *reinterpret_cast<uint32_t*>(bt_hi + off) = hi;
+                    *reinterpret_cast<uint32_t*>(bt_lo + off) = lo;
+                }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(kBtReady));
+        }
+    } else if (warp == kProducerWarp) {
+        // =========================== TMA producer ==============================================
+        if (lane == 0) {
+            int issued = 0;
+            for (int c = 0; c < nch; ++c) {
+                const int st = c & 1;
+                if (c >= 2 && !wait_bar(cx, kEmpty + st, ((c >> 1) - 1) & 1, 301)) break;
+                const uint32_t dst = cx.sm_u32 + oStage + st * kStageBytes;
+                const uint32_t bar = cx.bar(kFull + st);
+                const int tok = (int)(t_begin + (int64_t)c * C);
+                mbar_arrive_expect_tx(bar, kStageBytes);
+                tma_load_4d(dst, &map_k, bar, 0, tok, 0, (int)n);
+                tma_load_4d(dst + 8192, &map_k, bar, 0, tok, 1, (int)n);
+                tma_load_4d(dst + kTileF32, &map_v, bar, 0, tok, 0, (int)n);
+                tma_load_4d(dst + kTileF32 + 8192, &map_v, bar, 0, tok, 1, (int)n);
+                tma_load_4d(dst + 2 * kTileF32, &map_q, bar, 0, tok, 0, (int)n);
+                tma_load_4d(dst + 2 * kTileF32 + 8192, &map_q, bar, 0, tok, 1, (int)n);
+                issued = c + 1;
+            }
+            if (*cx.abort_flag) {
+                // copies still in flight must land before the CTA may exit
+                for (int c = max(0, issued - 2); c < issued; ++c) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(kFull + (c & 1)), (c >> 1) & 1) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
+            }
+        }
+    } else {
+        // =========================== MMA issuer ================================================
+        if (lane == 0) {
+            const uint32_t tril = cx.sm_u32 + oTril;
+            const uint32_t bt = cx.sm_u32 + oBt;
+            int st[2] = {0, 0};
+            int ch[2] = {0, 1};
+            uint32_t ph[2] = {0, 0};
+            int next_bupd = 0, next_wb = 0;
+            long long t_idle = clock64();
+            bool ok = true;
+            while (ok && (ch[0] < nch || ch[1] < nch)) {
+                bool progress = false;
+#pragma unroll
+                for (int wg = 0; wg < 2; ++wg) {
+                    const int c = ch[wg];
+                    if (c >= nch) continue;
+                    const uint32_t kt = cx.sm_u32 + oKt + wg * 2 * kOpTile;
+                    const uint32_t vt = cx.sm_u32 + oVt + wg * 2 * kOpTile;
+                    const uint32_t wt = cx.sm_u32 + oWt + wg * 2 * kOpTile;
+                    if (st[wg] == 0) {
+                        if (!mbar_try_wait(cx.bar(kKvReady + wg), ph[wg])) continue;
+                        tc_fence_after();
+                        // A_loc = tril . pK : A = tril (K-major), B = pK [token][s] (N-major)
+#pragma unroll
+                        for (int limb = 0; limb < 2; ++limb)
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                mma_bf16(tmAG(wg), make_desc(tril + k * 256, 128, 1024),
+                                         make_desc(kt + limb * kOpTile + k * 2048, 1024, 128),
+                                         kIdescBase | kBmn, (limb | k) ? 1u : 0u);
+                        mma_commit(cx.bar(kXReady + wg));
+                        st[wg] = 1; progress = true;
+                    } else if (st[wg] == 1) {
+                        if (c != next_bupd || !mbar_try_wait(cx.bar(kBaccFree), c & 1)) continue;
+                        tc_fence_after();
+                        // B += pK^T . V : A = pK [token][s] (M-major), B = V [token][c] (N-major)
+#pragma unroll
+                        for (int pass = 0; pass < 3; ++pass) {
+                            const uint32_t a = kt + (pass == 2 ? kOpTile : 0);
+                            const uint32_t b = vt + (pass == 1 ? kOpTile : 0);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                mma_bf16(tmB, make_desc(a + k * 2048, 1024, 128),
+                                         make_desc(b + k * 2048, 1024, 128), kIdescBase | kAmn | kBmn, 1u);
+                        }
+                        mma_commit(cx.bar(kBupdDone));
+                        ++next_bupd;
+                        st[wg] = 2; progress = true;
+                    } else if (st[wg] == 2) {
+                        if (c != next_wb || !mbar_try_wait(cx.bar(kWReady + wg), ph[wg]) ||
+                            !mbar_try_wait(cx.bar(kBtReady), c & 1))
+                            continue;
+                        tc_fence_after();
+#pragma unroll
+                        for (int pass = 0; pass < 3; ++pass) {
+                            // O = W . B : A = W (K-major), B = state [s][c] (N-major)
+                            const uint32_t a = wt + (pass == 2 ? kOpTile : 0);
+                            const uint32_t b = bt + (pass == 1 ? kOpTile : 0);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                mma_bf16(tmO(wg), make_desc(a + k * 256, 128, 1024),
+                                         make_desc(b + k * 2048, 1024, 128), kIdescBase | kBmn,
+                                         (pass | k) ? 1u : 0u);
+                        }
+#pragma unroll
+                        for (int pass = 0; pass < 3; ++pass) {
+                            // G = W . pK^T : A = W (K-major), B = pK [token][s] (K-major)
+                            const uint32_t a = wt + (pass == 2 ? kOpTile : 0);
+                            const uint32_t b = kt + (pass == 1 ? kOpTile : 0);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                mma_bf16(tmAG(wg), make_desc(a + k * 256, 128, 1024),
+                                         make_desc(b + k * 256, 128, 1024), kIdescBase,
+                                         (pass | k) ? 1u : 0u);
+                        }
+                        mma_commit(cx.bar(kGReady + wg));
+                        ++next_wb;
+                        st[wg] = 3; progress = true;
+                    } else {
+                        if (!mbar_try_wait(cx.bar(kGtReady + wg), ph[wg])) continue;
+                        tc_fence_after();
+#pragma unroll
+                        for (int pass = 0; pass < 3; ++pass) {
+                            // O += G . V : A = masked G (K-major), B = V [token][c] (N-major)
+                            const uint32_t a = wt + (pass == 2 ? kOpTile : 0);
+                            const uint32_t b = vt + (pass == 1 ? kOpTile : 0);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                mma_bf16(tmO(wg), make_desc(a + k * 256, 128, 1024),
+                                         make_desc(b + k * 2048, 1024, 128), kIdescBase | kBmn, 1u);
+                        }
+                        mma_commit(cx.bar(kOReady + wg));
+                        st[wg] = 0; ch[wg] += 2; ph[wg] ^= 1; progress = true;
+                    }
+                }
+                if (progress) {
+                    t_idle = clock64();
+                } else {
+                    if (*cx.abort_flag) ok = false;
+                    else if (clock64() - t_idle > kWaitCycles) {
+                        *cx.abort_flag = 1;
+                        if (status) atomicCAS(status, 0, 401);
+                        ok = false;
+                    }
+                }
+            }
+            // everything issued has to retire before TMEM is freed
+            mma_commit(cx.bar(kDrain));
+            const long long t0 = clock64();
+            while (!mbar_try_wait(cx.bar(kDrain), 0) && clock64() - t0 < kWaitCycles) {}
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    cudaFree(nullptr);  // make sure the runtime (and with it the driver) is initialised
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) !=
+            cudaSuccess || q != cudaDriverEntryPointSuccess)
+        p = nullptr;
+    if (!p) {
+        cudaGetLastError();
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+    }
+    if (!p) cudaGetLastError();
+    fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+    return fn;
+}
+
+// [N][T][width] fp32 viewed as (32 values, T tokens, width/32 column blocks, N streams); one box =
+// 32 values x 64 tokens (128-byte rows, 128B swizzle); tokens past T read as zero
+bool make_map(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width) {
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {32, (cuuint64_t)T, (cuuint64_t)(width / 32), (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)width * 4, 128, (cuuint64_t)T * width * 4};
+    cuuint32_t box[4] = {32, (cuuint32_t)C, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool tensor_supported(const Dims& dm, int dtype) {
+    // the shape test alone decides: a missing driver entry point surfaces as an error at launch
+    return dtype == RACE_DTYPE_F32 && dm.S == S && dm.D == D && dm.N >= 0 && dm.N <= 65535 &&
+           dm.T < (1ll << 31);
+}
+
+int tensor_chunk_tokens() { return C; }
+
+int tensor_default_tile_tokens(const Dims& dm, int, int sm_count) {
+    // one CTA per SM: aim for a few waves, tiles of at most 2048 tokens
+    int tile = 2048;
+    while (tile > C && dm.N * ((dm.T + tile - 1) / tile) < (int64_t)sm_count * 2) tile >>= 1;
+    return tile;
+}
+
+size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
+    const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
+    return (size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
+}
+
+cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
+                              const float* carry_in, float* state_out, void* ws, const Dims& dm,
+                              int dtype, int tile_tokens, cudaStream_t stream, int* status) {
+    // tile totals and the scan over tiles run on the CUDA-core kernels; the output pass below
+    // replaces the third launch
+    cudaError_t err = causal_fwd_simt(nullptr, pk, v, nullptr, carry_in, state_out, (float*)ws, dm,
+                                      dtype, tile_tokens, /*totals_only=*/false, stream, /*skip_output=*/true);
+    if (err != cudaSuccess) return err;
+    CUtensorMap mq, mk, mv;
+    if (!make_map(&mq, pq, dm.N, dm.T, dm.S) || !make_map(&mk, pk, dm.N, dm.T, dm.S) ||
+        !make_map(&mv, v, dm.N, dm.T, dm.D))
+        return cudaErrorInvalidValue;
+    err = cudaFuncSetAttribute(causal_out_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (err != cudaSuccess) return err;
+    const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
+    dim3 grid((unsigned)tiles, (unsigned)dm.N);
+    causal_out_tc<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, (float*)out, (const float*)ws, dm.T,
+                                                          tile_tokens, dm.eps, status);
+    return cudaGetLastError();
+}
+
 }  // namespace race

@@ -11,10 +11,12 @@ namespace race {
 int simt_groups(int S);
 bool simt_supported(const Dims& dm);
 int simt_default_tile_tokens(const Dims& dm, int sm_count);
-// tile totals -> scan -> outputs; totals_only stops after the scan and writes only state_out.
+// tile totals -> scan -> outputs; totals_only stops after the scan and writes only state_out;
+// skip_output stops after the scan but leaves the exclusive tile prefixes in ws.
 cudaError_t causal_fwd_simt(const void* pq, const void* pk, const void* v, void* out,
                             const float* carry_in, float* state_out, float* ws, const Dims& dm,
-                            int dtype, int tile_tokens, bool totals_only, cudaStream_t stream);
+                            int dtype, int tile_tokens, bool totals_only, cudaStream_t stream,
+                            bool skip_output = false);
 
 // ---- non-causal path (noncausal_simt.cu) ------------------------------------------------------
 cudaError_t noncausal_query(const void* pq, const float* totals, void* out, const Dims& dm, int dtype,

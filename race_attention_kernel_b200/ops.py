@@ -9,6 +9,7 @@ reference's binding does (src/causal_v2/kernels/torch_binding.cpp:74-90).
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -23,6 +24,29 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
+
+
+_STATUS: dict[int, torch.Tensor] = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 status word the kernels raise when a bounded device-side wait runs out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _STATUS:
+        _STATUS[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[idx]
+
+
+def device_status(device=None, reset: bool = True) -> int:
+    """Synchronise and return the status word of `device` (0 = every kernel ran to completion;
+    non-zero = code of the first wait that gave up).  Reading it costs a device sync, so the
+    operators never do it themselves unless RACE_B200_CHECK_STATUS=1 is set."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_word(dev)
+    val = int(word.item())
+    if reset and val:
+        word.zero_()
+    return val
 
 
 def _check_inputs(probsQ, probsK, V, need_q=True):
@@ -108,8 +132,12 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
         rc = L_.race_b200_causal_fwd(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry),
                                      _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh),
-                                     tile_tokens, var, _stream(), None)
+                                     tile_tokens, var, _stream(), _ptr(_status_word(V.device)))
     _lib.check(rc, "race_b200_causal_fwd")
+    if os.environ.get("RACE_B200_CHECK_STATUS") == "1":
+        code = device_status(V.device)
+        if code:
+            raise RuntimeError(f"race_b200_causal_fwd: a bounded device-side wait ran out (code {code})")
     if return_state:
         A, B = unpack_state(state, L, R, dk)
         return out, A, B

@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 import torch
 
+os.environ.setdefault("RACE_B200_CHECK_STATUS", "1")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
