@@ -426,6 +426,15 @@ cudaError_t dispatch_simt(const void* pq, const void* pk, const void* v, void* o
 
 }  // namespace
 
+cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out, const Dims& dm,
+                              int tile_tokens, cudaStream_t stream) {
+    const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
+    const int sf = state_floats_per_stream(dm.S, dm.D);
+    dim3 sgrid((unsigned)((sf + 255) / 256), (unsigned)dm.N);
+    tile_scan<<<sgrid, 256, 0, stream>>>(ws, carry_in, state_out, tiles, sf, 1);
+    return cudaGetLastError();
+}
+
 int simt_groups(int S) { return S <= kGroupBuckets ? 1 : (S + kGroupBuckets - 1) / kGroupBuckets; }
 
 bool simt_supported(const Dims& dm) {

@@ -176,7 +176,8 @@ struct Ctx {
     uint32_t sm_u32;    // same, shared-window address
     volatile int* abort_flag;
     int* status;
-    __device__ __forceinline__ uint32_t bar(int i) const { return sm_u32 + oBars + i * 8; }
+    int bars = oBars;   // byte offset of the mbarrier array
+    __device__ __forceinline__ uint32_t bar(int i) const { return sm_u32 + bars + i * 8; }
 };
 
 // Bounded wait: false if the wait ran out or another role already gave up.
@@ -609,6 +610,209 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Tile totals on the tensor cores: B_tile = sum_t pK^T V (tcgen05.mma into one TMEM accumulator),
+// A_tile = sum_t pK (fp32 adds while the keys are split into limbs).  A streaming kernel: two
+// converter warpgroups take alternate chunks from a four-stage TMA ring; nothing but the
+// accumulator is carried from chunk to chunk.
+// ------------------------------------------------------------------------------------------------
+constexpr int kT1Threads = 10 * 32;
+constexpr int kT1Stages = 4;
+constexpr int kT1StageBytes = 2 * kTileF32;            // pK | V
+constexpr int o1Stage = 0;
+constexpr int o1Kt = o1Stage + kT1Stages * kT1StageBytes;   // [2 wg][hi|lo]
+constexpr int o1Vt = o1Kt + 4 * kOpTile;
+constexpr int o1Red = o1Vt + 4 * kOpTile;              // [8 warps][4][8] fp32 column-sum partials
+constexpr int o1Bars = o1Red + 8 * 32 * 4;
+constexpr int o1Misc = o1Bars + 16 * 8;
+constexpr int kT1SmemBytes = o1Misc + 16 + 1024;
+enum Bar1 { k1Full = 0, k1Empty = 4, k1KvReady = 8, k1KvFree = 10, k1Done = 12 };
+
+// like convert_tile, and adds each thread's 8 values per item into asum[item][8]
+__device__ __forceinline__ void convert_tile_sum(const uint8_t* stage, uint8_t* hi, uint8_t* lo, int tid,
+                                                 float (&asum)[4][8]) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int idx = it * 128 + tid;
+        const int j = idx >> 6, r = idx & 63;
+        const uint8_t* src = stage + (j >> 2) * 8192 + r * 128;
+        const int jj = j & 3;
+        const float4 a = *reinterpret_cast<const float4*>(src + (((2 * jj) ^ (r & 7)) << 4));
+        const float4 b = *reinterpret_cast<const float4*>(src + (((2 * jj + 1) ^ (r & 7)) << 4));
+        asum[it][0] += a.x; asum[it][1] += a.y; asum[it][2] += a.z; asum[it][3] += a.w;
+        asum[it][4] += b.x; asum[it][5] += b.y; asum[it][6] += b.z; asum[it][7] += b.w;
+        uint4 h, l;
+        split2(a.x, a.y, h.x, l.x);
+        split2(a.z, a.w, h.y, l.y);
+        split2(b.x, b.y, h.z, l.z);
+        split2(b.z, b.w, h.w, l.w);
+        const uint32_t off = (uint32_t)((((r >> 3) * 8 + j) << 7) + ((r & 7) << 4));
+        *reinterpret_cast<uint4*>(hi + off) = h;
+        *reinterpret_cast<uint4*>(lo + off) = l;
+    }
+}
+
+__global__ void __launch_bounds__(kT1Threads, 1)
+tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+               float* __restrict__ ws, int64_t T, int tile_tokens, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cx;
+    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cx.sm_u32 = smem_u32(cx.sm);
+    cx.bars = o1Bars;
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + o1Misc + 4);
+    cx.status = status;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + o1Misc);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t tiles = gridDim.x, tile = blockIdx.x, n = blockIdx.y;
+    const int64_t t_begin = tile * tile_tokens;
+    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
+    const int nch = (int)((t_end - t_begin + C - 1) / C);
+    float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+
+    if (tid == 0) {
+        *cx.abort_flag = 0;
+        for (int i = 0; i < kT1Stages; ++i) {
+            mbar_init(cx.bar(k1Full + i), 1);
+            mbar_init(cx.bar(k1Empty + i), 4);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(cx.bar(k1KvReady + i), 4);
+            mbar_init(cx.bar(k1KvFree + i), 1);
+        }
+        mbar_init(cx.bar(k1Done), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(cx.sm_u32 + o1Misc), "r"(64u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        const int wg = warp >> 2, w = warp & 3, wtid = tid & 127;
+        uint8_t* kt_hi = cx.sm + o1Kt + wg * 2 * kOpTile;
+        uint8_t* vt_hi = cx.sm + o1Vt + wg * 2 * kOpTile;
+        float asum[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) asum[i][e] = 0.f;
+        bool ok = true;
+        for (int c = wg; c < nch && ok; c += 2) {
+            const int st = c % kT1Stages;
+            if (!(ok = wait_bar_warp(cx, k1Full + st, (c / kT1Stages) & 1, 111))) break;
+            if (c >= 2 && !(ok = wait_bar_warp(cx, k1KvFree + wg, ((c >> 1) - 1) & 1, 112))) break;
+            const uint8_t* stage = cx.sm + o1Stage + st * kT1StageBytes;
+            convert_tile_sum(stage, kt_hi, kt_hi + kOpTile, wtid, asum);
+            convert_tile(stage + kTileF32, vt_hi, vt_hi + kOpTile, wtid);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(k1KvReady + wg)); mbar_arrive(cx.bar(k1Empty + st)); }
+        }
+        // column sums: lanes of a warp hold different token rows of the same 8 columns
+        float* red = reinterpret_cast<float*>(cx.sm + o1Red) + warp * 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float x = asum[i][e];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+                if (lane == 0) red[i * 8 + e] = x;
+            }
+        (void)w;
+    } else if (warp == 8) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int c = 0; c < nch; ++c) {
+                const int st = c % kT1Stages;
+                if (c >= kT1Stages && !wait_bar(cx, k1Empty + st, ((c / kT1Stages) - 1) & 1, 311)) break;
+                const uint32_t dst = cx.sm_u32 + o1Stage + st * kT1StageBytes;
+                const uint32_t bar = cx.bar(k1Full + st);
+                const int tok = (int)(t_begin + (int64_t)c * C);
+                mbar_arrive_expect_tx(bar, kT1StageBytes);
+                tma_load_4d(dst, &map_k, bar, 0, tok, 0, (int)n);
+                tma_load_4d(dst + 8192, &map_k, bar, 0, tok, 1, (int)n);
+                tma_load_4d(dst + kTileF32, &map_v, bar, 0, tok, 0, (int)n);
+                tma_load_4d(dst + kTileF32 + 8192, &map_v, bar, 0, tok, 1, (int)n);
+                issued = c + 1;
+            }
+            if (*cx.abort_flag) {
+                for (int c = max(0, issued - kT1Stages); c < issued; ++c) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(k1Full + c % kT1Stages), (c / kT1Stages) & 1) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
+            }
+        }
+    } else {
+        if (lane == 0) {
+            bool ok = true;
+            for (int c = 0; c < nch && ok; ++c) {
+                const int wg = c & 1;
+                if (!(ok = wait_bar(cx, k1KvReady + wg, (c >> 1) & 1, 411))) break;
+                tc_fence_after();
+                const uint32_t kt = cx.sm_u32 + o1Kt + wg * 2 * kOpTile;
+                const uint32_t vt = cx.sm_u32 + o1Vt + wg * 2 * kOpTile;
+#pragma unroll
+                for (int pass = 0; pass < 3; ++pass) {
+                    const uint32_t a = kt + (pass == 2 ? kOpTile : 0);
+                    const uint32_t b = vt + (pass == 1 ? kOpTile : 0);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        mma_bf16(tmem, make_desc(a + k * 2048, 1024, 128), make_desc(b + k * 2048, 1024, 128),
+                                 kIdescBase | kAmn | kBmn, (c | pass | k) ? 1u : 0u);
+                }
+                mma_commit(cx.bar(k1KvFree + wg));
+            }
+            mma_commit(cx.bar(k1Done));
+        }
+    }
+    __syncthreads();   // column-sum partials are in shared memory
+    if (warp < 4) {
+        const bool ok = wait_bar_warp(cx, k1Done, 0, 113);
+        if (ok) {
+            tc_fence_after();
+            float v[32];
+            tmem_ld64(((uint32_t)(32 * warp) << 16) + tmem, v);
+            tc_fence_before();
+            const int q = lane & 3, rbase = 16 * warp + (lane >> 2);
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    *reinterpret_cast<float2*>(slice + (rbase + 8 * h) * D + 8 * x + 2 * q) =
+                        make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+            if (tid < 64) {
+                // column s = 8 j + e with j = 2 item + (warp_in_group >> 1); partials from both
+                // groups and both row halves, added in a fixed order
+                const int j = tid >> 3, e = tid & 7, it = j >> 1, wh = (j & 1) * 2;
+                const float* red = reinterpret_cast<const float*>(cx.sm + o1Red);
+                float a = 0.f;
+#pragma unroll
+                for (int g = 0; g < 2; ++g)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                        a += red[(g * 4 + wh + half) * 32 + it * 8 + e];
+                slice[S * D + tid] = a;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(64u) : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -669,19 +873,23 @@ size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
                               const float* carry_in, float* state_out, void* ws, const Dims& dm,
                               int dtype, int tile_tokens, cudaStream_t stream, int* status) {
-    // tile totals and the scan over tiles run on the CUDA-core kernels; the output pass below
-    // replaces the third launch
-    cudaError_t err = causal_fwd_simt(nullptr, pk, v, nullptr, carry_in, state_out, (float*)ws, dm,
-                                      dtype, tile_tokens, /*totals_only=*/false, stream, /*skip_output=*/true);
-    if (err != cudaSuccess) return err;
     CUtensorMap mq, mk, mv;
     if (!make_map(&mq, pq, dm.N, dm.T, dm.S) || !make_map(&mk, pk, dm.N, dm.T, dm.S) ||
         !make_map(&mv, v, dm.N, dm.T, dm.D))
         return cudaErrorInvalidValue;
-    err = cudaFuncSetAttribute(causal_out_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (err != cudaSuccess) return err;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     dim3 grid((unsigned)tiles, (unsigned)dm.N);
+    // 1. tile totals (tensor cores)  2. exclusive scan over tiles  3. output pass
+    cudaError_t err = cudaFuncSetAttribute(tile_totals_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kT1SmemBytes);
+    if (err != cudaSuccess) return err;
+    tile_totals_tc<<<grid, kT1Threads, kT1SmemBytes, stream>>>(mk, mv, (float*)ws, dm.T, tile_tokens, status);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream);
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(causal_out_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (err != cudaSuccess) return err;
     causal_out_tc<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, (float*)out, (const float*)ws, dm.T,
                                                           tile_tokens, dm.eps, status);
     return cudaGetLastError();

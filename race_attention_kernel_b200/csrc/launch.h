@@ -18,6 +18,10 @@ cudaError_t causal_fwd_simt(const void* pq, const void* pk, const void* v, void*
                             int dtype, int tile_tokens, bool totals_only, cudaStream_t stream,
                             bool skip_output = false);
 
+// in-place exclusive scan over the per-tile totals in ws (+ carry_in), inclusive total to state_out
+cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out, const Dims& dm,
+                              int tile_tokens, cudaStream_t stream);
+
 // ---- non-causal path (noncausal_simt.cu) ------------------------------------------------------
 cudaError_t noncausal_query(const void* pq, const float* totals, void* out, const Dims& dm, int dtype,
                             int sm_count, cudaStream_t stream);
