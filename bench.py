@@ -206,6 +206,9 @@ def main():
         e1.record()
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
+    code = rk.ops.device_status(dev)
+    if code:
+        raise SystemExit(f"a bounded device-side wait ran out during the timed region (code {code})")
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -14,7 +14,7 @@
 // Warp roles (14 warps): two worker warpgroups take alternate chunks (fp32 -> bf16 operand
 // tiles, W, mask of G, output store); a third warpgroup copies the running B from TMEM to its
 // bf16 operand tile after every update; one warp issues TMA loads into a two-stage ring; one
-// thread issues every tcgen05.mma.  All hand-offs are mbarriers; every wait is bounded and a
+// warp per worker group issues its tcgen05.mma instructions.  All hand-offs are mbarriers; every wait is bounded and a
 // wait that runs out raises the status word and makes the CTA drain and exit.
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -28,31 +28,31 @@ namespace {
 constexpr int C = 64;           // tokens per chunk
 constexpr int S = 64;           // buckets per CTA
 constexpr int D = 64;           // head dim
-constexpr int kThreads = 14 * 32;
+constexpr int kThreads = 15 * 32;
 constexpr int kProducerWarp = 12;
-constexpr int kMmaWarp = 13;
+constexpr int kMmaWarp = 13;       // warps 13 and 14 issue the MMAs of worker group 0 / 1
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitCycles = 1ll << 31;   // ~1 s: bound of every device-side wait
 
 // ---- shared memory map (bytes from a 1024-aligned base) ---------------------------------------
 constexpr int kTileF32 = C * 64 * 4;        // one staged fp32 tile: 64 tokens x 64 values
-constexpr int kStageBytes = 3 * kTileF32;   // pK | V | pQ
+constexpr int kStageBytes = 2 * kTileF32;   // pK | V  (pQ goes global -> registers)
 constexpr int kOpTile = C * 64 * 2;         // one bf16 operand tile (8 KB)
 constexpr int oStage = 0;                               // [2][kStageBytes]
 constexpr int oKt = oStage + 2 * kStageBytes;           // [2 wg][hi|lo]
 constexpr int oVt = oKt + 4 * kOpTile;
 constexpr int oWt = oVt + 4 * kOpTile;                  // W, then reused for masked G
-constexpr int oBt = oWt + 4 * kOpTile;                  // [hi|lo]
-constexpr int oTril = oBt + 2 * kOpTile;
+constexpr int oBt = oWt + 4 * kOpTile;                  // [2 buffers][hi|lo]
+constexpr int oTril = oBt + 4 * kOpTile;
 constexpr int oAcar = oTril + kOpTile;                  // [2][64] fp32
 constexpr int oBars = oAcar + 2 * 64 * 4;
-constexpr int kNumBars = 24;
+constexpr int kNumBars = 28;
 constexpr int oMisc = oBars + kNumBars * 8;             // tmem base, abort flag
 constexpr int kSmemBytes = oMisc + 16 + 1024;           // + slack for manual alignment
 
 enum Bar {
     kFull = 0,      // [2] stage filled by TMA
-    kEmpty = 2,     // [2] stage released by its worker group (8 warp arrivals)
+    kEmpty = 2,     // [2] stage released by its worker group (4 warp arrivals)
     kKvReady = 4,   // [2] Kt/Vt operand tiles written
     kXReady = 6,    // [2] A_loc accumulator complete
     kWReady = 8,    // [2] W operand tile written
@@ -61,9 +61,10 @@ enum Bar {
     kOReady = 14,   // [2] O accumulator complete
     kAcar = 16,     // [2] running A of the chunk published
     kBupdDone = 18, // B accumulator holds the state after chunk c
-    kBaccFree = 19, // B accumulator read out (count 4)
-    kBtReady = 20,  // B operand tile of chunk c written (count 4)
-    kDrain = 21
+    kBaccFree = 19, // [2] B accumulator read out, free for the update of chunk c: barrier c & 1
+    kBtReady = 21,  // [2] B operand buffer (c & 1) holds the state before chunk c (count 4)
+    kDrain = 23,    // [2]
+    kAcarFree = 25  // [2] running-A buffer of group g read by all four of its warps
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -154,6 +155,31 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint3
     return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
            ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
 }
+// The same descriptor split into words so that the issuing thread only adds a constant per
+// k-step: hi word is fixed per layout, lo word = (addr >> 4) | (lbo >> 4) << 16.
+//   K-major tile  (lbo 128, sbo 1024): 16 K-elements further = +256 B  = +16 in the lo word
+//   MN-major tile (lbo 1024, sbo 128): 16 K-elements further = +2048 B = +128 in the lo word
+constexpr uint32_t kHiK = (1024u >> 4) | (1u << 14);
+constexpr uint32_t kHiMN = (128u >> 4) | (1u << 14);
+__device__ __forceinline__ uint32_t lo_k(uint32_t addr) { return ((addr >> 4) & 0x3FFF) | ((128u >> 4) << 16); }
+__device__ __forceinline__ uint32_t lo_mn(uint32_t addr) { return ((addr >> 4) & 0x3FFF) | ((1024u >> 4) << 16); }
+__device__ __forceinline__ uint64_t desc64(uint32_t hi, uint32_t lo) { return ((uint64_t)hi << 32) | lo; }
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_issue(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(kAccumulate ? 1u : 0u));
+}
+// one 64-deep product = 4 k-steps; kAStep / kBStep are the lo-word increments per k-step
+template <bool kFirstZero, uint32_t kAHi, uint32_t kAStep, uint32_t kBHi, uint32_t kBStep>
+__device__ __forceinline__ void mma_k64(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    if (kFirstZero) mma_issue<false>(d_tmem, desc64(kAHi, a_lo), desc64(kBHi, b_lo), idesc);
+    else mma_issue<true>(d_tmem, desc64(kAHi, a_lo), desc64(kBHi, b_lo), idesc);
+#pragma unroll
+    for (uint32_t k = 1; k < 4; ++k)
+        mma_issue<true>(d_tmem, desc64(kAHi, a_lo + k * kAStep), desc64(kBHi, b_lo + k * kBStep), idesc);
+}
+
 // instruction descriptor: bf16 x bf16 -> fp32, M = 64, N = 64
 constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((64u >> 4) << 24);
 constexpr uint32_t kAmn = 1u << 15;  // A operand is M-major
@@ -171,6 +197,26 @@ __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t&
     lo = *reinterpret_cast<uint32_t*>(&l);
 }
 
+// Optional stage tracing (compiled in with -DRACE_TC_TRACE only): CTA (0,0) records clock64() at
+// stage boundaries into a device buffer [role][chunk][stage] for off-line latency analysis.
+#ifdef RACE_TC_TRACE
+__device__ long long* g_trace_buf = nullptr;
+#define RACE_TRACE(role, c, stage)                                                              \
+    do {                                                                                        \
+        if (g_trace_buf && blockIdx.x == 1 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (c) < 32) \
+            g_trace_buf[((role) * 32 + (c)) * 8 + (stage)] = clock64();                         \
+    } while (0)
+#define RACE_TRACE_STUCK(code, bar, parity)                                                     \
+    do {                                                                                        \
+        if (g_trace_buf && (threadIdx.x & 31) == 0)                                             \
+            g_trace_buf[5 * 32 * 8 + (threadIdx.x >> 5)] =                                      \
+                (long long)(code) * 10000 + (bar) * 10 + (parity) + 1000000ll * (blockIdx.x + 1); \
+    } while (0)
+#else
+#define RACE_TRACE(role, c, stage) do {} while (0)
+#define RACE_TRACE_STUCK(code, bar, parity) do {} while (0)
+#endif
+
 struct Ctx {
     uint8_t* sm;        // 1024-aligned shared base (generic pointer)
     uint32_t sm_u32;    // same, shared-window address
@@ -187,10 +233,11 @@ __device__ __forceinline__ bool wait_bar(const Ctx& cx, int bar, uint32_t parity
     int spins = 0;
     while (!mbar_try_wait(cx.bar(bar), parity)) {
         if ((++spins & 63) == 0) {
-            if (*cx.abort_flag) return false;
+            if (*cx.abort_flag) { RACE_TRACE_STUCK(code, bar, parity); return false; }
             if (clock64() - t0 > kWaitCycles) {
                 *cx.abort_flag = 1;
                 if (cx.status) atomicCAS(cx.status, 0, code);
+                RACE_TRACE_STUCK(code, bar, parity);
                 return false;
             }
         }
@@ -227,7 +274,7 @@ __device__ __forceinline__ void convert_tile(const uint8_t* stage, uint8_t* hi, 
 
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads, 1)
-causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, float* __restrict__ out,
               const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int* status) {
     extern __shared__ uint8_t smem_raw[];
@@ -251,7 +298,7 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         *cx.abort_flag = 0;
         for (int i = 0; i < 2; ++i) {
             mbar_init(cx.bar(kFull + i), 1);
-            mbar_init(cx.bar(kEmpty + i), 8);
+            mbar_init(cx.bar(kEmpty + i), 4);
             mbar_init(cx.bar(kKvReady + i), 4);
             mbar_init(cx.bar(kXReady + i), 1);
             mbar_init(cx.bar(kWReady + i), 4);
@@ -259,11 +306,15 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             mbar_init(cx.bar(kGtReady + i), 4);
             mbar_init(cx.bar(kOReady + i), 1);
             mbar_init(cx.bar(kAcar + i), 1);
+            mbar_init(cx.bar(kAcarFree + i), 4);
         }
         mbar_init(cx.bar(kBupdDone), 1);
         mbar_init(cx.bar(kBaccFree), 4);
+        mbar_init(cx.bar(kBaccFree + 1), 4);
         mbar_init(cx.bar(kBtReady), 4);
+        mbar_init(cx.bar(kBtReady + 1), 4);
         mbar_init(cx.bar(kDrain), 1);
+        mbar_init(cx.bar(kDrain + 1), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kMmaWarp) {
@@ -303,18 +354,65 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         uint8_t* wt_lo = wt_hi + kOpTile;
         const uint8_t* stage = cx.sm + oStage + wg * kStageBytes;
         float* out_n = out + n * T * D;
+        const float* pq_n = pq + n * T * S;
+        float v[32];
+
+        // O of chunk c: TMEM -> global (fragment rows rbase, rbase + 8; 8-byte stores, full sectors)
+        auto store_out = [&](int c) {
+            const int64_t tok0 = t_begin + (int64_t)c * C;
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+            tc_fence_after();
+            tmem_ld64(lane_base + tmO(wg), v);
+            tc_fence_before();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                if (row < valid) {
+                    float* orow = out_n + (tok0 + row) * D + 2 * q;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x)
+                        __stcs(reinterpret_cast<float2*>(orow + 8 * x),
+                               make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]));
+                }
+            }
+        };
+
         uint32_t ph = 0;   // parity of this group's per-chunk barriers (one use per chunk)
         bool ok = true;
+        int c_last = -1;
         for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
             const int64_t tok0 = t_begin + (int64_t)c * C;
             const int valid = (int)min((int64_t)C, t_end - tok0);
+            // the MMAs of this group's previous chunk have retired: its Kt/Vt tiles are free and
+            // its O accumulator is complete
+            RACE_TRACE(wg, c, 0);
+            if (c >= 2 && !(ok = wait_bar_warp(cx, kOReady + wg, ph ^ 1, 105))) break;
             // -- S1: staged pK, V -> operand tiles ------------------------------------------------
+            RACE_TRACE(wg, c, 1);
             if (!(ok = wait_bar_warp(cx, kFull + wg, ph, 101))) break;
+            RACE_TRACE(wg, c, 2);
             convert_tile(stage, kt_hi, kt_lo, wtid);
             convert_tile(stage + kTileF32, vt_hi, vt_lo, wtid);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) { mbar_arrive(cx.bar(kKvReady + wg)); mbar_arrive(cx.bar(kEmpty + wg)); }
+
+            // pQ of this chunk in the accumulator-fragment layout, straight from global memory;
+            // the loads are in flight while the previous chunk's output is stored
+            float2 pqv[16];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                const float* prow = pq_n + (tok0 + row) * S + 2 * q;
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    pqv[2 * x + h] = row < valid ? __ldcs(reinterpret_cast<const float2*>(prow + 8 * x))
+                                                 : make_float2(0.f, 0.f);
+            }
+            // -- S4 of the previous chunk, in the shadow of this chunk's running-sum MMA ----------
+            RACE_TRACE(wg, c, 3);
+            if (c >= 2) store_out(c - 2);
+            RACE_TRACE(wg, c, 4);
 
             // -- S2: W = pQ / (A + A_loc + eps) ----------------------------------------------------
             if (!(ok = wait_bar_warp(cx, kAcar + wg, ph, 102))) break;
@@ -327,35 +425,34 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     acar[2 * x] = a2.x; acar[2 * x + 1] = a2.y;
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(kAcarFree + wg));
+            // the warp that publishes the next running A overwrites the other group's buffer:
+            // every warp of that group must have read the values of its previous chunk
+            if (w == 3 && c >= 1 && !(ok = wait_bar_warp(cx, kAcarFree + (wg ^ 1), ((c - 1) >> 1) & 1, 107))) break;
             if (!(ok = wait_bar_warp(cx, kXReady + wg, ph, 103))) break;
+            RACE_TRACE(wg, c, 5);
             tc_fence_after();
-            float v[32];
             tmem_ld64(lane_base + tmAG(wg), v);
             tc_fence_before();
-            {
-                const uint8_t* sq = stage + 2 * kTileF32;
 #pragma unroll
-                for (int x = 0; x < 8; ++x) {
+            for (int x = 0; x < 8; ++x) {
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int row = rbase + 8 * h;
-                        const int chunk = 2 * (x & 3) + (q >> 1);
-                        const float2 pq = *reinterpret_cast<const float2*>(
-                            sq + (x >> 2) * 8192 + row * 128 + ((chunk ^ (row & 7)) << 4) + (q & 1) * 8);
-                        const float a0 = acar[2 * x] + v[4 * x + 2 * h];
-                        const float a1 = acar[2 * x + 1] + v[4 * x + 2 * h + 1];
-                        const float w0 = __fdividef(pq.x, a0 + eps);
-                        const float w1 = __fdividef(pq.y, a1 + eps);
-                        uint32_t hi, lo;
-                        split2(w0, w1, hi, lo);
-                        const uint32_t off = op_off(row, 8 * x + 2 * q);
-                        *reinterpret_cast<uint32_t*>(wt_hi + off) = hi;
-                        *reinterpret_cast<uint32_t*>(wt_lo + off) = lo;
-                        if (h == 1 && w == 3 && (lane >> 2) == 7) {
-                            // row 63: the running A after this chunk, for the other group
-                            float* an = reinterpret_cast<float*>(cx.sm + oAcar) + (wg ^ 1) * 64;
-                            *reinterpret_cast<float2*>(an + 8 * x + 2 * q) = make_float2(a0, a1);
-                        }
+                for (int h = 0; h < 2; ++h) {
+                    const int row = rbase + 8 * h;
+                    const float a0 = acar[2 * x] + v[4 * x + 2 * h];
+                    const float a1 = acar[2 * x + 1] + v[4 * x + 2 * h + 1];
+                    const float w0 = __fdividef(pqv[2 * x + h].x, a0 + eps);
+                    const float w1 = __fdividef(pqv[2 * x + h].y, a1 + eps);
+                    uint32_t hi, lo;
+                    split2(w0, w1, hi, lo);
+                    const uint32_t off = op_off(row, 8 * x + 2 * q);
+                    *reinterpret_cast<uint32_t*>(wt_hi + off) = hi;
+                    *reinterpret_cast<uint32_t*>(wt_lo + off) = lo;
+                    if (h == 1 && w == 3 && (lane >> 2) == 7) {
+                        // row 63: the running A after this chunk, for the other group
+                        float* an = reinterpret_cast<float*>(cx.sm + oAcar) + (wg ^ 1) * 64;
+                        *reinterpret_cast<float2*>(an + 8 * x + 2 * q) = make_float2(a0, a1);
                     }
                 }
             }
@@ -363,12 +460,13 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(cx.bar(kWReady + wg));
-                mbar_arrive(cx.bar(kEmpty + wg));
                 if (w == 3) mbar_arrive(cx.bar(kAcar + (wg ^ 1)));
             }
 
             // -- S3: G -> causal mask -> operand tile (over W's buffer) ----------------------------
+            RACE_TRACE(wg, c, 6);
             if (!(ok = wait_bar_warp(cx, kGReady + wg, ph, 104))) break;
+            RACE_TRACE(wg, c, 7);
             tc_fence_after();
             tmem_ld64(lane_base + tmAG(wg), v);
             tc_fence_before();
@@ -389,30 +487,15 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(cx.bar(kGtReady + wg));
-
-            // -- S4: O -> global -------------------------------------------------------------------
-            if (!(ok = wait_bar_warp(cx, kOReady + wg, ph, 105))) break;
-            tc_fence_after();
-            tmem_ld64(lane_base + tmO(wg), v);
-            tc_fence_before();
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int row = rbase + 8 * h;
-                if (row < valid) {
-                    float* orow = out_n + (tok0 + row) * D + 2 * q;
-#pragma unroll
-                    for (int x = 0; x < 8; ++x)
-                        __stcs(reinterpret_cast<float2*>(orow + 8 * x),
-                               make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]));
-                }
-            }
+            c_last = c;
         }
+        // -- S4 of this group's last chunk -------------------------------------------------------------
+        if (ok && c_last >= 0 && wait_bar_warp(cx, kOReady + wg, (uint32_t)((c_last >> 1) & 1), 106))
+            store_out(c_last);
     } else if (warp < 12) {
         // =========================== carry warpgroup ===========================================
         const int w = warp & 3, q = lane & 3, rbase = 16 * w + (lane >> 2);
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
-        uint8_t* bt_hi = cx.sm + oBt;
-        uint8_t* bt_lo = bt_hi + kOpTile;
         float v[32];
         // carry-in: B -> TMEM accumulator and operand tile; A -> the first chunk's running A
 #pragma unroll
@@ -441,11 +524,14 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             }
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(cx.bar(kBaccFree));
+                mbar_arrive(cx.bar(kBaccFree + ((c + 1) & 1)));
                 if (c < 0 && warp == 8) mbar_arrive(cx.bar(kAcar + 0));
             }
-            // the previous operand tile may be overwritten once W.B of chunk c has completed
-            if (c >= 0 && !(ok = wait_bar_warp(cx, kGReady + (c & 1), (c >> 1) & 1, 202))) break;
+            // state before chunk c + 1 goes to operand buffer (c + 1) & 1, last read by W.B of
+            // chunk c - 1: that product must have retired
+            if (c >= 1 && !(ok = wait_bar_warp(cx, kGReady + ((c - 1) & 1), ((c - 1) >> 1) & 1, 202))) break;
+            uint8_t* bt_hi = cx.sm + oBt + ((c + 1) & 1) * 2 * kOpTile;
+            uint8_t* bt_lo = bt_hi + kOpTile;
 #pragma unroll
             for (int x = 0; x < 8; ++x)
 #pragma unroll
@@ -458,7 +544,7 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(cx.bar(kBtReady));
+            if (lane == 0) mbar_arrive(cx.bar(kBtReady + ((c + 1) & 1)));
         }
     } else if (warp == kProducerWarp) {
         // =========================== TMA producer ==============================================
@@ -475,8 +561,6 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 tma_load_4d(dst + 8192, &map_k, bar, 0, tok, 1, (int)n);
                 tma_load_4d(dst + kTileF32, &map_v, bar, 0, tok, 0, (int)n);
                 tma_load_4d(dst + kTileF32 + 8192, &map_v, bar, 0, tok, 1, (int)n);
-                tma_load_4d(dst + 2 * kTileF32, &map_q, bar, 0, tok, 0, (int)n);
-                tma_load_4d(dst + 2 * kTileF32 + 8192, &map_q, bar, 0, tok, 1, (int)n);
                 issued = c + 1;
             }
             if (*cx.abort_flag) {
@@ -489,116 +573,66 @@ causal_out_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             }
         }
     } else {
-        // =========================== MMA issuer ================================================
+        // =========================== MMA issuers (one warp per worker group) ====================
+        const int wg = warp - kMmaWarp;
         if (lane == 0) {
-            const uint32_t tril = cx.sm_u32 + oTril;
-            const uint32_t bt = cx.sm_u32 + oBt;
-            int st[2] = {0, 0};
-            int ch[2] = {0, 1};
-            uint32_t ph[2] = {0, 0};
-            int next_bupd = 0, next_wb = 0;
-            long long t_idle = clock64();
+            // lo words of every operand tile's descriptor
+            constexpr uint32_t kLimb = kOpTile >> 4;   // hi -> lo limb tile, in lo-word units
+            const uint32_t tril_lo = lo_k(cx.sm_u32 + oTril);
+            const uint32_t kt_k = lo_k(cx.sm_u32 + oKt + wg * 2 * kOpTile);
+            const uint32_t kt_mn = lo_mn(cx.sm_u32 + oKt + wg * 2 * kOpTile);
+            const uint32_t vt_mn = lo_mn(cx.sm_u32 + oVt + wg * 2 * kOpTile);
+            const uint32_t wt_k = lo_k(cx.sm_u32 + oWt + wg * 2 * kOpTile);
+            const uint32_t bt_mn = lo_mn(cx.sm_u32 + oBt + wg * 2 * kOpTile);
+            const uint32_t dAG = tmAG(wg), dO = tmO(wg);
+            uint32_t ph = 0;
             bool ok = true;
-            while (ok && (ch[0] < nch || ch[1] < nch)) {
-                bool progress = false;
-#pragma unroll
-                for (int wg = 0; wg < 2; ++wg) {
-                    const int c = ch[wg];
-                    if (c >= nch) continue;
-                    const uint32_t kt = cx.sm_u32 + oKt + wg * 2 * kOpTile;
-                    const uint32_t vt = cx.sm_u32 + oVt + wg * 2 * kOpTile;
-                    const uint32_t wt = cx.sm_u32 + oWt + wg * 2 * kOpTile;
-                    if (st[wg] == 0) {
-                        if (!mbar_try_wait(cx.bar(kKvReady + wg), ph[wg])) continue;
-                        tc_fence_after();
-                        // A_loc = tril . pK : A = tril (K-major), B = pK [token][s] (N-major)
-#pragma unroll
-                        for (int limb = 0; limb < 2; ++limb)
-#pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                mma_bf16(tmAG(wg), make_desc(tril + k * 256, 128, 1024),
-                                         make_desc(kt + limb * kOpTile + k * 2048, 1024, 128),
-                                         kIdescBase | kBmn, (limb | k) ? 1u : 0u);
-                        mma_commit(cx.bar(kXReady + wg));
-                        st[wg] = 1; progress = true;
-                    } else if (st[wg] == 1) {
-                        if (c != next_bupd || !mbar_try_wait(cx.bar(kBaccFree), c & 1)) continue;
-                        tc_fence_after();
-                        // B += pK^T . V : A = pK [token][s] (M-major), B = V [token][c] (N-major)
-#pragma unroll
-                        for (int pass = 0; pass < 3; ++pass) {
-                            const uint32_t a = kt + (pass == 2 ? kOpTile : 0);
-                            const uint32_t b = vt + (pass == 1 ? kOpTile : 0);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                mma_bf16(tmB, make_desc(a + k * 2048, 1024, 128),
-                                         make_desc(b + k * 2048, 1024, 128), kIdescBase | kAmn | kBmn, 1u);
-                        }
-                        mma_commit(cx.bar(kBupdDone));
-                        ++next_bupd;
-                        st[wg] = 2; progress = true;
-                    } else if (st[wg] == 2) {
-                        if (c != next_wb || !mbar_try_wait(cx.bar(kWReady + wg), ph[wg]) ||
-                            !mbar_try_wait(cx.bar(kBtReady), c & 1))
-                            continue;
-                        tc_fence_after();
-#pragma unroll
-                        for (int pass = 0; pass < 3; ++pass) {
-                            // O = W . B : A = W (K-major), B = state [s][c] (N-major)
-                            const uint32_t a = wt + (pass == 2 ? kOpTile : 0);
-                            const uint32_t b = bt + (pass == 1 ? kOpTile : 0);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                mma_bf16(tmO(wg), make_desc(a + k * 256, 128, 1024),
-                                         make_desc(b + k * 2048, 1024, 128), kIdescBase | kBmn,
-                                         (pass | k) ? 1u : 0u);
-                        }
-#pragma unroll
-                        for (int pass = 0; pass < 3; ++pass) {
-                            // G = W . pK^T : A = W (K-major), B = pK [token][s] (K-major)
-                            const uint32_t a = wt + (pass == 2 ? kOpTile : 0);
-                            const uint32_t b = kt + (pass == 1 ? kOpTile : 0);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                mma_bf16(tmAG(wg), make_desc(a + k * 256, 128, 1024),
-                                         make_desc(b + k * 256, 128, 1024), kIdescBase,
-                                         (pass | k) ? 1u : 0u);
-                        }
-                        mma_commit(cx.bar(kGReady + wg));
-                        ++next_wb;
-                        st[wg] = 3; progress = true;
-                    } else {
-                        if (!mbar_try_wait(cx.bar(kGtReady + wg), ph[wg])) continue;
-                        tc_fence_after();
-#pragma unroll
-                        for (int pass = 0; pass < 3; ++pass) {
-                            // O += G . V : A = masked G (K-major), B = V [token][c] (N-major)
-                            const uint32_t a = wt + (pass == 2 ? kOpTile : 0);
-                            const uint32_t b = vt + (pass == 1 ? kOpTile : 0);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                mma_bf16(tmO(wg), make_desc(a + k * 256, 128, 1024),
-                                         make_desc(b + k * 2048, 1024, 128), kIdescBase | kBmn, 1u);
-                        }
-                        mma_commit(cx.bar(kOReady + wg));
-                        st[wg] = 0; ch[wg] += 2; ph[wg] ^= 1; progress = true;
-                    }
-                }
-                if (progress) {
-                    t_idle = clock64();
-                } else {
-                    if (*cx.abort_flag) ok = false;
-                    else if (clock64() - t_idle > kWaitCycles) {
-                        *cx.abort_flag = 1;
-                        if (status) atomicCAS(status, 0, 401);
-                        ok = false;
-                    }
-                }
+            for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
+                // A_loc = tril . pK : A = tril (K-major), B = pK [token][s] (N-major)
+                if (!(ok = wait_bar(cx, kKvReady + wg, ph, 401))) break;
+                tc_fence_after();
+                RACE_TRACE(4, c, 0);
+                mma_k64<true, kHiK, 16, kHiMN, 128>(dAG, tril_lo, kt_mn, kIdescBase | kBmn);
+                mma_k64<false, kHiK, 16, kHiMN, 128>(dAG, tril_lo, kt_mn + kLimb, kIdescBase | kBmn);
+                mma_commit(cx.bar(kXReady + wg));
+                RACE_TRACE(4, c, 1);
+                // B += pK^T . V, in chunk order: the accumulator is free once the state after
+                // chunk c - 1 has been read out
+                if (!(ok = wait_bar(cx, kBaccFree + wg, ph, 403))) break;
+                tc_fence_after();
+                RACE_TRACE(4, c, 2);
+                mma_k64<false, kHiMN, 128, kHiMN, 128>(tmB, kt_mn, vt_mn, kIdescBase | kAmn | kBmn);
+                mma_k64<false, kHiMN, 128, kHiMN, 128>(tmB, kt_mn, vt_mn + kLimb, kIdescBase | kAmn | kBmn);
+                mma_k64<false, kHiMN, 128, kHiMN, 128>(tmB, kt_mn + kLimb, vt_mn, kIdescBase | kAmn | kBmn);
+                mma_commit(cx.bar(kBupdDone));
+                RACE_TRACE(4, c, 3);
+                // O = W . B and G = W . pK^T
+                if (!(ok = wait_bar(cx, kWReady + wg, ph, 404))) break;
+                if (!(ok = wait_bar(cx, kBtReady + wg, ph, 405))) break;
+                tc_fence_after();
+                RACE_TRACE(4, c, 4);
+                mma_k64<true, kHiK, 16, kHiMN, 128>(dO, wt_k, bt_mn, kIdescBase | kBmn);
+                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k, bt_mn + kLimb, kIdescBase | kBmn);
+                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k + kLimb, bt_mn, kIdescBase | kBmn);
+                mma_k64<true, kHiK, 16, kHiK, 16>(dAG, wt_k, kt_k, kIdescBase);
+                mma_k64<false, kHiK, 16, kHiK, 16>(dAG, wt_k, kt_k + kLimb, kIdescBase);
+                mma_k64<false, kHiK, 16, kHiK, 16>(dAG, wt_k + kLimb, kt_k, kIdescBase);
+                mma_commit(cx.bar(kGReady + wg));
+                RACE_TRACE(4, c, 5);
+                // O += G . V : A = masked G (K-major), B = V [token][c] (N-major)
+                if (!(ok = wait_bar(cx, kGtReady + wg, ph, 406))) break;
+                tc_fence_after();
+                RACE_TRACE(4, c, 6);
+                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k, vt_mn, kIdescBase | kBmn);
+                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k, vt_mn + kLimb, kIdescBase | kBmn);
+                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k + kLimb, vt_mn, kIdescBase | kBmn);
+                mma_commit(cx.bar(kOReady + wg));
+                RACE_TRACE(4, c, 7);
             }
-            // everything issued has to retire before TMEM is freed
-            mma_commit(cx.bar(kDrain));
+            // everything this thread issued has to retire before TMEM is freed
+            mma_commit(cx.bar(kDrain + wg));
             const long long t0 = clock64();
-            while (!mbar_try_wait(cx.bar(kDrain), 0) && clock64() - t0 < kWaitCycles) {}
+            while (!mbar_try_wait(cx.bar(kDrain + wg), 0) && clock64() - t0 < kWaitCycles) {}
         }
     }
 
@@ -873,9 +907,8 @@ size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
                               const float* carry_in, float* state_out, void* ws, const Dims& dm,
                               int dtype, int tile_tokens, cudaStream_t stream, int* status) {
-    CUtensorMap mq, mk, mv;
-    if (!make_map(&mq, pq, dm.N, dm.T, dm.S) || !make_map(&mk, pk, dm.N, dm.T, dm.S) ||
-        !make_map(&mv, v, dm.N, dm.T, dm.D))
+    CUtensorMap mk, mv;
+    if (!make_map(&mk, pk, dm.N, dm.T, dm.S) || !make_map(&mv, v, dm.N, dm.T, dm.D))
         return cudaErrorInvalidValue;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     dim3 grid((unsigned)tiles, (unsigned)dm.N);
@@ -890,9 +923,15 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
     if (err != cudaSuccess) return err;
     err = cudaFuncSetAttribute(causal_out_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return err;
-    causal_out_tc<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, (float*)out, (const float*)ws, dm.T,
+    causal_out_tc<<<grid, kThreads, kSmemBytes, stream>>>((const float*)pq, mk, mv, (float*)out, (const float*)ws, dm.T,
                                                           tile_tokens, dm.eps, status);
     return cudaGetLastError();
 }
+
+#ifdef RACE_TC_TRACE
+extern "C" int race_b200_debug_set_trace(long long* buf) {
+    return (int)cudaMemcpyToSymbol(g_trace_buf, &buf, sizeof(buf));
+}
+#endif
 
 }  // namespace race
