@@ -79,7 +79,8 @@ def make_shape(N, T, L, R, dk, dtype, eps) -> _lib.RaceShape:
 def pack_state(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
     """(A [N,L,R], B [N,L,R,d_k]) -> packed fp32 state [N, S*d_k + S] (B first, then A)."""
     N = A.shape[0]
-    return torch.cat([B.reshape(N, -1).float(), A.reshape(N, -1).float()], dim=1).contiguous()
+    dt = torch.float64 if B.dtype == torch.float64 else torch.float32   # fp64 only in CPU tests
+    return torch.cat([B.reshape(N, -1).to(dt), A.reshape(N, -1).to(dt)], dim=1).contiguous()
 
 
 def unpack_state(state: torch.Tensor, L: int, R: int, dk: int):
