@@ -853,7 +853,8 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     if (fn) return fn;
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
-    cudaFree(nullptr);  // make sure the runtime (and with it the driver) is initialised
+    int dev_probe = 0;
+    cudaGetDevice(&dev_probe);  // make sure the runtime (and with it the driver) is initialised
     if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) !=
             cudaSuccess || q != cudaDriverEntryPointSuccess)
         p = nullptr;
