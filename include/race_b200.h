@@ -42,7 +42,8 @@ enum {
     RACE_ERR_WORKSPACE = -4,   /* workspace_bytes smaller than required */
     RACE_ERR_TILE = -5,        /* tile_tokens not a positive multiple of the chunk length */
     RACE_ERR_VARIANT = -6,     /* variant unknown or not available for this shape */
-    RACE_ERR_DEVICE_WAIT = -7  /* a bounded device-side wait ran out (read from status word) */
+    RACE_ERR_DEVICE_WAIT = -7, /* a bounded device-side wait ran out (read from status word) */
+    RACE_ERR_SCRATCH = -8      /* shape needs more workspace than the built-in scratch array holds */
 };
 
 typedef struct RaceShape {
@@ -151,6 +152,27 @@ int race_b200_bucket_probs(const void* x, const float* planes, void* probs, int6
 int race_b200_causal_fwd_host(const void* probs_q, const void* probs_k, const void* v, void* out,
                               const float* carry_in, float* state_out, const RaceShape* shape,
                               int64_t segment_tokens, int variant, int device);
+
+/*
+ * race_b200_causal_fwd without a caller-provided workspace, for callers that cannot allocate
+ * device memory at the point of the call (stream capture in progress, allocator callbacks,
+ * allocation-free real-time loops, embedders with a fixed memory plan).  It has no counterpart
+ * in the reference, whose binding always allocates its workspace from the torch allocator.
+ * Inputs, outputs, carry and state are still the caller's buffers; the workspace is a 16 MiB
+ * array inside the library (race_b200_static_scratch_bytes()), resident on every GPU that loads
+ * the library until the process exits.  No call allocates or frees anything.
+ *   - shapes whose workspace exceeds the array return RACE_ERR_SCRATCH and launch nothing
+ *     (at S = 64, d_k = 64 and 2048-token tiles: up to N * ceil(T / 2048) = 1008 tiles,
+ *     e.g. 8 streams of 258,048 tokens);
+ *   - the first call on a device looks the array's address up (cudaGetSymbolAddress) with that
+ *     device current; make that first call before any stream capture begins;
+ *   - every call uses the same array: calls that overlap on the GPU race on it, so order them
+ *     (one stream, or events).  The array needs no clearing between calls.
+ */
+size_t race_b200_static_scratch_bytes(void);
+int race_b200_causal_fwd_static(const void* probs_q, const void* probs_k, const void* v, void* out,
+                                const float* carry_in, float* state_out, const RaceShape* shape,
+                                int tile_tokens, int variant, void* stream, int* status);
 
 #ifdef __cplusplus
 }

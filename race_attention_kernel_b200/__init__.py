@@ -9,5 +9,5 @@ Public surface:
 """
 from .operator import BatchedACE  # noqa: F401
 from .ops import (bucket_probs, is_supported, pack_state, race_causal_prefix,  # noqa: F401
-                  race_causal_prefix_host, race_noncausal, race_tile_totals, select_tile_tokens,
+                  race_causal_prefix_host, race_causal_prefix_static, race_noncausal, race_tile_totals, select_tile_tokens,
                   unpack_state)

@@ -82,6 +82,7 @@ const char* race_b200_error_string(int code) {
         case RACE_ERR_TILE: return "tile_tokens is not a positive multiple of the chunk length";
         case RACE_ERR_VARIANT: return "kernel variant unknown or unavailable for this shape";
         case RACE_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
+        case RACE_ERR_SCRATCH: return "shape needs more workspace than the built-in scratch array holds";
         default: break;
     }
     if (code > 0) return cudaGetErrorString((cudaError_t)code);

@@ -268,3 +268,29 @@ def race_causal_prefix_host(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=No
         A, B = unpack_state(state, L, R, dk)
         return out, A, B
     return out
+
+
+def race_causal_prefix_static(probsQ, probsK, V, out, eps: float = 1e-6, *, carry_in=None,
+                              state_out: torch.Tensor | None = None, tile_tokens: int = 0,
+                              variant: str = "auto") -> torch.Tensor:
+    """``race_causal_prefix`` for callers that cannot allocate device memory when they call.
+
+    Examples of such callers: code that runs while a CUDA stream capture is open, hooks that the
+    caching allocator itself invokes, serving loops that pre-plan all device memory.  This
+    wrapper allocates nothing either: `out` (and `state_out`, a packed fp32 state
+    [N, S*(d_k+1)], if the final state is wanted) must be passed in, `carry_in` must already be a
+    packed state, and the kernels' workspace is the 16 MiB array built into the library.
+    Shapes that need more raise ``RuntimeError`` (RACE_ERR_SCRATCH).  All calls share that array:
+    issue them on one stream or order them with events.  Make the first call on each device
+    outside of stream capture (it looks up the array's device address)."""
+    N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
+    if out.shape != V.shape or out.dtype != V.dtype or not out.is_contiguous() or out.device != V.device:
+        raise RuntimeError("out must be a contiguous tensor like V")
+    sh = make_shape(N, T, L, R, dk, V.dtype, eps)
+    with torch.cuda.device(V.device):
+        rc = _lib.lib().race_b200_causal_fwd_static(
+            _ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry_in), _ptr(state_out),
+            ctypes.byref(sh), tile_tokens, _lib.VARIANTS[variant], _stream(),
+            _ptr(_status_word(V.device)))
+    _lib.check(rc, "race_b200_causal_fwd_static")
+    return out

@@ -31,7 +31,7 @@ def test_version_and_error_strings():
     L = _lib.lib()
     assert L.race_b200_version() >= 1000
     assert L.race_b200_error_string(0) == b"ok"
-    for code in range(-7, 0):
+    for code in range(-8, 0):
         assert L.race_b200_error_string(code) not in (b"", b"unknown error")
 
 
