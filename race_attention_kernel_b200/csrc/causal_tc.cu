@@ -89,6 +89,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -385,6 +391,18 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             const int valid = (int)min((int64_t)C, t_end - tok0);
             // the MMAs of this group's previous chunk have retired: its Kt/Vt tiles are free and
             // its O accumulator is complete
+            // pQ of this chunk in the accumulator-fragment layout, straight from global memory,
+            // issued first so that the conversion of pK and V below hides the latency
+            float2 pqv[16];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                const float* prow = pq_n + (tok0 + row) * S + 2 * q;
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    pqv[2 * x + h] = row < valid ? __ldcs(reinterpret_cast<const float2*>(prow + 8 * x))
+                                                 : make_float2(0.f, 0.f);
+            }
             RACE_TRACE(wg, c, 0);
             if (c >= 2 && !(ok = wait_bar_warp(cx, kOReady + wg, ph ^ 1, 105))) break;
             // -- S1: staged pK, V -> operand tiles ------------------------------------------------
@@ -397,18 +415,6 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             __syncwarp();
             if (lane == 0) { mbar_arrive(cx.bar(kKvReady + wg)); mbar_arrive(cx.bar(kEmpty + wg)); }
 
-            // pQ of this chunk in the accumulator-fragment layout, straight from global memory;
-            // the loads are in flight while the previous chunk's output is stored
-            float2 pqv[16];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int row = rbase + 8 * h;
-                const float* prow = pq_n + (tok0 + row) * S + 2 * q;
-#pragma unroll
-                for (int x = 0; x < 8; ++x)
-                    pqv[2 * x + h] = row < valid ? __ldcs(reinterpret_cast<const float2*>(prow + 8 * x))
-                                                 : make_float2(0.f, 0.f);
-            }
             // -- S4 of the previous chunk, in the shadow of this chunk's running-sum MMA ----------
             RACE_TRACE(wg, c, 3);
             if (c >= 2) store_out(c - 2);
@@ -574,17 +580,21 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
         }
     } else {
         // =========================== MMA issuers (one warp per worker group) ====================
-        const int wg = warp - kMmaWarp;
-        if (lane == 0) {
-            // lo words of every operand tile's descriptor
-            constexpr uint32_t kLimb = kOpTile >> 4;   // hi -> lo limb tile, in lo-word units
-            const uint32_t tril_lo = lo_k(cx.sm_u32 + oTril);
-            const uint32_t kt_k = lo_k(cx.sm_u32 + oKt + wg * 2 * kOpTile);
-            const uint32_t kt_mn = lo_mn(cx.sm_u32 + oKt + wg * 2 * kOpTile);
-            const uint32_t vt_mn = lo_mn(cx.sm_u32 + oVt + wg * 2 * kOpTile);
-            const uint32_t wt_k = lo_k(cx.sm_u32 + oWt + wg * 2 * kOpTile);
-            const uint32_t bt_mn = lo_mn(cx.sm_u32 + oBt + wg * 2 * kOpTile);
-            const uint32_t dAG = tmAG(wg), dO = tmO(wg);
+        // Everything the issuing thread feeds to tcgen05.mma is derived from warp-uniform values
+        // (the shuffles tell the compiler so), which keeps descriptor arithmetic on the uniform
+        // datapath.
+        const int wg = __shfl_sync(0xffffffffu, warp, 0) - kMmaWarp;
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
+        constexpr uint32_t kLimb = kOpTile >> 4;   // hi -> lo limb tile, in lo-word units
+        const uint32_t tril_lo = lo_k(smb + oTril);
+        const uint32_t kt_k = lo_k(smb + oKt + wg * 2 * kOpTile);
+        const uint32_t kt_mn = lo_mn(smb + oKt + wg * 2 * kOpTile);
+        const uint32_t vt_mn = lo_mn(smb + oVt + wg * 2 * kOpTile);
+        const uint32_t wt_k = lo_k(smb + oWt + wg * 2 * kOpTile);
+        const uint32_t bt_mn = lo_mn(smb + oBt + wg * 2 * kOpTile);
+        const uint32_t dB = tm, dAG = tm + 64 + wg * 128, dO = tm + 64 + wg * 128 + 64;
+        if (elect_one()) {
             uint32_t ph = 0;
             bool ok = true;
             for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
@@ -601,9 +611,9 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                 if (!(ok = wait_bar(cx, kBaccFree + wg, ph, 403))) break;
                 tc_fence_after();
                 RACE_TRACE(4, c, 2);
-                mma_k64<false, kHiMN, 128, kHiMN, 128>(tmB, kt_mn, vt_mn, kIdescBase | kAmn | kBmn);
-                mma_k64<false, kHiMN, 128, kHiMN, 128>(tmB, kt_mn, vt_mn + kLimb, kIdescBase | kAmn | kBmn);
-                mma_k64<false, kHiMN, 128, kHiMN, 128>(tmB, kt_mn + kLimb, vt_mn, kIdescBase | kAmn | kBmn);
+                mma_k64<false, kHiMN, 128, kHiMN, 128>(dB, kt_mn, vt_mn, kIdescBase | kAmn | kBmn);
+                mma_k64<false, kHiMN, 128, kHiMN, 128>(dB, kt_mn, vt_mn + kLimb, kIdescBase | kAmn | kBmn);
+                mma_k64<false, kHiMN, 128, kHiMN, 128>(dB, kt_mn + kLimb, vt_mn, kIdescBase | kAmn | kBmn);
                 mma_commit(cx.bar(kBupdDone));
                 RACE_TRACE(4, c, 3);
                 // O = W . B and G = W . pK^T
