@@ -349,16 +349,11 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
 
     if (warp < 8) {
         // =========================== worker warpgroups =========================================
-        const int wg = warp >> 2, w = warp & 3, wtid = tid & 127;
+        const int wg = warp >> 2, w = warp & 3;
         const int q = lane & 3, rbase = 16 * w + (lane >> 2);
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
-        uint8_t* kt_hi = cx.sm + oKt + wg * 2 * kOpTile;
-        uint8_t* kt_lo = kt_hi + kOpTile;
-        uint8_t* vt_hi = cx.sm + oVt + wg * 2 * kOpTile;
-        uint8_t* vt_lo = vt_hi + kOpTile;
         uint8_t* wt_hi = cx.sm + oWt + wg * 2 * kOpTile;
         uint8_t* wt_lo = wt_hi + kOpTile;
-        const uint8_t* stage = cx.sm + oStage + wg * kStageBytes;
         float* out_n = out + n * T * D;
         const float* pq_n = pq + n * T * S;
         float v[32];
@@ -385,14 +380,11 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
 
         uint32_t ph = 0;   // parity of this group's per-chunk barriers (one use per chunk)
         bool ok = true;
-        int c_last = -1;
         for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
             const int64_t tok0 = t_begin + (int64_t)c * C;
             const int valid = (int)min((int64_t)C, t_end - tok0);
-            // the MMAs of this group's previous chunk have retired: its Kt/Vt tiles are free and
-            // its O accumulator is complete
             // pQ of this chunk in the accumulator-fragment layout, straight from global memory,
-            // issued first so that the conversion of pK and V below hides the latency
+            // issued first so that the wait for the running-sum product hides the latency
             float2 pqv[16];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -404,21 +396,6 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                                                  : make_float2(0.f, 0.f);
             }
             RACE_TRACE(wg, c, 0);
-            if (c >= 2 && !(ok = wait_bar_warp(cx, kOReady + wg, ph ^ 1, 105))) break;
-            // -- S1: staged pK, V -> operand tiles ------------------------------------------------
-            RACE_TRACE(wg, c, 1);
-            if (!(ok = wait_bar_warp(cx, kFull + wg, ph, 101))) break;
-            RACE_TRACE(wg, c, 2);
-            convert_tile(stage, kt_hi, kt_lo, wtid);
-            convert_tile(stage + kTileF32, vt_hi, vt_lo, wtid);
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(cx.bar(kKvReady + wg)); mbar_arrive(cx.bar(kEmpty + wg)); }
-
-            // -- S4 of the previous chunk, in the shadow of this chunk's running-sum MMA ----------
-            RACE_TRACE(wg, c, 3);
-            if (c >= 2) store_out(c - 2);
-            RACE_TRACE(wg, c, 4);
 
             // -- S2: W = pQ / (A + A_loc + eps) ----------------------------------------------------
             if (!(ok = wait_bar_warp(cx, kAcar + wg, ph, 102))) break;
@@ -493,17 +470,38 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(cx.bar(kGtReady + wg));
-            c_last = c;
+
+            // -- S4: O -> global --------------------------------------------------------------------
+            if (!(ok = wait_bar_warp(cx, kOReady + wg, ph, 105))) break;
+            RACE_TRACE(wg, c, 3);
+            store_out(c);
+            RACE_TRACE(wg, c, 4);
         }
-        // -- S4 of this group's last chunk -------------------------------------------------------------
-        if (ok && c_last >= 0 && wait_bar_warp(cx, kOReady + wg, (uint32_t)((c_last >> 1) & 1), 106))
-            store_out(c_last);
     } else if (warp < 12) {
-        // =========================== carry warpgroup ===========================================
-        const int w = warp & 3, q = lane & 3, rbase = 16 * w + (lane >> 2);
+        // =========================== converter + carry warpgroup =================================
+        // Per chunk: staged fp32 pK, V -> bf16 limb tiles of the chunk's worker group, then the
+        // state left by the previous chunk: TMEM accumulator -> bf16 limb tile for the next W.B.
+        const int w = warp & 3, q = lane & 3, rbase = 16 * w + (lane >> 2), wtid = tid & 127;
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
         float v[32];
-        // carry-in: B -> TMEM accumulator and operand tile; A -> the first chunk's running A
+        auto write_bt = [&](int buf) {
+            uint8_t* bt_hi = cx.sm + oBt + buf * 2 * kOpTile;
+            uint8_t* bt_lo = bt_hi + kOpTile;
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t hi, lo;
+                    split2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1], hi, lo);
+                    const uint32_t off = op_off(rbase + 8 * h, 8 * x + 2 * q);
+                    *reinterpret_cast<uint32_t*>(bt_hi + off) = hi;
+                    *reinterpret_cast<uint32_t*>(bt_lo + off) = lo;
+                }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(kBtReady + buf));
+        };
+        // carry-in: B -> TMEM accumulator and operand buffer 0; A -> the first chunk's running A
 #pragma unroll
         for (int x = 0; x < 8; ++x)
 #pragma unroll
@@ -519,38 +517,46 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             ac[lane] = slice[S * D + lane];
             ac[lane + 32] = slice[S * D + lane + 32];
         }
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(cx.bar(kBaccFree + 0));
+            if (warp == 8) mbar_arrive(cx.bar(kAcar + 0));
+        }
+        write_bt(0);
+
         bool ok = true;
-        for (int c = -1; c < nch - 1 && ok; ++c) {
-            if (c >= 0) {
-                // state after chunk c: wait for its update, read it out, hand the accumulator back
-                if (!(ok = wait_bar_warp(cx, kBupdDone, c & 1, 201))) break;
+        for (int c = 0; c < nch && ok; ++c) {
+            const int wg = c & 1;
+            const uint32_t ph = (uint32_t)((c >> 1) & 1);
+            // the MMAs of chunk c - 2 (same group) have retired: its pK / V tiles are free
+            RACE_TRACE(2, c, 0);
+            if (c >= 2 && !(ok = wait_bar_warp(cx, kOReady + wg, ph ^ 1, 205))) break;
+            if (!(ok = wait_bar_warp(cx, kFull + wg, ph, 201))) break;
+            RACE_TRACE(2, c, 1);
+            {
+                const uint8_t* stage = cx.sm + oStage + wg * kStageBytes;
+                uint8_t* kt_hi = cx.sm + oKt + wg * 2 * kOpTile;
+                uint8_t* vt_hi = cx.sm + oVt + wg * 2 * kOpTile;
+                convert_tile(stage, kt_hi, kt_hi + kOpTile, wtid);
+                convert_tile(stage + kTileF32, vt_hi, vt_hi + kOpTile, wtid);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(kKvReady + wg)); mbar_arrive(cx.bar(kEmpty + wg)); }
+            RACE_TRACE(2, c, 2);
+            if (c >= 1 && c < nch) {
+                // state after chunk c - 1 -> operand buffer c & 1 (read by W.B of chunk c)
+                if (!(ok = wait_bar_warp(cx, kBupdDone, (c - 1) & 1, 202))) break;
                 tc_fence_after();
                 tmem_ld64(lane_base + tmB, v);
                 tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(cx.bar(kBaccFree + wg));   // update of chunk c may start
+                // buffer c & 1 was last read by W.B of chunk c - 2
+                if (c >= 2 && !(ok = wait_bar_warp(cx, kGReady + wg, ph ^ 1, 203))) break;
+                write_bt(wg);
             }
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(cx.bar(kBaccFree + ((c + 1) & 1)));
-                if (c < 0 && warp == 8) mbar_arrive(cx.bar(kAcar + 0));
-            }
-            // state before chunk c + 1 goes to operand buffer (c + 1) & 1, last read by W.B of
-            // chunk c - 1: that product must have retired
-            if (c >= 1 && !(ok = wait_bar_warp(cx, kGReady + ((c - 1) & 1), ((c - 1) >> 1) & 1, 202))) break;
-            uint8_t* bt_hi = cx.sm + oBt + ((c + 1) & 1) * 2 * kOpTile;
-            uint8_t* bt_lo = bt_hi + kOpTile;
-#pragma unroll
-            for (int x = 0; x < 8; ++x)
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    uint32_t hi, lo;
-                    split2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1], hi, lo);
-                    const uint32_t off = op_off(rbase + 8 * h, 8 * x + 2 * q);
-                    *reinterpret_cast<uint32_t*>(bt_hi + off) = hi;
-                    *reinterpret_cast<uint32_t*>(bt_lo + off) = lo;
-                }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(cx.bar(kBtReady + ((c + 1) & 1)));
+            RACE_TRACE(2, c, 3);
         }
     } else if (warp == kProducerWarp) {
         // =========================== TMA producer ==============================================
