@@ -46,14 +46,14 @@ constexpr int oBt = oWt + 4 * kOpTile;                  // [2 buffers][hi|lo]
 constexpr int oTril = oBt + 4 * kOpTile;
 constexpr int oAcar = oTril + kOpTile;                  // [2][64] fp32
 constexpr int oBars = oAcar + 2 * 64 * 4;
-constexpr int kNumBars = 28;
+constexpr int kNumBars = 30;
 constexpr int oMisc = oBars + kNumBars * 8;             // tmem base, abort flag
 constexpr int kSmemBytes = oMisc + 16 + 1024;           // + slack for manual alignment
 
 enum Bar {
     kFull = 0,      // [2] stage filled by TMA
     kEmpty = 2,     // [2] stage released by its worker group (4 warp arrivals)
-    kKvReady = 4,   // [2] Kt/Vt operand tiles written
+    kKvReady = 4,   // [2] pK operand tile written
     kXReady = 6,    // [2] A_loc accumulator complete
     kWReady = 8,    // [2] W operand tile written
     kGReady = 10,   // [2] W.B and G accumulators complete
@@ -64,7 +64,8 @@ enum Bar {
     kBaccFree = 19, // [2] B accumulator read out, free for the update of chunk c: barrier c & 1
     kBtReady = 21,  // [2] B operand buffer (c & 1) holds the state before chunk c (count 4)
     kDrain = 23,    // [2]
-    kAcarFree = 25  // [2] running-A buffer of group g read by all four of its warps
+    kAcarFree = 25, // [2] running-A buffer of group g read by all four of its warps
+    kVReady = 27    // [2] V operand tile written
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -313,6 +314,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             mbar_init(cx.bar(kOReady + i), 1);
             mbar_init(cx.bar(kAcar + i), 1);
             mbar_init(cx.bar(kAcarFree + i), 4);
+            mbar_init(cx.bar(kVReady + i), 4);
         }
         mbar_init(cx.bar(kBupdDone), 1);
         mbar_init(cx.bar(kBaccFree), 4);
@@ -528,35 +530,40 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
         for (int c = 0; c < nch && ok; ++c) {
             const int wg = c & 1;
             const uint32_t ph = (uint32_t)((c >> 1) & 1);
-            // the MMAs of chunk c - 2 (same group) have retired: its pK / V tiles are free
+            const uint8_t* stage = cx.sm + oStage + wg * kStageBytes;
+            uint8_t* kt_hi = cx.sm + oKt + wg * 2 * kOpTile;
+            uint8_t* vt_hi = cx.sm + oVt + wg * 2 * kOpTile;
+            // pK tile of the group: last read by the G product of chunk c - 2 (its commit also
+            // covers that chunk's running-sum and state-update products)
             RACE_TRACE(2, c, 0);
-            if (c >= 2 && !(ok = wait_bar_warp(cx, kOReady + wg, ph ^ 1, 205))) break;
+            if (c >= 2 && !(ok = wait_bar_warp(cx, kGReady + wg, ph ^ 1, 203))) break;
             if (!(ok = wait_bar_warp(cx, kFull + wg, ph, 201))) break;
             RACE_TRACE(2, c, 1);
-            {
-                const uint8_t* stage = cx.sm + oStage + wg * kStageBytes;
-                uint8_t* kt_hi = cx.sm + oKt + wg * 2 * kOpTile;
-                uint8_t* vt_hi = cx.sm + oVt + wg * 2 * kOpTile;
-                convert_tile(stage, kt_hi, kt_hi + kOpTile, wtid);
-                convert_tile(stage + kTileF32, vt_hi, vt_hi + kOpTile, wtid);
-            }
+            convert_tile(stage, kt_hi, kt_hi + kOpTile, wtid);
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(cx.bar(kKvReady + wg)); mbar_arrive(cx.bar(kEmpty + wg)); }
+            if (lane == 0) mbar_arrive(cx.bar(kKvReady + wg));
             RACE_TRACE(2, c, 2);
-            if (c >= 1 && c < nch) {
-                // state after chunk c - 1 -> operand buffer c & 1 (read by W.B of chunk c)
+            if (c >= 1) {
+                // state after chunk c - 1 -> operand buffer c & 1 (read by W.B of chunk c; last read
+                // by W.B of chunk c - 2, which the wait on kGReady above covers)
                 if (!(ok = wait_bar_warp(cx, kBupdDone, (c - 1) & 1, 202))) break;
                 tc_fence_after();
                 tmem_ld64(lane_base + tmB, v);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(cx.bar(kBaccFree + wg));   // update of chunk c may start
-                // buffer c & 1 was last read by W.B of chunk c - 2
-                if (c >= 2 && !(ok = wait_bar_warp(cx, kGReady + wg, ph ^ 1, 203))) break;
                 write_bt(wg);
             }
             RACE_TRACE(2, c, 3);
+            // V tile of the group: last read by the G.V product of chunk c - 2
+            if (c >= 2 && !(ok = wait_bar_warp(cx, kOReady + wg, ph ^ 1, 205))) break;
+            RACE_TRACE(2, c, 4);
+            convert_tile(stage + kTileF32, vt_hi, vt_hi + kOpTile, wtid);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(kVReady + wg)); mbar_arrive(cx.bar(kEmpty + wg)); }
+            RACE_TRACE(2, c, 5);
         }
     } else if (warp == kProducerWarp) {
         // =========================== TMA producer ==============================================
@@ -614,6 +621,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                 RACE_TRACE(4, c, 1);
                 // B += pK^T . V, in chunk order: the accumulator is free once the state after
                 // chunk c - 1 has been read out
+                if (!(ok = wait_bar(cx, kVReady + wg, ph, 407))) break;
                 if (!(ok = wait_bar(cx, kBaccFree + wg, ph, 403))) break;
                 tc_fence_after();
                 RACE_TRACE(4, c, 2);
