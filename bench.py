@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c5"],
+                    help="c2 (default): the contract line; the others print extra measurement lines")
     return ap.parse_args()
 
 
@@ -127,8 +129,107 @@ def cpu_run(T_sample: int, steps: int, warmup: int, dtype=torch.float32):
             "seconds_per_step": med}
 
 
+def _time_ms(fn, warmup, steps):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def extra_workloads(args):
+    """Measurement lines for the other BASELINE configurations on one GPU (not the contract line)."""
+    import race_attention_kernel_b200 as rk
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak = FALLBACK_HBM_GBS
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        pass
+
+    def probs(N, T, L, R, dtype, g):
+        # generated stream by stream to bound the fp32 temporaries
+        out = torch.empty(N, T, L, R, dtype=dtype, device=dev)
+        for n in range(N):
+            out[n] = torch.softmax(torch.randn(T, L, R, device=dev, generator=g), -1).to(dtype)
+        return out
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    if args.workload == "sweep":
+        N, L, R, dk = 8, 4, 16, 64
+        T = 4096
+        while True:
+            try:
+                pQ, pK = probs(N, T, L, R, torch.float32, g), probs(N, T, L, R, torch.float32, g)
+                V = torch.randn(N, T, dk, device=dev, generator=g)
+                out = torch.empty_like(V)
+                ms = _time_ms(lambda: rk.race_causal_prefix(pQ, pK, V, out=out), 3, 10 if T <= (1 << 21) else 3)
+            except (torch.OutOfMemoryError, RuntimeError) as e:
+                print(json.dumps({"workload": "sweep", "T": T, "failed": str(e)[:80]}), flush=True)
+                break
+            gbs = N * T * 1024 / (ms * 1e-3) / 1e9
+            print(json.dumps({"workload": "sweep", "N": N, "T": T, "ms": round(ms, 4),
+                              "Mtok_s": round(N * T / ms / 1e3, 1), "GB_s": round(gbs, 1),
+                              "frac_measured_peak": round(gbs / peak, 4),
+                              "peak_GiB": round(torch.cuda.max_memory_allocated() / 2**30, 2),
+                              "status": rk.ops.device_status(dev)}), flush=True)
+            del pQ, pK, V, out
+            torch.cuda.empty_cache()
+            torch.cuda.reset_peak_memory_stats()
+            T = T * 2 if T < (1 << 24) else T + (1 << 22)
+            if T > (3 << 23):
+                break
+    elif args.workload == "c3":
+        # BASELINE config 3 geometry: bf16, d_k=128, L=8, R=64 (S=512); per-GPU share of the 256 streams
+        L, R, dk = 8, 64, 128
+        for N, T in ((32, 65536), (32, 262144)):
+            pQ, pK = probs(N, T, L, R, torch.bfloat16, g), probs(N, T, L, R, torch.bfloat16, g)
+            V = torch.randn(N, T, dk, device=dev, generator=g).bfloat16()
+            out = torch.empty_like(V)
+            ms = _time_ms(lambda: rk.race_causal_prefix(pQ, pK, V, out=out), 2, 3)
+            gbs = N * T * 2560 / (ms * 1e-3) / 1e9
+            print(json.dumps({"workload": "c3", "dtype": "bf16", "N": N, "T": T, "ms": round(ms, 3),
+                              "Mtok_s": round(N * T / ms / 1e3, 1), "GB_s": round(gbs, 1),
+                              "frac_measured_peak": round(gbs / peak, 4), "variant": "simt (cluster of 8)"}),
+                  flush=True)
+            del pQ, pK, V, out
+            torch.cuda.empty_cache()
+    elif args.workload == "c5":
+        # BASELINE config 5: non-causal forward + backward, B=64, H=12 (N=768), T=4096, S=64, d_k=64
+        N, T, L, R, dk = 768, 4096, 4, 16, 64
+        for dtype, elt in ((torch.float32, 4), (torch.bfloat16, 2)):
+            pQ = probs(N, T, L, R, dtype, g).requires_grad_(True)
+            pK = probs(N, T, L, R, dtype, g).requires_grad_(True)
+            V = torch.randn(N, T, dk, device=dev, generator=g).to(dtype).requires_grad_(True)
+            dO = torch.randn(N, T, dk, device=dev, generator=g).to(dtype)
+            with torch.no_grad():
+                ms_f = _time_ms(lambda: rk.race_noncausal(pQ, pK, V), 3, 10)
+
+            def fb():
+                pQ.grad = pK.grad = V.grad = None
+                rk.race_noncausal(pQ, pK, V).backward(dO)
+            ms_fb = _time_ms(fb, 3, 10)
+            bf, bb = N * T * elt * (2 * 64 + 2 * 64), N * T * elt * (4 * 64 + 3 * 64)
+            print(json.dumps({"workload": "c5", "dtype": str(dtype), "N": N, "T": T,
+                              "fwd_ms": round(ms_f, 3), "fwd_bwd_ms": round(ms_fb, 3),
+                              "fwd_GB_s": round(bf / ms_f / 1e6, 1),
+                              "fwd_bwd_GB_s": round((bf + bb) / ms_fb / 1e6, 1),
+                              "fwd_frac": round(bf / ms_f / 1e6 / peak, 4),
+                              "fwd_bwd_frac": round((bf + bb) / ms_fb / 1e6 / peak, 4),
+                              "Mtok_s_fwd_bwd": round(N * T / ms_fb / 1e3, 1)}), flush=True)
+            del pQ, pK, V, dO
+
+
 def main():
     args = parse()
+    if args.workload != "c2":
+        return extra_workloads(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -176,7 +277,7 @@ def main():
     variant = args.variant
     if variant == "auto":
         variant = "tensor" if rk.is_supported(N, T, L, R, dk, tdtype, "tensor") else "simt"
-    launches_per_step = 3 if variant == "simt" else 1
+    launches_per_step = 3   # tile totals, scan over tiles, output pass
 
     def step():
         rk.race_causal_prefix(pQ, pK, V, variant=variant, out=out)
@@ -226,9 +327,12 @@ def main():
     except Exception:
         pass
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+    # DRAM traffic of one forward from the ncu capture in profiles/ (T=131072: output pass 1052.4 MB,
+    # totals pass 546.9 MB, scan 17 MB per 1073.7 MB of algorithmic bytes), scaled by tokens
+    traffic = alg_bytes * (1052.4 + 546.9 + 17.0) / 1073.7 if (variant == "tensor" and args.dtype == "f32") else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
-                "kernel": "causal forward (all launches of one step)",
+                "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
+                "kernel": "causal forward (tile_totals_tc + tile_scan + causal_out_tc of one step)",
                 "algorithmic_bytes_per_launch": alg_bytes}
 
     # e2e: host buffers through the C-ABI host entry point

@@ -105,7 +105,19 @@ int race_b200_causal_fwd(const void* probs_q, const void* probs_k, const void* v
  */
 int race_b200_tile_totals(const void* probs_k, const void* v, float* totals, void* workspace,
                           size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
-                          void* stream);
+                          int variant, void* stream, int* status);
+
+/*
+ * Second half of a causal forward whose first half was race_b200_tile_totals: `workspace` still
+ * holds the per-tile totals that call left there (same shape, tile_tokens and variant); this
+ * call scans them (adding carry_in) and runs the output pass, so pK and V are not reduced a
+ * second time.  The sequence-sharded driver calls race_b200_tile_totals, exchanges the totals
+ * between GPUs and then calls this with the received carry.  Arguments as race_b200_causal_fwd.
+ */
+int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const void* v, void* out,
+                                const float* carry_in, float* state_out, void* workspace,
+                                size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
+                                int variant, void* stream, int* status);
 
 /*
  * Non-causal per-bucket forward (upstream scaling/benchmark_time.py:155-162 as quoted in the

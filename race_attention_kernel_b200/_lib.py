@@ -20,7 +20,8 @@ VARIANTS = {"auto": 0, "simt": 1, "tensor": 2}
 EXPORTS = [
     "race_b200_version", "race_b200_error_string", "race_b200_is_supported",
     "race_b200_state_floats", "race_b200_select_tile_tokens", "race_b200_causal_workspace_bytes",
-    "race_b200_causal_fwd", "race_b200_tile_totals", "race_b200_noncausal_fwd",
+    "race_b200_causal_fwd", "race_b200_tile_totals", "race_b200_causal_fwd_resume",
+    "race_b200_noncausal_fwd",
     "race_b200_noncausal_bwd_workspace_bytes", "race_b200_noncausal_bwd",
     "race_b200_bucket_probs", "race_b200_causal_fwd_host",
     "race_b200_static_scratch_bytes", "race_b200_causal_fwd_static",
@@ -59,7 +60,9 @@ def lib() -> ctypes.CDLL:
     L.race_b200_causal_fwd.restype = i32
     L.race_b200_causal_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, i32, vp, vp]
     L.race_b200_tile_totals.restype = i32
-    L.race_b200_tile_totals.argtypes = [vp, vp, vp, vp, sz, shp, i32, vp]
+    L.race_b200_tile_totals.argtypes = [vp, vp, vp, vp, sz, shp, i32, i32, vp, vp]
+    L.race_b200_causal_fwd_resume.restype = i32
+    L.race_b200_causal_fwd_resume.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, i32, vp, vp]
     L.race_b200_noncausal_fwd.restype = i32
     L.race_b200_noncausal_fwd.argtypes = [vp, vp, vp, vp, vp, vp, sz, shp, vp]
     L.race_b200_noncausal_bwd_workspace_bytes.restype = sz

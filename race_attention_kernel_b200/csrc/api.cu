@@ -70,7 +70,7 @@ size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile) {
 
 extern "C" {
 
-int race_b200_version(void) { return 1000; }
+int race_b200_version(void) { return 1001; }
 
 const char* race_b200_error_string(int code) {
     switch (code) {
@@ -122,10 +122,10 @@ size_t race_b200_causal_workspace_bytes(const RaceShape* shape, int tile_tokens,
     return workspace_bytes_for(dm, shape->dtype, var, tile);
 }
 
-int race_b200_causal_fwd(const void* probs_q, const void* probs_k, const void* v, void* out,
-                         const float* carry_in, float* state_out, void* workspace,
-                         size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
-                         int variant, void* stream, int* status) {
+static int causal_entry(const void* probs_q, const void* probs_k, const void* v, void* out,
+                        const float* carry_in, float* state_out, void* workspace,
+                        size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
+                        int variant, void* stream, int* status, int phases) {
     Dims dm;
     int rc = check_shape(shape, &dm);
     if (rc != RACE_OK) return rc;
@@ -137,6 +137,8 @@ int race_b200_causal_fwd(const void* probs_q, const void* probs_k, const void* v
     if (tile % chunk_of(var) != 0) return RACE_ERR_TILE;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t sf = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D);
+    const bool want_out = (phases & kPhaseOutput) != 0;
+    if (!want_out && !state_out) return RACE_ERR_NULL;
     if (dm.N == 0) return RACE_OK;
     if (dm.T == 0) {
         // nothing to launch: the state passes through
@@ -148,40 +150,40 @@ int race_b200_causal_fwd(const void* probs_q, const void* probs_k, const void* v
         }
         return RACE_OK;
     }
-    if (!probs_q || !probs_k || !v || !out || !workspace) return RACE_ERR_NULL;
+    if (!probs_k || !v || !workspace || (want_out && (!probs_q || !out))) return RACE_ERR_NULL;
     if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(out) ||
         !aligned16(workspace) || !aligned16(carry_in) || !aligned16(state_out))
         return RACE_ERR_ALIGN;
     if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, var, tile)) return RACE_ERR_WORKSPACE;
     if (var == RACE_VARIANT_TENSOR)
         return (int)causal_fwd_tensor(probs_q, probs_k, v, out, carry_in, state_out, workspace,
-                                      dm, shape->dtype, tile, st, status);
+                                      dm, shape->dtype, tile, st, status, phases);
     return (int)causal_fwd_simt(probs_q, probs_k, v, out, carry_in, state_out, (float*)workspace,
-                                dm, shape->dtype, tile, false, st);
+                                dm, shape->dtype, tile, /*totals_only=*/!want_out, st,
+                                /*skip_output=*/false, /*skip_totals=*/!(phases & kPhaseTotals));
+}
+
+int race_b200_causal_fwd(const void* probs_q, const void* probs_k, const void* v, void* out,
+                         const float* carry_in, float* state_out, void* workspace,
+                         size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
+                         int variant, void* stream, int* status) {
+    return causal_entry(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes,
+                        shape, tile_tokens, variant, stream, status, kPhaseAll);
 }
 
 int race_b200_tile_totals(const void* probs_k, const void* v, float* totals, void* workspace,
                           size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
-                          void* stream) {
-    Dims dm;
-    int rc = check_shape(shape, &dm);
-    if (rc != RACE_OK) return rc;
-    if (!simt_supported(dm)) return RACE_ERR_SHAPE;
-    if (tile_tokens < 0) return RACE_ERR_TILE;
-    const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, RACE_VARIANT_SIMT);
-    if (tile % kSimtChunk != 0) return RACE_ERR_TILE;
-    if (!totals) return RACE_ERR_NULL;
-    cudaStream_t st = (cudaStream_t)stream;
-    const size_t sf = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D);
-    if (dm.N == 0) return RACE_OK;
-    if (dm.T == 0) return (int)cudaMemsetAsync(totals, 0, sf * sizeof(float), st);
-    if (!probs_k || !v || !workspace) return RACE_ERR_NULL;
-    if (!aligned16(probs_k) || !aligned16(v) || !aligned16(totals) || !aligned16(workspace))
-        return RACE_ERR_ALIGN;
-    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, RACE_VARIANT_SIMT, tile))
-        return RACE_ERR_WORKSPACE;
-    return (int)causal_fwd_simt(nullptr, probs_k, v, nullptr, nullptr, totals, (float*)workspace, dm,
-                                shape->dtype, tile, true, st);
+                          int variant, void* stream, int* status) {
+    return causal_entry(nullptr, probs_k, v, nullptr, nullptr, totals, workspace, workspace_bytes,
+                        shape, tile_tokens, variant, stream, status, kPhaseTotals);
+}
+
+int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const void* v, void* out,
+                                const float* carry_in, float* state_out, void* workspace,
+                                size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
+                                int variant, void* stream, int* status) {
+    return causal_entry(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes,
+                        shape, tile_tokens, variant, stream, status, kPhaseOutput);
 }
 
 int race_b200_noncausal_fwd(const void* probs_q, const void* probs_k, const void* v, void* out,
@@ -200,21 +202,17 @@ int race_b200_noncausal_fwd(const void* probs_q, const void* probs_k, const void
     if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(out) ||
         !aligned16(totals) || !aligned16(workspace))
         return RACE_ERR_ALIGN;
-    const int tile = pick_tile(dm, shape->dtype, RACE_VARIANT_SIMT);
-    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, RACE_VARIANT_SIMT, tile))
-        return RACE_ERR_WORKSPACE;
-    cudaError_t e = causal_fwd_simt(nullptr, probs_k, v, nullptr, nullptr, totals, (float*)workspace,
-                                    dm, shape->dtype, tile, true, st);
-    if (e != cudaSuccess) return (int)e;
+    rc = race_b200_tile_totals(probs_k, v, totals, workspace, workspace_bytes, shape, 0,
+                               RACE_VARIANT_AUTO, stream, nullptr);
+    if (rc != RACE_OK) return rc;
     return (int)noncausal_query(probs_q, totals, out, dm, shape->dtype, sm_count(), st);
 }
 
 size_t race_b200_noncausal_bwd_workspace_bytes(const RaceShape* shape) {
     Dims dm;
     if (check_shape(shape, &dm) != RACE_OK || !simt_supported(dm)) return 0;
-    const int tile = pick_tile(dm, shape->dtype, RACE_VARIANT_SIMT);
     const size_t sf = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
-    const size_t tile_ws = workspace_bytes_for(dm, shape->dtype, RACE_VARIANT_SIMT, tile);
+    const size_t tile_ws = race_b200_causal_workspace_bytes(shape, 0, RACE_VARIANT_AUTO);
     return (tile_ws + 255) / 256 * 256 + 2 * ((sf + 255) / 256 * 256);
 }
 
@@ -236,18 +234,17 @@ int race_b200_noncausal_bwd(const void* probs_q, const void* probs_k, const void
         return RACE_ERR_ALIGN;
     if (workspace_bytes < race_b200_noncausal_bwd_workspace_bytes(shape)) return RACE_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
-    const int tile = pick_tile(dm, shape->dtype, RACE_VARIANT_SIMT);
     const size_t sfb = ((size_t)dm.N * state_floats_per_stream(dm.S, dm.D) * sizeof(float) + 255) / 256 * 256;
-    const size_t tile_ws = workspace_bytes_for(dm, shape->dtype, RACE_VARIANT_SIMT, tile);
+    const size_t tile_ws = race_b200_causal_workspace_bytes(shape, 0, RACE_VARIANT_AUTO);
     // layout: [tile workspace | dE state | (dBs, dA) state], each part 256-byte aligned
     float* ws_tiles = (float*)workspace;
     float* dE_state = (float*)((char*)workspace + ((tile_ws + 255) / 256 * 256));
     float* grads = (float*)((char*)dE_state + sfb);
     // dE = pQ^T dO : the tile-totals pass with (pQ, dO) in the roles of (pK, V)
-    cudaError_t e = causal_fwd_simt(nullptr, probs_q, d_out, nullptr, nullptr, dE_state, ws_tiles, dm,
-                                    shape->dtype, tile, true, st);
-    if (e != cudaSuccess) return (int)e;
-    e = noncausal_state_grads(totals, dE_state, grads, dm, st);
+    rc = race_b200_tile_totals(probs_q, d_out, dE_state, ws_tiles, tile_ws, shape, 0, RACE_VARIANT_AUTO,
+                               stream, nullptr);
+    if (rc != RACE_OK) return rc;
+    cudaError_t e = noncausal_state_grads(totals, dE_state, grads, dm, st);
     if (e != cudaSuccess) return (int)e;
     return (int)noncausal_token_grads(probs_k, v, d_out, totals, grads, d_probs_q, d_probs_k, d_v, dm,
                                       shape->dtype, sm_count(), st);

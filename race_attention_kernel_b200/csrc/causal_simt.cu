@@ -370,16 +370,19 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
 template <typename Tin, int SPT, int DV>
 cudaError_t launch_simt(const Tin* pq, const Tin* pk, const Tin* v, Tin* out, const float* carry_in,
                         float* state_out, float* ws, const Dims& dm, int tile_tokens, int groups,
-                        bool totals_only, bool skip_output, cudaStream_t stream) {
+                        bool totals_only, bool skip_output, bool skip_totals, cudaStream_t stream) {
     using Ly = SimtLayout<SPT, DV>;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const int sf = state_floats_per_stream(dm.S, dm.D);
     dim3 grid((unsigned)(tiles * groups), (unsigned)dm.N);
 
     const size_t smem1 = (size_t)(C * Ly::LDS + C * Ly::LDD) * sizeof(float);
-    tile_totals_simt<Tin, SPT, DV><<<grid, kSimtThreads, smem1, stream>>>(pk, v, ws, dm, tile_tokens, groups);
-    cudaError_t err = cudaGetLastError();
-    if (err != cudaSuccess) return err;
+    cudaError_t err = cudaSuccess;
+    if (!skip_totals) {
+        tile_totals_simt<Tin, SPT, DV><<<grid, kSimtThreads, smem1, stream>>>(pk, v, ws, dm, tile_tokens, groups);
+        err = cudaGetLastError();
+        if (err != cudaSuccess) return err;
+    }
 
     dim3 sgrid((unsigned)((sf + 255) / 256), (unsigned)dm.N);
     tile_scan<<<sgrid, 256, 0, stream>>>(ws, carry_in, state_out, tiles, sf, totals_only ? 0 : 1);
@@ -408,7 +411,8 @@ cudaError_t launch_simt(const Tin* pq, const Tin* pk, const Tin* v, Tin* out, co
 template <typename Tin>
 cudaError_t dispatch_simt(const void* pq, const void* pk, const void* v, void* out,
                           const float* carry_in, float* state_out, float* ws, const Dims& dm,
-                          int tile_tokens, bool totals_only, bool skip_output, cudaStream_t stream) {
+                          int tile_tokens, bool totals_only, bool skip_output, bool skip_totals,
+                          cudaStream_t stream) {
     const int groups = simt_groups(dm.S);
     const int sg = dm.S > kGroupBuckets ? kGroupBuckets : dm.S;
     const int spt = sg <= 16 ? 1 : (sg <= 32 ? 2 : 4);
@@ -417,7 +421,7 @@ cudaError_t dispatch_simt(const void* pq, const void* pk, const void* v, void* o
     if (spt == SPT_ && dv == DV_)                                                                  \
         return launch_simt<Tin, SPT_, DV_>((const Tin*)pq, (const Tin*)pk, (const Tin*)v, (Tin*)out, \
                                            carry_in, state_out, ws, dm, tile_tokens, groups,       \
-                                           totals_only, skip_output, stream);
+                                           totals_only, skip_output, skip_totals, stream);
     RACE_SIMT_CASE(1, 1) RACE_SIMT_CASE(2, 1) RACE_SIMT_CASE(4, 1)
     RACE_SIMT_CASE(1, 2) RACE_SIMT_CASE(2, 2) RACE_SIMT_CASE(4, 2)
 #undef RACE_SIMT_CASE
@@ -427,11 +431,11 @@ cudaError_t dispatch_simt(const void* pq, const void* pk, const void* v, void* o
 }  // namespace
 
 cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out, const Dims& dm,
-                              int tile_tokens, cudaStream_t stream) {
+                              int tile_tokens, cudaStream_t stream, bool write_prefix) {
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const int sf = state_floats_per_stream(dm.S, dm.D);
     dim3 sgrid((unsigned)((sf + 255) / 256), (unsigned)dm.N);
-    tile_scan<<<sgrid, 256, 0, stream>>>(ws, carry_in, state_out, tiles, sf, 1);
+    tile_scan<<<sgrid, 256, 0, stream>>>(ws, carry_in, state_out, tiles, sf, write_prefix ? 1 : 0);
     return cudaGetLastError();
 }
 
@@ -455,12 +459,12 @@ int simt_default_tile_tokens(const Dims& dm, int sm_count) {
 cudaError_t causal_fwd_simt(const void* pq, const void* pk, const void* v, void* out,
                             const float* carry_in, float* state_out, float* ws, const Dims& dm,
                             int dtype, int tile_tokens, bool totals_only, cudaStream_t stream,
-                            bool skip_output) {
+                            bool skip_output, bool skip_totals) {
     if (dtype == RACE_DTYPE_F32)
         return dispatch_simt<float>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens,
-                                    totals_only, skip_output, stream);
+                                    totals_only, skip_output, skip_totals, stream);
     return dispatch_simt<__nv_bfloat16>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens,
-                                        totals_only, skip_output, stream);
+                                        totals_only, skip_output, skip_totals, stream);
 }
 
 }  // namespace race

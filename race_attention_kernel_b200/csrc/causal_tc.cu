@@ -931,20 +931,27 @@ size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
 
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
                               const float* carry_in, float* state_out, void* ws, const Dims& dm,
-                              int dtype, int tile_tokens, cudaStream_t stream, int* status) {
+                              int dtype, int tile_tokens, cudaStream_t stream, int* status, int phases) {
+    // Runtime calls first: they bind the device's primary context to the calling host thread,
+    // which the driver-level tensor-map encoder needs (a thread that has made no runtime call
+    // yet, e.g. an autograd worker, has no current context).
+    cudaError_t err = cudaFuncSetAttribute(tile_totals_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kT1SmemBytes);
+    if (err != cudaSuccess) return err;
     CUtensorMap mk, mv;
     if (!make_map(&mk, pk, dm.N, dm.T, dm.S) || !make_map(&mv, v, dm.N, dm.T, dm.D))
         return cudaErrorInvalidValue;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     dim3 grid((unsigned)tiles, (unsigned)dm.N);
     // 1. tile totals (tensor cores)  2. exclusive scan over tiles  3. output pass
-    cudaError_t err = cudaFuncSetAttribute(tile_totals_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           kT1SmemBytes);
-    if (err != cudaSuccess) return err;
-    tile_totals_tc<<<grid, kT1Threads, kT1SmemBytes, stream>>>(mk, mv, (float*)ws, dm.T, tile_tokens, status);
-    err = cudaGetLastError();
-    if (err != cudaSuccess) return err;
-    err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream);
+    if (phases & kPhaseTotals) {
+        tile_totals_tc<<<grid, kT1Threads, kT1SmemBytes, stream>>>(mk, mv, (float*)ws, dm.T, tile_tokens, status);
+        err = cudaGetLastError();
+        if (err != cudaSuccess) return err;
+    }
+    if (!(phases & kPhaseOutput))   // totals only: sum the tiles into state_out, keep the per-tile totals
+        return causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, /*write_prefix=*/false);
+    err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, /*write_prefix=*/true);
     if (err != cudaSuccess) return err;
     err = cudaFuncSetAttribute(causal_out_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return err;

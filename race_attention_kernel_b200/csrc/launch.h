@@ -16,11 +16,14 @@ int simt_default_tile_tokens(const Dims& dm, int sm_count);
 cudaError_t causal_fwd_simt(const void* pq, const void* pk, const void* v, void* out,
                             const float* carry_in, float* state_out, float* ws, const Dims& dm,
                             int dtype, int tile_tokens, bool totals_only, cudaStream_t stream,
-                            bool skip_output = false);
+                            bool skip_output = false, bool skip_totals = false);
 
 // in-place exclusive scan over the per-tile totals in ws (+ carry_in), inclusive total to state_out
 cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out, const Dims& dm,
-                              int tile_tokens, cudaStream_t stream);
+                              int tile_tokens, cudaStream_t stream, bool write_prefix = true);
+
+// which passes of a causal forward to run: totals (per-tile sums into ws) and/or scan + outputs
+constexpr int kPhaseTotals = 1, kPhaseOutput = 2, kPhaseAll = 3;
 
 // ---- non-causal path (noncausal_simt.cu) ------------------------------------------------------
 cudaError_t noncausal_query(const void* pq, const float* totals, void* out, const Dims& dm, int dtype,
@@ -42,6 +45,7 @@ int tensor_default_tile_tokens(const Dims& dm, int dtype, int sm_count);
 size_t tensor_workspace_bytes(const Dims& dm, int dtype, int tile_tokens);
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
                               const float* carry_in, float* state_out, void* ws, const Dims& dm,
-                              int dtype, int tile_tokens, cudaStream_t stream, int* status);
+                              int dtype, int tile_tokens, cudaStream_t stream, int* status,
+                              int phases = kPhaseAll);
 
 }  // namespace race

@@ -85,11 +85,18 @@ def sequence_sharded_prefix(probsQ: torch.Tensor, probsK: torch.Tensor, V: torch
     prefix_fn = prefix_fn or ops.race_causal_prefix
     N, T, L, R = probsK.shape
     dk = V.shape[-1]
-    A_tot, B_tot = totals_fn(probsK, V)                       # pass 1: local totals
+    kw = {}
+    if totals_fn is ops.race_tile_totals and prefix_fn is ops.race_causal_prefix:
+        # pass 1 leaves its per-tile totals in the workspace; pass 2 scans them instead of
+        # reducing pK and V again
+        A_tot, B_tot, ws = totals_fn(probsK, V, return_workspace=True)
+        kw["totals_workspace"] = ws
+    else:
+        A_tot, B_tot = totals_fn(probsK, V)                    # pass 1: local totals
     carry = exchange_carry(_pack(A_tot, B_tot), group, mode)   # one small message per hop
     A0, B0 = ops.unpack_state(carry, L, R, dk)
     return prefix_fn(probsQ, probsK, V, eps, carry_in=(A0.contiguous(), B0.contiguous()),
-                     return_state=return_state)                # pass 2: outputs with the carry
+                     return_state=return_state, **kw)          # pass 2: outputs with the carry
 
 
 def emulate_sequence_shards(probsQ, probsK, V, shards: int, eps: float = 1e-6,
@@ -104,11 +111,16 @@ def emulate_sequence_shards(probsQ, probsK, V, shards: int, eps: float = 1e-6,
     for r in range(shards):
         sl = shard_tokens(T, shards, r)
         q, k, v = (t[:, sl].contiguous() for t in (probsQ, probsK, V))
-        A_tot, B_tot = totals_fn(k, v)
+        kw = {}
+        if totals_fn is ops.race_tile_totals and prefix_fn is ops.race_causal_prefix:
+            A_tot, B_tot, ws = totals_fn(k, v, return_workspace=True)
+            kw["totals_workspace"] = ws
+        else:
+            A_tot, B_tot = totals_fn(k, v)
         totals = _pack(A_tot, B_tot)
         if carry is None:
             carry = torch.zeros_like(totals)
         A0, B0 = ops.unpack_state(carry, L, R, dk)
-        outs.append(prefix_fn(q, k, v, eps, carry_in=(A0.contiguous(), B0.contiguous())))
+        outs.append(prefix_fn(q, k, v, eps, carry_in=(A0.contiguous(), B0.contiguous()), **kw))
         carry = carry + totals
     return torch.cat(outs, dim=1)

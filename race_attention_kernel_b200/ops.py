@@ -104,7 +104,7 @@ def is_supported(N, T, L, R, dk, dtype=torch.float32, variant="auto") -> bool:
 
 def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
                        return_state: bool = False, tile_tokens: int = 0, variant: str = "auto",
-                       out: torch.Tensor | None = None):
+                       out: torch.Tensor | None = None, totals_workspace: torch.Tensor | None = None):
     """out[n,t,:] = sum_s pQ[n,t,s] * B_t[n,s,:] / (A_t[n,s] + eps) with inclusive prefixes
     A_t, B_t (src/race_baseline.py:45-51).
 
@@ -130,10 +130,18 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
         state = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device) \
             if return_state else None
         ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), tile_tokens, var)
-        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
-        rc = L_.race_b200_causal_fwd(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry),
-                                     _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh),
-                                     tile_tokens, var, _stream(), _ptr(_status_word(V.device)))
+        if totals_workspace is not None:
+            # second half after race_tile_totals(..., return_workspace=True) with the same
+            # tile_tokens / variant: the per-tile totals are already in the workspace
+            if totals_workspace.numel() < ws_bytes or totals_workspace.device != V.device:
+                raise RuntimeError("totals_workspace does not belong to this shape")
+            entry, ws = L_.race_b200_causal_fwd_resume, totals_workspace
+        else:
+            entry, ws = L_.race_b200_causal_fwd, torch.empty(max(ws_bytes, 16), dtype=torch.uint8,
+                                                             device=V.device)
+        rc = entry(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry),
+                   _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh),
+                   tile_tokens, var, _stream(), _ptr(_status_word(V.device)))
     _lib.check(rc, "race_b200_causal_fwd")
     if os.environ.get("RACE_B200_CHECK_STATUS") == "1":
         code = device_status(V.device)
@@ -145,21 +153,27 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
     return out
 
 
-def race_tile_totals(probsK, V, *, tile_tokens: int = 0):
+def race_tile_totals(probsK, V, *, tile_tokens: int = 0, variant: str = "auto",
+                     return_workspace: bool = False):
     """(A [N,L,R], B [N,L,R,d_k]) summed over all T tokens (pass 1 of the sequence-sharded
-    driver; the final carry of src/race_chunked.py:62-63)."""
+    driver; the final carry of src/race_chunked.py:62-63).  With return_workspace=True the
+    workspace holding the per-tile totals is returned as a third value; pass it to
+    ``race_causal_prefix(..., totals_workspace=...)`` to finish the forward without reducing
+    pK and V again."""
     N, T, L, R, dk = _check_inputs(None, probsK, V, need_q=False)
     L_ = _lib.lib()
     sh = make_shape(N, T, L, R, dk, V.dtype, 1e-6)
+    var = _lib.VARIANTS[variant]
     with torch.cuda.device(V.device):
         state = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device)
-        ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), tile_tokens,
-                                                       _lib.VARIANTS["simt"])
+        ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), tile_tokens, var)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
         rc = L_.race_b200_tile_totals(_ptr(probsK), _ptr(V), _ptr(state), _ptr(ws), ws_bytes,
-                                      ctypes.byref(sh), tile_tokens, _stream())
+                                      ctypes.byref(sh), tile_tokens, var, _stream(),
+                                      _ptr(_status_word(V.device)))
     _lib.check(rc, "race_b200_tile_totals")
-    return unpack_state(state, L, R, dk)
+    A, B = unpack_state(state, L, R, dk)
+    return (A, B, ws) if return_workspace else (A, B)
 
 
 def bucket_probs(x: torch.Tensor, planes: torch.Tensor, L: int, K: int,
@@ -197,7 +211,7 @@ class _RaceNonCausal(torch.autograd.Function):
         with torch.cuda.device(V.device):
             out = torch.empty_like(V)
             totals = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device)
-            ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), 0, _lib.VARIANTS["simt"])
+            ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), 0, _lib.VARIANTS["auto"])
             ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
             rc = L_.race_b200_noncausal_fwd(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out),
                                             _ptr(totals), _ptr(ws), ws_bytes, ctypes.byref(sh),

@@ -143,6 +143,24 @@ def test_carry_in_and_state_out():
         assert ro.rel_l2(A_t, A_ref) <= 1e-5 and ro.rel_l2(B_t, B_ref) <= 1e-5
 
 
+def test_totals_then_resume_equals_one_call():
+    # the two halves the sequence-sharded driver uses: totals pass, then scan + outputs from the
+    # per-tile totals left in the workspace; same kernels, same tile -> bitwise equal
+    rk = _ops()
+    N, T, L, R, dk = 4, 9000, 4, 16, 64
+    pQ, pK, V = (t.cuda() for t in ro.synthetic_probs(N, T, L, R, dk, seed=61))
+    A0 = torch.rand(N, L, R, device="cuda")
+    B0 = torch.randn(N, L, R, dk, device="cuda")
+    for variant in _variants(N, T, L, R, dk, torch.float32):
+        ref, A_ref, B_ref = rk.race_causal_prefix(pQ, pK, V, carry_in=(A0, B0), return_state=True,
+                                                  variant=variant)
+        A_t, B_t, ws = rk.race_tile_totals(pK, V, variant=variant, return_workspace=True)
+        out, A, B = rk.race_causal_prefix(pQ, pK, V, carry_in=(A0, B0), return_state=True,
+                                          variant=variant, totals_workspace=ws)
+        assert torch.equal(out, ref) and torch.equal(B, B_ref)
+        assert ro.rel_l2(A_t + A0, A_ref) <= 1e-6 and ro.rel_l2(B_t + B0, B_ref) <= 1e-5
+
+
 def test_known_answers_and_causality():
     rk = _ops()
     N, T, L, R, dk = 2, 200, 4, 16, 64
