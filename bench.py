@@ -48,7 +48,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c5"],
+    ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c4", "c5"],
                     help="c2 (default): the contract line; the others print extra measurement lines")
     return ap.parse_args()
 
@@ -142,8 +142,58 @@ def _time_ms(fn, warmup, steps):
     return e0.elapsed_time(e1) / steps
 
 
+def workload_c4(args):
+    """BASELINE config 4: one long sequence per stream (N=8, T=4,194,304, fp32) sharded contiguously
+    over the ranks (run under torchrun); carry chain over NCCL send/recv."""
+    import torch.distributed as dist
+
+    import race_attention_kernel_b200 as rk
+    from oracle import race_oracle as ro
+    from race_attention_kernel_b200 import multigpu as mg
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    N, L, R, dk, T = 8, 4, 16, 64, 4194304
+
+    def reduce_max(x):
+        t = torch.tensor([x], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    # parity on a short sequence first: every rank builds the same inputs and takes its slice
+    Ts = 20000
+    pQ, pK, V = ro.synthetic_probs(N, Ts, L, R, dk, seed=3)
+    sl = mg.shard_tokens(Ts, world, rank)
+    ref = ro.causal_prefix_chunked(pQ.double(), pK.double(), V.double(), chunk=512)[:, sl]
+    run = (lambda q, k, v, mode: mg.sequence_sharded_prefix(q, k, v, mode=mode)) if world > 1 else \
+          (lambda q, k, v, mode: rk.race_causal_prefix(q, k, v))
+    err = reduce_max(ro.rel_l2(run(pQ[:, sl].contiguous().cuda(), pK[:, sl].contiguous().cuda(),
+                                   V[:, sl].contiguous().cuda(), "chain"), ref))
+    if not err <= 1e-4:
+        raise SystemExit(f"parity gate failed: rel-L2 {err:.3e}")
+    Tl = T // world
+    g = torch.Generator(device=dev).manual_seed(rank)
+    q = torch.softmax(torch.randn(N, Tl, L, R, device=dev, generator=g), -1)
+    k = torch.softmax(torch.randn(N, Tl, L, R, device=dev, generator=g), -1)
+    v = torch.randn(N, Tl, dk, device=dev, generator=g)
+    for mode in (("chain", "allgather") if world > 1 else ("single",)):
+        ms = reduce_max(_time_ms(lambda: run(q, k, v, mode), args.warmup, args.steps))
+        if rank == 0:
+            print(json.dumps({"workload": "c4", "mode": mode, "n_gpus": world, "N": N, "T": T,
+                              "ms_per_step": round(ms, 3), "Mtok_s": round(N * T / ms / 1e3, 1),
+                              "scaling": "strong", "parity_rel_l2": err}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def extra_workloads(args):
     """Measurement lines for the other BASELINE configurations on one GPU (not the contract line)."""
+    if args.workload == "c4":
+        return workload_c4(args)
     import race_attention_kernel_b200 as rk
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
