@@ -246,7 +246,7 @@ def extra_workloads(args):
             gbs = N * T * 2560 / (ms * 1e-3) / 1e9
             print(json.dumps({"workload": "c3", "dtype": "bf16", "N": N, "T": T, "ms": round(ms, 3),
                               "Mtok_s": round(N * T / ms / 1e3, 1), "GB_s": round(gbs, 1),
-                              "frac_measured_peak": round(gbs / peak, 4), "variant": "simt (cluster of 8)"}),
+                              "frac_measured_peak": round(gbs / peak, 4), "variant": "auto"}),
                   flush=True)
             del pQ, pK, V, out
             torch.cuda.empty_cache()

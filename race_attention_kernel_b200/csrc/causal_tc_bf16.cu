@@ -1,0 +1,811 @@
+// tcgen05 / TMEM / TMA causal kernels for bf16 inputs (sm_100a): S = G * 64 buckets, d_k in
+// {64, 128}.  Same chunk identity and warp roles as the fp32 kernels (causal_tc.cu); what
+// differs:
+//   * operands are single bf16 tiles (the inputs already are bf16): every product is one
+//     tcgen05.mma pass, and the converter warps only move the TMA-staged (128B-swizzled) tiles
+//     into the canonical operand layout;
+//   * d_k = 128 runs the state update, W.B and G.V with N = 128 (TMEM: B 128 + 2 x (64 + 128)
+//     columns = all 512);
+//   * S > 64: the tables of this estimator are independent (out = sum over tables), so bucket
+//     group g (64 buckets) is owned by CTA g of a thread-block cluster of G CTAs working on the
+//     same (stream, tile).  Each CTA keeps its own state slice and forms a partial output; the
+//     partial outputs of a chunk are summed through distributed shared memory in group order
+//     (deterministic), rows dealt round-robin to the CTAs, and written once.  Cross-CTA hand-offs
+//     are mbarriers with remote arrivals; no TMA multicast anywhere.
+// Reference semantics: src/race_baseline.py:45-51 (docs/causal_v2_design.md:70-77 for the chunk
+// form); BASELINE configuration "N=256 streams, T=262144, d_k=128, L=8, K=6" is G = 8, D = 128.
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+#include "launch.h"
+#include "tc_common.cuh"
+
+namespace race {
+namespace {
+
+constexpr int C = 64;   // tokens per chunk
+constexpr int SG = 64;  // buckets per CTA
+constexpr int kThreads = 15 * 32;
+constexpr int kProducerWarp = 12;
+constexpr int kMmaWarp = 13;
+
+template <int D>
+struct Lay {
+    static constexpr int kTileP = C * 64 * 2;   // pK / W / G / tril tile: 64 x 64 bf16
+    static constexpr int kTileV = C * D * 2;    // V / B tile: 64 x D bf16
+    static constexpr int kStage = kTileP + kTileV;
+    static constexpr int oStage = 0;                    // [2] pK | V (D/64 boxes)
+    static constexpr int oKt = oStage + 2 * kStage;     // [2]
+    static constexpr int oVt = oKt + 2 * kTileP;        // [2]
+    static constexpr int oWt = oVt + 2 * kTileV;        // [2] W, then masked G
+    static constexpr int oBt = oWt + 2 * kTileP;        // [2]
+    static constexpr int oTril = oBt + 2 * kTileV;
+    static constexpr int oAcar = oTril + kTileP;        // [2][64] fp32
+    static constexpr int oObuf = oAcar + 2 * 64 * 4;    // [2][64][D] fp32 partial outputs (clusters)
+    static constexpr int oBars = oObuf + 2 * C * D * 4;
+    static constexpr int kNumBars = 36;
+    static constexpr int oMisc = oBars + kNumBars * 8;
+    static constexpr int kSmem = oMisc + 16 + 1024;
+    static constexpr uint32_t kTmemCols = D == 64 ? 512 : 512;
+    // MN-major descriptor words of a [64][D] tile
+    static constexpr uint32_t kLboV = (uint32_t)(D / 8) * 128;        // K-direction (row-group) stride
+    static constexpr uint32_t kStepV = (2 * kLboV) >> 4;              // lo-word step per 16 K-rows
+};
+
+enum BarB {
+    bFull = 0, bEmpty = 2, bKReady = 4, bVReady = 6, bXReady = 8, bWReady = 10, bGReady = 12,
+    bGtReady = 14, bOReady = 16, bAcar = 18, bAcarFree = 20, bBupdDone = 22, bBaccFree = 23,
+    bBtReady = 25, bDrain = 27, bObufReady = 29, bObufFree = 31
+};
+
+__device__ __forceinline__ uint32_t lo_mn_w(uint32_t addr, uint32_t lbo) {
+    return ((addr >> 4) & 0x3FFF) | ((lbo >> 4) << 16);
+}
+__device__ __forceinline__ constexpr uint32_t idesc_n(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((64u >> 4) << 24);
+}
+// byte offset of (row, col) in a [64][W] bf16 tile of 8x8 core matrices
+template <int W>
+__device__ __forceinline__ uint32_t off_w(int row, int col) {
+    return (uint32_t)((((row >> 3) * (W / 8) + (col >> 3)) << 7) + ((row & 7) << 4) + ((col & 7) << 1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+}
+
+// ---- cluster helpers --------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ float4 remote_ld4(uint32_t cluster_addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait on a barrier that CTAs of the cluster arrive on
+__device__ __forceinline__ bool wait_bar_cluster_warp(const Ctx& cx, int bar, uint32_t parity, int code) {
+    bool ok = true;
+    if (!mbar_try_wait_cluster(cx.bar(bar), parity)) {
+        const long long t0 = clock64();
+        int spins = 0;
+        while (!mbar_try_wait_cluster(cx.bar(bar), parity)) {
+            if ((++spins & 63) == 0) {
+                if (*cx.abort_flag) { ok = false; break; }
+                if (clock64() - t0 > kWaitCycles) {
+                    *cx.abort_flag = 1;
+                    if (cx.status) atomicCAS(cx.status, 0, code);
+                    ok = false;
+                    break;
+                }
+            }
+        }
+    }
+    return __all_sync(0xffffffffu, ok);
+}
+
+// TMA-staged bf16 tile [64 rows][64 values] (128-byte rows, 128B swizzle) -> operand tile
+// [64][W] columns [col0, col0 + 64); optionally adds the values into per-thread column sums
+template <int W, bool kSum>
+__device__ __forceinline__ void copy_tile(const uint8_t* stage, uint8_t* dst, int col0, int tid,
+                                          float (*asum)[8]) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int idx = it * 128 + tid;
+        const int j = idx >> 6, r = idx & 63;   // 16-byte chunk (8 values), token row
+        const uint4 x = *reinterpret_cast<const uint4*>(stage + r * 128 + ((j ^ (r & 7)) << 4));
+        if (kSum) {
+            const float2 a = unpack_bf16(x.x), b = unpack_bf16(x.y), c = unpack_bf16(x.z), d = unpack_bf16(x.w);
+            asum[it][0] += a.x; asum[it][1] += a.y; asum[it][2] += b.x; asum[it][3] += b.y;
+            asum[it][4] += c.x; asum[it][5] += c.y; asum[it][6] += d.x; asum[it][7] += d.y;
+        }
+        *reinterpret_cast<uint4*>(dst + off_w<W>(r, col0 + 8 * j)) = x;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// output pass
+// ------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                   const float* __restrict__ ws, int64_t T, int S, int G, int tile_tokens, float eps,
+                   int* status) {
+    using Ly = Lay<D>;
+    constexpr int DH = D / 64;   // 64-column halves of a [64][D] accumulator
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cx;
+    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cx.sm_u32 = smem_u32(cx.sm);
+    cx.bars = Ly::oBars;
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + Ly::oMisc + 4);
+    cx.status = status;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + Ly::oMisc);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = (int)(blockIdx.x % (unsigned)G);          // bucket group = rank in the cluster
+    const int64_t tiles = gridDim.x / G;
+    const int64_t tile = blockIdx.x / G, n = blockIdx.y;
+    const int64_t t_begin = tile * tile_tokens;
+    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
+    const int nch = (int)((t_end - t_begin + C - 1) / C);
+    const float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+    const float* sliceB = slice + (int64_t)g * SG * D;      // this group's rows of B
+    const float* sliceA = slice + (int64_t)S * D + g * SG;  // this group's part of A
+
+    if (tid == 0) {
+        *cx.abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(cx.bar(bFull + i), 1);
+            mbar_init(cx.bar(bEmpty + i), 4);
+            mbar_init(cx.bar(bKReady + i), 4);
+            mbar_init(cx.bar(bVReady + i), 4);
+            mbar_init(cx.bar(bXReady + i), 1);
+            mbar_init(cx.bar(bWReady + i), 4);
+            mbar_init(cx.bar(bGReady + i), 1);
+            mbar_init(cx.bar(bGtReady + i), 4);
+            mbar_init(cx.bar(bOReady + i), 1);
+            mbar_init(cx.bar(bAcar + i), 1);
+            mbar_init(cx.bar(bAcarFree + i), 4);
+            mbar_init(cx.bar(bBaccFree + i), 4);
+            mbar_init(cx.bar(bBtReady + i), 4);
+            mbar_init(cx.bar(bDrain + i), 1);
+            mbar_init(cx.bar(bObufReady + i), 4 * G);
+            mbar_init(cx.bar(bObufFree + i), 4 * G);
+        }
+        mbar_init(cx.bar(bBupdDone), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(cx.sm_u32 + Ly::oMisc), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    for (int i = tid; i < C * 8; i += kThreads) {   // tril[t][j] = (j <= t)
+        const int t = i >> 3, jg = i & 7;
+        uint32_t w[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int j0 = jg * 8 + 2 * p;
+            w[p] = (j0 <= t ? 0x3F80u : 0u) | (j0 + 1 <= t ? 0x3F800000u : 0u);
+        }
+        *reinterpret_cast<uint4*>(cx.sm + Ly::oTril + off_w<64>(t, jg * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (G > 1) {
+        // barriers of every CTA of the cluster exist before anyone arrives remotely
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmB = tmem;                                                   // [0, D)
+    auto tmAG = [&](int wg) { return tmem + D + wg * (64 + D); };                // A_loc, then G
+    auto tmO = [&](int wg) { return tmem + D + wg * (64 + D) + 64; };            // O
+
+    if (warp < 8) {
+        // =========================== worker warpgroups =========================================
+        const int wg = warp >> 2, w = warp & 3, wtid = tid & 127;
+        const int q = lane & 3, rbase = 16 * w + (lane >> 2);
+        const uint32_t lane_base = (uint32_t)(32 * w) << 16;
+        uint8_t* wt = cx.sm + Ly::oWt + wg * Ly::kTileP;
+        float* obuf = reinterpret_cast<float*>(cx.sm + Ly::oObuf) + wg * C * D;
+        const uint32_t obuf_u32 = cx.sm_u32 + Ly::oObuf + wg * C * D * 4;
+        __nv_bfloat16* out_n = out + n * T * D;
+        const __nv_bfloat16* pq_n = pq + n * T * S + g * SG;
+        float v[32];
+        uint32_t ph = 0;
+        int uses = 0;   // uses of this group's partial-output buffer so far
+        bool ok = true;
+        for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
+            const int64_t tok0 = t_begin + (int64_t)c * C;
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+            // pQ in the accumulator-fragment layout (pairs of bf16), issued first
+            uint32_t pqv[16];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                const __nv_bfloat16* prow = pq_n + (tok0 + row) * S + 2 * q;
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    pqv[2 * x + h] = row < valid ? __ldg(reinterpret_cast<const unsigned int*>(prow + 8 * x)) : 0u;
+            }
+            // ---- W = pQ / (A + A_loc + eps) --------------------------------------------------------
+            if (!(ok = wait_bar_warp(cx, bAcar + wg, ph, 102))) break;
+            float acar[16];
+            {
+                const float* ac = reinterpret_cast<const float*>(cx.sm + Ly::oAcar) + wg * 64;
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    const float2 a2 = *reinterpret_cast<const float2*>(ac + 8 * x + 2 * q);
+                    acar[2 * x] = a2.x; acar[2 * x + 1] = a2.y;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(bAcarFree + wg));
+            if (w == 3 && c >= 1 && !(ok = wait_bar_warp(cx, bAcarFree + (wg ^ 1), ((c - 1) >> 1) & 1, 107))) break;
+            if (!(ok = wait_bar_warp(cx, bXReady + wg, ph, 103))) break;
+            tc_fence_after();
+            tmem_ld64(lane_base + tmAG(wg), v);
+            tc_fence_before();
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = rbase + 8 * h;
+                    const float2 pq2 = unpack_bf16(pqv[2 * x + h]);
+                    const float a0 = acar[2 * x] + v[4 * x + 2 * h];
+                    const float a1 = acar[2 * x + 1] + v[4 * x + 2 * h + 1];
+                    *reinterpret_cast<uint32_t*>(wt + off_w<64>(row, 8 * x + 2 * q)) =
+                        pack_bf16(__fdividef(pq2.x, a0 + eps), __fdividef(pq2.y, a1 + eps));
+                    if (h == 1 && w == 3 && (lane >> 2) == 7) {
+                        float* an = reinterpret_cast<float*>(cx.sm + Ly::oAcar) + (wg ^ 1) * 64;
+                        *reinterpret_cast<float2*>(an + 8 * x + 2 * q) = make_float2(a0, a1);
+                    }
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(cx.bar(bWReady + wg));
+                if (w == 3) mbar_arrive(cx.bar(bAcar + (wg ^ 1)));
+            }
+            // ---- causal mask of G (over W's tile) ----------------------------------------------
+            if (!(ok = wait_bar_warp(cx, bGReady + wg, ph, 104))) break;
+            tc_fence_after();
+            tmem_ld64(lane_base + tmAG(wg), v);
+            tc_fence_before();
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = rbase + 8 * h, col = 8 * x + 2 * q;
+                    *reinterpret_cast<uint32_t*>(wt + off_w<64>(row, col)) =
+                        pack_bf16(col <= row ? v[4 * x + 2 * h] : 0.f, col + 1 <= row ? v[4 * x + 2 * h + 1] : 0.f);
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(bGtReady + wg));
+            // ---- O ---------------------------------------------------------------------------------
+            if (!(ok = wait_bar_warp(cx, bOReady + wg, ph, 105))) break;
+            if (G == 1) {
+#pragma unroll
+                for (int dh = 0; dh < DH; ++dh) {
+                    tc_fence_after();
+                    tmem_ld64(lane_base + tmO(wg) + dh * 64, v);
+                    tc_fence_before();
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int row = rbase + 8 * h;
+                        if (row < valid) {
+                            __nv_bfloat16* orow = out_n + (tok0 + row) * D + dh * 64 + 2 * q;
+#pragma unroll
+                            for (int x = 0; x < 8; ++x)
+                                *reinterpret_cast<uint32_t*>(orow + 8 * x) =
+                                    pack_bf16(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+                        }
+                    }
+                }
+            } else {
+                // partial output of this bucket group -> own shared memory; then the cluster sums
+                // the groups' partials in group order, rows dealt round-robin to the CTAs
+                if (uses >= 1 && !(ok = wait_bar_cluster_warp(cx, bObufFree + wg, (uint32_t)((uses - 1) & 1), 108))) break;
+#pragma unroll
+                for (int dh = 0; dh < DH; ++dh) {
+                    tc_fence_after();
+                    tmem_ld64(lane_base + tmO(wg) + dh * 64, v);
+                    tc_fence_before();
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int x = 0; x < 8; ++x)
+                            *reinterpret_cast<float2*>(obuf + (rbase + 8 * h) * D + dh * 64 + 8 * x + 2 * q) =
+                                make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+                }
+                asm volatile("fence.acq_rel.cluster;" ::: "memory");
+                __syncwarp();
+                if (lane == 0)
+                    for (int p = 0; p < G; ++p) remote_arrive(map_to_cta(cx.bar(bObufReady + wg), (uint32_t)p));
+                if (!(ok = wait_bar_cluster_warp(cx, bObufReady + wg, (uint32_t)(uses & 1), 109))) break;
+                const int rows_per = C / G;
+                for (int item = wtid; item < rows_per * (D / 8); item += 128) {
+                    const int row = g + G * (item / (D / 8));
+                    const int col = (item % (D / 8)) * 8;
+                    float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+                    for (int p = 0; p < G; ++p) {
+                        const uint32_t ra = map_to_cta(obuf_u32 + (uint32_t)(row * D + col) * 4, (uint32_t)p);
+                        const float4 a = remote_ld4(ra), b = remote_ld4(ra + 16);
+                        s0.x += a.x; s0.y += a.y; s0.z += a.z; s0.w += a.w;
+                        s1.x += b.x; s1.y += b.y; s1.z += b.z; s1.w += b.w;
+                    }
+                    if (row < valid)
+                        *reinterpret_cast<uint4*>(out_n + (tok0 + row) * D + col) =
+                            make_uint4(pack_bf16(s0.x, s0.y), pack_bf16(s0.z, s0.w), pack_bf16(s1.x, s1.y),
+                                       pack_bf16(s1.z, s1.w));
+                }
+                __syncwarp();
+                if (lane == 0)
+                    for (int p = 0; p < G; ++p) remote_arrive(map_to_cta(cx.bar(bObufFree + wg), (uint32_t)p));
+                ++uses;
+            }
+        }
+        // peers may still be reading this group's last partial output: stay until they are done
+        if (G > 1 && uses >= 1 && ok) wait_bar_cluster_warp(cx, bObufFree + wg, (uint32_t)((uses - 1) & 1), 110);
+    } else if (warp < 12) {
+        // =========================== converter + carry warpgroup =================================
+        const int w = warp & 3, q = lane & 3, rbase = 16 * w + (lane >> 2), wtid = tid & 127;
+        const uint32_t lane_base = (uint32_t)(32 * w) << 16;
+        float v[32];
+        auto write_bt = [&](int buf, int dh) {
+            uint8_t* bt = cx.sm + Ly::oBt + buf * Ly::kTileV;
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    *reinterpret_cast<uint32_t*>(bt + off_w<D>(rbase + 8 * h, dh * 64 + 8 * x + 2 * q)) =
+                        pack_bf16(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+        };
+        // carry-in: B -> TMEM accumulator and operand buffer 0; A -> the first chunk's running A
+#pragma unroll
+        for (int dh = 0; dh < DH; ++dh) {
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float2 b2 = *reinterpret_cast<const float2*>(
+                        sliceB + (rbase + 8 * h) * D + dh * 64 + 8 * x + 2 * q);
+                    v[4 * x + 2 * h] = b2.x; v[4 * x + 2 * h + 1] = b2.y;
+                }
+            tmem_st64(lane_base + tmB + dh * 64, v);
+            write_bt(0, dh);
+        }
+        tc_fence_before();
+        if (warp == 8) {
+            float* ac = reinterpret_cast<float*>(cx.sm + Ly::oAcar);
+            ac[lane] = sliceA[lane];
+            ac[lane + 32] = sliceA[lane + 32];
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(cx.bar(bBaccFree + 0));
+            mbar_arrive(cx.bar(bBtReady + 0));
+            if (warp == 8) mbar_arrive(cx.bar(bAcar + 0));
+        }
+        bool ok = true;
+        for (int c = 0; c < nch && ok; ++c) {
+            const int wg = c & 1;
+            const uint32_t ph = (uint32_t)((c >> 1) & 1);
+            const uint8_t* stage = cx.sm + Ly::oStage + wg * Ly::kStage;
+            // pK tile of the group: last read by the G product of chunk c - 2
+            if (c >= 2 && !(ok = wait_bar_warp(cx, bGReady + wg, ph ^ 1, 203))) break;
+            if (!(ok = wait_bar_warp(cx, bFull + wg, ph, 201))) break;
+            copy_tile<64, false>(stage, cx.sm + Ly::oKt + wg * Ly::kTileP, 0, wtid, nullptr);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(bKReady + wg));
+            if (c >= 1) {
+                // state after chunk c - 1 -> operand buffer c & 1
+                if (!(ok = wait_bar_warp(cx, bBupdDone, (c - 1) & 1, 202))) break;
+#pragma unroll
+                for (int dh = 0; dh < DH; ++dh) {
+                    tc_fence_after();
+                    tmem_ld64(lane_base + tmB + dh * 64, v);
+                    tc_fence_before();
+                    if (dh == DH - 1) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(cx.bar(bBaccFree + wg));   // update of chunk c may start
+                    }
+                    write_bt(wg, dh);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(cx.bar(bBtReady + wg));
+            }
+            // V tile of the group: last read by the G.V product of chunk c - 2
+            if (c >= 2 && !(ok = wait_bar_warp(cx, bOReady + wg, ph ^ 1, 205))) break;
+#pragma unroll
+            for (int dh = 0; dh < DH; ++dh)
+                copy_tile<D, false>(stage + Ly::kTileP + dh * 8192, cx.sm + Ly::oVt + wg * Ly::kTileV, dh * 64,
+                                    wtid, nullptr);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(bVReady + wg)); mbar_arrive(cx.bar(bEmpty + wg)); }
+        }
+    } else if (warp == kProducerWarp) {
+        // =========================== TMA producer ==============================================
+        if (lane == 0) {
+            int issued = 0;
+            for (int c = 0; c < nch; ++c) {
+                const int st = c & 1;
+                if (c >= 2 && !wait_bar(cx, bEmpty + st, ((c >> 1) - 1) & 1, 301)) break;
+                const uint32_t dst = cx.sm_u32 + Ly::oStage + st * Ly::kStage;
+                const uint32_t bar = cx.bar(bFull + st);
+                const int tok = (int)(t_begin + (int64_t)c * C);
+                mbar_arrive_expect_tx(bar, Ly::kStage);
+                tma_load_4d(dst, &map_k, bar, 0, tok, g, (int)n);
+#pragma unroll
+                for (int dh = 0; dh < DH; ++dh)
+                    tma_load_4d(dst + Ly::kTileP + dh * 8192, &map_v, bar, 0, tok, dh, (int)n);
+                issued = c + 1;
+            }
+            if (*cx.abort_flag) {
+                for (int c = max(0, issued - 2); c < issued; ++c) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(bFull + (c & 1)), (c >> 1) & 1) && clock64() - t0 < (1ll << 24)) {}
+                }
+            }
+        }
+    } else {
+        // =========================== MMA issuers (one warp per worker group) ====================
+        const int wg = __shfl_sync(0xffffffffu, warp, 0) - kMmaWarp;
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
+        const uint32_t tril_lo = lo_k(smb + Ly::oTril);
+        const uint32_t kt_k = lo_k(smb + Ly::oKt + wg * Ly::kTileP);
+        const uint32_t kt_mn = lo_mn(smb + Ly::oKt + wg * Ly::kTileP);
+        const uint32_t vt_mn = lo_mn_w(smb + Ly::oVt + wg * Ly::kTileV, Ly::kLboV);
+        const uint32_t wt_k = lo_k(smb + Ly::oWt + wg * Ly::kTileP);
+        const uint32_t bt_mn = lo_mn_w(smb + Ly::oBt + wg * Ly::kTileV, Ly::kLboV);
+        const uint32_t dB = tm, dAG = tm + D + wg * (64 + D), dO = dAG + 64;
+        constexpr uint32_t kI64 = idesc_n(64), kID = idesc_n(D);
+        if (elect_one()) {
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
+                if (!(ok = wait_bar(cx, bKReady + wg, ph, 401))) break;
+                tc_fence_after();
+                // A_loc = tril . pK
+                mma_k64<true, kHiK, 16, kHiMN, 128>(dAG, tril_lo, kt_mn, kI64 | kBmn);
+                mma_commit(cx.bar(bXReady + wg));
+                // B += pK^T . V (N = D)
+                if (!(ok = wait_bar(cx, bVReady + wg, ph, 407))) break;
+                if (!(ok = wait_bar(cx, bBaccFree + wg, ph, 403))) break;
+                tc_fence_after();
+                mma_k64<false, kHiMN, 128, kHiMN, Ly::kStepV>(dB, kt_mn, vt_mn, kID | kAmn | kBmn);
+                mma_commit(cx.bar(bBupdDone));
+                // O = W . B (N = D) and G = W . pK^T
+                if (!(ok = wait_bar(cx, bWReady + wg, ph, 404))) break;
+                if (!(ok = wait_bar(cx, bBtReady + wg, ph, 405))) break;
+                tc_fence_after();
+                mma_k64<true, kHiK, 16, kHiK, 16>(dAG, wt_k, kt_k, kI64);
+                mma_k64<true, kHiK, 16, kHiMN, Ly::kStepV>(dO, wt_k, bt_mn, kID | kBmn);
+                mma_commit(cx.bar(bGReady + wg));
+                // O += G . V
+                if (!(ok = wait_bar(cx, bGtReady + wg, ph, 406))) break;
+                tc_fence_after();
+                mma_k64<false, kHiK, 16, kHiMN, Ly::kStepV>(dO, wt_k, vt_mn, kID | kBmn);
+                mma_commit(cx.bar(bOReady + wg));
+            }
+            mma_commit(cx.bar(bDrain + wg));
+            const long long t0 = clock64();
+            while (!mbar_try_wait(cx.bar(bDrain + wg), 0) && clock64() - t0 < kWaitCycles) {}
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (G > 1) {
+        // no CTA leaves while a peer may still arrive on its barriers or read its shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// tile totals
+// ------------------------------------------------------------------------------------------------
+constexpr int kT1Threads = 10 * 32;
+constexpr int kT1Stages = 4;
+template <int D>
+struct Lay1 {
+    static constexpr int kTileP = C * 64 * 2, kTileV = C * D * 2, kStage = kTileP + kTileV;
+    static constexpr int oStage = 0;
+    static constexpr int oKt = oStage + kT1Stages * kStage;   // [2]
+    static constexpr int oVt = oKt + 2 * kTileP;              // [2]
+    static constexpr int oRed = oVt + 2 * kTileV;             // [8 warps][4][8] fp32
+    static constexpr int oBars = oRed + 8 * 32 * 4;
+    static constexpr int oMisc = oBars + 16 * 8;
+    static constexpr int kSmem = oMisc + 16 + 1024;
+};
+enum Bar1B { b1Full = 0, b1Empty = 4, b1KvReady = 8, b1KvFree = 10, b1Done = 12 };
+
+template <int D>
+__global__ void __launch_bounds__(kT1Threads, 1)
+tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                    float* __restrict__ ws, int64_t T, int S, int G, int tile_tokens, int* status) {
+    using Ly = Lay1<D>;
+    constexpr int DH = D / 64;
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cx;
+    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cx.sm_u32 = smem_u32(cx.sm);
+    cx.bars = Ly::oBars;
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + Ly::oMisc + 4);
+    cx.status = status;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + Ly::oMisc);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = (int)(blockIdx.x % (unsigned)G);
+    const int64_t tiles = gridDim.x / G, tile = blockIdx.x / G, n = blockIdx.y;
+    const int64_t t_begin = tile * tile_tokens;
+    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
+    const int nch = (int)((t_end - t_begin + C - 1) / C);
+    float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+    float* sliceB = slice + (int64_t)g * SG * D;
+    float* sliceA = slice + (int64_t)S * D + g * SG;
+
+    if (tid == 0) {
+        *cx.abort_flag = 0;
+        for (int i = 0; i < kT1Stages; ++i) {
+            mbar_init(cx.bar(b1Full + i), 1);
+            mbar_init(cx.bar(b1Empty + i), 4);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(cx.bar(b1KvReady + i), 4);
+            mbar_init(cx.bar(b1KvFree + i), 1);
+        }
+        mbar_init(cx.bar(b1Done), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(cx.sm_u32 + Ly::oMisc), "r"((uint32_t)D) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        const int wg = warp >> 2, wtid = tid & 127;
+        float asum[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) asum[i][e] = 0.f;
+        bool ok = true;
+        for (int c = wg; c < nch && ok; c += 2) {
+            const int st = c % kT1Stages;
+            if (!(ok = wait_bar_warp(cx, b1Full + st, (c / kT1Stages) & 1, 111))) break;
+            if (c >= 2 && !(ok = wait_bar_warp(cx, b1KvFree + wg, ((c >> 1) - 1) & 1, 112))) break;
+            const uint8_t* stage = cx.sm + Ly::oStage + st * Ly::kStage;
+            copy_tile<64, true>(stage, cx.sm + Ly::oKt + wg * Ly::kTileP, 0, wtid, asum);
+#pragma unroll
+            for (int dh = 0; dh < DH; ++dh)
+                copy_tile<D, false>(stage + Ly::kTileP + dh * 8192, cx.sm + Ly::oVt + wg * Ly::kTileV, dh * 64,
+                                    wtid, nullptr);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(b1KvReady + wg)); mbar_arrive(cx.bar(b1Empty + st)); }
+        }
+        // column sums: item it of a thread covers columns 8 j .. 8 j + 7 with j = 2 it + (wtid >> 6),
+        // lanes of a warp hold different token rows of the same columns
+        float* red = reinterpret_cast<float*>(cx.sm + Ly::oRed) + warp * 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float x = asum[i][e];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+                if (lane == 0) red[i * 8 + e] = x;
+            }
+    } else if (warp == 8) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int c = 0; c < nch; ++c) {
+                const int st = c % kT1Stages;
+                if (c >= kT1Stages && !wait_bar(cx, b1Empty + st, ((c / kT1Stages) - 1) & 1, 311)) break;
+                const uint32_t dst = cx.sm_u32 + Ly::oStage + st * Ly::kStage;
+                const uint32_t bar = cx.bar(b1Full + st);
+                const int tok = (int)(t_begin + (int64_t)c * C);
+                mbar_arrive_expect_tx(bar, Ly::kStage);
+                tma_load_4d(dst, &map_k, bar, 0, tok, g, (int)n);
+#pragma unroll
+                for (int dh = 0; dh < DH; ++dh)
+                    tma_load_4d(dst + Ly::kTileP + dh * 8192, &map_v, bar, 0, tok, dh, (int)n);
+                issued = c + 1;
+            }
+            if (*cx.abort_flag) {
+                for (int c = max(0, issued - kT1Stages); c < issued; ++c) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(b1Full + c % kT1Stages), (c / kT1Stages) & 1) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
+            }
+        }
+    } else {
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
+        if (elect_one()) {
+            bool ok = true;
+            for (int c = 0; c < nch && ok; ++c) {
+                const int wg = c & 1;
+                if (!(ok = wait_bar(cx, b1KvReady + wg, (c >> 1) & 1, 411))) break;
+                tc_fence_after();
+                const uint32_t kt_mn = lo_mn(smb + Ly::oKt + wg * Ly::kTileP);
+                const uint32_t vt_mn = lo_mn_w(smb + Ly::oVt + wg * Ly::kTileV, Lay<D>::kLboV);
+                if (c == 0) mma_k64<true, kHiMN, 128, kHiMN, Lay<D>::kStepV>(tm, kt_mn, vt_mn, idesc_n(D) | kAmn | kBmn);
+                else mma_k64<false, kHiMN, 128, kHiMN, Lay<D>::kStepV>(tm, kt_mn, vt_mn, idesc_n(D) | kAmn | kBmn);
+                mma_commit(cx.bar(b1KvFree + wg));
+            }
+            mma_commit(cx.bar(b1Done));
+        }
+    }
+    __syncthreads();   // column-sum partials are in shared memory
+    if (warp < 4) {
+        if (wait_bar_warp(cx, b1Done, 0, 113)) {
+            float v[32];
+            const int q = lane & 3, rbase = 16 * warp + (lane >> 2);
+#pragma unroll
+            for (int dh = 0; dh < DH; ++dh) {
+                tc_fence_after();
+                tmem_ld64(((uint32_t)(32 * warp) << 16) + tmem + dh * 64, v);
+                tc_fence_before();
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        *reinterpret_cast<float2*>(sliceB + (rbase + 8 * h) * D + dh * 64 + 8 * x + 2 * q) =
+                            make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+            }
+            if (tid < 64) {
+                // column s = 8 j + e, j = 2 item + (warp-in-group >> 1): partials of both groups and
+                // both row halves in a fixed order
+                const int j = tid >> 3, e = tid & 7, it = j >> 1, wh = (j & 1) * 2;
+                const float* red = reinterpret_cast<const float*>(cx.sm + Ly::oRed);
+                float a = 0.f;
+#pragma unroll
+                for (int gg = 0; gg < 2; ++gg)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) a += red[(gg * 4 + wh + half) * 32 + it * 8 + e];
+                sliceA[tid] = a;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)D) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn_bf16() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        p = nullptr;
+    if (!p) cudaGetLastError();
+    fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+    return fn;
+}
+
+// [N][T][width] bf16 viewed as (64 values, T tokens, width/64 column blocks, N streams); one box =
+// 64 values x 64 tokens (128-byte rows, 128B swizzle); tokens past T read as zero
+bool make_map_bf16(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width) {
+    auto fn = encode_fn_bf16();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {64, (cuuint64_t)T, (cuuint64_t)(width / 64), (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)width * 2, 128, (cuuint64_t)T * width * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)C, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D>
+cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out, const float* carry_in,
+                        float* state_out, void* ws, const Dims& dm, int tile_tokens, cudaStream_t stream,
+                        int* status, int phases) {
+    const int G = dm.S / SG;
+    auto k1 = tile_totals_tc_bf16<D>;
+    auto k3 = causal_out_tc_bf16<D>;
+    // runtime call first: binds the primary context to this host thread for the map encoder
+    cudaError_t err = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay1<D>::kSmem);
+    if (err != cudaSuccess) return err;
+    CUtensorMap mk, mv;
+    if (!make_map_bf16(&mk, pk, dm.N, dm.T, dm.S) || !make_map_bf16(&mv, v, dm.N, dm.T, dm.D))
+        return cudaErrorInvalidValue;
+    const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
+    dim3 grid((unsigned)(tiles * G), (unsigned)dm.N);
+    if (phases & kPhaseTotals) {
+        k1<<<grid, kT1Threads, Lay1<D>::kSmem, stream>>>(mk, mv, (float*)ws, dm.T, dm.S, G, tile_tokens, status);
+        err = cudaGetLastError();
+        if (err != cudaSuccess) return err;
+    }
+    if (!(phases & kPhaseOutput))
+        return causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, false);
+    err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, true);
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<D>::kSmem);
+    if (err != cudaSuccess) return err;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Lay<D>::kSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = G;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = G > 1 ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k3, (const __nv_bfloat16*)pq, mk, mv, (__nv_bfloat16*)out, (const float*)ws,
+                              dm.T, dm.S, G, tile_tokens, dm.eps, status);
+}
+
+}  // namespace
+
+bool tensor_bf16_supported(const Dims& dm) {
+    const int G = dm.S / SG;
+    return dm.S % SG == 0 && (G == 1 || G == 2 || G == 4 || G == 8) && (dm.D == 64 || dm.D == 128) &&
+           dm.N >= 0 && dm.N <= 65535 && dm.T < (1ll << 31);
+}
+
+cudaError_t causal_fwd_tensor_bf16(const void* pq, const void* pk, const void* v, void* out,
+                                   const float* carry_in, float* state_out, void* ws, const Dims& dm,
+                                   int tile_tokens, cudaStream_t stream, int* status, int phases) {
+    if (dm.D == 64)
+        return launch_bf16<64>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream, status, phases);
+    return launch_bf16<128>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream, status, phases);
+}
+
+}  // namespace race

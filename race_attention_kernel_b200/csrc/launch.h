@@ -48,4 +48,10 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
                               int dtype, int tile_tokens, cudaStream_t stream, int* status,
                               int phases = kPhaseAll);
 
+// bf16 tensor path (causal_tc_bf16.cu): S a multiple of 64 (1, 2, 4 or 8 bucket groups), d_k 64 or 128
+bool tensor_bf16_supported(const Dims& dm);
+cudaError_t causal_fwd_tensor_bf16(const void* pq, const void* pk, const void* v, void* out,
+                                   const float* carry_in, float* state_out, void* ws, const Dims& dm,
+                                   int tile_tokens, cudaStream_t stream, int* status, int phases);
+
 }  // namespace race
