@@ -8,10 +8,11 @@
 //     columns = all 512);
 //   * S > 64: the tables of this estimator are independent (out = sum over tables), so bucket
 //     group g (64 buckets) is owned by CTA g of a thread-block cluster of G CTAs working on the
-//     same (stream, tile).  Each CTA keeps its own state slice and forms a partial output; the
-//     partial outputs of a chunk are summed through distributed shared memory in group order
-//     (deterministic), rows dealt round-robin to the CTAs, and written once.  Cross-CTA hand-offs
-//     are mbarriers with remote arrivals; no TMA multicast anywhere.
+//     same (stream, tile).  Each CTA keeps its own state slice and forms a partial output; row r of
+//     a chunk belongs to CTA r % G: every CTA stores its partial rows into the owner's slot buffer
+//     through distributed shared memory (posted remote stores), the owner adds the G slots in
+//     group order (deterministic) and writes the rows once.  Cross-CTA hand-offs are mbarriers
+//     with remote arrivals; no TMA multicast anywhere.
 // Reference semantics: src/race_baseline.py:45-51 (docs/causal_v2_design.md:70-77 for the chunk
 // form); BASELINE configuration "N=256 streams, T=262144, d_k=128, L=8, K=6" is G = 8, D = 128.
 #include <cudaTypedefs.h>
@@ -46,7 +47,6 @@ struct Lay {
     static constexpr int kNumBars = 36;
     static constexpr int oMisc = oBars + kNumBars * 8;
     static constexpr int kSmem = oMisc + 16 + 1024;
-    static constexpr uint32_t kTmemCols = D == 64 ? 512 : 512;
     // MN-major descriptor words of a [64][D] tile
     static constexpr uint32_t kLboV = (uint32_t)(D / 8) * 128;        // K-direction (row-group) stride
     static constexpr uint32_t kStepV = (2 * kLboV) >> 4;              // lo-word step per 16 K-rows
@@ -78,11 +78,6 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
 }
 
 // ---- cluster helpers --------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta) {
     uint32_t r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
@@ -90,12 +85,6 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta)
 }
 __device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ float4 remote_ld4(uint32_t cluster_addr) {
-    float4 v;
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
-    return v;
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -195,7 +184,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             mbar_init(cx.bar(bBtReady + i), 4);
             mbar_init(cx.bar(bDrain + i), 1);
             mbar_init(cx.bar(bObufReady + i), 4 * G);
-            mbar_init(cx.bar(bObufFree + i), 4 * G);
+            mbar_init(cx.bar(bObufFree + i), G);
         }
         mbar_init(cx.bar(bBupdDone), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -246,6 +235,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             const int64_t tok0 = t_begin + (int64_t)c * C;
             const int valid = (int)min((int64_t)C, t_end - tok0);
             // pQ in the accumulator-fragment layout (pairs of bf16), issued first
+            RACE_TRACE(wg, c >> 1, 0);
             uint32_t pqv[16];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -313,7 +303,9 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive(cx.bar(bGtReady + wg));
             // ---- O ---------------------------------------------------------------------------------
+            RACE_TRACE(wg, c >> 1, 1);
             if (!(ok = wait_bar_warp(cx, bOReady + wg, ph, 105))) break;
+            RACE_TRACE(wg, c >> 1, 2);
             if (G == 1) {
 #pragma unroll
                 for (int dh = 0; dh < DH; ++dh) {
@@ -333,45 +325,58 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                     }
                 }
             } else {
-                // partial output of this bucket group -> own shared memory; then the cluster sums
-                // the groups' partials in group order, rows dealt round-robin to the CTAs
+                // Partial output of this bucket group: row r of the chunk belongs to CTA r % G of the
+                // cluster.  Every CTA stores its rows straight into the owner's slot buffer
+                // [source group][row / G][D] (posted remote stores), then tells the owner; the owner
+                // adds the G slots in group order from its own shared memory and writes the rows.
                 if (uses >= 1 && !(ok = wait_bar_cluster_warp(cx, bObufFree + wg, (uint32_t)((uses - 1) & 1), 108))) break;
+                RACE_TRACE(wg, c >> 1, 3);
+                {
+                    const int owner = rbase % G;                       // rbase and rbase + 8 share it
+                    const uint32_t slot = map_to_cta(obuf_u32 + (uint32_t)(g * (C / G) * D) * 4, (uint32_t)owner);
 #pragma unroll
-                for (int dh = 0; dh < DH; ++dh) {
-                    tc_fence_after();
-                    tmem_ld64(lane_base + tmO(wg) + dh * 64, v);
-                    tc_fence_before();
+                    for (int dh = 0; dh < DH; ++dh) {
+                        tc_fence_after();
+                        tmem_ld64(lane_base + tmO(wg) + dh * 64, v);
+                        tc_fence_before();
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t ra = slot + (uint32_t)(((rbase + 8 * h) / G) * D + dh * 64 + 2 * q) * 4;
 #pragma unroll
-                        for (int x = 0; x < 8; ++x)
-                            *reinterpret_cast<float2*>(obuf + (rbase + 8 * h) * D + dh * 64 + 8 * x + 2 * q) =
-                                make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+                            for (int x = 0; x < 8; ++x)
+                                asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};"
+                                             ::"r"(ra + 32 * x), "f"(v[4 * x + 2 * h]), "f"(v[4 * x + 2 * h + 1]) : "memory");
+                        }
+                    }
                 }
-                asm volatile("fence.acq_rel.cluster;" ::: "memory");
                 __syncwarp();
-                if (lane == 0)
-                    for (int p = 0; p < G; ++p) remote_arrive(map_to_cta(cx.bar(bObufReady + wg), (uint32_t)p));
+                // one release-arrival per owner this warp wrote to (its rows cover min(G, 8) owners)
+                if (lane < G && lane < 8) remote_arrive(map_to_cta(cx.bar(bObufReady + wg), (uint32_t)lane));
+                RACE_TRACE(wg, c >> 1, 4);
                 if (!(ok = wait_bar_cluster_warp(cx, bObufReady + wg, (uint32_t)(uses & 1), 109))) break;
+                RACE_TRACE(wg, c >> 1, 5);
                 const int rows_per = C / G;
                 for (int item = wtid; item < rows_per * (D / 8); item += 128) {
-                    const int row = g + G * (item / (D / 8));
-                    const int col = (item % (D / 8)) * 8;
+                    const int rl = item / (D / 8), col = (item % (D / 8)) * 8;
+                    const int row = g + G * rl;
                     float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
                     for (int p = 0; p < G; ++p) {
-                        const uint32_t ra = map_to_cta(obuf_u32 + (uint32_t)(row * D + col) * 4, (uint32_t)p);
-                        const float4 a = remote_ld4(ra), b = remote_ld4(ra + 16);
+                        const float* src = obuf + (p * rows_per + rl) * D + col;
+                        const float4 a = *reinterpret_cast<const float4*>(src);
+                        const float4 b4 = *reinterpret_cast<const float4*>(src + 4);
                         s0.x += a.x; s0.y += a.y; s0.z += a.z; s0.w += a.w;
-                        s1.x += b.x; s1.y += b.y; s1.z += b.z; s1.w += b.w;
+                        s1.x += b4.x; s1.y += b4.y; s1.z += b4.z; s1.w += b4.w;
                     }
                     if (row < valid)
                         *reinterpret_cast<uint4*>(out_n + (tok0 + row) * D + col) =
                             make_uint4(pack_bf16(s0.x, s0.y), pack_bf16(s0.z, s0.w), pack_bf16(s1.x, s1.y),
                                        pack_bf16(s1.z, s1.w));
                 }
-                __syncwarp();
-                if (lane == 0)
-                    for (int p = 0; p < G; ++p) remote_arrive(map_to_cta(cx.bar(bObufFree + wg), (uint32_t)p));
+                RACE_TRACE(wg, c >> 1, 6);
+                // the slots may be overwritten: tell every source CTA
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+                if (w == 0 && lane < G) remote_arrive(map_to_cta(cx.bar(bObufFree + wg), (uint32_t)lane));
+                RACE_TRACE(wg, c >> 1, 7);
                 ++uses;
             }
         }
@@ -807,5 +812,11 @@ cudaError_t causal_fwd_tensor_bf16(const void* pq, const void* pk, const void* v
         return launch_bf16<64>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream, status, phases);
     return launch_bf16<128>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream, status, phases);
 }
+
+#ifdef RACE_TC_TRACE
+extern "C" int race_b200_debug_set_trace_bf16(long long* buf) {
+    return (int)cudaMemcpyToSymbol(g_trace_buf, &buf, sizeof(buf));
+}
+#endif
 
 }  // namespace race

@@ -47,6 +47,9 @@ def test_state_floats_and_support():
     assert L.race_b200_is_supported(ctypes.byref(_shape(dk=96 * 4)), 1) == 0     # d_k > 128
     assert L.race_b200_is_supported(ctypes.byref(_shape(L=3, R=32)), 1) == 0      # S=96: not /64
     assert L.race_b200_is_supported(ctypes.byref(_shape(L=8, R=64, dk=128, dtype=1)), 1) == 1
+    assert L.race_b200_is_supported(ctypes.byref(_shape(L=8, R=64, dk=128, dtype=1)), 2) == 1   # tensor, cluster of 8
+    assert L.race_b200_is_supported(ctypes.byref(_shape(L=3, R=64, dk=128, dtype=1)), 2) == 0   # 3 groups
+    assert L.race_b200_is_supported(ctypes.byref(_shape(dk=128)), 2) == 0                       # fp32 d_k=128
     assert L.race_b200_is_supported(ctypes.byref(_shape(dtype=7)), 0) == 0
     assert L.race_b200_is_supported(ctypes.byref(_shape(reserved=1)), 0) == 0
 

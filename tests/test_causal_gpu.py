@@ -62,7 +62,8 @@ def test_fp32_parity(N, T, L, R, dk):
 
 @pytest.mark.parametrize("N,T,L,R,dk", [(8, 4096, 4, 16, 64), (2, 333, 4, 16, 64),
                                         (2, 300, 8, 64, 128), (2, 257, 4, 16, 128),
-                                        (2, 300, 1, 32, 64)])
+                                        (2, 300, 1, 32, 64), (2, 1000, 2, 64, 64), (2, 700, 4, 64, 128),
+                                        (3, 5000, 8, 64, 128), (1, 65, 8, 64, 128)])
 def test_bf16_parity(N, T, L, R, dk):
     rk = _ops()
     pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=7 + T)
