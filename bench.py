@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--seq-len T]
 
-Workload (BASELINE config 2 at its headline length): N=8 streams per GPU, T=1,048,576 tokens,
+Workload (the causal fp32 sweep configuration at its headline length): N=8 streams per GPU, T=1,048,576 tokens,
 d_k=64, L=4 tables, R=16 buckets, fp32; probsQ/probsK rows are a softmax of N(0,1) logits and
 V ~ N(0,1) (seeded synthetic data -- the reference measures on synthetic randn data too).
 One step = one forward over all streams.  Metric: M tokens/s = streams*T / seconds / 1e6.
@@ -143,7 +143,7 @@ def _time_ms(fn, warmup, steps):
 
 
 def workload_c4(args):
-    """BASELINE config 4: one long sequence per stream (N=8, T=4,194,304, fp32) sharded contiguously
+    """Single ultra-long sequence configuration: one long sequence per stream (N=8, T=4,194,304, fp32) sharded contiguously
     over the ranks (run under torchrun); carry chain over NCCL send/recv."""
     import torch.distributed as dist
 
@@ -191,7 +191,7 @@ def workload_c4(args):
 
 
 def extra_workloads(args):
-    """Measurement lines for the other BASELINE configurations on one GPU (not the contract line)."""
+    """Measurement lines for the other benchmark configurations on one GPU (not the contract line)."""
     if args.workload == "c4":
         return workload_c4(args)
     import race_attention_kernel_b200 as rk
@@ -236,7 +236,7 @@ def extra_workloads(args):
             if T > (3 << 23):
                 break
     elif args.workload == "c3":
-        # BASELINE config 3 geometry: bf16, d_k=128, L=8, R=64 (S=512); per-GPU share of the 256 streams
+        # multi-head batched bf16 configuration: bf16, d_k=128, L=8, R=64 (S=512); per-GPU share of the 256 streams
         L, R, dk = 8, 64, 128
         for N, T in ((32, 65536), (32, 262144)):
             pQ, pK = probs(N, T, L, R, torch.bfloat16, g), probs(N, T, L, R, torch.bfloat16, g)
@@ -251,7 +251,7 @@ def extra_workloads(args):
             del pQ, pK, V, out
             torch.cuda.empty_cache()
     elif args.workload == "c5":
-        # BASELINE config 5: non-causal forward + backward, B=64, H=12 (N=768), T=4096, S=64, d_k=64
+        # non-causal configuration: forward + backward, B=64, H=12 (N=768), T=4096, S=64, d_k=64
         N, T, L, R, dk = 768, 4096, 4, 16, 64
         for dtype, elt in ((torch.float32, 4), (torch.bfloat16, 2)):
             pQ = probs(N, T, L, R, dtype, g).requires_grad_(True)

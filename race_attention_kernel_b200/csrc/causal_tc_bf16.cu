@@ -14,7 +14,7 @@
 //     group order (deterministic) and writes the rows once.  Cross-CTA hand-offs are mbarriers
 //     with remote arrivals; no TMA multicast anywhere.
 // Reference semantics: src/race_baseline.py:45-51 (docs/causal_v2_design.md:70-77 for the chunk
-// form); BASELINE configuration "N=256 streams, T=262144, d_k=128, L=8, K=6" is G = 8, D = 128.
+// form).  The multi-head configuration N=256 streams, T=262144, d_k=128, L=8, K=6 is G = 8, D = 128.
 #include <cudaTypedefs.h>
 
 #include "common.cuh"

@@ -45,7 +45,7 @@ def test_seeded_buffers_match_reference(golden):
 
 
 def test_config1_matches_reference(golden):
-    # BASELINE config 1: N=8, T=4096, d_k=64, L=4, K=4, fp32; stored every 64th token.
+    # the reference benchmark configuration: N=8, T=4096, d_k=64, L=4, K=4, fp32; stored every 64th token.
     M, B, H, dk, K, L, T, stride = _cfg(golden, "c1_t4096")
     Kh, Vh, Qh = draw_kvq(M, B, T, H, dk, torch.float32)
     planes_T = torch.from_numpy(golden["c1_t4096/planes_T"])
