@@ -41,10 +41,8 @@ constexpr int kOpTile = C * 64 * 2;         // one bf16 operand tile (8 KB)
 constexpr int oStage = 0;                               // [2][kStageBytes]
 constexpr int oKt = oStage + 2 * kStageBytes;           // [2 wg][hi|lo]
 constexpr int oVt = oKt + 4 * kOpTile;
-constexpr int oWt = oVt + 4 * kOpTile;                  // W, then reused for masked G
-constexpr int oBt = oWt + 4 * kOpTile;                  // [2 buffers][hi|lo]
-constexpr int oTril = oBt + 4 * kOpTile;
-constexpr int oAcar = oTril + kOpTile;                  // [2][64] fp32
+constexpr int oBt = oVt + 4 * kOpTile;                  // [2 buffers][hi|lo]
+constexpr int oAcar = oBt + 4 * kOpTile;                // [2][64] fp32
 constexpr int oBars = oAcar + 2 * 64 * 4;
 constexpr int kNumBars = 30;
 constexpr int oMisc = oBars + kNumBars * 8;             // tmem base, abort flag
@@ -141,16 +139,6 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                      ::"r"(cx.sm_u32 + oMisc), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int i = tid; i < C * 8; i += kThreads) {   // tril[t][j] = (j <= t), 8 columns per item
-        const int t = i >> 3, jg = i & 7;
-        uint32_t w[4];
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            const int j0 = jg * 8 + 2 * p;
-            w[p] = (j0 <= t ? 0x3F80u : 0u) | (j0 + 1 <= t ? 0x3F800000u : 0u);
-        }
-        *reinterpret_cast<uint4*>(cx.sm + oTril + op_off(t, jg * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
@@ -159,17 +147,20 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
     const uint32_t tmB = tmem;                               // B accumulator, columns [0, 64)
     auto tmAG = [&](int wg) { return tmem + 64 + wg * 128; };      // A_loc, then G
     auto tmO = [&](int wg) { return tmem + 64 + wg * 128 + 64; };  // O
+    // MMA A operands kept in tensor memory (bf16 pairs, 32 columns per limb): W of the chunk, later its
+    // masked G, per group [hi | lo]; and the constant lower-triangular ones matrix
+    auto tmWG = [&](int wg) { return tmem + 320 + wg * 64; };
+    const uint32_t tmTril = tmem + 448;
 
     if (warp < 8) {
         // =========================== worker warpgroups =========================================
         const int wg = warp >> 2, w = warp & 3;
         const int q = lane & 3, rbase = 16 * w + (lane >> 2);
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
-        uint8_t* wt_hi = cx.sm + oWt + wg * 2 * kOpTile;
-        uint8_t* wt_lo = wt_hi + kOpTile;
         float* out_n = out + n * T * D;
         const float* pq_n = pq + n * T * S;
         float v[32];
+        uint32_t ohi[16], olo[16];   // operand limbs of W / masked G on their way to tensor memory
 
         // O of chunk c: TMEM -> global (fragment rows rbase, rbase + 8; 8-byte stores, full sectors)
         auto store_out = [&](int c) {
@@ -235,16 +226,11 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             for (int x = 0; x < 8; ++x) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int row = rbase + 8 * h;
                     const float a0 = acar[2 * x] + v[4 * x + 2 * h];
                     const float a1 = acar[2 * x + 1] + v[4 * x + 2 * h + 1];
                     const float w0 = __fdividef(pqv[2 * x + h].x, a0 + eps);
                     const float w1 = __fdividef(pqv[2 * x + h].y, a1 + eps);
-                    uint32_t hi, lo;
-                    split2(w0, w1, hi, lo);
-                    const uint32_t off = op_off(row, 8 * x + 2 * q);
-                    *reinterpret_cast<uint32_t*>(wt_hi + off) = hi;
-                    *reinterpret_cast<uint32_t*>(wt_lo + off) = lo;
+                    split2(w0, w1, ohi[2 * x + h], olo[2 * x + h]);
                     if (h == 1 && w == 3 && (lane >> 2) == 7) {
                         // row 63: the running A after this chunk, for the other group
                         float* an = reinterpret_cast<float*>(cx.sm + oAcar) + (wg ^ 1) * 64;
@@ -252,7 +238,10 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                     }
                 }
             }
-            fence_proxy_async();
+            tmem_st_pairs(lane_base + tmWG(wg), ohi);
+            tmem_st_pairs(lane_base + tmWG(wg) + 32, olo);
+            tmem_wait_st();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(cx.bar(kWReady + wg));
@@ -273,14 +262,13 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                     const int row = rbase + 8 * h, col = 8 * x + 2 * q;
                     const float g0 = col <= row ? v[4 * x + 2 * h] : 0.f;
                     const float g1 = col + 1 <= row ? v[4 * x + 2 * h + 1] : 0.f;
-                    uint32_t hi, lo;
-                    split2(g0, g1, hi, lo);
-                    const uint32_t off = op_off(row, col);
-                    *reinterpret_cast<uint32_t*>(wt_hi + off) = hi;
-                    *reinterpret_cast<uint32_t*>(wt_lo + off) = lo;
+                    split2(g0, g1, ohi[2 * x + h], olo[2 * x + h]);
                 }
             }
-            fence_proxy_async();
+            tmem_st_pairs(lane_base + tmWG(wg), ohi);
+            tmem_st_pairs(lane_base + tmWG(wg) + 32, olo);
+            tmem_wait_st();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(cx.bar(kGtReady + wg));
 
@@ -323,7 +311,18 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                     slice + (rbase + 8 * h) * D + 8 * x + 2 * q);
                 v[4 * x + 2 * h] = b2.x; v[4 * x + 2 * h + 1] = b2.y;
             }
-        tmem_st64(lane_base + tmB, v);
+        {   // tril[t][j] = (j <= t), exact in bf16, as an A operand in tensor memory
+            uint32_t tr[16];
+#pragma unroll
+            for (int y = 0; y < 8; ++y)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = rbase + 8 * h, j0 = 8 * y + 2 * q;
+                    tr[2 * y + h] = (j0 <= row ? 0x3F80u : 0u) | (j0 + 1 <= row ? 0x3F800000u : 0u);
+                }
+            tmem_st_pairs(lane_base + tmTril, tr);
+        }
+        tmem_st64(lane_base + tmB, v);   // waits for both stores
         tc_fence_before();
         if (warp == 8) {
             float* ac = reinterpret_cast<float*>(cx.sm + oAcar);
@@ -411,23 +410,23 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
         const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
         const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
         constexpr uint32_t kLimb = kOpTile >> 4;   // hi -> lo limb tile, in lo-word units
-        const uint32_t tril_lo = lo_k(smb + oTril);
         const uint32_t kt_k = lo_k(smb + oKt + wg * 2 * kOpTile);
         const uint32_t kt_mn = lo_mn(smb + oKt + wg * 2 * kOpTile);
         const uint32_t vt_mn = lo_mn(smb + oVt + wg * 2 * kOpTile);
-        const uint32_t wt_k = lo_k(smb + oWt + wg * 2 * kOpTile);
         const uint32_t bt_mn = lo_mn(smb + oBt + wg * 2 * kOpTile);
         const uint32_t dB = tm, dAG = tm + 64 + wg * 128, dO = tm + 64 + wg * 128 + 64;
+        const uint32_t a_hi = tm + 320 + wg * 64, a_lo = a_hi + 32;   // W / masked G limbs (A operand in TMEM)
+        const uint32_t a_tril = tm + 448;
         if (elect_one()) {
             uint32_t ph = 0;
             bool ok = true;
             for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
-                // A_loc = tril . pK : A = tril (K-major), B = pK [token][s] (N-major)
+                // A_loc = tril . pK : A = tril (tensor memory), B = pK [token][s] (N-major)
                 if (!(ok = wait_bar(cx, kKvReady + wg, ph, 401))) break;
                 tc_fence_after();
                 RACE_TRACE(4, c, 0);
-                mma_k64<true, kHiK, 16, kHiMN, 128>(dAG, tril_lo, kt_mn, kIdescBase | kBmn);
-                mma_k64<false, kHiK, 16, kHiMN, 128>(dAG, tril_lo, kt_mn + kLimb, kIdescBase | kBmn);
+                mma_k64_ta<true, kHiMN, 128>(dAG, a_tril, kt_mn, kIdescBase | kBmn);
+                mma_k64_ta<false, kHiMN, 128>(dAG, a_tril, kt_mn + kLimb, kIdescBase | kBmn);
                 mma_commit(cx.bar(kXReady + wg));
                 RACE_TRACE(4, c, 1);
                 // B += pK^T . V, in chunk order: the accumulator is free once the state after
@@ -446,21 +445,21 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                 if (!(ok = wait_bar(cx, kBtReady + wg, ph, 405))) break;
                 tc_fence_after();
                 RACE_TRACE(4, c, 4);
-                mma_k64<true, kHiK, 16, kHiMN, 128>(dO, wt_k, bt_mn, kIdescBase | kBmn);
-                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k, bt_mn + kLimb, kIdescBase | kBmn);
-                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k + kLimb, bt_mn, kIdescBase | kBmn);
-                mma_k64<true, kHiK, 16, kHiK, 16>(dAG, wt_k, kt_k, kIdescBase);
-                mma_k64<false, kHiK, 16, kHiK, 16>(dAG, wt_k, kt_k + kLimb, kIdescBase);
-                mma_k64<false, kHiK, 16, kHiK, 16>(dAG, wt_k + kLimb, kt_k, kIdescBase);
+                mma_k64_ta<true, kHiMN, 128>(dO, a_hi, bt_mn, kIdescBase | kBmn);
+                mma_k64_ta<false, kHiMN, 128>(dO, a_hi, bt_mn + kLimb, kIdescBase | kBmn);
+                mma_k64_ta<false, kHiMN, 128>(dO, a_lo, bt_mn, kIdescBase | kBmn);
+                mma_k64_ta<true, kHiK, 16>(dAG, a_hi, kt_k, kIdescBase);
+                mma_k64_ta<false, kHiK, 16>(dAG, a_hi, kt_k + kLimb, kIdescBase);
+                mma_k64_ta<false, kHiK, 16>(dAG, a_lo, kt_k, kIdescBase);
                 mma_commit(cx.bar(kGReady + wg));
                 RACE_TRACE(4, c, 5);
-                // O += G . V : A = masked G (K-major), B = V [token][c] (N-major)
+                // O += G . V : A = masked G (tensor memory), B = V [token][c] (N-major)
                 if (!(ok = wait_bar(cx, kGtReady + wg, ph, 406))) break;
                 tc_fence_after();
                 RACE_TRACE(4, c, 6);
-                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k, vt_mn, kIdescBase | kBmn);
-                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k, vt_mn + kLimb, kIdescBase | kBmn);
-                mma_k64<false, kHiK, 16, kHiMN, 128>(dO, wt_k + kLimb, vt_mn, kIdescBase | kBmn);
+                mma_k64_ta<false, kHiMN, 128>(dO, a_hi, vt_mn, kIdescBase | kBmn);
+                mma_k64_ta<false, kHiMN, 128>(dO, a_hi, vt_mn + kLimb, kIdescBase | kBmn);
+                mma_k64_ta<false, kHiMN, 128>(dO, a_lo, vt_mn, kIdescBase | kBmn);
                 mma_commit(cx.bar(kOReady + wg));
                 RACE_TRACE(4, c, 7);
             }

@@ -101,6 +101,21 @@ __device__ __forceinline__ void tmem_st64(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 16 lanes x 32 columns of packed bf16 pairs (a 16 x 64 slice of an MMA A operand kept in tensor
+// memory): register 2y + h of thread t <-> lane t/4 + 8h, column 4y + t%4, i.e. the K-pair
+// (8y + 2(t%4), +1) -- the pairs a thread owns in the 16x256b accumulator fragment.  No wait inside.
+__device__ __forceinline__ void tmem_st_pairs(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x128b.x8.b32 [%16], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // shared-memory matrix descriptor, no swizzle: 8x(16 B) core matrices of 128 contiguous bytes;
 // lbo = byte stride between core matrices along K, sbo = along M/N
 __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -130,6 +145,23 @@ __device__ __forceinline__ void mma_k64(uint32_t d_tmem, uint32_t a_lo, uint32_t
 #pragma unroll
     for (uint32_t k = 1; k < 4; ++k)
         mma_issue<true>(d_tmem, desc64(kAHi, a_lo + k * kAStep), desc64(kBHi, b_lo + k * kBStep), idesc);
+}
+
+// The same with the A operand in tensor memory (bf16 pairs, 8 columns per k-step; for M = 64 row r
+// lives in lane (r % 16) + 32 (r / 16), like the accumulator).
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_issue_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(kAccumulate ? 1u : 0u));
+}
+template <bool kFirstZero, uint32_t kBHi, uint32_t kBStep>
+__device__ __forceinline__ void mma_k64_ta(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc) {
+    if (kFirstZero) mma_issue_ta<false>(d_tmem, a_tmem, desc64(kBHi, b_lo), idesc);
+    else mma_issue_ta<true>(d_tmem, a_tmem, desc64(kBHi, b_lo), idesc);
+#pragma unroll
+    for (uint32_t k = 1; k < 4; ++k)
+        mma_issue_ta<true>(d_tmem, a_tmem + 8 * k, desc64(kBHi, b_lo + k * kBStep), idesc);
 }
 
 // instruction descriptor: bf16 x bf16 -> fp32, M = 64, N = 64
