@@ -39,12 +39,12 @@ constexpr int kTileF32 = C * 64 * 4;        // one staged fp32 tile: 64 tokens x
 constexpr int kStageBytes = 2 * kTileF32;   // pK | V  (pQ goes global -> registers)
 constexpr int kOpTile = C * 64 * 2;         // one bf16 operand tile (8 KB)
 constexpr int oStage = 0;                               // [2][kStageBytes]
-constexpr int oKt = oStage + 2 * kStageBytes;           // [2 wg][hi|lo]
-constexpr int oVt = oKt + 4 * kOpTile;
+constexpr int oKt = oStage + 2 * kStageBytes;           // [2 wg][2 buffers][hi|lo]
+constexpr int oVt = oKt + 8 * kOpTile;
 constexpr int oBt = oVt + 4 * kOpTile;                  // [2 buffers][hi|lo]
 constexpr int oAcar = oBt + 4 * kOpTile;                // [2][64] fp32
 constexpr int oBars = oAcar + 2 * 64 * 4;
-constexpr int kNumBars = 30;
+constexpr int kNumBars = 34;
 constexpr int oMisc = oBars + kNumBars * 8;             // tmem base, abort flag
 constexpr int kSmemBytes = oMisc + 16 + 1024;           // + slack for manual alignment
 
@@ -63,7 +63,8 @@ enum Bar {
     kBtReady = 21,  // [2] B operand buffer (c & 1) holds the state before chunk c (count 4)
     kDrain = 23,    // [2]
     kAcarFree = 25, // [2] running-A buffer of group g read by all four of its warps
-    kVReady = 27    // [2] V operand tile written
+    kVReady = 27,   // [2] V operand tile written
+    kKtFree = 29    // [2 wg][2 buffers] pK operand buffer no longer read by any product
 };
 
 // fp32 staged tile (two 128B-swizzled halves of 32 columns) -> bf16 hi/lo operand tiles
@@ -124,6 +125,8 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             mbar_init(cx.bar(kAcar + i), 1);
             mbar_init(cx.bar(kAcarFree + i), 4);
             mbar_init(cx.bar(kVReady + i), 4);
+            mbar_init(cx.bar(kKtFree + 2 * i), 1);
+            mbar_init(cx.bar(kKtFree + 2 * i + 1), 1);
         }
         mbar_init(cx.bar(kBupdDone), 1);
         mbar_init(cx.bar(kBaccFree), 4);
@@ -341,12 +344,12 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             const int wg = c & 1;
             const uint32_t ph = (uint32_t)((c >> 1) & 1);
             const uint8_t* stage = cx.sm + oStage + wg * kStageBytes;
-            uint8_t* kt_hi = cx.sm + oKt + wg * 2 * kOpTile;
+            const int kb = (int)ph;   // pK operand buffer of this chunk within its group
+            uint8_t* kt_hi = cx.sm + oKt + (wg * 2 + kb) * 2 * kOpTile;
             uint8_t* vt_hi = cx.sm + oVt + wg * 2 * kOpTile;
-            // pK tile of the group: last read by the G product of chunk c - 2 (its commit also
-            // covers that chunk's running-sum and state-update products)
+            // pK buffer: last read by the products of chunk c - 4
             RACE_TRACE(2, c, 0);
-            if (c >= 2 && !(ok = wait_bar_warp(cx, kGReady + wg, ph ^ 1, 203))) break;
+            if (c >= 4 && !(ok = wait_bar_warp(cx, kKtFree + wg * 2 + kb, (uint32_t)(((c >> 2) - 1) & 1), 203))) break;
             if (!(ok = wait_bar_warp(cx, kFull + wg, ph, 201))) break;
             RACE_TRACE(2, c, 1);
             convert_tile(stage, kt_hi, kt_hi + kOpTile, wtid);
@@ -356,7 +359,8 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             RACE_TRACE(2, c, 2);
             if (c >= 1) {
                 // state after chunk c - 1 -> operand buffer c & 1 (read by W.B of chunk c; last read
-                // by W.B of chunk c - 2, which the wait on kGReady above covers)
+                // by W.B of chunk c - 2)
+                if (c >= 2 && !(ok = wait_bar_warp(cx, kGReady + wg, ph ^ 1, 204))) break;
                 if (!(ok = wait_bar_warp(cx, kBupdDone, (c - 1) & 1, 202))) break;
                 tc_fence_after();
                 tmem_ld64(lane_base + tmB, v);
@@ -410,8 +414,8 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
         const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
         const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
         constexpr uint32_t kLimb = kOpTile >> 4;   // hi -> lo limb tile, in lo-word units
-        const uint32_t kt_k = lo_k(smb + oKt + wg * 2 * kOpTile);
-        const uint32_t kt_mn = lo_mn(smb + oKt + wg * 2 * kOpTile);
+        const uint32_t kt_k0 = lo_k(smb + oKt + wg * 4 * kOpTile);
+        const uint32_t kt_mn0 = lo_mn(smb + oKt + wg * 4 * kOpTile);
         const uint32_t vt_mn = lo_mn(smb + oVt + wg * 2 * kOpTile);
         const uint32_t bt_mn = lo_mn(smb + oBt + wg * 2 * kOpTile);
         const uint32_t dB = tm, dAG = tm + 64 + wg * 128, dO = tm + 64 + wg * 128 + 64;
@@ -421,6 +425,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             uint32_t ph = 0;
             bool ok = true;
             for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
+                const uint32_t kt_k = kt_k0 + ph * 2 * kLimb, kt_mn = kt_mn0 + ph * 2 * kLimb;   // buffer (c >> 1) & 1
                 // A_loc = tril . pK : A = tril (tensor memory), B = pK [token][s] (N-major)
                 if (!(ok = wait_bar(cx, kKvReady + wg, ph, 401))) break;
                 tc_fence_after();
@@ -452,6 +457,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                 mma_k64_ta<false, kHiK, 16>(dAG, a_hi, kt_k + kLimb, kIdescBase);
                 mma_k64_ta<false, kHiK, 16>(dAG, a_lo, kt_k, kIdescBase);
                 mma_commit(cx.bar(kGReady + wg));
+                mma_commit(cx.bar(kKtFree + wg * 2 + (int)ph));   // no later product reads this pK buffer
                 RACE_TRACE(4, c, 5);
                 // O += G . V : A = masked G (tensor memory), B = V [token][c] (N-major)
                 if (!(ok = wait_bar(cx, kGtReady + wg, ph, 406))) break;
