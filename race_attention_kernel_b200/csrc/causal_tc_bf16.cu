@@ -42,8 +42,8 @@ struct Lay {
     static constexpr int oBt = oWt + 2 * kTileP;        // [2]
     static constexpr int oTril = oBt + 2 * kTileV;
     static constexpr int oAcar = oTril + kTileP;        // [2][64] fp32
-    static constexpr int oObuf = oAcar + 2 * 64 * 4;    // [2][64][D] fp32 partial outputs (clusters)
-    static constexpr int oBars = oObuf + 2 * C * D * 4;
+    static constexpr int oObuf = oAcar + 2 * 64 * 4;    // [2][64][D] bf16 partial outputs (clusters)
+    static constexpr int oBars = oObuf + 2 * C * D * 2;
     static constexpr int kNumBars = 36;
     static constexpr int oMisc = oBars + kNumBars * 8;
     static constexpr int kSmem = oMisc + 16 + 1024;
@@ -223,8 +223,8 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
         const int q = lane & 3, rbase = 16 * w + (lane >> 2);
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
         uint8_t* wt = cx.sm + Ly::oWt + wg * Ly::kTileP;
-        float* obuf = reinterpret_cast<float*>(cx.sm + Ly::oObuf) + wg * C * D;
-        const uint32_t obuf_u32 = cx.sm_u32 + Ly::oObuf + wg * C * D * 4;
+        const uint8_t* obuf = cx.sm + Ly::oObuf + wg * C * D * 2;
+        const uint32_t obuf_u32 = cx.sm_u32 + Ly::oObuf + wg * C * D * 2;
         __nv_bfloat16* out_n = out + n * T * D;
         const __nv_bfloat16* pq_n = pq + n * T * S + g * SG;
         float v[32];
@@ -333,7 +333,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                 RACE_TRACE(wg, c >> 1, 3);
                 {
                     const int owner = rbase % G;                       // rbase and rbase + 8 share it
-                    const uint32_t slot = map_to_cta(obuf_u32 + (uint32_t)(g * (C / G) * D) * 4, (uint32_t)owner);
+                    const uint32_t slot = map_to_cta(obuf_u32 + (uint32_t)(g * (C / G) * D) * 2, (uint32_t)owner);
 #pragma unroll
                     for (int dh = 0; dh < DH; ++dh) {
                         tc_fence_after();
@@ -341,11 +341,18 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                         tc_fence_before();
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const uint32_t ra = slot + (uint32_t)(((rbase + 8 * h) / G) * D + dh * 64 + 2 * q) * 4;
+                            // bf16 partials; neighbouring lanes of a quad swap one pair so that every lane
+                            // owns four consecutive columns: half as many remote stores, 8 bytes each
+                            const uint32_t ra = slot + (uint32_t)(((rbase + 8 * h) / G) * D + dh * 64 + 4 * (q >> 1) + 8 * (q & 1)) * 2;
 #pragma unroll
-                            for (int x = 0; x < 8; ++x)
-                                asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};"
-                                             ::"r"(ra + 32 * x), "f"(v[4 * x + 2 * h]), "f"(v[4 * x + 2 * h + 1]) : "memory");
+                            for (int x = 0; x < 8; x += 2) {
+                                const uint32_t p0 = pack_bf16(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+                                const uint32_t p1 = pack_bf16(v[4 * x + 4 + 2 * h], v[4 * x + 4 + 2 * h + 1]);
+                                const uint32_t got = __shfl_xor_sync(0xffffffffu, (q & 1) ? p0 : p1, 1);
+                                const uint32_t lo = (q & 1) ? got : p0, hi = (q & 1) ? p1 : got;
+                                asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};"
+                                             ::"r"(ra + 16 * x), "r"(lo), "r"(hi) : "memory");
+                            }
                         }
                     }
                 }
@@ -361,11 +368,10 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                     const int row = g + G * rl;
                     float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
                     for (int p = 0; p < G; ++p) {
-                        const float* src = obuf + (p * rows_per + rl) * D + col;
-                        const float4 a = *reinterpret_cast<const float4*>(src);
-                        const float4 b4 = *reinterpret_cast<const float4*>(src + 4);
-                        s0.x += a.x; s0.y += a.y; s0.z += a.z; s0.w += a.w;
-                        s1.x += b4.x; s1.y += b4.y; s1.z += b4.z; s1.w += b4.w;
+                        const uint4 u = *reinterpret_cast<const uint4*>(obuf + ((p * rows_per + rl) * D + col) * 2);
+                        const float2 a = unpack_bf16(u.x), b2 = unpack_bf16(u.y), c2 = unpack_bf16(u.z), d2 = unpack_bf16(u.w);
+                        s0.x += a.x; s0.y += a.y; s0.z += b2.x; s0.w += b2.y;
+                        s1.x += c2.x; s1.y += c2.y; s1.z += d2.x; s1.w += d2.y;
                     }
                     if (row < valid)
                         *reinterpret_cast<uint4*>(out_n + (tok0 + row) * D + col) =
