@@ -8,10 +8,11 @@
 //     columns = all 512);
 //   * S > 64: the tables of this estimator are independent (out = sum over tables), so bucket
 //     group g (64 buckets) is owned by CTA g of a thread-block cluster of G CTAs working on the
-//     same (stream, tile).  Each CTA keeps its own state slice and forms a partial output; row r of
-//     a chunk belongs to CTA r % G: every CTA stores its partial rows into the owner's slot buffer
-//     through distributed shared memory (posted remote stores), the owner adds the G slots in
-//     group order (deterministic) and writes the rows once.  Cross-CTA hand-offs are mbarriers
+//     same (stream, tile).  Each CTA keeps its own state slice and forms a partial output; CTA j
+//     owns the output columns [j d_k/G, (j+1) d_k/G): every CTA stores its partial values (bf16)
+//     into the owner's slot buffer through distributed shared memory (posted remote stores, one
+//     owner per warp-wide store), the owner adds the G slots in group order (deterministic, fp32)
+//     and writes its columns once.  Cross-CTA hand-offs are mbarriers
 //     with remote arrivals; no TMA multicast anywhere.
 // Reference semantics: src/race_baseline.py:45-51 (docs/causal_v2_design.md:70-77 for the chunk
 // form).  The multi-head configuration N=256 streams, T=262144, d_k=128, L=8, K=6 is G = 8, D = 128.
@@ -42,8 +43,9 @@ struct Lay {
     static constexpr int oBt = oWt + 2 * kTileP;        // [2]
     static constexpr int oTril = oBt + 2 * kTileV;
     static constexpr int oAcar = oTril + kTileP;        // [2][64] fp32
-    static constexpr int oObuf = oAcar + 2 * 64 * 4;    // [2][64][D] bf16 partial outputs (clusters)
-    static constexpr int oBars = oObuf + 2 * C * D * 2;
+    static constexpr int oObuf = oAcar + 2 * 64 * 4;    // [2][G sources][64][D/G] bf16 partial outputs received
+    static constexpr int oOst = oObuf + 2 * C * D * 2;  // [2][G owners][64][D/G] bf16 partial outputs to send
+    static constexpr int oBars = oOst + 2 * C * D * 2;
     static constexpr int kNumBars = 36;
     static constexpr int oMisc = oBars + kNumBars * 8;
     static constexpr int kSmem = oMisc + 16 + 1024;
@@ -82,6 +84,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta)
     uint32_t r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
     return r;
+}
+// bulk copy own shared memory -> shared memory of a CTA of the cluster; completes (bytes) on that CTA's mbarrier
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes, uint32_t bar_cluster) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster) : "memory");
 }
 __device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
@@ -183,7 +190,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             mbar_init(cx.bar(bBaccFree + i), 4);
             mbar_init(cx.bar(bBtReady + i), 4);
             mbar_init(cx.bar(bDrain + i), 1);
-            mbar_init(cx.bar(bObufReady + i), 4 * G);
+            mbar_init(cx.bar(bObufReady + i), 1);
             mbar_init(cx.bar(bObufFree + i), G);
         }
         mbar_init(cx.bar(bBupdDone), 1);
@@ -325,56 +332,66 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                     }
                 }
             } else {
-                // Partial output of this bucket group: row r of the chunk belongs to CTA r % G of the
-                // cluster.  Every CTA stores its rows straight into the owner's slot buffer
-                // [source group][row / G][D] (posted remote stores), then tells the owner; the owner
-                // adds the G slots in group order from its own shared memory and writes the rows.
+                // Partial output of this bucket group: CTA j of the cluster owns the columns
+                // [j D/G, (j+1) D/G) of the chunk's rows.  Every CTA lays its partial values out per owner
+                // in its own shared memory (bf16) and sends each owner its block with one bulk copy through
+                // distributed shared memory, which completes on the owner's mbarrier; the owner adds the G
+                // blocks in group order and writes its columns.  The owners' "consumed" arrivals (below)
+                // also tell this CTA that its previous copies have left the staging buffer.
                 if (uses >= 1 && !(ok = wait_bar_cluster_warp(cx, bObufFree + wg, (uint32_t)((uses - 1) & 1), 108))) break;
                 RACE_TRACE(wg, c >> 1, 3);
+                const int cpo = D / G;   // columns per owner
                 {
-                    const int owner = rbase % G;                       // rbase and rbase + 8 share it
-                    const uint32_t slot = map_to_cta(obuf_u32 + (uint32_t)(g * (C / G) * D) * 2, (uint32_t)owner);
+                    uint8_t* ost = cx.sm + Ly::oOst + wg * C * D * 2;
 #pragma unroll
                     for (int dh = 0; dh < DH; ++dh) {
                         tc_fence_after();
                         tmem_ld64(lane_base + tmO(wg) + dh * 64, v);
                         tc_fence_before();
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            // bf16 partials; neighbouring lanes of a quad swap one pair so that every lane
-                            // owns four consecutive columns: half as many remote stores, 8 bytes each
-                            const uint32_t ra = slot + (uint32_t)(((rbase + 8 * h) / G) * D + dh * 64 + 4 * (q >> 1) + 8 * (q & 1)) * 2;
+                        for (int x = 0; x < 8; x += 2) {
+                            // neighbouring lanes of a quad swap one pair so that every lane owns four
+                            // consecutive columns: 8-byte stores
+                            const int col0 = dh * 64 + 8 * (x + (q & 1)) + 4 * (q >> 1);
+                            const int owner = col0 / cpo;
+                            uint8_t* blk = ost + ((owner * C) * cpo + (col0 - owner * cpo)) * 2;
 #pragma unroll
-                            for (int x = 0; x < 8; x += 2) {
+                            for (int h = 0; h < 2; ++h) {
                                 const uint32_t p0 = pack_bf16(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
                                 const uint32_t p1 = pack_bf16(v[4 * x + 4 + 2 * h], v[4 * x + 4 + 2 * h + 1]);
                                 const uint32_t got = __shfl_xor_sync(0xffffffffu, (q & 1) ? p0 : p1, 1);
-                                const uint32_t lo = (q & 1) ? got : p0, hi = (q & 1) ? p1 : got;
-                                asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};"
-                                             ::"r"(ra + 16 * x), "r"(lo), "r"(hi) : "memory");
+                                *reinterpret_cast<uint2*>(blk + (rbase + 8 * h) * cpo * 2) =
+                                    (q & 1) ? make_uint2(got, p1) : make_uint2(p0, got);
                             }
                         }
                     }
                 }
-                __syncwarp();
-                // one release-arrival per owner this warp wrote to (its rows cover min(G, 8) owners)
-                if (lane < G && lane < 8) remote_arrive(map_to_cta(cx.bar(bObufReady + wg), (uint32_t)lane));
+                fence_proxy_async();
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+                if (w == 0 && lane == 0) {
+                    const uint32_t blk_bytes = (uint32_t)(C * cpo * 2);
+                    mbar_arrive_expect_tx(cx.bar(bObufReady + wg), (uint32_t)(C * D * 2));   // G blocks will land here
+                    const uint32_t src = cx.sm_u32 + Ly::oOst + wg * C * D * 2;
+                    for (int j = 0; j < G; ++j)
+                        bulk_copy_to_cta(map_to_cta(obuf_u32 + (uint32_t)g * blk_bytes, (uint32_t)j),
+                                         src + (uint32_t)j * blk_bytes, blk_bytes,
+                                         map_to_cta(cx.bar(bObufReady + wg), (uint32_t)j));
+                }
                 RACE_TRACE(wg, c >> 1, 4);
                 if (!(ok = wait_bar_cluster_warp(cx, bObufReady + wg, (uint32_t)(uses & 1), 109))) break;
                 RACE_TRACE(wg, c >> 1, 5);
-                const int rows_per = C / G;
-                for (int item = wtid; item < rows_per * (D / 8); item += 128) {
-                    const int rl = item / (D / 8), col = (item % (D / 8)) * 8;
-                    const int row = g + G * rl;
+                const int blocks = cpo / 8;   // 8-column blocks per row of this owner
+                for (int item = wtid; item < C * blocks; item += 128) {
+                    const int row = item / blocks, cb = item % blocks;
                     float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
                     for (int p = 0; p < G; ++p) {
-                        const uint4 u = *reinterpret_cast<const uint4*>(obuf + ((p * rows_per + rl) * D + col) * 2);
+                        const uint4 u = *reinterpret_cast<const uint4*>(obuf + ((p * C + row) * cpo + cb * 8) * 2);
                         const float2 a = unpack_bf16(u.x), b2 = unpack_bf16(u.y), c2 = unpack_bf16(u.z), d2 = unpack_bf16(u.w);
                         s0.x += a.x; s0.y += a.y; s0.z += b2.x; s0.w += b2.y;
                         s1.x += c2.x; s1.y += c2.y; s1.z += d2.x; s1.w += d2.y;
                     }
                     if (row < valid)
-                        *reinterpret_cast<uint4*>(out_n + (tok0 + row) * D + col) =
+                        *reinterpret_cast<uint4*>(out_n + (tok0 + row) * D + g * cpo + cb * 8) =
                             make_uint4(pack_bf16(s0.x, s0.y), pack_bf16(s0.z, s0.w), pack_bf16(s1.x, s1.y),
                                        pack_bf16(s1.z, s1.w));
                 }
