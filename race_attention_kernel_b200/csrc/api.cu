@@ -205,6 +205,8 @@ int race_b200_noncausal_fwd(const void* probs_q, const void* probs_k, const void
     rc = race_b200_tile_totals(probs_k, v, totals, workspace, workspace_bytes, shape, 0,
                                RACE_VARIANT_AUTO, stream, nullptr);
     if (rc != RACE_OK) return rc;
+    if (noncausal_tensor_supported(dm, shape->dtype))
+        return (int)noncausal_query_tensor(probs_q, totals, out, dm, shape->dtype, sm_count(), st);
     return (int)noncausal_query(probs_q, totals, out, dm, shape->dtype, sm_count(), st);
 }
 
@@ -246,6 +248,9 @@ int race_b200_noncausal_bwd(const void* probs_q, const void* probs_k, const void
     if (rc != RACE_OK) return rc;
     cudaError_t e = noncausal_state_grads(totals, dE_state, grads, dm, st);
     if (e != cudaSuccess) return (int)e;
+    if (noncausal_tensor_supported(dm, shape->dtype))
+        return (int)noncausal_token_grads_tensor(probs_k, v, d_out, totals, grads, d_probs_q, d_probs_k, d_v,
+                                                 dm, shape->dtype, sm_count(), st);
     return (int)noncausal_token_grads(probs_k, v, d_out, totals, grads, d_probs_q, d_probs_k, d_v, dm,
                                       shape->dtype, sm_count(), st);
 }

@@ -34,6 +34,14 @@ cudaError_t noncausal_token_grads(const void* pk, const void* v, const void* dou
                                   const float* grads, void* dpq, void* dpk, void* dv, const Dims& dm,
                                   int dtype, int sm_count, cudaStream_t stream);
 
+// tensor-core token kernels of the non-causal path (noncausal_tc.cu): S = 64, d_k = 64
+bool noncausal_tensor_supported(const Dims& dm, int dtype);
+cudaError_t noncausal_query_tensor(const void* pq, const float* totals, void* out, const Dims& dm, int dtype,
+                                   int sm_count, cudaStream_t stream);
+cudaError_t noncausal_token_grads_tensor(const void* pk, const void* v, const void* dout, const float* totals,
+                                         const float* grads, void* dpq, void* dpk, void* dv, const Dims& dm,
+                                         int dtype, int sm_count, cudaStream_t stream);
+
 // ---- bucket-probability producer (bucket_probs.cu) --------------------------------------------
 cudaError_t bucket_probs(const void* x, const float* planes, void* probs, int64_t rows, int d, int L,
                          int K, int dtype_x, int dtype_probs, cudaStream_t stream);
