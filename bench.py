@@ -377,9 +377,9 @@ def main():
     except Exception:
         pass
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
-    # DRAM traffic of one forward from the ncu capture in profiles/ (T=131072: output pass 1052.4 MB,
-    # totals pass 546.9 MB, scan 17 MB per 1073.7 MB of algorithmic bytes), scaled by tokens
-    traffic = alg_bytes * (1052.4 + 546.9 + 17.0) / 1073.7 if (variant == "tensor" and args.dtype == "f32") else None
+    # DRAM traffic of one forward from the ncu capture in profiles/ (T=131072: output pass 1053.7 MB,
+    # totals pass 547.9 MB, scan 17 MB per 1073.7 MB of algorithmic bytes), scaled by tokens
+    traffic = alg_bytes * (1053.7 + 547.9 + 17.0) / 1073.7 if (variant == "tensor" and args.dtype == "f32") else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                 "kernel": "causal forward (tile_totals_tc + tile_scan + causal_out_tc of one step)",
