@@ -128,23 +128,24 @@ tile_totals_simt(const Tin* __restrict__ pk, const Tin* __restrict__ v, float* _
 }
 
 // ------------------------------------------------------------------------------------------
-// K2: exclusive scan over tiles, one thread per state float, 8 loads in flight
+// K2: exclusive scan over tiles, one thread per state float, 32 loads in flight
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 tile_scan(float* __restrict__ ws, const float* __restrict__ carry_in, float* __restrict__ state_out,
           int64_t tiles, int state_floats, int write_prefix) {
+    constexpr int kInFlight = 32;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= state_floats) return;
     const int64_t n = blockIdx.y;
     float run = carry_in ? carry_in[n * state_floats + i] : 0.f;
     float* p = ws + n * tiles * state_floats + i;
     int64_t t = 0;
-    for (; t + 8 <= tiles; t += 8) {
-        float x[8];
+    for (; t + kInFlight <= tiles; t += kInFlight) {
+        float x[kInFlight];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = p[(t + j) * state_floats];
+        for (int j = 0; j < kInFlight; ++j) x[j] = p[(t + j) * state_floats];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < kInFlight; ++j) {
             if (write_prefix) p[(t + j) * state_floats] = run;
             run += x[j];
         }
@@ -384,8 +385,8 @@ cudaError_t launch_simt(const Tin* pq, const Tin* pk, const Tin* v, Tin* out, co
         if (err != cudaSuccess) return err;
     }
 
-    dim3 sgrid((unsigned)((sf + 255) / 256), (unsigned)dm.N);
-    tile_scan<<<sgrid, 256, 0, stream>>>(ws, carry_in, state_out, tiles, sf, totals_only ? 0 : 1);
+    dim3 sgrid((unsigned)((sf + 127) / 128), (unsigned)dm.N);
+    tile_scan<<<sgrid, 128, 0, stream>>>(ws, carry_in, state_out, tiles, sf, totals_only ? 0 : 1);
     err = cudaGetLastError();
     if (err != cudaSuccess || totals_only || skip_output) return err;
 
@@ -434,8 +435,8 @@ cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out
                               int tile_tokens, cudaStream_t stream, bool write_prefix) {
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const int sf = state_floats_per_stream(dm.S, dm.D);
-    dim3 sgrid((unsigned)((sf + 255) / 256), (unsigned)dm.N);
-    tile_scan<<<sgrid, 256, 0, stream>>>(ws, carry_in, state_out, tiles, sf, write_prefix ? 1 : 0);
+    dim3 sgrid((unsigned)((sf + 127) / 128), (unsigned)dm.N);
+    tile_scan<<<sgrid, 128, 0, stream>>>(ws, carry_in, state_out, tiles, sf, write_prefix ? 1 : 0);
     return cudaGetLastError();
 }
 
