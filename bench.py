@@ -48,7 +48,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c4", "c5"],
+    ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c4", "c5", "operator"],
                     help="c2 (default): the contract line; the others print extra measurement lines")
     return ap.parse_args()
 
@@ -274,6 +274,24 @@ def extra_workloads(args):
                               "fwd_bwd_frac": round((bf + bb) / ms_fb / 1e6 / peak, 4),
                               "Mtok_s_fwd_bwd": round(N * T / ms_fb / 1e3, 1)}), flush=True)
             del pQ, pK, V, dO
+    elif args.workload == "operator":
+        # the drop-in operator end to end on the device: BatchedACE.forward(K, V, Q) = stream flattening +
+        # bucket-probability producer (probabilities written to HBM) + causal prefix kernels; fp32,
+        # M=1, B=1, H=8, d_k=64, K=4, L=4 (the reference CPU configuration at longer T)
+        M, B, H, dk, K, L = 1, 1, 8, 64, 4, 4
+        for T in (4096, 131072, 1048576):
+            torch.manual_seed(1234)
+            ace = rk.BatchedACE(dk, K, L, M, device=dev)
+            Kh, Vh, Qh = (torch.randn(M, B, T, H, dk, device=dev, generator=g) for _ in range(3))
+            with torch.no_grad():
+                ms = _time_ms(lambda: ace(Kh, Vh, Qh), 3, 10)
+            n_tok = M * B * H * T
+            print(json.dumps({"workload": "operator", "M,B,H": [M, B, H], "T": T, "ms": round(ms, 4),
+                              "Mtok_s": round(n_tok / ms / 1e3, 1),
+                              "qkvo_GB_s": round(n_tok * 4 * dk * 4 / ms / 1e6, 1),
+                              "peak_GiB": round(torch.cuda.max_memory_allocated() / 2**30, 2)}), flush=True)
+            del Kh, Vh, Qh
+            torch.cuda.empty_cache()
 
 
 def main():

@@ -147,12 +147,22 @@ int race_b200_noncausal_bwd(const void* probs_q, const void* probs_k, const void
 /*
  * Bucket-probability producer (src/race_baseline.py:41-44):
  *   probs[row, l, :] = softmax_r( (tanh(x[row] . planes[l,k]) / sqrt(d_k)) . corner_r ),
- * corner r has +1 on plane k iff bit (K-1-k) of r is set.  x [rows, d_k] (dtype_x),
+ * corner r has +1 on plane k iff bit (K-1-k) of r is set.  x [rows, d_k] (dtype_x; d_k a power of two, 4..256),
  * planes [L*K, d_k] fp32 (row-major: planes_T transposed), probs [rows, L, 2^K] (dtype_probs).
  */
 int race_b200_bucket_probs(const void* x, const float* planes, void* probs, int64_t rows,
                            int32_t d_k, int32_t n_tables, int32_t n_bits, int32_t dtype_x,
                            int32_t dtype_probs, void* stream);
+
+/*
+ * The same producer reading the operator's own layout: x [outer, seq_len, heads, d_k] (outer = M*B of
+ * the reference's [M,B,T,H,d_k]) -> probs [outer*heads, seq_len, L, 2^K], i.e. the stream flattening
+ * of src/race_baseline.py:35-40 (permute + contiguous) happens inside the read and the flattened
+ * copy of x is never written.
+ */
+int race_b200_bucket_probs_streams(const void* x, const float* planes, void* probs, int64_t outer,
+                                   int64_t seq_len, int32_t heads, int32_t d_k, int32_t n_tables,
+                                   int32_t n_bits, int32_t dtype_x, int32_t dtype_probs, void* stream);
 
 /*
  * Host-buffer causal forward: same arithmetic as race_b200_causal_fwd with every tensor in

@@ -6,8 +6,9 @@ Public surface:
   race_tile_totals                per-stream totals (A, B) of a token range
   race_noncausal                  non-causal forward with autograd
   bucket_probs                    bucket-probability producer
+  bucket_probs_streams            the producer reading [M,B,T,H,d_k] directly (flattening fused)
 """
 from .operator import BatchedACE  # noqa: F401
-from .ops import (bucket_probs, is_supported, pack_state, race_causal_prefix,  # noqa: F401
+from .ops import (bucket_probs, bucket_probs_streams, is_supported, pack_state, race_causal_prefix,  # noqa: F401
                   race_causal_prefix_host, race_causal_prefix_static, race_noncausal, race_tile_totals, select_tile_tokens,
                   unpack_state)

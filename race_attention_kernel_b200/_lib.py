@@ -23,7 +23,7 @@ EXPORTS = [
     "race_b200_causal_fwd", "race_b200_tile_totals", "race_b200_causal_fwd_resume",
     "race_b200_noncausal_fwd",
     "race_b200_noncausal_bwd_workspace_bytes", "race_b200_noncausal_bwd",
-    "race_b200_bucket_probs", "race_b200_causal_fwd_host",
+    "race_b200_bucket_probs", "race_b200_bucket_probs_streams", "race_b200_causal_fwd_host",
     "race_b200_static_scratch_bytes", "race_b200_causal_fwd_static",
 ]
 
@@ -71,6 +71,8 @@ def lib() -> ctypes.CDLL:
     L.race_b200_noncausal_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, shp, vp]
     L.race_b200_bucket_probs.restype = i32
     L.race_b200_bucket_probs.argtypes = [vp, vp, vp, i64, i32, i32, i32, i32, i32, vp]
+    L.race_b200_bucket_probs_streams.restype = i32
+    L.race_b200_bucket_probs_streams.argtypes = [vp, vp, vp, i64, i64, i32, i32, i32, i32, i32, i32, vp]
     L.race_b200_causal_fwd_host.restype = i32
     L.race_b200_causal_fwd_host.argtypes = [vp, vp, vp, vp, vp, vp, shp, i64, i32, i32]
     L.race_b200_static_scratch_bytes.restype = sz

@@ -70,7 +70,7 @@ size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile) {
 
 extern "C" {
 
-int race_b200_version(void) { return 1001; }
+int race_b200_version(void) { return 1002; }
 
 const char* race_b200_error_string(int code) {
     switch (code) {
@@ -255,19 +255,36 @@ int race_b200_noncausal_bwd(const void* probs_q, const void* probs_k, const void
                                       shape->dtype, sm_count(), st);
 }
 
-int race_b200_bucket_probs(const void* x, const float* planes, void* probs, int64_t rows,
-                           int32_t d_k, int32_t n_tables, int32_t n_bits, int32_t dtype_x,
-                           int32_t dtype_probs, void* stream) {
-    if (rows < 0 || d_k <= 0 || d_k > 256 || n_tables <= 0 || n_bits < 1 || n_bits > 6 ||
-        n_tables * n_bits > 64)
+namespace {
+int probs_entry(const void* x, const float* planes, void* probs, int64_t outer, int64_t seq_len, int32_t heads,
+                int32_t d_k, int32_t n_tables, int32_t n_bits, int32_t dtype_x, int32_t dtype_probs,
+                void* stream) {
+    if (outer < 0 || seq_len < 0 || heads < 1 || d_k < 4 || d_k > 256 || (d_k & (d_k - 1)) || n_tables <= 0 ||
+        n_bits < 1 || n_bits > 6 || n_tables * n_bits > 64)
         return RACE_ERR_SHAPE;
     if ((dtype_x != RACE_DTYPE_F32 && dtype_x != RACE_DTYPE_BF16) ||
         (dtype_probs != RACE_DTYPE_F32 && dtype_probs != RACE_DTYPE_BF16))
         return RACE_ERR_SHAPE;
+    const int64_t rows = outer * heads * seq_len;
     if (rows == 0) return RACE_OK;
     if (!x || !planes || !probs) return RACE_ERR_NULL;
-    return (int)bucket_probs(x, planes, probs, rows, d_k, n_tables, n_bits, dtype_x, dtype_probs,
+    if (!aligned16(x) || !aligned16(planes) || !aligned16(probs)) return RACE_ERR_ALIGN;
+    return (int)bucket_probs(x, planes, probs, rows, seq_len, heads, d_k, n_tables, n_bits, dtype_x, dtype_probs,
                              (cudaStream_t)stream);
+}
+}  // namespace
+
+int race_b200_bucket_probs(const void* x, const float* planes, void* probs, int64_t rows,
+                           int32_t d_k, int32_t n_tables, int32_t n_bits, int32_t dtype_x,
+                           int32_t dtype_probs, void* stream) {
+    return probs_entry(x, planes, probs, 1, rows, 1, d_k, n_tables, n_bits, dtype_x, dtype_probs, stream);
+}
+
+int race_b200_bucket_probs_streams(const void* x, const float* planes, void* probs, int64_t outer,
+                                   int64_t seq_len, int32_t heads, int32_t d_k, int32_t n_tables,
+                                   int32_t n_bits, int32_t dtype_x, int32_t dtype_probs, void* stream) {
+    return probs_entry(x, planes, probs, outer, seq_len, heads, d_k, n_tables, n_bits, dtype_x, dtype_probs,
+                       stream);
 }
 
 }  // extern "C"

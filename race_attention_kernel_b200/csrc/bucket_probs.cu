@@ -5,56 +5,149 @@
 // prod_k sigmoid(+-2 th[l,k]) because sum_r exp(z_r) = prod_k (e^th_k + e^-th_k); the kernel
 // evaluates that product (the reference checks the same identity numerically,
 // src/verify_factorization.py:42-57).
+//
+// The stream flattening of the operator ([M,B,T,H,d_k] -> [N,T,d_k], src/race_baseline.py:35-40)
+// can be fused into the read: with heads = H the input row of output row (n = mb*H + h, t) is
+// ((mb*T + t)*H + h)*d_k; heads = 1 is the plain contiguous case.
+//
+// A streaming kernel: one row per thread, 128 rows per CTA (several CTAs per SM overlap their phases).  The x tile is read with coalesced
+// 16-byte loads into shared memory, each thread then keeps its row in registers (d_k <= 64) and
+// runs the L*K dot products against plane values broadcast from shared memory with 16-byte loads
+// (4 FMAs per load), the probabilities of a row go back through the same shared-memory tile and
+// are written with coalesced 16-byte stores.  Algorithmic bytes per row: d_k*elt in, L*R*elt out.
 #include "common.cuh"
 #include "launch.h"
 
 namespace race {
 namespace {
 
-constexpr int RB = 64;  // rows per CTA
+constexpr int RB = 128;  // rows per CTA = threads per CTA
 
-template <typename T> __device__ __forceinline__ float to_float(T x);
-template <> __device__ __forceinline__ float to_float<float>(float x) { return x; }
-template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = __ldcs(reinterpret_cast<const uint2*>(p));
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a);
+        u.y = *reinterpret_cast<uint32_t*>(&b);
+        __stcs(reinterpret_cast<uint2*>(p), u);
+    }
+};
 
-template <typename Tx, typename Tp, int K>
-__global__ void __launch_bounds__(256)
+// tanh(a) = sign(a) (1 - e)/(1 + e), e = exp(-2|a|): absolute error ~1e-7, which is what the logits
+// need (they are tanh/sqrt(d_k), and the projections of unit-variance rows mostly saturate)
+__device__ __forceinline__ float fast_tanh(float a) {
+    const float e = __expf(-2.f * fabsf(a));
+    return copysignf(__fdividef(1.f - e, 1.f + e), a);
+}
+
+// kXReg: d <= 64, the thread's row lives in registers; the tile is then free for the outputs, which go
+// through it (stage_out) when a row of L*R values fits, and straight from registers otherwise
+template <typename Tx, typename Tp, int K, bool kXReg>
+__global__ void __launch_bounds__(RB)
 bucket_probs_kernel(const Tx* __restrict__ x, const float* __restrict__ planes, Tp* __restrict__ probs,
-                    int64_t rows, int d, int L) {
+                    int64_t rows, int64_t T, int heads, int d, int L, int stage_out) {
     constexpr int R = 1 << K;
     extern __shared__ __align__(16) float smem[];
-    const int LK = L * K;
-    float* sx = smem;                     // [RB][d+1]
-    float* sp = sx + RB * (d + 1);        // [LK][d]
-    float* sth = sp + LK * d;             // [RB][LK+1]
+    const int LK = L * K, LR = L * R;
+    const int ldx = d + 4, ldo = LR + 4;                       // row strides, = 4 (mod 32): no bank conflicts
+    float* sp = smem;                                          // [LK][d]
+    float* sx = sp + LK * d;                                   // [RB][ldx]
+    float* so = sx;                                            // [RB][ldo], only with stage_out
     const int tid = threadIdx.x;
     const int64_t row0 = (int64_t)blockIdx.x * RB;
     const int valid = (int)min((int64_t)RB, rows - row0);
 
-    for (int i = tid; i < LK * d; i += 256) sp[i] = planes[i];
-    for (int i = tid; i < RB * d; i += 256) {
-        const int r = i / d, c = i - r * d;
-        sx[r * (d + 1) + c] = r < valid ? to_float<Tx>(x[(row0 + r) * d + c]) : 0.f;
+    for (int i = tid; i < LK * d / 4; i += RB)
+        reinterpret_cast<float4*>(sp)[i] = reinterpret_cast<const float4*>(planes)[i];
+    // element offset of every row of the tile in x (the flattening, if any, happens here)
+    int64_t* srow = reinterpret_cast<int64_t*>(sx + RB * (kXReg && stage_out && LR > d ? ldo : ldx));
+    if (tid < valid) {
+        const int64_t g = row0 + tid;                          // output row: stream n, token t
+        const int64_t n = g / T, t = g - n * T;
+        const int64_t mb = n / heads, h = n - mb * heads;
+        srow[tid] = ((mb * T + t) * heads + h) * d;
     }
     __syncthreads();
     {
-        const int r = tid & (RB - 1);
-        const float inv_scale = rsqrtf((float)d);
-        for (int p = tid / RB; p < LK; p += 256 / RB) {
-            float acc = 0.f;
-            for (int c = 0; c < d; ++c) acc = fmaf(sx[r * (d + 1) + c], sp[p * d + c], acc);
-            sth[r * (LK + 1) + p] = tanhf(acc) * inv_scale;
+        // eight 16-byte loads in flight per thread; consecutive threads read consecutive 16 bytes of a row
+        const int d4 = d >> 2;                                 // 16-byte items per row; divides RB
+        const int c = (tid % d4) * 4, r0 = tid / d4, rstep = RB / d4;
+        for (int u0 = 0; u0 < d4; u0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int r = r0 + (u0 + u) * rstep;
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (u0 + u < d4 && r < valid) v[u] = Vec4<Tx>::load(x + srow[r] + c);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int r = r0 + (u0 + u) * rstep;
+                if (u0 + u < d4) *reinterpret_cast<float4*>(sx + r * ldx + c) = v[u];
+            }
         }
     }
     __syncthreads();
-    for (int item = tid; item < RB * L; item += 256) {
-        const int r = item / L, l = item - r * L;
-        if (r >= valid) continue;
+
+    const float* xrow = sx + tid * ldx;
+    float xr[kXReg ? 64 : 4];
+    if (kXReg) {
+#pragma unroll
+        for (int c = 0; c < 64; c += 4) {
+            const float4 v = c < d ? *reinterpret_cast<const float4*>(xrow + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            xr[c] = v.x; xr[c + 1] = v.y; xr[c + 2] = v.z; xr[c + 3] = v.w;
+        }
+        __syncthreads();   // every row is in registers: the tile may take the outputs
+    }
+    const float inv_scale = rsqrtf((float)d);
+    float* orow = so + tid * ldo;
+    for (int l = 0; l < L; ++l) {
+        float acc[K];
+#pragma unroll
+        for (int k = 0; k < K; ++k) acc[k] = 0.f;
+        if (kXReg) {
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+                if (c < d) {
+#pragma unroll
+                    for (int k = 0; k < K; ++k) {
+                        const float4 p = *reinterpret_cast<const float4*>(sp + (l * K + k) * d + c);
+                        acc[k] = fmaf(xr[c], p.x, acc[k]);
+                        acc[k] = fmaf(xr[c + 1], p.y, acc[k]);
+                        acc[k] = fmaf(xr[c + 2], p.z, acc[k]);
+                        acc[k] = fmaf(xr[c + 3], p.w, acc[k]);
+                    }
+                }
+            }
+        } else {
+            for (int c = 0; c < d; c += 4) {
+                const float4 xv = *reinterpret_cast<const float4*>(xrow + c);
+#pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    const float4 p = *reinterpret_cast<const float4*>(sp + (l * K + k) * d + c);
+                    acc[k] = fmaf(xv.x, p.x, acc[k]);
+                    acc[k] = fmaf(xv.y, p.y, acc[k]);
+                    acc[k] = fmaf(xv.z, p.z, acc[k]);
+                    acc[k] = fmaf(xv.w, p.w, acc[k]);
+                }
+            }
+        }
         float vals[R];
         vals[0] = 1.f;
 #pragma unroll
         for (int k = 0; k < K; ++k) {
-            const float th = sth[r * (LK + 1) + l * K + k];
+            const float th = fast_tanh(acc[k]) * inv_scale;
             const float e = __expf(-2.f * th);            // |th| <= 1/sqrt(d): no overflow
             const float p1 = 1.f / (1.f + e);             // sigmoid(+2 th)
             const float p0 = e * p1;                      // sigmoid(-2 th)
@@ -65,46 +158,96 @@ bucket_probs_kernel(const Tx* __restrict__ x, const float* __restrict__ planes, 
                 vals[2 * i + 1] = b * p1;
             }
         }
-        Tp* dst = probs + ((row0 + r) * L + l) * (int64_t)R;
+        if (stage_out) {
+            if (R >= 4) {
 #pragma unroll
-        for (int i = 0; i < R; ++i) dst[i] = (Tp)vals[i];
+                for (int i = 0; i < R; i += 4)
+                    *reinterpret_cast<float4*>(orow + l * R + i) =
+                        make_float4(vals[i], vals[(i + 1) % R], vals[(i + 2) % R], vals[(i + 3) % R]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < R; ++i) orow[l * R + i] = vals[i];
+            }
+        } else if (tid < valid) {
+            Tp* dst = probs + ((row0 + tid) * L + l) * (int64_t)R;
+            if (R >= 4) {
+#pragma unroll
+                for (int i = 0; i < R; i += 4)
+                    Vec4<Tp>::store(dst + i, make_float4(vals[i], vals[(i + 1) % R], vals[(i + 2) % R], vals[(i + 3) % R]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < R; ++i) dst[i] = (Tp)vals[i];
+            }
+        }
+    }
+    if (!stage_out) return;
+    __syncthreads();
+    if ((LR & 3) == 0) {
+        const int o4 = LR >> 2;
+        for (int i = tid; i < RB * o4; i += RB) {
+            const int r = i / o4, c = (i - r * o4) * 4;
+            if (r < valid)
+                Vec4<Tp>::store(probs + (row0 + r) * LR + c, *reinterpret_cast<const float4*>(so + r * ldo + c));
+        }
+    } else {   // L*R = 2 (one table, one plane) or another count not divisible by 4
+        for (int i = tid; i < RB * LR; i += RB) {
+            const int r = i / LR, c = i - r * LR;
+            if (r < valid) probs[(row0 + r) * LR + c] = (Tp)so[r * ldo + c];
+        }
     }
 }
 
-template <typename Tx, typename Tp>
-cudaError_t launch_probs(const void* x, const float* planes, void* probs, int64_t rows, int d, int L,
-                         int K, cudaStream_t stream) {
-    const size_t smem = (size_t)(RB * (d + 1) + L * K * d + RB * (L * K + 1)) * sizeof(float);
+template <typename Tx, typename Tp, int K>
+cudaError_t launch_probs_k(const void* x, const float* planes, void* probs, int64_t rows, int64_t T, int heads,
+                           int d, int L, cudaStream_t stream) {
+    const int LR = L << K;
+    const bool xreg = d <= 64;
+    const int stage_out = (xreg && LR <= 128) ? 1 : 0;
+    const size_t tile = (size_t)RB * (size_t)((stage_out && LR > d ? LR : d) + 4);
+    const size_t smem = ((size_t)L * K * d + tile) * sizeof(float) + RB * sizeof(int64_t);
+    if (smem > 227 * 1024) return cudaErrorInvalidValue;
     const unsigned blocks = (unsigned)((rows + RB - 1) / RB);
-#define RACE_PROBS_CASE(K_)                                                                        \
-    case K_: {                                                                                     \
-        auto kern = bucket_probs_kernel<Tx, Tp, K_>;                                               \
-        cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                                               (int)smem);                                         \
-        if (err != cudaSuccess) return err;                                                        \
-        kern<<<blocks, 256, smem, stream>>>((const Tx*)x, planes, (Tp*)probs, rows, d, L);         \
-        return cudaGetLastError();                                                                 \
+    cudaError_t err;
+    if (xreg) {
+        auto kern = bucket_probs_kernel<Tx, Tp, K, true>;
+        err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return err;
+        kern<<<blocks, RB, smem, stream>>>((const Tx*)x, planes, (Tp*)probs, rows, T, heads, d, L, stage_out);
+    } else {
+        auto kern = bucket_probs_kernel<Tx, Tp, K, false>;
+        err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return err;
+        kern<<<blocks, RB, smem, stream>>>((const Tx*)x, planes, (Tp*)probs, rows, T, heads, d, L, stage_out);
     }
+    return cudaGetLastError();
+}
+
+template <typename Tx, typename Tp>
+cudaError_t launch_probs(const void* x, const float* planes, void* probs, int64_t rows, int64_t T, int heads,
+                         int d, int L, int K, cudaStream_t stream) {
     switch (K) {
-        RACE_PROBS_CASE(1) RACE_PROBS_CASE(2) RACE_PROBS_CASE(3)
-        RACE_PROBS_CASE(4) RACE_PROBS_CASE(5) RACE_PROBS_CASE(6)
+        case 1: return launch_probs_k<Tx, Tp, 1>(x, planes, probs, rows, T, heads, d, L, stream);
+        case 2: return launch_probs_k<Tx, Tp, 2>(x, planes, probs, rows, T, heads, d, L, stream);
+        case 3: return launch_probs_k<Tx, Tp, 3>(x, planes, probs, rows, T, heads, d, L, stream);
+        case 4: return launch_probs_k<Tx, Tp, 4>(x, planes, probs, rows, T, heads, d, L, stream);
+        case 5: return launch_probs_k<Tx, Tp, 5>(x, planes, probs, rows, T, heads, d, L, stream);
+        case 6: return launch_probs_k<Tx, Tp, 6>(x, planes, probs, rows, T, heads, d, L, stream);
         default: return cudaErrorInvalidValue;
     }
-#undef RACE_PROBS_CASE
 }
 
 }  // namespace
 
-cudaError_t bucket_probs(const void* x, const float* planes, void* probs, int64_t rows, int d, int L,
-                         int K, int dtype_x, int dtype_probs, cudaStream_t stream) {
+cudaError_t bucket_probs(const void* x, const float* planes, void* probs, int64_t rows, int64_t T, int heads,
+                         int d, int L, int K, int dtype_x, int dtype_probs, cudaStream_t stream) {
     if (dtype_x == RACE_DTYPE_F32 && dtype_probs == RACE_DTYPE_F32)
-        return launch_probs<float, float>(x, planes, probs, rows, d, L, K, stream);
+        return launch_probs<float, float>(x, planes, probs, rows, T, heads, d, L, K, stream);
     if (dtype_x == RACE_DTYPE_BF16 && dtype_probs == RACE_DTYPE_BF16)
-        return launch_probs<__nv_bfloat16, __nv_bfloat16>(x, planes, probs, rows, d, L, K, stream);
+        return launch_probs<__nv_bfloat16, __nv_bfloat16>(x, planes, probs, rows, T, heads, d, L, K, stream);
     if (dtype_x == RACE_DTYPE_F32 && dtype_probs == RACE_DTYPE_BF16)
-        return launch_probs<float, __nv_bfloat16>(x, planes, probs, rows, d, L, K, stream);
+        return launch_probs<float, __nv_bfloat16>(x, planes, probs, rows, T, heads, d, L, K, stream);
     if (dtype_x == RACE_DTYPE_BF16 && dtype_probs == RACE_DTYPE_F32)
-        return launch_probs<__nv_bfloat16, float>(x, planes, probs, rows, d, L, K, stream);
+        return launch_probs<__nv_bfloat16, float>(x, planes, probs, rows, T, heads, d, L, K, stream);
     return cudaErrorInvalidValue;
 }
 

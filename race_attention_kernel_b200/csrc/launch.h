@@ -43,8 +43,9 @@ cudaError_t noncausal_token_grads_tensor(const void* pk, const void* v, const vo
                                          int dtype, int sm_count, cudaStream_t stream);
 
 // ---- bucket-probability producer (bucket_probs.cu) --------------------------------------------
-cudaError_t bucket_probs(const void* x, const float* planes, void* probs, int64_t rows, int d, int L,
-                         int K, int dtype_x, int dtype_probs, cudaStream_t stream);
+// x [outer, T, heads, d] -> probs [outer*heads, T, L, 2^K]; rows = outer*heads*T (heads = 1: plain rows)
+cudaError_t bucket_probs(const void* x, const float* planes, void* probs, int64_t rows, int64_t T, int heads,
+                         int d, int L, int K, int dtype_x, int dtype_probs, cudaStream_t stream);
 
 // ---- tcgen05 tensor-core causal path (causal_tc.cu) ------------------------------------------
 bool tensor_supported(const Dims& dm, int dtype);

@@ -57,9 +57,12 @@ class BatchedACE(nn.Module):
             Khf, Vhf, Qhf = (t.to(dev, non_blocking=True) for t in (Khf, Vhf, Qhf))
         if Khf.dtype not in (torch.float32, torch.bfloat16):
             raise RuntimeError("fp32 or bf16 inputs only")
-        K2, Q2, V2 = self._streams(Khf), self._streams(Qhf), self._streams(Vhf)
-        pK = self.bucket_probs(K2)
-        pQ = self.bucket_probs(Q2)
+        # K and Q are only read by the producer, which flattens [M,B,T,H,d_k] -> streams on the fly;
+        # V is consumed by the prefix kernels as [N,T,d_k] and is copied once
+        planes = self.planes_T.T.contiguous().float()
+        pK = ops.bucket_probs_streams(Khf.contiguous(), planes, self.L, self.K)
+        pQ = ops.bucket_probs_streams(Qhf.contiguous(), planes, self.L, self.K)
+        V2 = self._streams(Vhf)
         res = ops.race_causal_prefix(pQ, pK, V2, self.eps, carry_in=carry_in,
                                      return_state=return_state, variant=self.variant)
         out2 = res[0] if return_state else res

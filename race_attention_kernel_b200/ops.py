@@ -197,6 +197,27 @@ def bucket_probs(x: torch.Tensor, planes: torch.Tensor, L: int, K: int,
     return probs
 
 
+def bucket_probs_streams(x: torch.Tensor, planes: torch.Tensor, L: int, K: int,
+                         out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """x [M, B, T, H, d_k] (the operator's layout) -> probs [M*B*H, T, L, 2**K]: the stream flattening
+    of src/race_baseline.py:35-40 fused into the producer of :41-44; no flattened copy of x is made.
+
+    planes: fp32 [L*K, d_k] row-major (``planes_T.T``)."""
+    if not x.is_cuda or x.dtype not in _DTYPES or not x.is_contiguous() or x.dim() != 5:
+        raise RuntimeError("x must be a contiguous fp32/bf16 CUDA tensor [M,B,T,H,d_k]")
+    M, B, T, H, dk = x.shape
+    planes = planes.to(device=x.device, dtype=torch.float32).contiguous()
+    if planes.shape != (L * K, dk):
+        raise RuntimeError(f"planes must be [L*K, d_k] = [{L * K}, {dk}]")
+    out_dtype = out_dtype or x.dtype
+    with torch.cuda.device(x.device):
+        probs = torch.empty(M * B * H, T, L, 1 << K, dtype=out_dtype, device=x.device)
+        rc = _lib.lib().race_b200_bucket_probs_streams(_ptr(x), _ptr(planes), _ptr(probs), M * B, T, H, dk,
+                                                       L, K, _DTYPES[x.dtype], _DTYPES[out_dtype], _stream())
+    _lib.check(rc, "race_b200_bucket_probs_streams")
+    return probs
+
+
 class _RaceNonCausal(torch.autograd.Function):
     """out = pQ . (pK^T V / (sum_t pK + eps)) with the hand-written backward kernels.
 

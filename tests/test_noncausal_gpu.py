@@ -91,3 +91,22 @@ def test_bucket_probs(dk, K, L, rows):
     got16 = rk.bucket_probs(x.bfloat16().cuda(), planes_T.T.contiguous().cuda(), L, K)
     ref16 = ro.bucket_probs(x.bfloat16().double(), planes_T.double(), protos_T.double(), L, K)
     assert got16.dtype == torch.bfloat16 and ro.rel_l2(got16, ref16) <= 1e-2
+
+
+@pytest.mark.parametrize("M,B,T,H,dk,K,L", [(1, 1, 300, 8, 64, 4, 4), (2, 2, 37, 3, 32, 3, 2), (1, 2, 130, 2, 128, 6, 8),
+                                            (1, 1, 257, 1, 64, 1, 3), (2, 1, 1, 4, 64, 2, 2)])
+def test_bucket_probs_streams(M, B, T, H, dk, K, L):
+    """The producer reading the operator layout [M,B,T,H,d_k] equals flatten-then-produce
+    (src/race_baseline.py:35-44), bit for bit, and matches the oracle."""
+    rk = _rk()
+    torch.manual_seed(1234)
+    planes_T, protos_T = ro.make_planes(dk, K, L), ro.make_protos(K)
+    x = torch.randn(M, B, T, H, dk, generator=torch.Generator().manual_seed(5))
+    planes = planes_T.T.contiguous().cuda()
+    got = rk.bucket_probs_streams(x.cuda(), planes, L, K)
+    x2 = ro.to_streams(x)
+    flat = rk.bucket_probs(x2.cuda().contiguous(), planes, L, K)
+    assert got.shape == (M * B * H, T, L, 1 << K)
+    assert torch.equal(got, flat)
+    ref = ro.bucket_probs(x2.double(), planes_T.double(), protos_T.double(), L, K)
+    assert ro.rel_l2(got, ref) <= 1e-5
