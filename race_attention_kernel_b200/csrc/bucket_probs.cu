@@ -80,19 +80,19 @@ bucket_probs_kernel(const Tx* __restrict__ x, const float* __restrict__ planes, 
     }
     __syncthreads();
     {
-        // eight 16-byte loads in flight per thread; consecutive threads read consecutive 16 bytes of a row
+        // sixteen 16-byte loads in flight per thread; consecutive threads read consecutive 16 bytes of a row
         const int d4 = d >> 2;                                 // 16-byte items per row; divides RB
         const int c = (tid % d4) * 4, r0 = tid / d4, rstep = RB / d4;
-        for (int u0 = 0; u0 < d4; u0 += 8) {
-            float4 v[8];
+        for (int u0 = 0; u0 < d4; u0 += 16) {
+            float4 v[16];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < 16; ++u) {
                 const int r = r0 + (u0 + u) * rstep;
                 v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (u0 + u < d4 && r < valid) v[u] = Vec4<Tx>::load(x + srow[r] + c);
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < 16; ++u) {
                 const int r = r0 + (u0 + u) * rstep;
                 if (u0 + u < d4) *reinterpret_cast<float4*>(sx + r * ldx + c) = v[u];
             }
