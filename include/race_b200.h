@@ -18,6 +18,12 @@
  *                    A[s] at S*d_k + s  (A = sum of key probabilities, B = sum of pK (x) v)
  * N = M*B*H independent streams (the reference's BatchedACE flattens [M,B,T,H,d_k] to
  * [N,T,d_k], src/race_baseline.py:35-40).
+ * With RaceShape.heads = H > 1 the causal entry points read V and write out in the operator's own
+ * layout [N/H, T, H, d_k] (stream n = outer*H + h), so that neither the flattened copy of V nor the
+ * permuted view of the output (src/race_baseline.py:40,52) is needed; the probabilities stay
+ * [N, T, L, R].  Supported by the fp32 tensor variant (S = 64, d_k = 64) of race_b200_causal_fwd,
+ * race_b200_tile_totals and race_b200_causal_fwd_resume; every other entry point and variant
+ * rejects heads > 1 with RACE_ERR_SHAPE / reports it as unsupported.
  */
 #ifndef RACE_B200_H_
 #define RACE_B200_H_
@@ -54,7 +60,7 @@ typedef struct RaceShape {
     int32_t head_dim;  /* d_k */
     int32_t dtype;     /* RACE_DTYPE_* of probsQ/probsK/V/out */
     float eps;         /* added to A before the divide; the reference uses 1e-6 */
-    int32_t reserved;  /* must be 0 */
+    int32_t heads;     /* layout of V and out: 0 or 1 = [N, T, d_k]; H > 1 = [N/H, T, H, d_k] (below) */
 } RaceShape;
 
 /* Library / ABI version (major*1000 + minor). */

@@ -33,7 +33,7 @@ class RaceShape(ctypes.Structure):
         ("n_streams", ctypes.c_int64), ("seq_len", ctypes.c_int64),
         ("n_tables", ctypes.c_int32), ("n_buckets", ctypes.c_int32),
         ("head_dim", ctypes.c_int32), ("dtype", ctypes.c_int32),
-        ("eps", ctypes.c_float), ("reserved", ctypes.c_int32),
+        ("eps", ctypes.c_float), ("heads", ctypes.c_int32),
     ]
 
 

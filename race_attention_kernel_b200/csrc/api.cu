@@ -18,7 +18,7 @@ int elt_bytes(int dtype) { return dtype == RACE_DTYPE_BF16 ? 2 : 4; }
 int check_shape(const RaceShape* sh, Dims* dm) {
     if (!sh) return RACE_ERR_NULL;
     if (sh->dtype != RACE_DTYPE_F32 && sh->dtype != RACE_DTYPE_BF16) return RACE_ERR_SHAPE;
-    if (sh->reserved != 0) return RACE_ERR_SHAPE;
+    if (sh->heads < 0) return RACE_ERR_SHAPE;
     if (sh->n_streams < 0 || sh->seq_len < 0) return RACE_ERR_SHAPE;
     if (sh->n_tables <= 0 || sh->n_buckets <= 0 || sh->head_dim <= 0) return RACE_ERR_SHAPE;
     if ((int64_t)sh->n_tables * sh->n_buckets > 4096) return RACE_ERR_SHAPE;
@@ -28,6 +28,8 @@ int check_shape(const RaceShape* sh, Dims* dm) {
     dm->S = sh->n_tables * sh->n_buckets;
     dm->D = sh->head_dim;
     dm->eps = sh->eps;
+    dm->H = sh->heads > 1 ? sh->heads : 1;
+    if (dm->N % dm->H != 0) return RACE_ERR_SHAPE;
     const int eb = elt_bytes(sh->dtype);
     if ((dm->S * eb) % 16 != 0 || (dm->D * eb) % 16 != 0) return RACE_ERR_ALIGN;
     return RACE_OK;
@@ -42,11 +44,14 @@ int sm_count() {
 
 int resolve_variant(const Dims& dm, int dtype, int variant) {
     if (variant == RACE_VARIANT_AUTO)
-        return tensor_supported(dm, dtype) ? RACE_VARIANT_TENSOR : RACE_VARIANT_SIMT;
+        return (tensor_supported(dm, dtype) && (dm.H == 1 || dtype == RACE_DTYPE_F32)) ? RACE_VARIANT_TENSOR
+                                                                                   : RACE_VARIANT_SIMT;
     return variant;
 }
 
 bool variant_supported(const Dims& dm, int dtype, int variant) {
+    // the heads layout of V / out is read by the fp32 tensor kernels only
+    if (dm.H > 1 && !(variant == RACE_VARIANT_TENSOR && dtype == RACE_DTYPE_F32)) return false;
     if (variant == RACE_VARIANT_SIMT) return simt_supported(dm);
     if (variant == RACE_VARIANT_TENSOR) return tensor_supported(dm, dtype);
     return false;
@@ -192,7 +197,7 @@ int race_b200_noncausal_fwd(const void* probs_q, const void* probs_k, const void
     Dims dm;
     int rc = check_shape(shape, &dm);
     if (rc != RACE_OK) return rc;
-    if (!simt_supported(dm)) return RACE_ERR_SHAPE;
+    if (!simt_supported(dm) || dm.H > 1) return RACE_ERR_SHAPE;
     if (dm.N == 0) return RACE_OK;
     if (!totals) return RACE_ERR_NULL;
     cudaStream_t st = (cudaStream_t)stream;
@@ -225,7 +230,7 @@ int race_b200_noncausal_bwd(const void* probs_q, const void* probs_k, const void
     Dims dm;
     int rc = check_shape(shape, &dm);
     if (rc != RACE_OK) return rc;
-    if (!simt_supported(dm)) return RACE_ERR_SHAPE;
+    if (!simt_supported(dm) || dm.H > 1) return RACE_ERR_SHAPE;
     if (dm.N == 0 || dm.T == 0) return RACE_OK;
     if (!probs_q || !probs_k || !v || !totals || !d_out || !d_probs_q || !d_probs_k || !d_v ||
         !workspace)

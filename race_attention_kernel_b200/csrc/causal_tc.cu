@@ -92,7 +92,7 @@ __device__ __forceinline__ void convert_tile(const uint8_t* stage, uint8_t* hi, 
 __global__ void __launch_bounds__(kThreads, 1)
 causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, float* __restrict__ out,
-              const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int* status) {
+              const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int heads, int* status) {
     extern __shared__ uint8_t smem_raw[];
     Ctx cx;
     cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -160,7 +160,9 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
         const int wg = warp >> 2, w = warp & 3;
         const int q = lane & 3, rbase = 16 * w + (lane >> 2);
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
-        float* out_n = out + n * T * D;
+        // V and out are [N/heads, T, heads, D]: stream n = outer * heads + h (heads = 1: plain [N, T, D])
+        const int64_t orow_stride = (int64_t)heads * D;
+        float* out_n = out + ((n / heads) * T * heads + (n % heads)) * D;
         const float* pq_n = pq + n * T * S;
         float v[32];
         uint32_t ohi[16], olo[16];   // operand limbs of W / masked G on their way to tensor memory
@@ -176,7 +178,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             for (int h = 0; h < 2; ++h) {
                 const int row = rbase + 8 * h;
                 if (row < valid) {
-                    float* orow = out_n + (tok0 + row) * D + 2 * q;
+                    float* orow = out_n + (tok0 + row) * orow_stride + 2 * q;
 #pragma unroll
                     for (int x = 0; x < 8; ++x)
                         __stcs(reinterpret_cast<float2*>(orow + 8 * x),
@@ -392,8 +394,8 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                 mbar_arrive_expect_tx(bar, kStageBytes);
                 tma_load_4d(dst, &map_k, bar, 0, tok, 0, (int)n);
                 tma_load_4d(dst + 8192, &map_k, bar, 0, tok, 1, (int)n);
-                tma_load_4d(dst + kTileF32, &map_v, bar, 0, tok, 0, (int)n);
-                tma_load_4d(dst + kTileF32 + 8192, &map_v, bar, 0, tok, 1, (int)n);
+                tma_load_5d(dst + kTileF32, &map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                tma_load_5d(dst + kTileF32 + 8192, &map_v, bar, 0, tok, 1, (int)(n % heads), (int)(n / heads));
                 issued = c + 1;
             }
             if (*cx.abort_flag) {
@@ -529,7 +531,7 @@ __device__ __forceinline__ void convert_tile_sum(const uint8_t* stage, uint8_t* 
 
 __global__ void __launch_bounds__(kT1Threads, 1)
 tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-               float* __restrict__ ws, int64_t T, int tile_tokens, int* status) {
+               float* __restrict__ ws, int64_t T, int tile_tokens, int heads, int* status) {
     extern __shared__ uint8_t smem_raw[];
     Ctx cx;
     cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -614,8 +616,8 @@ tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 mbar_arrive_expect_tx(bar, kT1StageBytes);
                 tma_load_4d(dst, &map_k, bar, 0, tok, 0, (int)n);
                 tma_load_4d(dst + 8192, &map_k, bar, 0, tok, 1, (int)n);
-                tma_load_4d(dst + kTileF32, &map_v, bar, 0, tok, 0, (int)n);
-                tma_load_4d(dst + kTileF32 + 8192, &map_v, bar, 0, tok, 1, (int)n);
+                tma_load_5d(dst + kTileF32, &map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                tma_load_5d(dst + kTileF32 + 8192, &map_v, bar, 0, tok, 1, (int)(n % heads), (int)(n / heads));
                 issued = c + 1;
             }
             if (*cx.abort_flag) {
@@ -709,8 +711,23 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     return fn;
 }
 
-// [N][T][width] fp32 viewed as (32 values, T tokens, width/32 column blocks, N streams); one box =
-// 32 values x 64 tokens (128-byte rows, 128B swizzle); tokens past T read as zero
+// V in the layout [N/heads, T, heads, width] (heads = 1: [N, T, width]) viewed as (32 values, T tokens,
+// width/32 column blocks, heads, N/heads); one box = 32 values x 64 tokens (128-byte rows, 128B swizzle);
+// tokens past T read as zero
+bool make_map_heads(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width, int heads) {
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[5] = {32, (cuuint64_t)T, (cuuint64_t)(width / 32), (cuuint64_t)heads, (cuuint64_t)(N / heads)};
+    cuuint64_t strides[4] = {(cuuint64_t)heads * width * 4, 128, (cuuint64_t)width * 4,
+                             (cuuint64_t)T * heads * width * 4};
+    cuuint32_t box[5] = {32, (cuuint32_t)C, 1, 1, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// [N][T][width] fp32 viewed as (32 values, T tokens, width/32 column blocks, N streams); boxes as above
 bool make_map(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width) {
     auto fn = encode_fn();
     if (!fn) return false;
@@ -760,13 +777,13 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
                                            kT1SmemBytes);
     if (err != cudaSuccess) return err;
     CUtensorMap mk, mv;
-    if (!make_map(&mk, pk, dm.N, dm.T, dm.S) || !make_map(&mv, v, dm.N, dm.T, dm.D))
+    if (!make_map(&mk, pk, dm.N, dm.T, dm.S) || !make_map_heads(&mv, v, dm.N, dm.T, dm.D, dm.H))
         return cudaErrorInvalidValue;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     dim3 grid((unsigned)tiles, (unsigned)dm.N);
     // 1. tile totals (tensor cores)  2. exclusive scan over tiles  3. output pass
     if (phases & kPhaseTotals) {
-        tile_totals_tc<<<grid, kT1Threads, kT1SmemBytes, stream>>>(mk, mv, (float*)ws, dm.T, tile_tokens, status);
+        tile_totals_tc<<<grid, kT1Threads, kT1SmemBytes, stream>>>(mk, mv, (float*)ws, dm.T, tile_tokens, dm.H, status);
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
     }
@@ -777,7 +794,7 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
     err = cudaFuncSetAttribute(causal_out_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return err;
     causal_out_tc<<<grid, kThreads, kSmemBytes, stream>>>((const float*)pq, mk, mv, (float*)out, (const float*)ws, dm.T,
-                                                          tile_tokens, dm.eps, status);
+                                                          tile_tokens, dm.eps, dm.H, status);
     return cudaGetLastError();
 }
 

@@ -16,6 +16,7 @@ struct Dims {
     int S;      // L*R bucket features per token
     int D;      // head dim
     float eps;
+    int H = 1;  // heads of the V / out layout: [N/H, T, H, D] (1: the plain [N, T, D])
 };
 
 constexpr int kSimtThreads = 256;

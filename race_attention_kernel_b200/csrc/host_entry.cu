@@ -50,6 +50,7 @@ extern "C" int race_b200_causal_fwd_host(const void* probs_q, const void* probs_
                                          int device) {
     if (!shape) return RACE_ERR_NULL;
     if (shape->n_streams <= 0 || shape->seq_len < 0) return shape->n_streams == 0 ? RACE_OK : RACE_ERR_SHAPE;
+    if (shape->heads > 1) return RACE_ERR_SHAPE;   // segments are cut from contiguous [N, T, .] host tensors
     RACE_TRY(cudaSetDevice(device));
     RaceShape seg_shape = *shape;
     const int64_t N = shape->n_streams, T = shape->seq_len;

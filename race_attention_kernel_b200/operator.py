@@ -62,11 +62,18 @@ class BatchedACE(nn.Module):
         planes = self.planes_T.T.contiguous().float()
         pK = ops.bucket_probs_streams(Khf.contiguous(), planes, self.L, self.K)
         pQ = ops.bucket_probs_streams(Qhf.contiguous(), planes, self.L, self.K)
-        V2 = self._streams(Vhf)
-        res = ops.race_causal_prefix(pQ, pK, V2, self.eps, carry_in=carry_in,
-                                     return_state=return_state, variant=self.variant)
-        out2 = res[0] if return_state else res
-        out = out2.view(M, B, H, T, dk).permute(0, 1, 3, 2, 4)
+        N, S_l, S_r = M * B * H, self.L, 1 << self.K
+        if self.variant == "auto" and ops.is_supported(N, T, S_l, S_r, dk, Vhf.dtype, "auto", heads=H):
+            # the prefix kernels read V and write the output in [M,B,T,H,d_k] directly
+            res = ops.race_causal_prefix(pQ, pK, Vhf.contiguous(), self.eps, carry_in=carry_in,
+                                         return_state=return_state, variant=self.variant)
+            out = res[0] if return_state else res
+        else:
+            V2 = self._streams(Vhf)
+            res = ops.race_causal_prefix(pQ, pK, V2, self.eps, carry_in=carry_in,
+                                         return_state=return_state, variant=self.variant)
+            out2 = res[0] if return_state else res
+            out = out2.view(M, B, H, T, dk).permute(0, 1, 3, 2, 4)
         if host:
             out = out.cpu()
         return (out, res[1], res[2]) if return_state else out

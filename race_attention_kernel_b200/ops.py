@@ -62,18 +62,25 @@ def _check_inputs(probsQ, probsK, V, need_q=True):
             raise RuntimeError(f"{name} must be contiguous")
         if t.device != V.device or t.dtype != V.dtype:
             raise RuntimeError(f"{name}: device/dtype differ from V")
-    if probsK.dim() != 4 or V.dim() != 3:
-        raise RuntimeError("expected probs [N,T,L,R] and V [N,T,d_k]")
+    if probsK.dim() != 4 or V.dim() not in (3, 5):
+        raise RuntimeError("expected probs [N,T,L,R] and V [N,T,d_k] (or [M,B,T,H,d_k])")
     if need_q and probsQ.shape != probsK.shape:
         raise RuntimeError("probsQ and probsK shapes differ")
     N, T, L, R = probsK.shape
-    if V.shape[0] != N or V.shape[1] != T:
+    if V.dim() == 5:   # the operator's layout: stream n = (m*B + b)*H + h
+        if V.shape[0] * V.shape[1] * V.shape[3] != N or V.shape[2] != T:
+            raise RuntimeError("V [M,B,T,H,d_k] does not match probs in M*B*H or T")
+    elif V.shape[0] != N or V.shape[1] != T:
         raise RuntimeError("V does not match probs in N or T")
-    return N, T, L, R, V.shape[2]
+    return N, T, L, R, V.shape[-1]
 
 
-def make_shape(N, T, L, R, dk, dtype, eps) -> _lib.RaceShape:
-    return _lib.RaceShape(N, T, L, R, dk, _DTYPES[dtype], float(eps), 0)
+def _heads(V) -> int:
+    return int(V.shape[3]) if V.dim() == 5 else 0
+
+
+def make_shape(N, T, L, R, dk, dtype, eps, heads: int = 0) -> _lib.RaceShape:
+    return _lib.RaceShape(N, T, L, R, dk, _DTYPES[dtype], float(eps), heads)
 
 
 def pack_state(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
@@ -97,8 +104,9 @@ def select_tile_tokens(N, T, L, R, dk, dtype=torch.float32, variant="auto") -> i
     return out.value
 
 
-def is_supported(N, T, L, R, dk, dtype=torch.float32, variant="auto") -> bool:
-    sh = make_shape(N, T, L, R, dk, dtype, 1e-6)
+def is_supported(N, T, L, R, dk, dtype=torch.float32, variant="auto", heads: int = 0) -> bool:
+    """heads = H > 1 asks for V / out in the operator's layout [N/H, T, H, d_k]."""
+    sh = make_shape(N, T, L, R, dk, dtype, 1e-6, heads)
     return bool(_lib.lib().race_b200_is_supported(ctypes.byref(sh), _lib.VARIANTS[variant]))
 
 
@@ -108,6 +116,10 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
     """out[n,t,:] = sum_s pQ[n,t,s] * B_t[n,s,:] / (A_t[n,s] + eps) with inclusive prefixes
     A_t, B_t (src/race_baseline.py:45-51).
 
+    V may also be given in the operator's layout [M,B,T,H,d_k] (stream n = (m*B+b)*H + h, the order of
+    src/race_baseline.py:35-40); the output then has that layout too and no flattened copy is made
+    (fp32, S = 64, d_k = 64 only: see ``is_supported(..., heads=H)``).
+
     carry_in: None, a packed state [N, S*d_k+S] or a tuple (A [N,L,R], B [N,L,R,d_k]) holding the
     sums over tokens before this call's first token.  return_state=True also returns (A, B)
     after the last token.  tile_tokens / variant are test hooks (0 / "auto" = automatic).
@@ -116,7 +128,7 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
     if variant not in _lib.VARIANTS:
         raise RuntimeError(f"unknown variant {variant!r}")
     L_ = _lib.lib()
-    sh = make_shape(N, T, L, R, dk, V.dtype, eps)
+    sh = make_shape(N, T, L, R, dk, V.dtype, eps, _heads(V))
     var = _lib.VARIANTS[variant]
     carry = None
     if carry_in is not None:
@@ -162,7 +174,7 @@ def race_tile_totals(probsK, V, *, tile_tokens: int = 0, variant: str = "auto",
     pK and V again."""
     N, T, L, R, dk = _check_inputs(None, probsK, V, need_q=False)
     L_ = _lib.lib()
-    sh = make_shape(N, T, L, R, dk, V.dtype, 1e-6)
+    sh = make_shape(N, T, L, R, dk, V.dtype, 1e-6, _heads(V))
     var = _lib.VARIANTS[variant]
     with torch.cuda.device(V.device):
         state = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device)

@@ -35,8 +35,8 @@ def test_version_and_error_strings():
         assert L.race_b200_error_string(code) not in (b"", b"unknown error")
 
 
-def _shape(N=8, T=4096, L=4, R=16, dk=64, dtype=0, eps=1e-6, reserved=0):
-    return _lib.RaceShape(N, T, L, R, dk, dtype, eps, reserved)
+def _shape(N=8, T=4096, L=4, R=16, dk=64, dtype=0, eps=1e-6, heads=0):
+    return _lib.RaceShape(N, T, L, R, dk, dtype, eps, heads)
 
 
 def test_state_floats_and_support():
@@ -51,12 +51,12 @@ def test_state_floats_and_support():
     assert L.race_b200_is_supported(ctypes.byref(_shape(L=3, R=64, dk=128, dtype=1)), 2) == 0   # 3 groups
     assert L.race_b200_is_supported(ctypes.byref(_shape(dk=128)), 2) == 0                       # fp32 d_k=128
     assert L.race_b200_is_supported(ctypes.byref(_shape(dtype=7)), 0) == 0
-    assert L.race_b200_is_supported(ctypes.byref(_shape(reserved=1)), 0) == 0
+    assert L.race_b200_is_supported(ctypes.byref(_shape(heads=3)), 0) == 0
 
 
 @pytest.mark.parametrize("kw,code", [
     (dict(dtype=5), -2), (dict(N=-1), -2), (dict(L=0), -2), (dict(eps=-1.0), -2),
-    (dict(reserved=3), -2), (dict(), -1),      # a valid shape then fails on the NULL pointers
+    (dict(heads=3), -2), (dict(), -1),      # a valid shape then fails on the NULL pointers
 ])
 def test_argument_errors_without_launch(kw, code):
     L = _lib.lib()

@@ -261,3 +261,36 @@ def test_long_sequence_spot_check():
                                    V[n:, T - w:].double().cpu(), carry=(A0, B0), return_state=True)
     assert ro.rel_l2(out[n:, T - w:], ref) <= FP32_TOL
     assert ro.rel_l2(A[n:], A1) <= 1e-5 and ro.rel_l2(B[n:], B1) <= 1e-4
+
+
+@pytest.mark.parametrize("M,B,T,H", [(1, 1, 4096, 8), (2, 2, 333, 3), (1, 2, 2049, 2), (1, 1, 64, 1)])
+def test_heads_layout_equals_flattened_streams(M, B, T, H):
+    """V and out in the operator's layout [M,B,T,H,d_k] (stream flattening of
+    src/race_baseline.py:35-40 done by the kernels' addressing) give bit-identical results to the
+    flattened call, for the whole forward and for the totals / resume pair."""
+    rk = _ops()
+    L, R, dk = 4, 16, 64
+    N = M * B * H
+    pQ, pK, V2 = ro.synthetic_probs(N, T, L, R, dk, seed=H + T)
+    V5 = V2.view(M, B, H, T, dk).permute(0, 1, 3, 2, 4).contiguous()      # [M,B,T,H,d_k]
+    q, k = pQ.cuda(), pK.cuda()
+    assert rk.is_supported(N, T, L, R, dk, torch.float32, "auto", heads=H)
+    flat, A0, B0 = rk.race_causal_prefix(q, k, V2.cuda(), return_state=True)
+    got, A1, B1 = rk.race_causal_prefix(q, k, V5.cuda(), return_state=True)
+    assert got.shape == (M, B, T, H, dk)
+    assert torch.equal(got.permute(0, 1, 3, 2, 4).reshape(N, T, dk), flat)
+    assert torch.equal(A0, A1) and torch.equal(B0, B1)
+    At, Bt, ws = rk.race_tile_totals(k, V5.cuda(), return_workspace=True)
+    assert torch.equal(At, A0) and torch.equal(Bt, B0)
+    again = rk.race_causal_prefix(q, k, V5.cuda(), totals_workspace=ws)
+    assert torch.equal(again, got)
+    ref = ro.causal_prefix(pQ.double(), pK.double(), V2.double())
+    assert ro.rel_l2(flat, ref) <= 1e-4
+
+
+def test_heads_layout_rejected_where_not_built():
+    rk = _ops()
+    assert not rk.is_supported(8, 256, 4, 16, 64, torch.bfloat16, "auto", heads=4)   # bf16 path
+    assert not rk.is_supported(8, 256, 4, 16, 64, torch.float32, "simt", heads=4)    # CUDA-core path
+    assert not rk.is_supported(8, 256, 8, 64, 128, torch.float32, "auto", heads=4)   # no tensor path: S=512 fp32
+    assert not rk.is_supported(8, 256, 4, 16, 64, torch.float32, "auto", heads=3)    # 8 streams / 3 heads
