@@ -191,6 +191,18 @@ int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const 
                         shape, tile_tokens, variant, stream, status, kPhaseOutput);
 }
 
+namespace {
+// tile length of the totals pass of the non-causal path: with many streams one tile per stream (no scan
+// over tiles is needed then); never longer than the automatic choice allows the workspace to be
+int noncausal_totals_tile(const RaceShape* shape, const Dims& dm) {
+    int tile = 0;
+    if (race_b200_select_tile_tokens(shape, RACE_VARIANT_AUTO, &tile) != RACE_OK || tile <= 0) return 0;
+    const int64_t sms = sm_count();
+    while (tile < 16384 && tile < dm.T && dm.N * ((dm.T + 2 * tile - 1) / (2 * tile)) >= 2 * sms) tile *= 2;
+    return tile;
+}
+}  // namespace
+
 int race_b200_noncausal_fwd(const void* probs_q, const void* probs_k, const void* v, void* out,
                             float* totals, void* workspace, size_t workspace_bytes,
                             const RaceShape* shape, void* stream) {
@@ -207,8 +219,8 @@ int race_b200_noncausal_fwd(const void* probs_q, const void* probs_k, const void
     if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(out) ||
         !aligned16(totals) || !aligned16(workspace))
         return RACE_ERR_ALIGN;
-    rc = race_b200_tile_totals(probs_k, v, totals, workspace, workspace_bytes, shape, 0,
-                               RACE_VARIANT_AUTO, stream, nullptr);
+    rc = race_b200_tile_totals(probs_k, v, totals, workspace, workspace_bytes, shape,
+                               noncausal_totals_tile(shape, dm), RACE_VARIANT_AUTO, stream, nullptr);
     if (rc != RACE_OK) return rc;
     if (noncausal_tensor_supported(dm, shape->dtype))
         return (int)noncausal_query_tensor(probs_q, totals, out, dm, shape->dtype, sm_count(), st);
@@ -248,8 +260,8 @@ int race_b200_noncausal_bwd(const void* probs_q, const void* probs_k, const void
     float* dE_state = (float*)((char*)workspace + ((tile_ws + 255) / 256 * 256));
     float* grads = (float*)((char*)dE_state + sfb);
     // dE = pQ^T dO : the tile-totals pass with (pQ, dO) in the roles of (pK, V)
-    rc = race_b200_tile_totals(probs_q, d_out, dE_state, ws_tiles, tile_ws, shape, 0, RACE_VARIANT_AUTO,
-                               stream, nullptr);
+    rc = race_b200_tile_totals(probs_q, d_out, dE_state, ws_tiles, tile_ws, shape,
+                               noncausal_totals_tile(shape, dm), RACE_VARIANT_AUTO, stream, nullptr);
     if (rc != RACE_OK) return rc;
     cudaError_t e = noncausal_state_grads(totals, dE_state, grads, dm, st);
     if (e != cudaSuccess) return (int)e;

@@ -435,6 +435,8 @@ cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out
                               int tile_tokens, cudaStream_t stream, bool write_prefix) {
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const int sf = state_floats_per_stream(dm.S, dm.D);
+    if (tiles == 1 && !carry_in && !write_prefix && state_out)   // one tile per stream: its totals are the state
+        return cudaMemcpyAsync(state_out, ws, (size_t)dm.N * sf * sizeof(float), cudaMemcpyDeviceToDevice, stream);
     dim3 sgrid((unsigned)((sf + 127) / 128), (unsigned)dm.N);
     tile_scan<<<sgrid, 128, 0, stream>>>(ws, carry_in, state_out, tiles, sf, write_prefix ? 1 : 0);
     return cudaGetLastError();
