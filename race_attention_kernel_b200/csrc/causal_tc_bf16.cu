@@ -6,14 +6,10 @@
 //     into the canonical operand layout;
 //   * d_k = 128 runs the state update, W.B and G.V with N = 128 (TMEM: B 128 + 2 x (64 + 128)
 //     columns = all 512);
-//   * S > 64: the tables of this estimator are independent (out = sum over tables), so bucket
-//     group g (64 buckets) is owned by CTA g of a thread-block cluster of G CTAs working on the
-//     same (stream, tile).  Each CTA keeps its own state slice and forms a partial output; CTA j
-//     owns the output columns [j d_k/G, (j+1) d_k/G): every CTA stores its partial values (bf16)
-//     into the owner's slot buffer through distributed shared memory (posted remote stores, one
-//     owner per warp-wide store), the owner adds the G slots in group order (deterministic, fp32)
-//     and writes its columns once.  Cross-CTA hand-offs are mbarriers
-//     with remote arrivals; no TMA multicast anywhere.
+//   * S > 64 (2, 4 or 8 groups of 64 buckets): the tables of this estimator are independent (out = sum
+//     over tables), and the sum over groups commutes with the causal mask; causal_out_wide_bf16 (below)
+//     walks all groups in one CTA and accumulates their products in tensor memory.  No thread-block
+//     clusters, no TMA multicast anywhere.
 // Reference semantics: src/race_baseline.py:45-51 (docs/causal_v2_design.md:70-77 for the chunk
 // form).  The multi-head configuration N=256 streams, T=262144, d_k=128, L=8, K=6 is G = 8, D = 128.
 #include <cudaTypedefs.h>
@@ -43,9 +39,7 @@ struct Lay {
     static constexpr int oBt = oWt + 2 * kTileP;        // [2]
     static constexpr int oTril = oBt + 2 * kTileV;
     static constexpr int oAcar = oTril + kTileP;        // [2][64] fp32
-    static constexpr int oObuf = oAcar + 2 * 64 * 4;    // [2][G sources][64][D/G] bf16 partial outputs received
-    static constexpr int oOst = oObuf + 2 * C * D * 2;  // [2][G owners][64][D/G] bf16 partial outputs to send
-    static constexpr int oBars = oOst + 2 * C * D * 2;
+    static constexpr int oBars = oAcar + 2 * 64 * 4;
     static constexpr int kNumBars = 36;
     static constexpr int oMisc = oBars + kNumBars * 8;
     static constexpr int kSmem = oMisc + 16 + 1024;
@@ -57,7 +51,7 @@ struct Lay {
 enum BarB {
     bFull = 0, bEmpty = 2, bKReady = 4, bVReady = 6, bXReady = 8, bWReady = 10, bGReady = 12,
     bGtReady = 14, bOReady = 16, bAcar = 18, bAcarFree = 20, bBupdDone = 22, bBaccFree = 23,
-    bBtReady = 25, bDrain = 27, bObufReady = 29, bObufFree = 31
+    bBtReady = 25, bDrain = 27
 };
 
 __device__ __forceinline__ uint32_t lo_mn_w(uint32_t addr, uint32_t lbo) {
@@ -77,50 +71,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
     return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
-}
-
-// ---- cluster helpers --------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
-    return r;
-}
-// bulk copy own shared memory -> shared memory of a CTA of the cluster; completes (bytes) on that CTA's mbarrier
-__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes, uint32_t bar_cluster) {
-    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster) : "memory");
-}
-__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// bounded wait on a barrier that CTAs of the cluster arrive on
-__device__ __forceinline__ bool wait_bar_cluster_warp(const Ctx& cx, int bar, uint32_t parity, int code) {
-    bool ok = true;
-    if (!mbar_try_wait_cluster(cx.bar(bar), parity)) {
-        const long long t0 = clock64();
-        int spins = 0;
-        while (!mbar_try_wait_cluster(cx.bar(bar), parity)) {
-            if ((++spins & 63) == 0) {
-                if (*cx.abort_flag) { ok = false; break; }
-                if (clock64() - t0 > kWaitCycles) {
-                    *cx.abort_flag = 1;
-                    if (cx.status) atomicCAS(cx.status, 0, code);
-                    ok = false;
-                    break;
-                }
-            }
-        }
-    }
-    return __all_sync(0xffffffffu, ok);
 }
 
 // TMA-staged bf16 tile [64 rows][64 values] (128-byte rows, 128B swizzle) -> operand tile
@@ -190,8 +140,6 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             mbar_init(cx.bar(bBaccFree + i), 4);
             mbar_init(cx.bar(bBtReady + i), 4);
             mbar_init(cx.bar(bDrain + i), 1);
-            mbar_init(cx.bar(bObufReady + i), 1);
-            mbar_init(cx.bar(bObufFree + i), G);
         }
         mbar_init(cx.bar(bBupdDone), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -214,10 +162,6 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
-    if (G > 1) {
-        // barriers of every CTA of the cluster exist before anyone arrives remotely
-        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    }
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmB = tmem;                                                   // [0, D)
@@ -226,17 +170,14 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
 
     if (warp < 8) {
         // =========================== worker warpgroups =========================================
-        const int wg = warp >> 2, w = warp & 3, wtid = tid & 127;
+        const int wg = warp >> 2, w = warp & 3;
         const int q = lane & 3, rbase = 16 * w + (lane >> 2);
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
         uint8_t* wt = cx.sm + Ly::oWt + wg * Ly::kTileP;
-        const uint8_t* obuf = cx.sm + Ly::oObuf + wg * C * D * 2;
-        const uint32_t obuf_u32 = cx.sm_u32 + Ly::oObuf + wg * C * D * 2;
         __nv_bfloat16* out_n = out + n * T * D;
         const __nv_bfloat16* pq_n = pq + n * T * S + g * SG;
         float v[32];
         uint32_t ph = 0;
-        int uses = 0;   // uses of this group's partial-output buffer so far
         bool ok = true;
         for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
             const int64_t tok0 = t_begin + (int64_t)c * C;
@@ -313,98 +254,24 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             RACE_TRACE(wg, c >> 1, 1);
             if (!(ok = wait_bar_warp(cx, bOReady + wg, ph, 105))) break;
             RACE_TRACE(wg, c >> 1, 2);
-            if (G == 1) {
 #pragma unroll
-                for (int dh = 0; dh < DH; ++dh) {
-                    tc_fence_after();
-                    tmem_ld64(lane_base + tmO(wg) + dh * 64, v);
-                    tc_fence_before();
+            for (int dh = 0; dh < DH; ++dh) {
+                tc_fence_after();
+                tmem_ld64(lane_base + tmO(wg) + dh * 64, v);
+                tc_fence_before();
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int row = rbase + 8 * h;
-                        if (row < valid) {
-                            __nv_bfloat16* orow = out_n + (tok0 + row) * D + dh * 64 + 2 * q;
+                for (int h = 0; h < 2; ++h) {
+                    const int row = rbase + 8 * h;
+                    if (row < valid) {
+                        __nv_bfloat16* orow = out_n + (tok0 + row) * D + dh * 64 + 2 * q;
 #pragma unroll
-                            for (int x = 0; x < 8; ++x)
-                                *reinterpret_cast<uint32_t*>(orow + 8 * x) =
-                                    pack_bf16(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
-                        }
+                        for (int x = 0; x < 8; ++x)
+                            *reinterpret_cast<uint32_t*>(orow + 8 * x) =
+                                pack_bf16(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
                     }
                 }
-            } else {
-                // Partial output of this bucket group: CTA j of the cluster owns the columns
-                // [j D/G, (j+1) D/G) of the chunk's rows.  Every CTA lays its partial values out per owner
-                // in its own shared memory (bf16) and sends each owner its block with one bulk copy through
-                // distributed shared memory, which completes on the owner's mbarrier; the owner adds the G
-                // blocks in group order and writes its columns.  The owners' "consumed" arrivals (below)
-                // also tell this CTA that its previous copies have left the staging buffer.
-                if (uses >= 1 && !(ok = wait_bar_cluster_warp(cx, bObufFree + wg, (uint32_t)((uses - 1) & 1), 108))) break;
-                RACE_TRACE(wg, c >> 1, 3);
-                const int cpo = D / G;   // columns per owner
-                {
-                    uint8_t* ost = cx.sm + Ly::oOst + wg * C * D * 2;
-#pragma unroll
-                    for (int dh = 0; dh < DH; ++dh) {
-                        tc_fence_after();
-                        tmem_ld64(lane_base + tmO(wg) + dh * 64, v);
-                        tc_fence_before();
-#pragma unroll
-                        for (int x = 0; x < 8; x += 2) {
-                            // neighbouring lanes of a quad swap one pair so that every lane owns four
-                            // consecutive columns: 8-byte stores
-                            const int col0 = dh * 64 + 8 * (x + (q & 1)) + 4 * (q >> 1);
-                            const int owner = col0 / cpo;
-                            uint8_t* blk = ost + ((owner * C) * cpo + (col0 - owner * cpo)) * 2;
-#pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                const uint32_t p0 = pack_bf16(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
-                                const uint32_t p1 = pack_bf16(v[4 * x + 4 + 2 * h], v[4 * x + 4 + 2 * h + 1]);
-                                const uint32_t got = __shfl_xor_sync(0xffffffffu, (q & 1) ? p0 : p1, 1);
-                                *reinterpret_cast<uint2*>(blk + (rbase + 8 * h) * cpo * 2) =
-                                    (q & 1) ? make_uint2(got, p1) : make_uint2(p0, got);
-                            }
-                        }
-                    }
-                }
-                fence_proxy_async();
-                asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
-                if (w == 0 && lane == 0) {
-                    const uint32_t blk_bytes = (uint32_t)(C * cpo * 2);
-                    mbar_arrive_expect_tx(cx.bar(bObufReady + wg), (uint32_t)(C * D * 2));   // G blocks will land here
-                    const uint32_t src = cx.sm_u32 + Ly::oOst + wg * C * D * 2;
-                    for (int j = 0; j < G; ++j)
-                        bulk_copy_to_cta(map_to_cta(obuf_u32 + (uint32_t)g * blk_bytes, (uint32_t)j),
-                                         src + (uint32_t)j * blk_bytes, blk_bytes,
-                                         map_to_cta(cx.bar(bObufReady + wg), (uint32_t)j));
-                }
-                RACE_TRACE(wg, c >> 1, 4);
-                if (!(ok = wait_bar_cluster_warp(cx, bObufReady + wg, (uint32_t)(uses & 1), 109))) break;
-                RACE_TRACE(wg, c >> 1, 5);
-                const int blocks = cpo / 8;   // 8-column blocks per row of this owner
-                for (int item = wtid; item < C * blocks; item += 128) {
-                    const int row = item / blocks, cb = item % blocks;
-                    float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
-                    for (int p = 0; p < G; ++p) {
-                        const uint4 u = *reinterpret_cast<const uint4*>(obuf + ((p * C + row) * cpo + cb * 8) * 2);
-                        const float2 a = unpack_bf16(u.x), b2 = unpack_bf16(u.y), c2 = unpack_bf16(u.z), d2 = unpack_bf16(u.w);
-                        s0.x += a.x; s0.y += a.y; s0.z += b2.x; s0.w += b2.y;
-                        s1.x += c2.x; s1.y += c2.y; s1.z += d2.x; s1.w += d2.y;
-                    }
-                    if (row < valid)
-                        *reinterpret_cast<uint4*>(out_n + (tok0 + row) * D + g * cpo + cb * 8) =
-                            make_uint4(pack_bf16(s0.x, s0.y), pack_bf16(s0.z, s0.w), pack_bf16(s1.x, s1.y),
-                                       pack_bf16(s1.z, s1.w));
-                }
-                RACE_TRACE(wg, c >> 1, 6);
-                // the slots may be overwritten: tell every source CTA
-                asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
-                if (w == 0 && lane < G) remote_arrive(map_to_cta(cx.bar(bObufFree + wg), (uint32_t)lane));
-                RACE_TRACE(wg, c >> 1, 7);
-                ++uses;
             }
         }
-        // peers may still be reading this group's last partial output: stay until they are done
-        if (G > 1 && uses >= 1 && ok) wait_bar_cluster_warp(cx, bObufFree + wg, (uint32_t)((uses - 1) & 1), 110);
     } else if (warp < 12) {
         // =========================== converter + carry warpgroup =================================
         const int w = warp & 3, q = lane & 3, rbase = 16 * w + (lane >> 2), wtid = tid & 127;
@@ -559,10 +426,6 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
 
     tc_fence_before();
     __syncthreads();
-    if (G > 1) {
-        // no CTA leaves while a peer may still arrive on its barriers or read its shared memory
-        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    }
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
@@ -750,6 +613,455 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Output pass for S > 64 ("wide"): one CTA owns a (stream, tile, 32-column slice of the head
+// dimension) and ALL bucket groups.  Per 64-token chunk it walks the groups one after the other
+// ("items"); because out = sum_g [ W_g B_g + tril(W_g pK_g^T) V ] = (sum_g W_g B_g) +
+// tril(sum_g W_g pK_g^T) V, the W.B products of all groups accumulate in one TMEM accumulator
+// and the W.pK^T products in another, so the causal mask and the G.V product run once per chunk
+// and nothing is exchanged between CTAs.  The price: the CTAs of the d_k/32 slices each recompute
+// W and G.  TMEM (512 columns): the state B_g of the G <= 8 groups ([64 x 32] each: 256), A_loc /
+// W per worker group (2 x 64), G (64; its first 32 columns take the masked operand afterwards) and
+// O for even / odd chunks (2 x 32).
+// Roles (18 warps): 2 worker warpgroups on alternate items (W of the item -> tensor memory as the
+// MMA A operand; the running A of every group stays in shared memory with the group's owner),
+// 1 converter warpgroup (TMA-staged pK item tiles and the V slice -> operand layout), 1 auxiliary
+// warpgroup (state of a group after its update -> bf16 operand tile; mask of G; output store),
+// 1 TMA producer warp, 1 MMA-issuing warp that runs the running-sum product one item ahead.
+// ------------------------------------------------------------------------------------------------
+constexpr int kWThreads = 18 * 32;
+constexpr int kWProducerWarp = 16, kWMmaWarp = 17;
+constexpr int kWStages = 4;       // ring of pK item tiles (stage and operand buffers)
+constexpr int DS = 32;            // head-dim slice of a CTA
+struct LayW {
+    static constexpr int kTileP = C * 64 * 2;    // 64 x 64 bf16
+    static constexpr int kTileS = C * DS * 2;    // 64 x 32 bf16
+    static constexpr int oStage = 0;                          // [kWStages][kTileP] staged pK
+    static constexpr int oVst = oStage + kWStages * kTileP;   // [2][kTileS] staged V slice
+    static constexpr int oKt = oVst + 2 * kTileS;             // [kWStages][kTileP]
+    static constexpr int oVt = oKt + kWStages * kTileP;       // [2][kTileS]
+    static constexpr int oBt = oVt + 2 * kTileS;              // [8][kTileS]
+    static constexpr int oTril = oBt + 8 * kTileS;
+    static constexpr int oAcar = oTril + kTileP;              // [8][64] fp32
+    static constexpr int oBars = oAcar + 8 * 64 * 4;
+    static constexpr int kNumBars = 62;
+    static constexpr int oMisc = oBars + kNumBars * 8;
+    static constexpr int kSmem = oMisc + 16 + 1024;
+    static constexpr uint32_t kLboS = (DS / 8) * 128;         // MN-major [64][32] tile: K-direction stride
+    static constexpr uint32_t kStepS = (2 * kLboS) >> 4;
+};
+enum BarW {
+    wFull = 0, wEmpty = 4, wVFull = 8, wVEmpty = 10, wKReady = 12, wKFree = 16, wVReady = 20, wVFree = 22,
+    wXReady = 24, wWReady = 26, wItemDone = 28, wBtReady = 44, wGtReady = 52, wOReady = 53,
+    wOFree = 54, wDrain = 56,
+    wAcarReady = 57,   // [2] the group's running A written by the warp that owns row 63
+    wAcarRead = 59     // [2] ... read by the four warps of the worker group
+};
+
+// 16 lanes x 32 columns of fp32: thread t gets rows (t/4, t/4+8), column pairs 8x + 2(t%4) + {0,1}, x < 4
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x256b.x4.b32 [%16], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+        ::"r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(kWThreads, 1)
+causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_vs, __nv_bfloat16* __restrict__ out,
+                     const float* __restrict__ ws, int64_t T, int S, int D, int G, int tile_tokens, float eps,
+                     int* status) {
+    using Ly = LayW;
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cx;
+    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cx.sm_u32 = smem_u32(cx.sm);
+    cx.bars = Ly::oBars;
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + Ly::oMisc + 4);
+    cx.status = status;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + Ly::oMisc);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int NS = D / DS;                                   // slices of the head dimension
+    const int js = (int)(blockIdx.x % (unsigned)NS);
+    const int64_t tiles = gridDim.x / NS;
+    const int64_t tile = blockIdx.x / NS, n = blockIdx.y;
+    const int64_t t_begin = tile * tile_tokens;
+    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
+    const int nch = (int)((t_end - t_begin + C - 1) / C);
+    const int nitems = nch * G;
+    const float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+
+    if (tid == 0) {
+        *cx.abort_flag = 0;
+        for (int i = 0; i < kWStages; ++i) {
+            mbar_init(cx.bar(wFull + i), 1);
+            mbar_init(cx.bar(wEmpty + i), 4);
+            mbar_init(cx.bar(wKReady + i), 4);
+            mbar_init(cx.bar(wKFree + i), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(cx.bar(wVFull + i), 1);
+            mbar_init(cx.bar(wVEmpty + i), 4);
+            mbar_init(cx.bar(wVReady + i), 4);
+            mbar_init(cx.bar(wVFree + i), 1);
+            mbar_init(cx.bar(wXReady + i), 1);
+            mbar_init(cx.bar(wWReady + i), 4);
+            mbar_init(cx.bar(wOFree + i), 4);
+            mbar_init(cx.bar(wAcarReady + i), 1);
+            mbar_init(cx.bar(wAcarRead + i), 4);
+        }
+        for (int i = 0; i < 8; ++i) {
+            mbar_init(cx.bar(wItemDone + i), 1);
+            mbar_init(cx.bar(wBtReady + i), 4);
+        }
+        mbar_init(cx.bar(wGtReady), 4);
+        mbar_init(cx.bar(wOReady), 1);
+        mbar_init(cx.bar(wDrain), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kWMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(cx.sm_u32 + Ly::oMisc), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    for (int i = tid; i < C * 8; i += kWThreads) {   // tril[t][j] = (j <= t)
+        const int t = i >> 3, jg = i & 7;
+        uint32_t w[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int j0 = jg * 8 + 2 * p;
+            w[p] = (j0 <= t ? 0x3F80u : 0u) | (j0 + 1 <= t ? 0x3F800000u : 0u);
+        }
+        *reinterpret_cast<uint4*>(cx.sm + Ly::oTril + off_w<64>(t, jg * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    for (int i = tid; i < G * 64; i += kWThreads)   // running A of every group: the carry-in
+        reinterpret_cast<float*>(cx.sm + Ly::oAcar)[i] = slice[(int64_t)S * D + i];
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    auto tmBg = [&](int g) { return tmem + g * DS; };                 // [0, 256)
+    auto tmX = [&](int wg) { return tmem + 256 + wg * 64; };          // A_loc, then W (32 columns of pairs)
+    const uint32_t tmG = tmem + 384;                                  // G, then masked G (32 columns of pairs)
+    auto tmO = [&](int c) { return tmem + 448 + (c & 1) * DS; };
+
+    if (warp < 8) {
+        // =========================== worker warpgroups: W of every other item ====================
+        const int wg = warp >> 2, w = warp & 3;
+        const int q = lane & 3, rbase = 16 * w + (lane >> 2);
+        const uint32_t lane_base = (uint32_t)(32 * w) << 16;
+        float v[32];
+        bool ok = true;
+        // pQ of an item in the accumulator-fragment layout (pairs of bf16), loaded one item of this worker
+        // group ahead: an item lasts about as long as a load from HBM takes
+        auto load_pq = [&](int i, uint32_t (&f)[16]) {
+            const int c = i / G, g = i - c * G;
+            const int64_t tok0 = t_begin + (int64_t)c * C;
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                const __nv_bfloat16* prow = pq + (n * T + tok0 + row) * S + g * SG + 2 * q;
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    f[2 * x + h] = row < valid ? __ldg(reinterpret_cast<const unsigned int*>(prow + 8 * x)) : 0u;
+            }
+        };
+        uint32_t pq_next[16];
+        if (wg < nitems) load_pq(wg, pq_next);
+        for (int i = wg, k = 0; i < nitems && ok; i += 2, ++k) {
+            const int c = i / G, g = i - c * G;
+            uint32_t pqv[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) pqv[j] = pq_next[j];
+            if (i + 2 < nitems) load_pq(i + 2, pq_next);
+            // running A of the group: written at the end of the previous item of this worker group
+            // (which is the same bucket group when G = 2)
+            if (!(ok = wait_bar_warp(cx, wAcarReady + wg, (uint32_t)((k & 1) ^ 1), 101))) break;
+            float* ac = reinterpret_cast<float*>(cx.sm + Ly::oAcar) + g * 64;
+            float acar[16];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                const float2 a2 = *reinterpret_cast<const float2*>(ac + 8 * x + 2 * q);
+                acar[2 * x] = a2.x; acar[2 * x + 1] = a2.y;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(wAcarRead + wg));
+            // the warp that owns row 63 overwrites the values below: all four warps must hold them first
+            if (w == 3 && !(ok = wait_bar_warp(cx, wAcarRead + wg, (uint32_t)(k & 1), 102))) break;
+            if (w == 0) RACE_TRACE(wg, i - 64, 0);
+            if (!(ok = wait_bar_warp(cx, wXReady + wg, (uint32_t)(k & 1), 103))) break;
+            if (w == 0) RACE_TRACE(wg, i - 64, 1);
+            tc_fence_after();
+            tmem_ld64(lane_base + tmX(wg), v);
+            tc_fence_before();
+            if (w == 0) RACE_TRACE(wg, i - 64, 2);
+            uint32_t wv[16];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float2 pq2 = unpack_bf16(pqv[2 * x + h]);
+                    const float a0 = acar[2 * x] + v[4 * x + 2 * h];
+                    const float a1 = acar[2 * x + 1] + v[4 * x + 2 * h + 1];
+                    wv[2 * x + h] = pack_bf16(__fdividef(pq2.x, a0 + eps), __fdividef(pq2.y, a1 + eps));
+                    if (h == 1 && w == 3 && (lane >> 2) == 7)    // row 63: the running A after this chunk
+                        *reinterpret_cast<float2*>(ac + 8 * x + 2 * q) = make_float2(a0, a1);
+                }
+            }
+            tmem_st_pairs(lane_base + tmX(wg), wv);
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(cx.bar(wWReady + wg));
+                if (w == 3) mbar_arrive(cx.bar(wAcarReady + wg));   // the new running A is in place
+            }
+            if (w == 0) RACE_TRACE(wg, i - 64, 3);
+        }
+    } else if (warp < 12) {
+        // =========================== converter warpgroup ==========================================
+        const int wtid = tid & 127;
+        bool ok = true;
+        for (int i = 0; i < nitems && ok; ++i) {
+            const int c = i / G, g = i - c * G, st = i % kWStages;
+            const uint32_t rp = (uint32_t)((i / kWStages) & 1);
+            if (i >= kWStages && !(ok = wait_bar_warp(cx, wKFree + st, rp ^ 1, 203))) break;
+            if (!(ok = wait_bar_warp(cx, wFull + st, rp, 201))) break;
+            copy_tile<64, false>(cx.sm + Ly::oStage + st * Ly::kTileP, cx.sm + Ly::oKt + st * Ly::kTileP, 0, wtid, nullptr);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(wKReady + st)); mbar_arrive(cx.bar(wEmpty + st)); }
+            if (g == 0) {
+                // V slice of the chunk: [64 tokens][32 values], staged without swizzle
+                const int vb = c & 1;
+                const uint32_t vp = (uint32_t)((c >> 1) & 1);
+                if (c >= 2 && !(ok = wait_bar_warp(cx, wVFree + vb, vp ^ 1, 205))) break;
+                if (!(ok = wait_bar_warp(cx, wVFull + vb, vp, 206))) break;
+                const uint8_t* src = cx.sm + Ly::oVst + vb * Ly::kTileS;
+                uint8_t* dst = cx.sm + Ly::oVt + vb * Ly::kTileS;
+#pragma unroll
+                for (int it = 0; it < 2; ++it) {
+                    const int idx = it * 128 + wtid;          // 256 items of 16 bytes
+                    const int r = idx >> 2, j = idx & 3;
+                    *reinterpret_cast<uint4*>(dst + off_w<DS>(r, 8 * j)) =
+                        *reinterpret_cast<const uint4*>(src + r * 64 + j * 16);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(cx.bar(wVReady + vb)); mbar_arrive(cx.bar(wVEmpty + vb)); }
+            }
+        }
+    } else if (warp < 16) {
+        // =========================== auxiliary warpgroup: state operands, mask, output ============
+        const int w = warp & 3, q = lane & 3, rbase = 16 * w + (lane >> 2);
+        const uint32_t lane_base = (uint32_t)(32 * w) << 16;
+        float b[16];
+        auto write_bt = [&](int g) {
+            uint8_t* bt = cx.sm + Ly::oBt + g * Ly::kTileS;
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    *reinterpret_cast<uint32_t*>(bt + off_w<DS>(rbase + 8 * h, 8 * x + 2 * q)) =
+                        pack_bf16(b[4 * x + 2 * h], b[4 * x + 2 * h + 1]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(wBtReady + g));
+        };
+        // carry-in of every group: accumulator and operand tile
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float2 b2 = *reinterpret_cast<const float2*>(
+                        slice + (int64_t)(g * SG + rbase + 8 * h) * D + js * DS + 8 * x + 2 * q);
+                    b[4 * x + 2 * h] = b2.x; b[4 * x + 2 * h + 1] = b2.y;
+                }
+            tmem_st32(lane_base + tmBg(g), b);
+            tc_fence_before();
+            write_bt(g);
+        }
+        bool ok = true;
+        for (int c = 0; c < nch && ok; ++c) {
+            const uint32_t cp = (uint32_t)(c & 1);
+            const int64_t tok0 = t_begin + (int64_t)c * C;
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+            auto carry = [&](int g) {   // state of group g after this chunk -> operand tile for the next chunk
+                tc_fence_after();
+                tmem_ld32(lane_base + tmBg(g), b);
+                tc_fence_before();
+                write_bt(g);   // its arrival also tells the issuer that the accumulator has been read
+            };
+            for (int g = 0; g < G - 1 && ok; ++g) {
+                if (!(ok = wait_bar_warp(cx, wItemDone + g, cp, 501))) break;
+                if (c + 1 < nch) carry(g);
+            }
+            if (!ok) break;
+            // all groups have accumulated into G: causal mask -> bf16 pairs over G's first 32 columns
+            if (!(ok = wait_bar_warp(cx, wItemDone + G - 1, cp, 502))) break;
+            {
+                float v[32];
+                uint32_t gv[16];
+                tc_fence_after();
+                tmem_ld64(lane_base + tmG, v);
+                tc_fence_before();
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int row = rbase + 8 * h, col = 8 * x + 2 * q;
+                        gv[2 * x + h] = pack_bf16(col <= row ? v[4 * x + 2 * h] : 0.f,
+                                                  col + 1 <= row ? v[4 * x + 2 * h + 1] : 0.f);
+                    }
+                tmem_st_pairs(lane_base + tmG, gv);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(cx.bar(wGtReady));
+            }
+            if (c + 1 < nch) carry(G - 1);
+            // O of the chunk (this CTA's 32 columns)
+            if (!(ok = wait_bar_warp(cx, wOReady, cp, 503))) break;
+            tc_fence_after();
+            tmem_ld32(lane_base + tmO(c), b);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(wOFree + (c & 1)));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                if (row < valid) {
+                    __nv_bfloat16* orow = out + (n * T + tok0 + row) * D + js * DS + 2 * q;
+#pragma unroll
+                    for (int x = 0; x < 4; ++x)
+                        *reinterpret_cast<uint32_t*>(orow + 8 * x) = pack_bf16(b[4 * x + 2 * h], b[4 * x + 2 * h + 1]);
+                }
+            }
+        }
+    } else if (warp == kWProducerWarp) {
+        // =========================== TMA producer ==================================================
+        if (lane == 0) {
+            int issued = 0, v_issued = 0;
+            for (int i = 0; i < nitems; ++i) {
+                const int c = i / G, g = i - c * G, st = i % kWStages;
+                const int tok = (int)(t_begin + (int64_t)c * C);
+                if (i >= kWStages && !wait_bar(cx, wEmpty + st, (uint32_t)(((i / kWStages) - 1) & 1), 301)) break;
+                mbar_arrive_expect_tx(cx.bar(wFull + st), Ly::kTileP);
+                tma_load_4d(cx.sm_u32 + Ly::oStage + st * Ly::kTileP, &map_k, cx.bar(wFull + st), 0, tok, g, (int)n);
+                issued = i + 1;
+                if (g == 0) {
+                    const int vb = c & 1;
+                    if (c >= 2 && !wait_bar(cx, wVEmpty + vb, (uint32_t)(((c >> 1) - 1) & 1), 302)) break;
+                    mbar_arrive_expect_tx(cx.bar(wVFull + vb), Ly::kTileS);
+                    tma_load_4d(cx.sm_u32 + Ly::oVst + vb * Ly::kTileS, &map_vs, cx.bar(wVFull + vb), 0, tok, js, (int)n);
+                    v_issued = c + 1;
+                }
+            }
+            if (*cx.abort_flag) {   // copies in flight must land before the CTA may exit
+                for (int i = max(0, issued - kWStages); i < issued; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(wFull + i % kWStages), (uint32_t)((i / kWStages) & 1)) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
+                for (int c = max(0, v_issued - 2); c < v_issued; ++c) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(wVFull + (c & 1)), (uint32_t)((c >> 1) & 1)) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
+            }
+        }
+    } else {
+        // =========================== MMA issuer ======================================================
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
+        const int Gu = __shfl_sync(0xffffffffu, G, 0);
+        const uint32_t tril_lo = lo_k(smb + Ly::oTril);
+        constexpr uint32_t kI64 = idesc_n(64), kIS = idesc_n(DS);
+        if (elect_one()) {
+            bool ok = true;
+            auto cumsum = [&](int i) -> bool {   // A_loc of item i = tril . pK_g
+                const int st = i % kWStages;
+                if (!wait_bar(cx, wKReady + st, (uint32_t)((i / kWStages) & 1), 401)) return false;
+                tc_fence_after();
+                mma_k64<true, kHiK, 16, kHiMN, 128>(tm + 256 + (i & 1) * 64, tril_lo,
+                                                    lo_mn(smb + Ly::oKt + st * Ly::kTileP), kI64 | kBmn);
+                mma_commit(cx.bar(wXReady + (i & 1)));
+                return true;
+            };
+            auto gv = [&](int c) -> bool {       // O += masked G . V, once per chunk
+                if (!wait_bar(cx, wGtReady, (uint32_t)(c & 1), 406)) return false;
+                tc_fence_after();
+                mma_k64_ta<false, kHiMN, Ly::kStepS>(tm + 448 + (c & 1) * DS, tm + 384,
+                                                     lo_mn_w(smb + Ly::oVt + (c & 1) * Ly::kTileS, Ly::kLboS), kIS | kBmn);
+                mma_commit(cx.bar(wOReady));
+                mma_commit(cx.bar(wVFree + (c & 1)));
+                return true;
+            };
+            if (nitems > 0) ok = cumsum(0);
+            for (int i = 0; i < nitems && ok; ++i) {
+                const int c = i / Gu, g = i - c * Gu, st = i % kWStages, wg = i & 1;
+                if (i + 1 < nitems && !(ok = cumsum(i + 1))) break;      // one item ahead
+                if (g == 0 && c >= 1 && !(ok = gv(c - 1))) break;        // frees G for this chunk
+                // W of the item in tensor memory; state operand of the group written (which also means that
+                // the group's accumulator has been read out after the previous chunk)
+                if (!(ok = wait_bar2(cx, wWReady + wg, (uint32_t)((i >> 1) & 1), wBtReady + g, (uint32_t)(c & 1), 404))) break;
+                if (g == 0) {
+                    if (c >= 2 && !(ok = wait_bar(cx, wOFree + (c & 1), (uint32_t)(((c >> 1) - 1) & 1), 408))) break;
+                    if (!(ok = wait_bar(cx, wVReady + (c & 1), (uint32_t)((c >> 1) & 1), 407))) break;
+                }
+                tc_fence_after();
+                const uint32_t a_w = tm + 256 + wg * 64;
+                const uint32_t kt = smb + Ly::oKt + st * Ly::kTileP;
+                const uint32_t bt_mn = lo_mn_w(smb + Ly::oBt + g * Ly::kTileS, Ly::kLboS);
+                const uint32_t vt_mn = lo_mn_w(smb + Ly::oVt + (c & 1) * Ly::kTileS, Ly::kLboS);
+                const uint32_t dO = tm + 448 + (c & 1) * DS;
+                if (g == 0) {
+                    mma_k64_ta<true, kHiK, 16>(tm + 384, a_w, lo_k(kt), kI64);                 // G  = W . pK^T
+                    mma_k64_ta<true, kHiMN, Ly::kStepS>(dO, a_w, bt_mn, kIS | kBmn);           // O  = W . B_g
+                } else {
+                    mma_k64_ta<false, kHiK, 16>(tm + 384, a_w, lo_k(kt), kI64);                // G += ...
+                    mma_k64_ta<false, kHiMN, Ly::kStepS>(dO, a_w, bt_mn, kIS | kBmn);          // O += ...
+                }
+                mma_k64<false, kHiMN, 128, kHiMN, Ly::kStepS>(tm + g * DS, lo_mn(kt), vt_mn, kIS | kAmn | kBmn);   // B_g += pK^T . V
+                mma_commit(cx.bar(wItemDone + g));
+                mma_commit(cx.bar(wKFree + st));
+            }
+            if (ok && nch > 0) ok = gv(nch - 1);
+            mma_commit(cx.bar(wDrain));
+            const long long t0 = clock64();
+            while (!mbar_try_wait(cx.bar(wDrain), 0) && clock64() - t0 < kWaitCycles) {}
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kWMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn_bf16() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -778,6 +1090,20 @@ bool make_map_bf16(CUtensorMap* map, const void* base, int64_t N, int64_t T, int
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// V [N][T][width] bf16 viewed as (32 values, T tokens, width/32 column blocks, N streams); one box =
+// 32 values x 64 tokens (64-byte rows, no swizzle); tokens past T read as zero
+bool make_map_bf16_slice(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width) {
+    auto fn = encode_fn_bf16();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {DS, (cuuint64_t)T, (cuuint64_t)(width / DS), (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)width * 2, DS * 2, (cuuint64_t)T * width * 2};
+    cuuint32_t box[4] = {DS, (cuuint32_t)C, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int D>
 cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out, const float* carry_in,
                         float* state_out, void* ws, const Dims& dm, int tile_tokens, cudaStream_t stream,
@@ -802,22 +1128,23 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
         return causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, false);
     err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, true);
     if (err != cudaSuccess) return err;
+    if (G > 1) {
+        // all bucket groups in one CTA, the head dimension in slices of 32 columns
+        CUtensorMap mvs;
+        if (!make_map_bf16_slice(&mvs, v, dm.N, dm.T, dm.D)) return cudaErrorInvalidValue;
+        err = cudaFuncSetAttribute(causal_out_wide_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, LayW::kSmem);
+        if (err != cudaSuccess) return err;
+        dim3 wgrid((unsigned)(tiles * (D / DS)), (unsigned)dm.N);
+        causal_out_wide_bf16<<<wgrid, kWThreads, LayW::kSmem, stream>>>(
+            (const __nv_bfloat16*)pq, mk, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
+            dm.eps, status);
+        return cudaGetLastError();
+    }
     err = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<D>::kSmem);
     if (err != cudaSuccess) return err;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = Lay<D>::kSmem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = G;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = G > 1 ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, k3, (const __nv_bfloat16*)pq, mk, mv, (__nv_bfloat16*)out, (const float*)ws,
-                              dm.T, dm.S, G, tile_tokens, dm.eps, status);
+    k3<<<grid, kThreads, Lay<D>::kSmem, stream>>>((const __nv_bfloat16*)pq, mk, mv, (__nv_bfloat16*)out,
+                                                  (const float*)ws, dm.T, dm.S, G, tile_tokens, dm.eps, status);
+    return cudaGetLastError();
 }
 
 }  // namespace

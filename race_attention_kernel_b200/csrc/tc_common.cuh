@@ -194,7 +194,7 @@ __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t&
 __device__ long long* g_trace_buf = nullptr;
 #define RACE_TRACE(role, c, stage)                                                              \
     do {                                                                                        \
-        if (g_trace_buf && blockIdx.x == 1 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (c) < 32) \
+        if (g_trace_buf && blockIdx.x == 1 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (c) >= 0 && (c) < 32) \
             g_trace_buf[((role) * 32 + (c)) * 8 + (stage)] = clock64();                         \
     } while (0)
 #define RACE_TRACE_STUCK(code, bar, parity)                                                     \
@@ -234,6 +234,29 @@ __device__ __forceinline__ bool wait_bar(const Ctx& cx, int bar, uint32_t parity
         }
     }
     return true;
+}
+
+// Two barriers at once (their polls overlap): true when both phases have completed.
+__device__ __forceinline__ bool wait_bar2(const Ctx& cx, int bar_a, uint32_t parity_a, int bar_b,
+                                          uint32_t parity_b, int code) {
+    bool a = mbar_try_wait(cx.bar(bar_a), parity_a), b = mbar_try_wait(cx.bar(bar_b), parity_b);
+    if (a && b) return true;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (true) {
+        if (!a) a = mbar_try_wait(cx.bar(bar_a), parity_a);
+        if (!b) b = mbar_try_wait(cx.bar(bar_b), parity_b);
+        if (a && b) return true;
+        if ((++spins & 63) == 0) {
+            if (*cx.abort_flag) { RACE_TRACE_STUCK(code, a ? bar_b : bar_a, 0); return false; }
+            if (clock64() - t0 > kWaitCycles) {
+                *cx.abort_flag = 1;
+                if (cx.status) atomicCAS(cx.status, 0, code);
+                RACE_TRACE_STUCK(code, a ? bar_b : bar_a, 0);
+                return false;
+            }
+        }
+    }
 }
 
 // Warp-uniform flavour: every lane gets the same answer, so .aligned instructions that follow
