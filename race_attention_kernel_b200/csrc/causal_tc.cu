@@ -752,11 +752,22 @@ bool tensor_supported(const Dims& dm, int dtype) {
 int tensor_chunk_tokens() { return C; }
 
 int tensor_default_tile_tokens(const Dims& dm, int, int sm_count) {
-    // one CTA per SM (and per bucket group): aim for a few waves, tiles of at most 2048 tokens
+    // One CTA per SM (and per bucket group) at a time: the CTAs run in waves of sm_count, so the tile
+    // length (a multiple of the chunk, at most 2048 tokens) is chosen to fill the last wave:
+    // cost = waves x (tokens per tile + the set-up of a CTA, about one and a half chunks).  For long
+    // sequences this stays at 2048; for shorter ones it avoids a mostly empty last wave.
     const int64_t groups = dm.S > 64 ? dm.S / 64 : 1;
-    int tile = 2048;
-    while (tile > C && dm.N * groups * ((dm.T + tile - 1) / tile) < (int64_t)sm_count * 2) tile >>= 1;
-    return tile;
+    const int64_t sms = sm_count > 0 ? sm_count : 148;
+    int best = 2048;
+    double best_cost = 1e300;
+    for (int tile = 2048; tile >= C; tile -= C) {
+        const int64_t ctas = dm.N * groups * ((dm.T + tile - 1) / tile);
+        const int64_t waves = (ctas + sms - 1) / sms;
+        const double cost = (double)waves * (tile + 96.0);
+        if (cost < best_cost * 0.999) { best_cost = cost; best = tile; }
+        if (ctas > 64 * sms) break;   // many waves already: shorter tiles only add state traffic
+    }
+    return best;
 }
 
 size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
