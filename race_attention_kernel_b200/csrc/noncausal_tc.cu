@@ -243,10 +243,21 @@ nc_rows_tc(const NcArgs args, const float* __restrict__ totals, const float* __r
     }
 }
 
+// Tokens per CTA: four CTAs share an SM, so the grid runs in waves of 4 x sm_count; pick the multiple
+// of 64 that minimises waves x (tokens per CTA + the set-up of a CTA, about three chunks' worth: it splits
+// the stream's 64 x 64 matrices into limb tiles).
 int nc_tile_tokens(const Dims& dm, int sm_count) {
-    int tile = 1024;
-    while (tile > 64 && dm.N * ((dm.T + tile - 1) / tile) < (int64_t)sm_count * 16) tile >>= 1;
-    return tile;
+    const int64_t slots = 4 * (int64_t)(sm_count > 0 ? sm_count : 148);
+    int best = 64;
+    double best_cost = 1e300;
+    for (int tile = 4096; tile >= 64; tile -= 64) {
+        const int64_t ctas = dm.N * ((dm.T + tile - 1) / tile);
+        const int64_t waves = (ctas + slots - 1) / slots;
+        const double cost = (double)waves * (tile + 192.0);
+        if (cost < best_cost * 0.999) { best_cost = cost; best = tile; }
+        if (ctas > 64 * slots) break;
+    }
+    return best;
 }
 
 cudaError_t launch_nc(const NcArgs& args, const float* totals, const float* grads, const Dims& dm, int dtype,
