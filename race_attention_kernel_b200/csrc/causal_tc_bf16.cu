@@ -167,6 +167,11 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
     const uint32_t tmB = tmem;                                                   // [0, D)
     auto tmAG = [&](int wg) { return tmem + D + wg * (64 + D); };                // A_loc, then G
     auto tmO = [&](int wg) { return tmem + D + wg * (64 + D) + 64; };            // O
+    // d_k = 64 leaves 192 columns: W / masked G and the triangular ones matrix are MMA A operands in
+    // tensor memory (bf16 pairs, 32 columns each) instead of operand tiles in shared memory
+    constexpr bool kTA = (D == 64);
+    auto tmW = [&](int wg) { return tmem + 320 + wg * 32; };
+    const uint32_t tmTril = tmem + 384;
 
     if (warp < 8) {
         // =========================== worker warpgroups =========================================
@@ -177,6 +182,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
         __nv_bfloat16* out_n = out + n * T * D;
         const __nv_bfloat16* pq_n = pq + n * T * S + g * SG;
         float v[32];
+        uint32_t ov[16];   // W / masked G pairs on their way to tensor memory (d_k = 64)
         uint32_t ph = 0;
         bool ok = true;
         for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
@@ -219,15 +225,22 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                     const float2 pq2 = unpack_bf16(pqv[2 * x + h]);
                     const float a0 = acar[2 * x] + v[4 * x + 2 * h];
                     const float a1 = acar[2 * x + 1] + v[4 * x + 2 * h + 1];
-                    *reinterpret_cast<uint32_t*>(wt + off_w<64>(row, 8 * x + 2 * q)) =
-                        pack_bf16(__fdividef(pq2.x, a0 + eps), __fdividef(pq2.y, a1 + eps));
+                    const uint32_t wp = pack_bf16(__fdividef(pq2.x, a0 + eps), __fdividef(pq2.y, a1 + eps));
+                    if constexpr (kTA) ov[2 * x + h] = wp;
+                    else *reinterpret_cast<uint32_t*>(wt + off_w<64>(row, 8 * x + 2 * q)) = wp;
                     if (h == 1 && w == 3 && (lane >> 2) == 7) {
                         float* an = reinterpret_cast<float*>(cx.sm + Ly::oAcar) + (wg ^ 1) * 64;
                         *reinterpret_cast<float2*>(an + 8 * x + 2 * q) = make_float2(a0, a1);
                     }
                 }
             }
-            fence_proxy_async();
+            if constexpr (kTA) {
+                tmem_st_pairs(lane_base + tmW(wg), ov);
+                tmem_wait_st();
+                tc_fence_before();
+            } else {
+                fence_proxy_async();
+            }
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(cx.bar(bWReady + wg));
@@ -243,11 +256,19 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int row = rbase + 8 * h, col = 8 * x + 2 * q;
-                    *reinterpret_cast<uint32_t*>(wt + off_w<64>(row, col)) =
+                    const uint32_t gp =
                         pack_bf16(col <= row ? v[4 * x + 2 * h] : 0.f, col + 1 <= row ? v[4 * x + 2 * h + 1] : 0.f);
+                    if constexpr (kTA) ov[2 * x + h] = gp;
+                    else *reinterpret_cast<uint32_t*>(wt + off_w<64>(row, col)) = gp;
                 }
             }
-            fence_proxy_async();
+            if constexpr (kTA) {
+                tmem_st_pairs(lane_base + tmW(wg), ov);
+                tmem_wait_st();
+                tc_fence_before();
+            } else {
+                fence_proxy_async();
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(cx.bar(bGtReady + wg));
             // ---- O ---------------------------------------------------------------------------------
@@ -286,6 +307,17 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                     *reinterpret_cast<uint32_t*>(bt + off_w<D>(rbase + 8 * h, dh * 64 + 8 * x + 2 * q)) =
                         pack_bf16(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
         };
+        if constexpr (kTA) {   // tril[t][j] = (j <= t) as an A operand in tensor memory
+            uint32_t tr[16];
+#pragma unroll
+            for (int y = 0; y < 8; ++y)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = rbase + 8 * h, j0 = 8 * y + 2 * q;
+                    tr[2 * y + h] = (j0 <= row ? 0x3F80u : 0u) | (j0 + 1 <= row ? 0x3F800000u : 0u);
+                }
+            tmem_st_pairs(lane_base + tmTril, tr);
+        }
         // carry-in: B -> TMEM accumulator and operand buffer 0; A -> the first chunk's running A
 #pragma unroll
         for (int dh = 0; dh < DH; ++dh) {
@@ -397,7 +429,8 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                 if (!(ok = wait_bar(cx, bKReady + wg, ph, 401))) break;
                 tc_fence_after();
                 // A_loc = tril . pK
-                mma_k64<true, kHiK, 16, kHiMN, 128>(dAG, tril_lo, kt_mn, kI64 | kBmn);
+                if constexpr (D == 64) mma_k64_ta<true, kHiMN, 128>(dAG, tm + 384, kt_mn, kI64 | kBmn);
+                else mma_k64<true, kHiK, 16, kHiMN, 128>(dAG, tril_lo, kt_mn, kI64 | kBmn);
                 mma_commit(cx.bar(bXReady + wg));
                 // B += pK^T . V (N = D)
                 if (!(ok = wait_bar(cx, bVReady + wg, ph, 407))) break;
@@ -409,13 +442,19 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                 if (!(ok = wait_bar(cx, bWReady + wg, ph, 404))) break;
                 if (!(ok = wait_bar(cx, bBtReady + wg, ph, 405))) break;
                 tc_fence_after();
-                mma_k64<true, kHiK, 16, kHiK, 16>(dAG, wt_k, kt_k, kI64);
-                mma_k64<true, kHiK, 16, kHiMN, Ly::kStepV>(dO, wt_k, bt_mn, kID | kBmn);
+                if constexpr (D == 64) {
+                    mma_k64_ta<true, kHiK, 16>(dAG, tm + 320 + wg * 32, kt_k, kI64);
+                    mma_k64_ta<true, kHiMN, Ly::kStepV>(dO, tm + 320 + wg * 32, bt_mn, kID | kBmn);
+                } else {
+                    mma_k64<true, kHiK, 16, kHiK, 16>(dAG, wt_k, kt_k, kI64);
+                    mma_k64<true, kHiK, 16, kHiMN, Ly::kStepV>(dO, wt_k, bt_mn, kID | kBmn);
+                }
                 mma_commit(cx.bar(bGReady + wg));
                 // O += G . V
                 if (!(ok = wait_bar(cx, bGtReady + wg, ph, 406))) break;
                 tc_fence_after();
-                mma_k64<false, kHiK, 16, kHiMN, Ly::kStepV>(dO, wt_k, vt_mn, kID | kBmn);
+                if constexpr (D == 64) mma_k64_ta<false, kHiMN, Ly::kStepV>(dO, tm + 320 + wg * 32, vt_mn, kID | kBmn);
+                else mma_k64<false, kHiK, 16, kHiMN, Ly::kStepV>(dO, wt_k, vt_mn, kID | kBmn);
                 mma_commit(cx.bar(bOReady + wg));
             }
             mma_commit(cx.bar(bDrain + wg));
