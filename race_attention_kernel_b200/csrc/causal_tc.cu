@@ -3,19 +3,24 @@
 // One CTA owns a (stream, state tile) and walks it in chunks of C = 64 tokens.  Per chunk
 // (S = 64 buckets, D = 64 head dim, carry (A [S], B [S,D]) from the tiles before it):
 //     A_in = A + tril_ones . pK            tcgen05.mma   (inclusive running sum inside the chunk)
-//     W    = pQ / (A_in + eps)             CUDA cores, from TMEM
-//     G    = tril(W . pK^T)                tcgen05.mma, masked on the way TMEM -> shared memory
+//     W    = pQ / (A_in + eps)             CUDA cores, TMEM -> registers -> TMEM (MMA A operand)
+//     G    = tril(W . pK^T)                tcgen05.mma, masked on the way TMEM -> registers -> TMEM
 //     O    = W . B + G . V                 tcgen05.mma
 //     B   += pK^T . V                      tcgen05.mma, accumulator resident in TMEM
 // which is the chunk identity of the estimator in src/race_baseline.py:45-51
 // (docs/causal_v2_design.md:70-77).  fp32 inputs are split into bf16 hi + lo limbs and every
 // product runs as hi*hi + hi*lo + lo*hi with fp32 accumulation, so operand error is ~2^-17.
+// pK, V and the state B are limb tiles in shared memory; W, the masked G and the triangular ones
+// matrix are A operands in tensor memory and never touch shared memory.
 //
-// Warp roles (14 warps): two worker warpgroups take alternate chunks (fp32 -> bf16 operand
-// tiles, W, mask of G, output store); a third warpgroup copies the running B from TMEM to its
-// bf16 operand tile after every update; one warp issues TMA loads into a two-stage ring; one
-// warp per worker group issues its tcgen05.mma instructions.  All hand-offs are mbarriers; every wait is bounded and a
-// wait that runs out raises the status word and makes the CTA drain and exit.
+// Warp roles (15 warps): two worker warpgroups take alternate chunks (W, mask of G, output
+// store); a converter warpgroup turns the TMA-staged fp32 pK and V tiles into limb tiles and
+// copies the running B from TMEM to its bf16 operand tile after every update; one warp issues
+// TMA loads into a two-stage ring; one warp per worker group issues its tcgen05.mma
+// instructions.  All hand-offs are mbarriers; every wait is bounded and a wait that runs out
+// raises the status word and makes the CTA drain and exit.
+// With heads = H > 1, V is read and out written in the layout [N/H, T, H, D] (stream n =
+// outer * H + h): V through a five-dimensional tensor map, out with the head stride.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
