@@ -236,15 +236,16 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             for (int x = 0; x < 8; ++x) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const float a0 = acar[2 * x] + v[4 * x + 2 * h];
-                    const float a1 = acar[2 * x + 1] + v[4 * x + 2 * h + 1];
-                    const float w0 = __fdividef(pqv[2 * x + h].x, a0 + eps);
-                    const float w1 = __fdividef(pqv[2 * x + h].y, a1 + eps);
-                    split2(w0, w1, ohi[2 * x + h], olo[2 * x + h]);
+                    // packed fp32x2 arithmetic: (a0, a1) = running A + A_loc; W = pQ / (a + eps)
+                    const float2 a2 = __fadd2_rn(make_float2(acar[2 * x], acar[2 * x + 1]),
+                                                 make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]));
+                    const float2 d2 = __fadd2_rn(a2, make_float2(eps, eps));
+                    const float2 w2 = __fmul2_rn(pqv[2 * x + h], make_float2(__fdividef(1.f, d2.x), __fdividef(1.f, d2.y)));
+                    split2(w2.x, w2.y, ohi[2 * x + h], olo[2 * x + h]);
                     if (h == 1 && w == 3 && (lane >> 2) == 7) {
                         // row 63: the running A after this chunk, for the other group
                         float* an = reinterpret_cast<float*>(cx.sm + oAcar) + (wg ^ 1) * 64;
-                        *reinterpret_cast<float2*>(an + 8 * x + 2 * q) = make_float2(a0, a1);
+                        *reinterpret_cast<float2*>(an + 8 * x + 2 * q) = a2;
                     }
                 }
             }

@@ -183,8 +183,10 @@ __device__ __forceinline__ uint32_t op_off(int row, int col) {
 
 __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t& lo) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    __nv_bfloat162 l = __floats2bfloat162_rn(a - __low2float(h), b - __high2float(h));
     hi = *reinterpret_cast<uint32_t*>(&h);
+    // remainder of both values with one packed fp32x2 add: (a, b) - (hi_a, hi_b)
+    const float2 r = __fadd2_rn(make_float2(a, b), make_float2(-__uint_as_float(hi << 16), -__uint_as_float(hi & 0xffff0000u)));
+    __nv_bfloat162 l = __floats2bfloat162_rn(r.x, r.y);
     lo = *reinterpret_cast<uint32_t*>(&l);
 }
 
