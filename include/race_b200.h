@@ -126,6 +126,20 @@ int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const 
                                 int variant, void* stream, int* status);
 
 /*
+ * Incremental (decode) step: race_b200_causal_fwd for a few NEW tokens per stream (seq_len <= 64,
+ * typically 1) against a running state kept in device memory between calls, i.e. chunked_forward's
+ * state update (src/race_chunked.py:54-63) with a chunk of seq_len tokens, costing one read and one
+ * write of the state.  The reference has no incremental entry point; its launcher only returns the
+ * final state of a full forward (src/causal_v2/kernels/race_causal_fwd.h:101,126-130).
+ *   state_in   nullable (zeros); state layout; sums over all earlier tokens
+ *   state_out  required; receives state_in + sums over the new tokens.  May be the same pointer as
+ *              state_in (updated in place); otherwise the two buffers must not overlap.
+ * Needs no workspace.  L*R <= 2048, heads <= 1, any d_k whose rows are 16-byte multiples.
+ */
+int race_b200_decode_step(const void* probs_q, const void* probs_k, const void* v, void* out,
+                          const float* state_in, float* state_out, const RaceShape* shape, void* stream);
+
+/*
  * Non-causal per-bucket forward (upstream scaling/benchmark_time.py:155-162 as quoted in the
  * reference's analysis/hot-path.md:157-162):
  *   Bs = pK^T V, A = sum_t pK, E = Bs/(A+eps), out = pQ E.

@@ -75,7 +75,7 @@ size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile) {
 
 extern "C" {
 
-int race_b200_version(void) { return 1002; }
+int race_b200_version(void) { return 1003; }
 
 const char* race_b200_error_string(int code) {
     switch (code) {
@@ -189,6 +189,28 @@ int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const 
                                 int variant, void* stream, int* status) {
     return causal_entry(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes,
                         shape, tile_tokens, variant, stream, status, kPhaseOutput);
+}
+
+int race_b200_decode_step(const void* probs_q, const void* probs_k, const void* v, void* out,
+                          const float* state_in, float* state_out, const RaceShape* shape, void* stream) {
+    Dims dm;
+    int rc = check_shape(shape, &dm);
+    if (rc != RACE_OK) return rc;
+    if (dm.H > 1 || dm.S > 2048 || dm.T > decode_max_tokens()) return RACE_ERR_SHAPE;
+    if (!state_out) return RACE_ERR_NULL;
+    if (dm.N == 0) return RACE_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t sf = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D);
+    if (dm.T == 0) {
+        if (state_in == state_out) return RACE_OK;
+        return (int)(state_in ? cudaMemcpyAsync(state_out, state_in, sf * sizeof(float), cudaMemcpyDeviceToDevice, st)
+                              : cudaMemsetAsync(state_out, 0, sf * sizeof(float), st));
+    }
+    if (!probs_q || !probs_k || !v || !out) return RACE_ERR_NULL;
+    if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(out) || !aligned16(state_in) ||
+        !aligned16(state_out))
+        return RACE_ERR_ALIGN;
+    return (int)decode_step_launch(probs_q, probs_k, v, out, state_in, state_out, dm, shape->dtype, st);
 }
 
 namespace {

@@ -47,6 +47,13 @@ cudaError_t noncausal_token_grads_tensor(const void* pk, const void* v, const vo
 cudaError_t bucket_probs(const void* x, const float* planes, void* probs, int64_t rows, int64_t T, int heads,
                          int d, int L, int K, int dtype_x, int dtype_probs, cudaStream_t stream);
 
+// ---- incremental step (decode.cu) -------------------------------------------------------------
+// a few new tokens per stream (dm.T <= decode_max_tokens()) against a running state; state_in may be
+// null (zeros) or equal state_out (in place)
+int decode_max_tokens();
+cudaError_t decode_step_launch(const void* pq, const void* pk, const void* v, void* out, const float* state_in,
+                               float* state_out, const Dims& dm, int dtype, cudaStream_t stream);
+
 // ---- tcgen05 tensor-core causal path (causal_tc.cu) ------------------------------------------
 bool tensor_supported(const Dims& dm, int dtype);
 int tensor_chunk_tokens();

@@ -165,6 +165,30 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
     return out
 
 
+def race_decode_step(probsQ, probsK, V, state: torch.Tensor, eps: float = 1e-6, *,
+                     state_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Incremental step: outputs of T <= 64 new tokens per stream (typically one) given the packed
+    running state [N, S*d_k+S] of everything before them, which is advanced IN PLACE (or written to
+    ``state_out``, leaving ``state`` untouched).  One chunk step of src/race_chunked.py:54-63; start
+    from ``torch.zeros`` or from the state a ``race_causal_prefix(..., return_state=True)`` prefill
+    returned (``pack_state(A, B)``)."""
+    N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
+    if V.dim() != 3:
+        raise RuntimeError("race_decode_step takes V as [N,T,d_k]")
+    dst = state if state_out is None else state_out
+    for st in (state, dst):
+        if (not st.is_cuda or st.device != V.device or st.dtype != torch.float32 or not st.is_contiguous()
+                or st.numel() != N * L * R * (dk + 1)):
+            raise RuntimeError("state must be a contiguous fp32 CUDA state of N*S*(d_k+1) floats")
+    sh = make_shape(N, T, L, R, dk, V.dtype, eps)
+    with torch.cuda.device(V.device):
+        out = torch.empty_like(V)
+        rc = _lib.lib().race_b200_decode_step(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(state),
+                                              _ptr(dst), ctypes.byref(sh), _stream())
+    _lib.check(rc, "race_b200_decode_step")
+    return out
+
+
 def race_tile_totals(probsK, V, *, tile_tokens: int = 0, variant: str = "auto",
                      return_workspace: bool = False):
     """(A [N,L,R], B [N,L,R,d_k]) summed over all T tokens (pass 1 of the sequence-sharded

@@ -106,3 +106,14 @@ def test_python_binding_rejects_cpu_tensors():
     pq = torch.rand(1, 8, 2, 4)
     with pytest.raises(RuntimeError):
         race_causal_prefix(pq, pq, torch.rand(1, 8, 4))
+
+
+def test_decode_step_argument_errors_without_launch():
+    L = _lib.lib()
+    call = lambda sh, state=None: L.race_b200_decode_step(None, None, None, None, None, state, ctypes.byref(sh), None)
+    assert call(_shape(T=1)) == -1                       # state_out is required
+    assert call(_shape(T=65), 256) == -2                 # more new tokens than one step takes
+    assert call(_shape(T=1, heads=8), 256) == -2         # the heads layout is not read by this entry point
+    assert call(_shape(T=1, L=64, R=64), 256) == -2      # S > 2048
+    assert call(_shape(T=1), 256) == -1                  # valid shape, NULL token pointers
+    assert call(_shape(N=0, T=1), 256) == 0              # nothing to do

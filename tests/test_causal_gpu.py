@@ -294,3 +294,64 @@ def test_heads_layout_rejected_where_not_built():
     assert not rk.is_supported(8, 256, 4, 16, 64, torch.float32, "simt", heads=4)    # CUDA-core path
     assert not rk.is_supported(8, 256, 8, 64, 128, torch.float32, "auto", heads=4)   # no tensor path: S=512 fp32
     assert not rk.is_supported(8, 256, 4, 16, 64, torch.float32, "auto", heads=3)    # 8 streams / 3 heads
+
+
+DECODE_SHAPES = [
+    # N, prefill, steps (tokens per step), L, R, dk
+    (8, 256, (1, 1, 1, 1), 4, 16, 64),      # config 1's geometry, token by token after a prefill
+    (3, 0, (1, 2, 5, 64), 4, 16, 64),       # from an empty state, ragged step lengths up to the limit
+    (2, 100, (1, 3), 8, 64, 128),           # config 3's bucket geometry (S = 512, d_k = 128)
+    (5, 33, (1, 7), 2, 8, 40),              # d_k not a multiple of the 32-column slice
+    (200, 16, (1, 1), 4, 16, 64),           # more streams than SMs
+]
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, BF16_TOL)])
+@pytest.mark.parametrize("N,prefill,steps,L,R,dk", DECODE_SHAPES)
+def test_decode_steps_equal_full_forward(N, prefill, steps, L, R, dk, dtype, tol):
+    """Prefill with the full forward, then advance with race_decode_step: every step's outputs and the
+    final state equal the oracle's forward over the whole sequence (src/race_chunked.py:54-63)."""
+    rk = _ops()
+    T = prefill + sum(steps)
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=7 * N + T, dtype=dtype)
+    ref, A_ref, B_ref = _oracle(pQ, pK, V, return_state=True)
+    q, k, v = pQ.cuda(), pK.cuda(), V.cuda()
+    got = torch.empty(N, T, dk, dtype=dtype, device="cuda")
+    if prefill:
+        o, A, B = rk.race_causal_prefix(q[:, :prefill].contiguous(), k[:, :prefill].contiguous(),
+                                        v[:, :prefill].contiguous(), return_state=True)
+        got[:, :prefill] = o
+        state = rk.pack_state(A, B)
+    else:
+        state = torch.zeros(N, L * R * (dk + 1), device="cuda")
+    t0 = prefill
+    for i, n_new in enumerate(steps):
+        sl = slice(t0, t0 + n_new)
+        args = (q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous())
+        if i % 2 == 0:      # in place
+            got[:, sl] = rk.race_decode_step(*args, state)
+        else:               # into a second buffer, the source left untouched
+            before = state.clone()
+            nxt = torch.empty_like(state)
+            got[:, sl] = rk.race_decode_step(*args, state, state_out=nxt)
+            assert torch.equal(state, before)
+            state = nxt
+        t0 += n_new
+    err = ro.rel_l2(got, ref)
+    assert err <= tol, f"outputs rel-L2 {err:.3e}"
+    A, B = rk.unpack_state(state, L, R, dk)
+    assert ro.rel_l2(A, A_ref) <= tol and ro.rel_l2(B, B_ref) <= tol
+
+
+def test_decode_step_rejections():
+    rk = _ops()
+    pQ, pK, V = ro.synthetic_probs(2, 65, 4, 16, 64, seed=1)
+    state = torch.zeros(2, 64 * 65, device="cuda")
+    with pytest.raises(RuntimeError):       # more new tokens than one step takes
+        rk.race_decode_step(pQ.cuda(), pK.cuda(), V.cuda(), state)
+    with pytest.raises(RuntimeError):       # state of the wrong size
+        rk.race_decode_step(pQ[:, :1].contiguous().cuda(), pK[:, :1].contiguous().cuda(),
+                            V[:, :1].contiguous().cuda(), state[:, :-1].contiguous())
+    out = rk.race_decode_step(pQ[:, :0].contiguous().cuda(), pK[:, :0].contiguous().cuda(),
+                              V[:, :0].contiguous().cuda(), state)
+    assert out.shape == (2, 0, 64) and not state.any()
