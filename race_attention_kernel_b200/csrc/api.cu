@@ -196,7 +196,7 @@ int race_b200_decode_step(const void* probs_q, const void* probs_k, const void* 
     Dims dm;
     int rc = check_shape(shape, &dm);
     if (rc != RACE_OK) return rc;
-    if (dm.H > 1 || dm.S > 2048 || dm.T > decode_max_tokens()) return RACE_ERR_SHAPE;
+    if (dm.H > 1 || dm.S > 2048 || dm.T > decode_max_tokens() || dm.N > 0x7fffffff) return RACE_ERR_SHAPE;
     if (!state_out) return RACE_ERR_NULL;
     if (dm.N == 0) return RACE_OK;
     cudaStream_t st = (cudaStream_t)stream;

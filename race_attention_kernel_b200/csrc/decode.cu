@@ -1,10 +1,12 @@
 // Incremental (decode) step of the causal per-bucket forward: a few new tokens per stream against a
 // running state that stays in device memory between calls.  One step of the reference's chunked
-// evaluation (src/race_chunked.py:54-63) with a chunk of 1..kDecodeMaxTokens tokens:
+// evaluation (src/race_chunked.py:54-63) with a chunk of 1..64 tokens:
 //   A += pK_t ;  B += pK_t (x) v_t ;  out_t = sum_s pQ_t[s] * B[s,:] / (A[s] + eps).
 // The work is one read and one write of the state ([S, d_k] + [S] floats per stream): HBM-bound,
-// CUDA cores.  A warp owns 32 consecutive columns of B (128-byte rows), the 8 warps of a CTA split
-// the buckets, and a CTA owns a 32-column slice of one stream.
+// CUDA cores.  One CTA owns one stream.  A thread holds four consecutive columns of B (16-byte
+// accesses), d_k/4 lanes cover a row, so a warp covers 32/(d_k/4) rows per access and the eight warps
+// of the CTA split the buckets.  The rows of B are requested before the token's A / W / pK are
+// staged, eight 16-byte loads per thread in flight, so the state read overlaps the prologue.
 #include "launch.h"
 
 namespace race {
@@ -13,27 +15,30 @@ namespace {
 
 constexpr int kDecodeThreads = 256;
 constexpr int kDecodeWarps = kDecodeThreads / 32;
-constexpr int kDecodeCols = 32;
+constexpr int kDecodeCols = 128;   // columns one pass over the state covers (32 lanes x 4)
+constexpr int kDecodeDepth = 8;    // 16-byte state loads a thread keeps in flight
 
 __device__ __forceinline__ float ld1(const float* p) { return *p; }
 __device__ __forceinline__ float ld1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-__device__ __forceinline__ void st1(float* p, float x) { *p = x; }
-__device__ __forceinline__ void st1(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
 
-// grid (column slices or 1, N).  state_in may be null (zeros) and may equal state_out; in that
-// in-place case the launcher gives one CTA per stream, because every slice reads all of A and A is
-// rewritten at the end.  Shared memory: 3*S + kDecodeWarps*kDecodeCols floats.
+// grid (N).  state_in may be null (zeros) and may equal state_out: a thread only re-reads state it
+// wrote itself, and A is stored after the last read of it.  lpr = lanes per row of B (a power of
+// two, >= min(d_k, 128)/4).  Shared memory: 3*S + kDecodeWarps*kDecodeCols floats.
 template <typename Tin>
-__global__ void __launch_bounds__(kDecodeThreads)
+__global__ void __launch_bounds__(kDecodeThreads, 4)
 decode_step(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Tin* __restrict__ v, Tin* __restrict__ out,
-            const float* state_in, float* state_out, int T, int S, int D, float eps) {
-    extern __shared__ float sm[];
+            const float* state_in, float* state_out, int T, int S, int D, float eps, int lpr_log2) {
+    extern __shared__ __align__(16) float sm[];
     float* a = sm;             // running A
     float* w = sm + S;         // pQ / (A + eps) of the current token
     float* pks = sm + 2 * S;   // pK of the current token
-    float* red = sm + 3 * S;   // [warps][32] partial outputs
+    float* red = sm + 3 * S;   // [warps][128] partial outputs
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int64_t n = blockIdx.y;
+    const int lpr = 1 << lpr_log2;
+    const int cl = lane & (lpr - 1);              // column quad of this lane
+    const int rows_iter = kDecodeWarps * (32 >> lpr_log2);     // rows of B the CTA covers per access
+    const int row0 = warp * (32 >> lpr_log2) + (lane >> lpr_log2);
+    const int64_t n = blockIdx.x;
     const int64_t sf = (int64_t)state_floats_per_stream(S, D);
     const float* sin = state_in ? state_in + n * sf : nullptr;
     float* sout = state_out + n * sf;
@@ -42,14 +47,27 @@ decode_step(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Tin* _
     const Tin* v_n = v + n * (int64_t)T * D;
     Tin* out_n = out + n * (int64_t)T * D;
     const int slices = (D + kDecodeCols - 1) / kDecodeCols;
+    // all rows of a thread fit its registers: B stays there across the tokens and is stored once
+    const bool fits = S <= kDecodeDepth * rows_iter;
 
-    for (int slice = blockIdx.x; slice < slices; slice += gridDim.x) {
-        const int c = slice * kDecodeCols + lane;
+    for (int slice = 0; slice < slices; ++slice) {
+        const int c = slice * kDecodeCols + cl * 4;
         const bool cv = c < D;
-        __syncthreads();  // the previous slice is done with a / w / pks / red
+        __syncthreads();  // the previous slice is done with a
         for (int s = tid; s < S; s += kDecodeThreads) a[s] = sin ? sin[(int64_t)S * D + s] : 0.f;
+        float4 b[kDecodeDepth];
         for (int t = 0; t < T; ++t) {
-            __syncthreads();
+            // the first token reads the incoming state, later tokens what this thread wrote
+            const float* bsrc = (t == 0) ? sin : sout;
+            if (!(fits && t > 0)) {
+#pragma unroll
+                for (int i = 0; i < kDecodeDepth; ++i) {
+                    const int s = row0 + i * rows_iter;
+                    b[i] = (cv && s < S && bsrc) ? *reinterpret_cast<const float4*>(bsrc + (int64_t)s * D + c)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            __syncthreads();  // readers of w / pks / red of the previous token are done; a is initialised
             for (int s = tid; s < S; s += kDecodeThreads) {
                 const float k = ld1(pk_n + (int64_t)t * S + s);
                 const float an = a[s] + k;
@@ -57,34 +75,51 @@ decode_step(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Tin* _
                 pks[s] = k;
                 w[s] = ld1(pq_n + (int64_t)t * S + s) / (an + eps);
             }
+            const float4 vv = cv ? load4(v_n + (int64_t)t * D + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             __syncthreads();
-            const float vc = cv ? ld1(v_n + (int64_t)t * D + c) : 0.f;
-            // the first token reads the incoming state, later tokens what this thread wrote
-            const float* bsrc = (t == 0) ? sin : sout;
-            float acc = 0.f;
-            if (cv) {
-#pragma unroll 4
-                for (int s = warp; s < S; s += kDecodeWarps) {
-                    float b = bsrc ? bsrc[(int64_t)s * D + c] : 0.f;
-                    b = fmaf(pks[s], vc, b);
-                    sout[(int64_t)s * D + c] = b;
-                    acc = fmaf(w[s], b, acc);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int base = 0; base < S; base += kDecodeDepth * rows_iter) {
+#pragma unroll
+                for (int i = 0; i < kDecodeDepth; ++i) {
+                    const int s = base + row0 + i * rows_iter;
+                    if (cv && s < S) {
+                        const float k = pks[s], ws = w[s];
+                        float4 x = b[i];
+                        x.x = fmaf(k, vv.x, x.x); x.y = fmaf(k, vv.y, x.y);
+                        x.z = fmaf(k, vv.z, x.z); x.w = fmaf(k, vv.w, x.w);
+                        if (!fits || t == T - 1) *reinterpret_cast<float4*>(sout + (int64_t)s * D + c) = x;
+                        if (fits) b[i] = x;
+                        acc.x = fmaf(ws, x.x, acc.x); acc.y = fmaf(ws, x.y, acc.y);
+                        acc.z = fmaf(ws, x.z, acc.z); acc.w = fmaf(ws, x.w, acc.w);
+                    }
+                    if (fits) continue;
+                    const int s2 = s + kDecodeDepth * rows_iter;   // the same slot of the next block of rows
+                    b[i] = (cv && s2 < S && bsrc) ? *reinterpret_cast<const float4*>(bsrc + (int64_t)s2 * D + c)
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
-            red[warp * kDecodeCols + lane] = acc;
+            // lanes that share a column quad hold different rows: add them up, then the warps
+            for (int off = lpr; off < 32; off <<= 1) {
+                acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+                acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+                acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+                acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+            }
+            if (lane < lpr) *reinterpret_cast<float4*>(red + warp * kDecodeCols + cl * 4) = acc;
             __syncthreads();
-            if (warp == 0 && cv) {
-                float o = 0.f;
+            if (tid < lpr && cv) {
+                float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                for (int i = 0; i < kDecodeWarps; ++i) o += red[i * kDecodeCols + lane];
-                st1(out_n + (int64_t)t * D + c, o);
+                for (int i = 0; i < kDecodeWarps; ++i) {
+                    const float4 x = *reinterpret_cast<const float4*>(red + i * kDecodeCols + tid * 4);
+                    o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
+                }
+                store4_stream(out_n + (int64_t)t * D + c, o);
             }
         }
     }
     __syncthreads();
-    // every CTA of a stream holds the same A; the first one stores it
-    if (blockIdx.x == 0)
-        for (int s = tid; s < S; s += kDecodeThreads) sout[(int64_t)S * D + s] = a[s];
+    for (int s = tid; s < S; s += kDecodeThreads) sout[(int64_t)S * D + s] = a[s];
 }
 
 }  // namespace
@@ -93,36 +128,20 @@ int decode_max_tokens() { return 64; }
 
 cudaError_t decode_step_launch(const void* pq, const void* pk, const void* v, void* out, const float* state_in,
                                float* state_out, const Dims& dm, int dtype, cudaStream_t stream) {
-    const int slices = (dm.D + kDecodeCols - 1) / kDecodeCols;
-    const bool in_place = state_in == state_out;
-    const int64_t max_y = 65535;
+    const int width = dm.D < kDecodeCols ? dm.D : kDecodeCols;
+    int lpr_log2 = 0;
+    while ((4 << lpr_log2) < width) ++lpr_log2;
     const size_t smem = (size_t)(3 * dm.S + kDecodeWarps * kDecodeCols) * sizeof(float);
-    for (int64_t n0 = 0; n0 < dm.N; n0 += max_y) {
-        const int64_t nn = dm.N - n0 < max_y ? dm.N - n0 : max_y;
-        dim3 grid(in_place ? 1 : slices, (unsigned)nn);
-        const int64_t sf = state_floats_per_stream(dm.S, dm.D);
-        const float* sin = state_in ? state_in + n0 * sf : nullptr;
-        float* sout = state_out + n0 * sf;
-        const int64_t T = dm.T;
-        if (dtype == RACE_DTYPE_BF16) {
-            auto* q = (const __nv_bfloat16*)pq + n0 * T * dm.S;
-            auto* k = (const __nv_bfloat16*)pk + n0 * T * dm.S;
-            auto* vv = (const __nv_bfloat16*)v + n0 * T * dm.D;
-            auto* o = (__nv_bfloat16*)out + n0 * T * dm.D;
-            decode_step<__nv_bfloat16><<<grid, kDecodeThreads, smem, stream>>>(q, k, vv, o, sin, sout, (int)T, dm.S,
-                                                                              dm.D, dm.eps);
-        } else {
-            auto* q = (const float*)pq + n0 * T * dm.S;
-            auto* k = (const float*)pk + n0 * T * dm.S;
-            auto* vv = (const float*)v + n0 * T * dm.D;
-            auto* o = (float*)out + n0 * T * dm.D;
-            decode_step<float><<<grid, kDecodeThreads, smem, stream>>>(q, k, vv, o, sin, sout, (int)T, dm.S, dm.D,
-                                                                       dm.eps);
-        }
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-    }
-    return cudaSuccess;
+    const unsigned grid = (unsigned)dm.N;
+    if (dtype == RACE_DTYPE_BF16)
+        decode_step<__nv_bfloat16><<<grid, kDecodeThreads, smem, stream>>>(
+            (const __nv_bfloat16*)pq, (const __nv_bfloat16*)pk, (const __nv_bfloat16*)v, (__nv_bfloat16*)out, state_in,
+            state_out, (int)dm.T, dm.S, dm.D, dm.eps, lpr_log2);
+    else
+        decode_step<float><<<grid, kDecodeThreads, smem, stream>>>((const float*)pq, (const float*)pk, (const float*)v,
+                                                                  (float*)out, state_in, state_out, (int)dm.T, dm.S,
+                                                                  dm.D, dm.eps, lpr_log2);
+    return cudaGetLastError();
 }
 
 }  // namespace race
