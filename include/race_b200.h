@@ -126,6 +126,21 @@ int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const 
                                 int variant, void* stream, int* status);
 
 /*
+ * Causal forward in the GLOBAL-normalisation form (paper Algorithm 1 made causal, the estimator of
+ * the reference's own CUDA kernels and of race_causal_reference, src/causal_v2/reference.py:106-127):
+ *   out[n,t,:] = (sum_s pQ[n,t,s] * B_t[n,s,:]) / (sum_s pQ[n,t,s] * A_t[n,s])
+ * with the prefixes A_t, B_t of race_b200_causal_fwd; one denominator per token, shape.eps is not
+ * used, and a row whose denominator is exactly 0 is written as 0 (:77-81).  carry_in / state_out /
+ * workspace as in race_b200_causal_fwd with RACE_VARIANT_SIMT (the CUDA-core kernels compute this
+ * form; size the workspace with that variant); heads <= 1.
+ * Replaces race_causal_forward (src/causal_v2/kernels/race_causal_fwd.h:126-130) at the
+ * probabilities boundary for callers that want the reference kernels' estimator.
+ */
+int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const void* v, void* out,
+                                const float* carry_in, float* state_out, void* workspace,
+                                size_t workspace_bytes, const RaceShape* shape, int tile_tokens, void* stream);
+
+/*
  * Incremental (decode) step: race_b200_causal_fwd for a few NEW tokens per stream (seq_len <= 64,
  * typically 1) against a running state kept in device memory between calls, i.e. chunked_forward's
  * state update (src/race_chunked.py:54-63) with a chunk of seq_len tokens, costing one read and one

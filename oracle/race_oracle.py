@@ -120,6 +120,37 @@ def causal_prefix_chunked(probsQ, probsK, V, chunk: int = 4096, eps: float = EPS
     return out
 
 
+def causal_prefix_global(probsQ: torch.Tensor, probsK: torch.Tensor, V: torch.Tensor, carry=None,
+                         return_state: bool = False, chunk: int = 256):
+    """Global-normalisation causal form (paper Algorithm 1 made causal; the estimator of the
+    reference's own CUDA kernels): out[n,t,:] = (pQ_t . B_t) / (pQ_t . A_t) with the same inclusive
+    prefixes A_t, B_t as ``causal_prefix``, one denominator per token, no eps, and an output row of 0
+    where the denominator is exactly 0 (src/causal_v2/reference.py:77-81,106-127), evaluated a block of
+    tokens at a time with the running (A, B) carried (:84-103)."""
+    N, T, L, R = probsK.shape
+    dk = V.shape[-1]
+    S = L * R
+    if carry is None:
+        A = torch.zeros(N, L, R, dtype=V.dtype)
+        B = torch.zeros(N, L, R, dk, dtype=V.dtype)
+    else:
+        A, B = carry[0].clone(), carry[1].clone()
+    out = torch.empty(N, T, dk, dtype=V.dtype)
+    for t0 in range(0, T, chunk):
+        t1 = min(t0 + chunk, T)
+        pk, q, v = probsK[:, t0:t1], probsQ[:, t0:t1].reshape(N, t1 - t0, S), V[:, t0:t1]
+        mass = A.unsqueeze(1) + pk.cumsum(dim=1)
+        values = B.unsqueeze(1) + (pk.unsqueeze(-1) * v.unsqueeze(2).unsqueeze(3)).cumsum(dim=1)
+        num = torch.einsum("nts,ntsd->ntd", q, values.reshape(N, t1 - t0, S, dk))
+        den = torch.einsum("nts,nts->nt", q, mass.reshape(N, t1 - t0, S)).unsqueeze(-1)
+        empty = den == 0
+        out[:, t0:t1] = torch.where(empty, torch.zeros_like(num), num / torch.where(empty, torch.ones_like(den), den))
+        A, B = mass[:, -1].clone(), values[:, -1].clone()
+    if return_state:
+        return out, A, B
+    return out
+
+
 def tile_totals(probsK: torch.Tensor, V: torch.Tensor):
     """(A_tot [N,L,R], B_tot [N,L,R,d_k]) over all T tokens: the ``pref[:, -1:]`` carry of
     src/race_chunked.py:62-63 without forming the prefixes."""

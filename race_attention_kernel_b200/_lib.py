@@ -25,6 +25,7 @@ EXPORTS = [
     "race_b200_noncausal_bwd_workspace_bytes", "race_b200_noncausal_bwd",
     "race_b200_bucket_probs", "race_b200_bucket_probs_streams", "race_b200_causal_fwd_host",
     "race_b200_static_scratch_bytes", "race_b200_causal_fwd_static", "race_b200_decode_step",
+    "race_b200_causal_fwd_global",
 ]
 
 
@@ -79,6 +80,8 @@ def lib() -> ctypes.CDLL:
     L.race_b200_static_scratch_bytes.argtypes = []
     L.race_b200_causal_fwd_static.restype = i32
     L.race_b200_causal_fwd_static.argtypes = [vp, vp, vp, vp, vp, vp, shp, i32, i32, vp, vp]
+    L.race_b200_causal_fwd_global.restype = i32
+    L.race_b200_causal_fwd_global.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, vp]
     L.race_b200_decode_step.restype = i32
     L.race_b200_decode_step.argtypes = [vp, vp, vp, vp, vp, vp, shp, vp]
     return L

@@ -75,7 +75,7 @@ size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile) {
 
 extern "C" {
 
-int race_b200_version(void) { return 1003; }
+int race_b200_version(void) { return 1004; }
 
 const char* race_b200_error_string(int code) {
     switch (code) {
@@ -130,7 +130,7 @@ size_t race_b200_causal_workspace_bytes(const RaceShape* shape, int tile_tokens,
 static int causal_entry(const void* probs_q, const void* probs_k, const void* v, void* out,
                         const float* carry_in, float* state_out, void* workspace,
                         size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
-                        int variant, void* stream, int* status, int phases) {
+                        int variant, void* stream, int* status, int phases, bool global_norm = false) {
     Dims dm;
     int rc = check_shape(shape, &dm);
     if (rc != RACE_OK) return rc;
@@ -160,12 +160,13 @@ static int causal_entry(const void* probs_q, const void* probs_k, const void* v,
         !aligned16(workspace) || !aligned16(carry_in) || !aligned16(state_out))
         return RACE_ERR_ALIGN;
     if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, var, tile)) return RACE_ERR_WORKSPACE;
+    if (global_norm && var != RACE_VARIANT_SIMT) return RACE_ERR_VARIANT;
     if (var == RACE_VARIANT_TENSOR)
         return (int)causal_fwd_tensor(probs_q, probs_k, v, out, carry_in, state_out, workspace,
                                       dm, shape->dtype, tile, st, status, phases);
     return (int)causal_fwd_simt(probs_q, probs_k, v, out, carry_in, state_out, (float*)workspace,
                                 dm, shape->dtype, tile, /*totals_only=*/!want_out, st,
-                                /*skip_output=*/false, /*skip_totals=*/!(phases & kPhaseTotals));
+                                /*skip_output=*/false, /*skip_totals=*/!(phases & kPhaseTotals), global_norm);
 }
 
 int race_b200_causal_fwd(const void* probs_q, const void* probs_k, const void* v, void* out,
@@ -189,6 +190,13 @@ int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const 
                                 int variant, void* stream, int* status) {
     return causal_entry(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes,
                         shape, tile_tokens, variant, stream, status, kPhaseOutput);
+}
+
+int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const void* v, void* out,
+                                const float* carry_in, float* state_out, void* workspace,
+                                size_t workspace_bytes, const RaceShape* shape, int tile_tokens, void* stream) {
+    return causal_entry(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes, shape,
+                        tile_tokens, RACE_VARIANT_SIMT, stream, nullptr, kPhaseAll, /*global_norm=*/true);
 }
 
 int race_b200_decode_step(const void* probs_q, const void* probs_k, const void* v, void* out,

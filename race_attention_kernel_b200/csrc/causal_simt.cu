@@ -161,7 +161,10 @@ tile_scan(float* __restrict__ ws, const float* __restrict__ carry_in, float* __r
 // ------------------------------------------------------------------------------------------
 // K3: outputs
 // ------------------------------------------------------------------------------------------
-template <typename Tin, int SPT, int DV>
+// GLOBAL: the global-normalisation estimator (src/causal_v2/reference.py:106-127) on the same states:
+// W = pQ, out = (W B + tril(W pK^T) V) / den with den_t = pQ_t . A_t = pQ_t . A_carry + rowsum(tril(W pK^T)),
+// and an output row of 0 where den is exactly 0 (:77-81).
+template <typename Tin, int SPT, int DV, bool GLOBAL>
 __global__ void __launch_bounds__(kSimtThreads)
 causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Tin* __restrict__ v,
                 Tin* __restrict__ out, const float* __restrict__ ws, Dims dm, int tile_tokens,
@@ -234,7 +237,8 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
             for (int j = 0; j < Ly::SEGLEN; ++j) {
                 const int t = seg * Ly::SEGLEN + j;
                 a += sK[t * Ly::LDS + scol];
-                sQ[t * Ly::LDS + scol] = (scol < s_valid) ? sQ[t * Ly::LDS + scol] / (a + dm.eps) : 0.f;
+                const float q = sQ[t * Ly::LDS + scol];
+                sQ[t * Ly::LDS + scol] = (scol < s_valid) ? (GLOBAL ? q : q / (a + dm.eps)) : 0.f;
             }
             if (seg == Ly::NSEG - 1) sA[(a_cur ^ 1) * Ly::SG + scol] = a;
         }
@@ -271,9 +275,16 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
         for (int i = 0; i < 2; ++i)
 #pragma unroll
             for (int j = 0; j < 4 * DV; ++j) o[i][j] = 0.f;
+        float den0 = 0.f, den1 = 0.f;                       // GLOBAL only
+        const float* sAc = sA + (a_cur ^ 1) * Ly::SG;       // A before this chunk
 #pragma unroll 4
         for (int s = 0; s < Ly::SG; ++s) {
             const float w0 = sQ[(ty * 2) * Ly::LDS + s], w1 = sQ[(ty * 2 + 1) * Ly::LDS + s];
+            if (GLOBAL) {
+                const float ac = sAc[s];
+                den0 = fmaf(w0, ac, den0);
+                den1 = fmaf(w1, ac, den1);
+            }
 #pragma unroll
             for (int dv = 0; dv < DV; ++dv) {
                 const float4 b = *reinterpret_cast<const float4*>(sB + s * Ly::LDD + dv * 64 + tx * 4);
@@ -286,6 +297,7 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
 #pragma unroll 4
         for (int j = 0; j < C; ++j) {
             const float g0 = sG[(ty * 2) * Ly::LDG + j], g1 = sG[(ty * 2 + 1) * Ly::LDG + j];
+            if (GLOBAL) { den0 += g0; den1 += g1; }
 #pragma unroll
             for (int dv = 0; dv < DV; ++dv) {
                 const float4 b = *reinterpret_cast<const float4*>(sV + j * Ly::LDD + dv * 64 + tx * 4);
@@ -319,6 +331,12 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int t = ty * 2 + i;
+                if (GLOBAL) {
+                    const float den = i ? den1 : den0;
+                    const float r = den == 0.f ? 0.f : 1.f / den;
+#pragma unroll
+                    for (int j = 0; j < 4 * DV; ++j) o[i][j] *= r;
+                }
                 if (t < valid) {
 #pragma unroll
                     for (int dv = 0; dv < DV; ++dv) {
@@ -339,6 +357,10 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
                 for (int dv = 0; dv < DV; ++dv)
                     *reinterpret_cast<float4*>(sO + (ty * 2 + i) * Ly::LDD + dv * 64 + tx * 4) =
                         make_float4(o[i][dv * 4], o[i][dv * 4 + 1], o[i][dv * 4 + 2], o[i][dv * 4 + 3]);
+            if (GLOBAL && tx == 0) {   // this group's share of the denominators, in the row padding
+                sO[(ty * 2) * Ly::LDD + Ly::DP] = den0;
+                sO[(ty * 2 + 1) * Ly::LDD + Ly::DP] = den1;
+            }
             cg::cluster_group cluster = cg::this_cluster();
             cluster.sync();
             // rows are dealt round-robin to the CTAs of the cluster
@@ -347,10 +369,16 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
                 const int c = (idx % (Ly::DP / 4)) * 4;
                 if ((t % groups) != group || t >= valid || c >= dm.D) continue;
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float den = 0.f;
                 for (int g = 0; g < groups; ++g) {
                     const float* remote = cluster.map_shared_rank(sO, g);
                     const float4 x = *reinterpret_cast<const float4*>(remote + t * Ly::LDD + c);
                     acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+                    if (GLOBAL) den += remote[t * Ly::LDD + Ly::DP];
+                }
+                if (GLOBAL) {
+                    const float r = den == 0.f ? 0.f : 1.f / den;
+                    acc.x *= r; acc.y *= r; acc.z *= r; acc.w *= r;
                 }
                 store4_stream(out_n + (c0 + t) * dm.D + c, acc);
             }
@@ -371,7 +399,8 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
 template <typename Tin, int SPT, int DV>
 cudaError_t launch_simt(const Tin* pq, const Tin* pk, const Tin* v, Tin* out, const float* carry_in,
                         float* state_out, float* ws, const Dims& dm, int tile_tokens, int groups,
-                        bool totals_only, bool skip_output, bool skip_totals, cudaStream_t stream) {
+                        bool totals_only, bool skip_output, bool skip_totals, bool global_norm,
+                        cudaStream_t stream) {
     using Ly = SimtLayout<SPT, DV>;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const int sf = state_floats_per_stream(dm.S, dm.D);
@@ -391,7 +420,7 @@ cudaError_t launch_simt(const Tin* pq, const Tin* pk, const Tin* v, Tin* out, co
     if (err != cudaSuccess || totals_only || skip_output) return err;
 
     const size_t smem3 = (size_t)(groups > 1 ? Ly::floats_cluster : Ly::floats_single) * sizeof(float);
-    auto kern = causal_out_simt<Tin, SPT, DV>;
+    auto kern = global_norm ? causal_out_simt<Tin, SPT, DV, true> : causal_out_simt<Tin, SPT, DV, false>;
     err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
@@ -413,7 +442,7 @@ template <typename Tin>
 cudaError_t dispatch_simt(const void* pq, const void* pk, const void* v, void* out,
                           const float* carry_in, float* state_out, float* ws, const Dims& dm,
                           int tile_tokens, bool totals_only, bool skip_output, bool skip_totals,
-                          cudaStream_t stream) {
+                          bool global_norm, cudaStream_t stream) {
     const int groups = simt_groups(dm.S);
     const int sg = dm.S > kGroupBuckets ? kGroupBuckets : dm.S;
     const int spt = sg <= 16 ? 1 : (sg <= 32 ? 2 : 4);
@@ -422,7 +451,7 @@ cudaError_t dispatch_simt(const void* pq, const void* pk, const void* v, void* o
     if (spt == SPT_ && dv == DV_)                                                                  \
         return launch_simt<Tin, SPT_, DV_>((const Tin*)pq, (const Tin*)pk, (const Tin*)v, (Tin*)out, \
                                            carry_in, state_out, ws, dm, tile_tokens, groups,       \
-                                           totals_only, skip_output, skip_totals, stream);
+                                           totals_only, skip_output, skip_totals, global_norm, stream);
     RACE_SIMT_CASE(1, 1) RACE_SIMT_CASE(2, 1) RACE_SIMT_CASE(4, 1)
     RACE_SIMT_CASE(1, 2) RACE_SIMT_CASE(2, 2) RACE_SIMT_CASE(4, 2)
 #undef RACE_SIMT_CASE
@@ -462,12 +491,12 @@ int simt_default_tile_tokens(const Dims& dm, int sm_count) {
 cudaError_t causal_fwd_simt(const void* pq, const void* pk, const void* v, void* out,
                             const float* carry_in, float* state_out, float* ws, const Dims& dm,
                             int dtype, int tile_tokens, bool totals_only, cudaStream_t stream,
-                            bool skip_output, bool skip_totals) {
+                            bool skip_output, bool skip_totals, bool global_norm) {
     if (dtype == RACE_DTYPE_F32)
         return dispatch_simt<float>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens,
-                                    totals_only, skip_output, skip_totals, stream);
+                                    totals_only, skip_output, skip_totals, global_norm, stream);
     return dispatch_simt<__nv_bfloat16>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens,
-                                        totals_only, skip_output, skip_totals, stream);
+                                        totals_only, skip_output, skip_totals, global_norm, stream);
 }
 
 }  // namespace race

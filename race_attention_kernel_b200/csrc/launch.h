@@ -12,11 +12,12 @@ int simt_groups(int S);
 bool simt_supported(const Dims& dm);
 int simt_default_tile_tokens(const Dims& dm, int sm_count);
 // tile totals -> scan -> outputs; totals_only stops after the scan and writes only state_out;
-// skip_output stops after the scan but leaves the exclusive tile prefixes in ws.
+// skip_output stops after the scan but leaves the exclusive tile prefixes in ws; global_norm selects
+// the global-normalisation estimator (one denominator per token) in the output pass.
 cudaError_t causal_fwd_simt(const void* pq, const void* pk, const void* v, void* out,
                             const float* carry_in, float* state_out, float* ws, const Dims& dm,
                             int dtype, int tile_tokens, bool totals_only, cudaStream_t stream,
-                            bool skip_output = false, bool skip_totals = false);
+                            bool skip_output = false, bool skip_totals = false, bool global_norm = false);
 
 // in-place exclusive scan over the per-tile totals in ws (+ carry_in), inclusive total to state_out
 cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out, const Dims& dm,

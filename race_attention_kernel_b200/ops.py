@@ -112,7 +112,8 @@ def is_supported(N, T, L, R, dk, dtype=torch.float32, variant="auto", heads: int
 
 def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
                        return_state: bool = False, tile_tokens: int = 0, variant: str = "auto",
-                       out: torch.Tensor | None = None, totals_workspace: torch.Tensor | None = None):
+                       out: torch.Tensor | None = None, totals_workspace: torch.Tensor | None = None,
+                       normalization: str = "bucket"):
     """out[n,t,:] = sum_s pQ[n,t,s] * B_t[n,s,:] / (A_t[n,s] + eps) with inclusive prefixes
     A_t, B_t (src/race_baseline.py:45-51).
 
@@ -123,6 +124,10 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
     carry_in: None, a packed state [N, S*d_k+S] or a tuple (A [N,L,R], B [N,L,R,d_k]) holding the
     sums over tokens before this call's first token.  return_state=True also returns (A, B)
     after the last token.  tile_tokens / variant are test hooks (0 / "auto" = automatic).
+
+    normalization="global" computes the global-normalisation estimator instead (one denominator per
+    token, no eps: out_t = (pQ_t . B_t) / (pQ_t . A_t), src/causal_v2/reference.py:106-127) on the
+    CUDA-core kernels; states and carries are the same quantities in both forms.
     """
     N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
     if variant not in _lib.VARIANTS:
@@ -130,6 +135,13 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
     L_ = _lib.lib()
     sh = make_shape(N, T, L, R, dk, V.dtype, eps, _heads(V))
     var = _lib.VARIANTS[variant]
+    if normalization not in ("bucket", "global"):
+        raise RuntimeError(f"unknown normalization {normalization!r}")
+    glob = normalization == "global"
+    if glob:
+        if variant == "tensor" or totals_workspace is not None or V.dim() != 3:
+            raise RuntimeError("normalization='global' runs on the CUDA-core kernels with V [N,T,d_k] only")
+        var = _lib.VARIANTS["simt"]
     carry = None
     if carry_in is not None:
         carry = pack_state(*carry_in) if isinstance(carry_in, (tuple, list)) else carry_in
@@ -151,9 +163,14 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
         else:
             entry, ws = L_.race_b200_causal_fwd, torch.empty(max(ws_bytes, 16), dtype=torch.uint8,
                                                              device=V.device)
-        rc = entry(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry),
-                   _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh),
-                   tile_tokens, var, _stream(), _ptr(_status_word(V.device)))
+        if glob:
+            rc = L_.race_b200_causal_fwd_global(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry),
+                                                _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh), tile_tokens,
+                                                _stream())
+        else:
+            rc = entry(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry),
+                       _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh),
+                       tile_tokens, var, _stream(), _ptr(_status_word(V.device)))
     _lib.check(rc, "race_b200_causal_fwd")
     if os.environ.get("RACE_B200_CHECK_STATUS") == "1":
         code = device_status(V.device)

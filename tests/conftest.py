@@ -34,6 +34,24 @@ def golden():
     return np.load(GOLDEN_PATH)
 
 
+GLOBAL_CASES = ["g_k4l4", "g_k2l2", "g_k6l8_d128", "g_k3l2_d32", "g_k4l4_t700"]
+
+
+@pytest.fixture(scope="session")
+def golden_global():
+    """Global-normalisation vectors written by tests/golden/make_golden_global.py from the reference's
+    race_causal_reference."""
+    return np.load(os.path.join(ROOT, "tests", "golden", "race_global_golden.npz"))
+
+
+def global_case(golden_global, name):
+    """(pQ [N,T,L,R], pK, V [N,T,d], out [N,T,d]) of one stored case, streams flattened."""
+    B, H, T, d, L, R = (int(x) for x in golden_global[f"{name}/cfg"])
+    t = {k: torch.from_numpy(golden_global[f"{name}/{k}"]) for k in ("phi_q", "phi_k", "v", "out")}
+    return (t["phi_q"].reshape(B * H, T, L, R), t["phi_k"].reshape(B * H, T, L, R),
+            t["v"].reshape(B * H, T, d), t["out"].reshape(B * H, T, d))
+
+
 def draw_kvq(M, B, T, H, dk, dtype, seed=0):
     """Inputs drawn the way the reference's tests draw them (src/test_equivalence.py:21-24):
     one generator seeded 0, order K, V, Q."""

@@ -117,3 +117,13 @@ def test_decode_step_argument_errors_without_launch():
     assert call(_shape(T=1, L=64, R=64), 256) == -2      # S > 2048
     assert call(_shape(T=1), 256) == -1                  # valid shape, NULL token pointers
     assert call(_shape(N=0, T=1), 256) == 0              # nothing to do
+
+
+def test_global_form_argument_errors_without_launch():
+    L = _lib.lib()
+    call = lambda sh: L.race_b200_causal_fwd_global(None, None, None, None, None, None, None, 0, ctypes.byref(sh),
+                                                    0, None)
+    assert call(_shape(heads=8)) == -6                  # the heads layout is read by the fp32 tensor kernels only
+    assert call(_shape(dk=96 * 4)) == -6                # outside the CUDA-core kernels' range
+    assert call(_shape()) == -1                         # valid shape, NULL pointers
+    assert call(_shape(T=0)) == 0                       # nothing to launch

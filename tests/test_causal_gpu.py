@@ -355,3 +355,57 @@ def test_decode_step_rejections():
     out = rk.race_decode_step(pQ[:, :0].contiguous().cuda(), pK[:, :0].contiguous().cuda(),
                               V[:, :0].contiguous().cuda(), state)
     assert out.shape == (2, 0, 64) and not state.any()
+
+
+from conftest import GLOBAL_CASES, global_case  # noqa: E402
+
+
+@pytest.mark.parametrize("name", GLOBAL_CASES)
+def test_global_form_matches_reference_vectors(golden_global, name):
+    """normalization="global" against the outputs of the reference's race_causal_reference
+    (src/causal_v2/reference.py:106-127) on the features that function computed."""
+    rk = _ops()
+    pQ, pK, V, ref = global_case(golden_global, name)
+    out = rk.race_causal_prefix(pQ.float().cuda(), pK.float().cuda(), V.float().cuda(), normalization="global")
+    assert ro.rel_l2(out, ref) <= FP32_TOL
+    assert torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("N,T,L,R,dk,dtype,tol", [
+    (8, 4096, 4, 16, 64, torch.float32, FP32_TOL),      # config 1's geometry, several tiles
+    (2, 4097, 4, 16, 64, torch.float32, FP32_TOL),
+    (2, 300, 8, 64, 128, torch.float32, FP32_TOL),      # S = 512: eight bucket groups share the denominator
+    (1, 100, 2, 64, 64, torch.float32, FP32_TOL),
+    (3, 150, 2, 8, 32, torch.float32, FP32_TOL),
+    (2, 1000, 4, 16, 64, torch.bfloat16, BF16_TOL),
+    (2, 300, 8, 64, 128, torch.bfloat16, BF16_TOL),
+])
+def test_global_form_parity_and_carry(N, T, L, R, dk, dtype, tol):
+    rk = _ops()
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=11 * N + T, dtype=dtype)
+    ref, A_ref, B_ref = ro.causal_prefix_global(pQ.double(), pK.double(), V.double(), return_state=True)
+    q, k, v = pQ.cuda(), pK.cuda(), V.cuda()
+    out, A, B = rk.race_causal_prefix(q, k, v, normalization="global", return_state=True)
+    assert ro.rel_l2(out, ref) <= tol
+    assert ro.rel_l2(A, A_ref) <= tol and ro.rel_l2(B, B_ref) <= tol
+    # two calls with the carried state equal one call; small tiles exercise the scan
+    h = T // 3
+    o1, A1, B1 = rk.race_causal_prefix(q[:, :h].contiguous(), k[:, :h].contiguous(), v[:, :h].contiguous(),
+                                       normalization="global", return_state=True, tile_tokens=32)
+    o2 = rk.race_causal_prefix(q[:, h:].contiguous(), k[:, h:].contiguous(), v[:, h:].contiguous(),
+                               normalization="global", carry_in=(A1, B1), tile_tokens=64)
+    assert ro.rel_l2(torch.cat([o1, o2], 1), ref) <= tol
+
+
+def test_global_form_zero_denominator_and_rejections():
+    rk = _ops()
+    pQ, pK, V = ro.synthetic_probs(2, 64, 4, 16, 64, seed=3)
+    pK[0, :10] = 0          # stream 0 has no key mass for its first ten tokens: those rows are 0
+    out = rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="global")
+    ref = ro.causal_prefix_global(pQ.double(), pK.double(), V.double())
+    assert not out[0, :10].any() and torch.isfinite(out).all()
+    assert ro.rel_l2(out, ref) <= FP32_TOL
+    with pytest.raises(RuntimeError):
+        rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="global", variant="tensor")
+    with pytest.raises(RuntimeError):
+        rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="paper")

@@ -130,3 +130,21 @@ def test_noncausal_closed_form_matches_autograd():
     # last causal token sees every key: equals the non-causal output at that token
     last = ro.causal_prefix(pQ, pK, V)[:, -1]
     assert torch.allclose(last, ro.noncausal_forward(pQ, pK, V)[:, -1], atol=1e-12)
+
+
+from conftest import GLOBAL_CASES, global_case  # noqa: E402
+
+
+@pytest.mark.parametrize("name", GLOBAL_CASES)
+def test_global_form_matches_reference(golden_global, name):
+    # the restatement of src/causal_v2/reference.py:106-127 against that function's own output
+    pQ, pK, V, ref = global_case(golden_global, name)
+    tol = 1e-12 if ref.dtype == torch.float64 else 1e-5
+    for chunk in (256, 33):
+        got = ro.causal_prefix_global(pQ, pK, V, chunk=chunk)
+        assert ro.rel_l2(got, ref) <= tol
+    # carried state: two halves equal one pass
+    h = pQ.shape[1] // 2
+    o1, A, B = ro.causal_prefix_global(pQ[:, :h], pK[:, :h], V[:, :h], return_state=True)
+    o2 = ro.causal_prefix_global(pQ[:, h:], pK[:, h:], V[:, h:], carry=(A, B))
+    assert ro.rel_l2(torch.cat([o1, o2], 1), ref) <= tol
