@@ -141,6 +141,22 @@ int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const 
                                 size_t workspace_bytes, const RaceShape* shape, int tile_tokens, void* stream);
 
 /*
+ * Backward of race_b200_causal_fwd (carry_in = none): gradients w.r.t. probsQ, probsK and V given
+ * d_out [N,T,d_k]; d_probs_q / d_probs_k / d_v have the layouts and dtype of their primals.  The
+ * reference has no causal backward (its design note only outlines one for the global form,
+ * docs/causal_v2_design.md:689-741); this is the derivative of src/race_baseline.py:45-51:
+ *   X_t[s] = B_t[s,:].dO_t, dPQ_t = X_t/(A_t+eps), g_t = -X_t*W_t/(A_t+eps), W_t = pQ_t/(A_t+eps),
+ *   dPK_j[s] = sum_{t>=j} g_t[s] + (sum_{t>=j} W_t[s] dO_t).V_j,  dV_j = sum_s pK_j[s] sum_{t>=j} W_t[s] dO_t.
+ * Recomputes the forward's prefix states (nothing has to be saved by the forward).  CUDA-core kernels;
+ * L*R <= 64, d_k <= 128, heads <= 1.  workspace: 256-byte aligned, >= race_b200_causal_bwd_workspace_bytes()
+ * (two fp32 [N,T,L*R] scratch arrays plus tile states).
+ */
+size_t race_b200_causal_bwd_workspace_bytes(const RaceShape* shape);
+int race_b200_causal_bwd(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
+                         void* d_probs_q, void* d_probs_k, void* d_v, void* workspace, size_t workspace_bytes,
+                         const RaceShape* shape, void* stream);
+
+/*
  * Incremental (decode) step: race_b200_causal_fwd for a few NEW tokens per stream (seq_len <= 64,
  * typically 1) against a running state kept in device memory between calls, i.e. chunked_forward's
  * state update (src/race_chunked.py:54-63) with a chunk of seq_len tokens, costing one read and one

@@ -232,6 +232,42 @@ def noncausal_backward_autograd(probsQ, probsK, V, dO, eps: float = EPS):
     return pq.grad, pk.grad, v.grad
 
 
+def causal_backward_autograd(probsQ, probsK, V, dO, eps: float = EPS):
+    """Gradients of ``causal_prefix`` (src/race_baseline.py:45-51) w.r.t. (probsQ, probsK, V) by
+    torch.autograd through the restated cumsum / divide / bmm.  The reference has no causal backward
+    (its design note only outlines one for the global form), so this is the checker."""
+    pq = probsQ.detach().clone().requires_grad_(True)
+    pk = probsK.detach().clone().requires_grad_(True)
+    v = V.detach().clone().requires_grad_(True)
+    out = causal_prefix(pq, pk, v, eps)
+    out.backward(dO)
+    return pq.grad, pk.grad, v.grad
+
+
+def causal_backward_closed_form(probsQ, probsK, V, dO, eps: float = EPS):
+    """The same gradients written out by hand, the arithmetic the kernels follow.  With
+    inv_t = 1/(A_t+eps), W_t = pQ_t*inv_t (prefixes A_t, B_t as in ``causal_prefix``):
+      X_t[s] = B_t[s,:].dO_t ;  dPQ_t = X_t*inv_t ;  g_t = -X_t*W_t*inv_t   (gradient reaching A_t)
+      SA_j = sum_{t>=j} g_t ;  SB_j = sum_{t>=j} W_t (x) dO_t                (suffix sums)
+      dPK_j[s] = SA_j[s] + SB_j[s,:].V_j ;  dV_j = sum_s pK_j[s] SB_j[s,:].
+    Checked against ``causal_backward_autograd`` in the tests."""
+    N, T, L, R = probsK.shape
+    S = L * R
+    pK, pQ = probsK.reshape(N, T, S), probsQ.reshape(N, T, S)
+    A = pK.cumsum(dim=1)
+    B = (pK.unsqueeze(-1) * V.unsqueeze(2)).cumsum(dim=1)            # [N,T,S,d]
+    inv = 1.0 / (A + eps)
+    W = pQ * inv
+    X = torch.einsum("ntsd,ntd->nts", B, dO)
+    dPQ = X * inv
+    g = -X * W * inv
+    SA = g.flip(1).cumsum(dim=1).flip(1)
+    SB = (W.unsqueeze(-1) * dO.unsqueeze(2)).flip(1).cumsum(dim=1).flip(1)
+    dPK = SA + torch.einsum("ntsd,ntd->nts", SB, V)
+    dV = torch.einsum("nts,ntsd->ntd", pK, SB)
+    return dPQ.view_as(probsQ), dPK.view_as(probsK), dV
+
+
 # --------------------------------------------------------------------------------------
 # helpers shared by the tests
 # --------------------------------------------------------------------------------------

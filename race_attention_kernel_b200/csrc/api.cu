@@ -75,7 +75,7 @@ size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile) {
 
 extern "C" {
 
-int race_b200_version(void) { return 1004; }
+int race_b200_version(void) { return 1005; }
 
 const char* race_b200_error_string(int code) {
     switch (code) {
@@ -197,6 +197,30 @@ int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const 
                                 size_t workspace_bytes, const RaceShape* shape, int tile_tokens, void* stream) {
     return causal_entry(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes, shape,
                         tile_tokens, RACE_VARIANT_SIMT, stream, nullptr, kPhaseAll, /*global_norm=*/true);
+}
+
+size_t race_b200_causal_bwd_workspace_bytes(const RaceShape* shape) {
+    Dims dm;
+    if (check_shape(shape, &dm) != RACE_OK || !causal_bwd_supported(dm)) return 0;
+    return causal_bwd_workspace_bytes(dm, causal_bwd_tile_tokens(dm, sm_count()));
+}
+
+int race_b200_causal_bwd(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
+                         void* d_probs_q, void* d_probs_k, void* d_v, void* workspace, size_t workspace_bytes,
+                         const RaceShape* shape, void* stream) {
+    Dims dm;
+    int rc = check_shape(shape, &dm);
+    if (rc != RACE_OK) return rc;
+    if (!causal_bwd_supported(dm)) return RACE_ERR_SHAPE;
+    if (dm.N == 0 || dm.T == 0) return RACE_OK;
+    if (!probs_q || !probs_k || !v || !d_out || !d_probs_q || !d_probs_k || !d_v || !workspace) return RACE_ERR_NULL;
+    if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(d_out) || !aligned16(d_probs_q) ||
+        !aligned16(d_probs_k) || !aligned16(d_v) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return RACE_ERR_ALIGN;
+    const int tile = causal_bwd_tile_tokens(dm, sm_count());
+    if (workspace_bytes < causal_bwd_workspace_bytes(dm, tile)) return RACE_ERR_WORKSPACE;
+    return (int)causal_bwd_simt(probs_q, probs_k, v, d_out, d_probs_q, d_probs_k, d_v, workspace, dm, shape->dtype,
+                                tile, (cudaStream_t)stream);
 }
 
 int race_b200_decode_step(const void* probs_q, const void* probs_k, const void* v, void* out,

@@ -26,6 +26,13 @@ cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out
 // which passes of a causal forward to run: totals (per-tile sums into ws) and/or scan + outputs
 constexpr int kPhaseTotals = 1, kPhaseOutput = 2, kPhaseAll = 3;
 
+// ---- causal backward (causal_bwd_simt.cu): S <= 64, d_k <= 128 ---------------------------------
+bool causal_bwd_supported(const Dims& dm);
+int causal_bwd_tile_tokens(const Dims& dm, int sm_count);
+size_t causal_bwd_workspace_bytes(const Dims& dm, int tile_tokens);
+cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const void* dout, void* dpq, void* dpk,
+                            void* dv, void* ws, const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream);
+
 // ---- non-causal path (noncausal_simt.cu) ------------------------------------------------------
 cudaError_t noncausal_query(const void* pq, const float* totals, void* out, const Dims& dm, int dtype,
                             int sm_count, cudaStream_t stream);

@@ -271,6 +271,56 @@ def bucket_probs_streams(x: torch.Tensor, planes: torch.Tensor, L: int, K: int,
     return probs
 
 
+class _RaceCausal(torch.autograd.Function):
+    """The causal forward (``race_causal_prefix``) with the hand-written backward kernels.  Only the
+    three inputs are saved: the backward recomputes the prefix states tile by tile."""
+
+    @staticmethod
+    def forward(ctx, probsQ, probsK, V, eps):
+        out = race_causal_prefix(probsQ, probsK, V, eps)
+        ctx.save_for_backward(probsQ, probsK, V)
+        ctx.eps = eps
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_out):
+        probsQ, probsK, V = ctx.saved_tensors
+        if not any(ctx.needs_input_grad[:3]):
+            return None, None, None, None
+        dpq, dpk, dv = race_causal_backward(probsQ, probsK, V, grad_out, ctx.eps)
+        g = ctx.needs_input_grad
+        return (dpq if g[0] else None, dpk if g[1] else None, dv if g[2] else None, None)
+
+
+def race_causal_backward(probsQ, probsK, V, grad_out, eps: float = 1e-6):
+    """(d probsQ, d probsK, d V) of ``race_causal_prefix(probsQ, probsK, V, eps)`` for the output
+    gradient ``grad_out`` [N,T,d_k] (derivative of src/race_baseline.py:45-51; L*R <= 64, d_k <= 128)."""
+    N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
+    if V.dim() != 3:
+        raise RuntimeError("race_causal_backward takes V as [N,T,d_k]")
+    if grad_out.shape != V.shape or not grad_out.is_cuda:
+        raise RuntimeError("grad_out must be a CUDA tensor shaped like V")
+    # autograd may hand over an expanded (stride-0) gradient: the kernels need dense rows
+    grad_out = grad_out.to(V.dtype).contiguous()
+    L_ = _lib.lib()
+    sh = make_shape(N, T, L, R, dk, V.dtype, eps)
+    with torch.cuda.device(V.device):
+        dpq, dpk, dv = torch.empty_like(probsQ), torch.empty_like(probsK), torch.empty_like(V)
+        ws_bytes = L_.race_b200_causal_bwd_workspace_bytes(ctypes.byref(sh))
+        ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=V.device)
+        rc = L_.race_b200_causal_bwd(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(grad_out), _ptr(dpq), _ptr(dpk),
+                                     _ptr(dv), _ptr(ws), ws_bytes, ctypes.byref(sh), _stream())
+    _lib.check(rc, "race_b200_causal_bwd")
+    return dpq, dpk, dv
+
+
+def race_causal(probsQ, probsK, V, eps: float = 1e-6) -> torch.Tensor:
+    """Differentiable causal per-bucket forward: ``race_causal_prefix`` with gradients for all three
+    inputs (the training-time form; the reference has none)."""
+    return _RaceCausal.apply(probsQ, probsK, V, eps)
+
+
 class _RaceNonCausal(torch.autograd.Function):
     """out = pQ . (pK^T V / (sum_t pK + eps)) with the hand-written backward kernels.
 

@@ -409,3 +409,75 @@ def test_global_form_zero_denominator_and_rejections():
         rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="global", variant="tensor")
     with pytest.raises(RuntimeError):
         rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="paper")
+
+
+BWD_SHAPES = [
+    # N, T, L, R, dk
+    (2, 70, 4, 16, 64), (2, 2100, 4, 16, 64),   # config 1's geometry; the second spans many state tiles
+    (1, 32, 4, 16, 64), (1, 33, 1, 32, 64),
+    (3, 150, 2, 8, 32), (2, 300, 4, 16, 128), (5, 97, 2, 4, 40),
+]
+
+
+def _grad_out(N, T, dk, dtype, seed):
+    return torch.randn(N, T, dk, generator=torch.Generator().manual_seed(seed)).to(dtype)
+
+
+@pytest.mark.parametrize("N,T,L,R,dk", BWD_SHAPES)
+def test_causal_backward_fp32(N, T, L, R, dk):
+    """The backward kernels against the hand-derived gradients evaluated in fp64 (which the CPU suite
+    checks against torch.autograd through the restated reference forward, src/race_baseline.py:45-51)."""
+    rk = _ops()
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=5 * N + T)
+    dO = _grad_out(N, T, dk, torch.float32, T)
+    ref = ro.causal_backward_closed_form(pQ.double(), pK.double(), V.double(), dO.double())
+    got = rk.race_causal_backward(pQ.cuda(), pK.cuda(), V.cuda(), dO.cuda())
+    for name, g, r in zip(("dPQ", "dPK", "dV"), got, ref):
+        err = ro.rel_l2(g, r)
+        assert err <= FP32_TOL, f"{name}: rel-L2 {err:.3e}"
+        assert torch.isfinite(g).all()
+
+
+def test_causal_backward_single_token():
+    """T = 1: dPK is the difference of two terms that cancel to O(eps) (analytically
+    pQ (v.dO) eps / (pK+eps)^2), so it is held to an absolute bound on the scale of those terms;
+    dPQ and dV keep the relative bound."""
+    rk = _ops()
+    pQ, pK, V = ro.synthetic_probs(3, 1, 4, 16, 64, seed=6)
+    dO = _grad_out(3, 1, 64, torch.float32, 1)
+    ref = ro.causal_backward_closed_form(pQ.double(), pK.double(), V.double(), dO.double())
+    got = rk.race_causal_backward(pQ.cuda(), pK.cuda(), V.cuda(), dO.cuda())
+    assert ro.rel_l2(got[0], ref[0]) <= FP32_TOL and ro.rel_l2(got[2], ref[2]) <= FP32_TOL
+    scale = ((pQ / (pK + 1e-6)).abs().amax() * (V * dO).sum(-1).abs().amax()).item()
+    assert (got[1].cpu().double() - ref[1]).abs().max().item() <= 1e-5 * scale
+
+
+def test_causal_backward_bf16_and_autograd():
+    rk = _ops()
+    N, T, L, R, dk = 2, 500, 4, 16, 64
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=9, dtype=torch.bfloat16)
+    dO = _grad_out(N, T, dk, torch.bfloat16, 10)
+    ref = ro.causal_backward_closed_form(pQ.double(), pK.double(), V.double(), dO.double())
+    got = rk.race_causal_backward(pQ.cuda(), pK.cuda(), V.cuda(), dO.cuda())
+    for name, g, r in zip(("dPQ", "dPK", "dV"), got, ref):
+        assert ro.rel_l2(g, r) <= BF16_TOL, name
+    # through autograd, fp32, against torch.autograd of the oracle forward
+    pQ, pK, V = ro.synthetic_probs(N, 200, L, R, dk, seed=4)
+    dO = _grad_out(N, 200, dk, torch.float32, 5)
+    ref = ro.causal_backward_autograd(pQ.double(), pK.double(), V.double(), dO.double())
+    q, k, v = (t.cuda().requires_grad_(True) for t in (pQ, pK, V))
+    out = rk.race_causal(q, k, v)
+    assert ro.rel_l2(out, ro.causal_prefix(pQ.double(), pK.double(), V.double())) <= FP32_TOL
+    out.backward(dO.cuda())
+    for g, r in zip((q.grad, k.grad, v.grad), ref):
+        assert ro.rel_l2(g, r) <= FP32_TOL
+
+
+def test_causal_backward_rejections():
+    rk = _ops()
+    pQ, pK, V = ro.synthetic_probs(1, 40, 8, 64, 64, seed=2)      # S = 512: outside the backward's range
+    with pytest.raises(RuntimeError):
+        rk.race_causal_backward(pQ.cuda(), pK.cuda(), V.cuda(), torch.zeros_like(V).cuda())
+    pQ, pK, V = ro.synthetic_probs(1, 40, 4, 16, 64, seed=2)
+    with pytest.raises(RuntimeError):
+        rk.race_causal_backward(pQ.cuda(), pK.cuda(), V.cuda(), torch.zeros(1, 39, 64).cuda())

@@ -148,3 +148,13 @@ def test_global_form_matches_reference(golden_global, name):
     o1, A, B = ro.causal_prefix_global(pQ[:, :h], pK[:, :h], V[:, :h], return_state=True)
     o2 = ro.causal_prefix_global(pQ[:, h:], pK[:, h:], V[:, h:], carry=(A, B))
     assert ro.rel_l2(torch.cat([o1, o2], 1), ref) <= tol
+
+
+@pytest.mark.parametrize("N,T,L,R,dk", [(2, 70, 4, 16, 64), (1, 33, 2, 4, 8), (2, 20, 8, 64, 16)])
+def test_causal_closed_form_matches_autograd(N, T, L, R, dk):
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=T, dtype=torch.float64)
+    dO = torch.randn(N, T, dk, generator=torch.Generator().manual_seed(T + 1), dtype=torch.float64)
+    got = ro.causal_backward_closed_form(pQ, pK, V, dO)
+    ref = ro.causal_backward_autograd(pQ, pK, V, dO)
+    for g, r in zip(got, ref):
+        assert ro.rel_l2(g, r) <= 1e-12
