@@ -48,7 +48,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c4", "c5", "operator"],
+    ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c4", "c5", "operator", "next"],
                     help="c2 (default): the contract line; the others print extra measurement lines")
     return ap.parse_args()
 
@@ -274,6 +274,33 @@ def extra_workloads(args):
                               "fwd_bwd_frac": round((bf + bb) / ms_fb / 1e6 / peak, 4),
                               "Mtok_s_fwd_bwd": round(N * T / ms_fb / 1e3, 1)}), flush=True)
             del pQ, pK, V, dO
+    elif args.workload == "next":
+        # the widened rows: incremental step, causal backward, global-normalisation forward (CUDA cores)
+        for N, L, R, dk, dtype in ((8192, 4, 16, 64, torch.float32), (1024, 8, 64, 128, torch.bfloat16)):
+            pQ, pK = probs(N, 1, L, R, dtype, g), probs(N, 1, L, R, dtype, g)
+            V = torch.randn(N, 1, dk, device=dev, generator=g).to(dtype)
+            state = torch.rand(N, L * R * (dk + 1), device=dev)
+            ms = _time_ms(lambda: rk.race_decode_step(pQ, pK, V, state), 5, 50)
+            byts = 2 * state.numel() * 4
+            print(json.dumps({"workload": "decode_step", "dtype": str(dtype), "N": N, "S": L * R, "d_k": dk,
+                              "us_per_step": round(ms * 1e3, 1), "state_GB_s": round(byts / ms / 1e6, 1),
+                              "frac_measured_peak": round(byts / ms / 1e6 / peak, 4),
+                              "Mtok_s": round(N / ms / 1e3, 2)}), flush=True)
+            del pQ, pK, V, state
+        N, T, L, R, dk = 8, 131072, 4, 16, 64
+        pQ, pK = probs(N, T, L, R, torch.float32, g), probs(N, T, L, R, torch.float32, g)
+        V = torch.randn(N, T, dk, device=dev, generator=g)
+        dO = torch.randn(N, T, dk, device=dev, generator=g)
+        ms = _time_ms(lambda: rk.race_causal_backward(pQ, pK, V, dO), 3, 10)
+        bb = N * T * 4 * (4 * 64 + 3 * 64)
+        print(json.dumps({"workload": "causal_bwd", "dtype": "f32", "N": N, "T": T, "ms": round(ms, 3),
+                          "Mtok_s": round(N * T / ms / 1e3, 1), "GB_s": round(bb / ms / 1e6, 1),
+                          "frac_measured_peak": round(bb / ms / 1e6 / peak, 4)}), flush=True)
+        for norm in ("bucket", "global"):
+            ms = _time_ms(lambda: rk.race_causal_prefix(pQ, pK, V, variant="simt", normalization=norm), 3, 10)
+            print(json.dumps({"workload": "causal_fwd_cuda_cores", "normalization": norm, "N": N, "T": T,
+                              "ms": round(ms, 3), "Mtok_s": round(N * T / ms / 1e3, 1),
+                              "frac_measured_peak": round(N * T * 1024 / ms / 1e6 / peak, 4)}), flush=True)
     elif args.workload == "operator":
         # the drop-in operator end to end on the device: BatchedACE.forward(K, V, Q) = stream flattening +
         # bucket-probability producer (probabilities written to HBM) + causal prefix kernels; fp32,
