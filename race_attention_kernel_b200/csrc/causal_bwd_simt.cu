@@ -13,9 +13,15 @@
 //   bwd_suffix_pass : walks a tile backwards with SB on chip; per chunk
 //                       dPK = SA + V SB^T + triu(V dO^T) W ;  dV = pK SB + triu(pK W^T) dO ;
 //                       SB += W^T dO ;  SA += colsum(g)
-// Shapes: S <= 64 buckets (one bucket group), d_k <= 128, fp32 or bf16 tokens; scratch is fp32.
+// S > 64 buckets are split into groups of 64, one CTA each; only dV sums over buckets, and the CTAs of a
+// tile (one thread-block cluster) add their shares of it through distributed shared memory in group order.
+// Shapes: S <= 64 or a multiple of 64 up to 512, d_k <= 128, fp32 or bf16 tokens; scratch is fp32.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "launch.h"
+
+namespace cg = cooperative_groups;
 
 namespace race {
 namespace {
@@ -110,10 +116,11 @@ __device__ __forceinline__ void publish_state(float* sB, int ldd, const float (&
                 make_float4(r[i][dv * 4], r[i][dv * 4 + 1], r[i][dv * 4 + 2], r[i][dv * 4 + 3]);
 }
 
-// load a state slice ([S][D] then [S]) into registers + shared memory; rows / columns past S / D read 0
+// load the rows [s0, s0+sv) of a state slice ([S][D] then [S]) into registers + shared memory; rows past sv and
+// columns past D read 0
 template <int SPT, int DV>
 __device__ __forceinline__ void load_state(float (&r)[SPT][4 * DV], float* sB, int ldd, float* sA, const float* slice,
-                                           int S, int D, int tid, int ty, int tx) {
+                                           int S, int D, int s0, int sv, int tid, int ty, int tx) {
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
         const int s = ty * SPT + i;
@@ -121,31 +128,31 @@ __device__ __forceinline__ void load_state(float (&r)[SPT][4 * DV], float* sB, i
         for (int dv = 0; dv < DV; ++dv) {
             const int c = dv * 64 + tx * 4;
             float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (slice && s < S && c < D) b = load4(slice + (int64_t)s * D + c);
+            if (slice && s < sv && c < D) b = load4(slice + (int64_t)(s0 + s) * D + c);
             r[i][dv * 4 + 0] = b.x; r[i][dv * 4 + 1] = b.y; r[i][dv * 4 + 2] = b.z; r[i][dv * 4 + 3] = b.w;
             *reinterpret_cast<float4*>(sB + s * ldd + c) = b;
         }
     }
-    if (tid < 16 * SPT) sA[tid] = (slice && tid < S) ? slice[(int64_t)S * D + tid] : 0.f;
+    if (tid < 16 * SPT) sA[tid] = (slice && tid < sv) ? slice[(int64_t)S * D + s0 + tid] : 0.f;
 }
 
 template <int SPT, int DV>
 __device__ __forceinline__ void store_state(float* slice, const float (&r)[SPT][4 * DV], float a_sum, int S, int D,
-                                            int tid, int ty, int tx) {
+                                            int s0, int sv, int tid, int ty, int tx) {
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
         const int s = ty * SPT + i;
-        if (s < S) {
+        if (s < sv) {
 #pragma unroll
             for (int dv = 0; dv < DV; ++dv) {
                 const int c = dv * 64 + tx * 4;
                 if (c < D)
-                    *reinterpret_cast<float4*>(slice + (int64_t)s * D + c) =
+                    *reinterpret_cast<float4*>(slice + (int64_t)(s0 + s) * D + c) =
                         make_float4(r[i][dv * 4], r[i][dv * 4 + 1], r[i][dv * 4 + 2], r[i][dv * 4 + 3]);
             }
         }
     }
-    if (tid < S) slice[(int64_t)S * D + tid] = a_sum;
+    if (tid < sv) slice[(int64_t)S * D + s0 + tid] = a_sum;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -156,7 +163,7 @@ __global__ void __launch_bounds__(kSimtThreads)
 bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Tin* __restrict__ v,
                 const Tin* __restrict__ dout, Tin* __restrict__ dpq, float* __restrict__ w_out,
                 float* __restrict__ g_out, const float* __restrict__ ws_prefix, float* __restrict__ ws_suffix,
-                Dims dm, int tile_tokens) {
+                Dims dm, int tile_tokens, int groups) {
     using Ly = BwdLayout<SPT, DV>;
     extern __shared__ __align__(16) float smem[];
     float* sQ = smem + Ly::oQ;
@@ -170,8 +177,11 @@ bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
     float* sP = smem + Ly::oP;
 
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-    const int64_t tile = blockIdx.x, tiles = gridDim.x, n = blockIdx.y;
+    const int group = blockIdx.x % groups;
+    const int64_t tile = blockIdx.x / groups, tiles = gridDim.x / groups, n = blockIdx.y;
     const int S = dm.S, D = dm.D;
+    const int s0 = group * kGroupBuckets;          // first bucket of this CTA's group
+    const int sv = min(S - s0, Ly::SG);            // buckets it owns
     const int64_t t_begin = tile * tile_tokens;
     const int64_t t_end = min(dm.T, t_begin + tile_tokens);
     const Tin* pq_n = pq + n * dm.T * S;
@@ -184,7 +194,7 @@ bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
     const int64_t sf = state_floats_per_stream(S, D);
 
     float rB[SPT][4 * DV], rR[SPT][4 * DV];
-    load_state<SPT, DV>(rB, sB, Ly::LDD, sA, ws_prefix + (n * tiles + tile) * sf, S, D, tid, ty, tx);
+    load_state<SPT, DV>(rB, sB, Ly::LDD, sA, ws_prefix + (n * tiles + tile) * sf, S, D, s0, sv, tid, ty, tx);
 #pragma unroll
     for (int i = 0; i < SPT; ++i)
 #pragma unroll
@@ -195,8 +205,8 @@ bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
 
     for (int64_t c0 = t_begin; c0 < t_end; c0 += C) {
         const int valid = (int)min((int64_t)C, t_end - c0);
-        stage_block(sQ, Ly::LDS, pq_n, c0, C, valid, S, 0, Ly::SG, S, tid, kSimtThreads);
-        stage_block(sK, Ly::LDS, pk_n, c0, C, valid, S, 0, Ly::SG, S, tid, kSimtThreads);
+        stage_block(sQ, Ly::LDS, pq_n, c0, C, valid, S, s0, Ly::SG, sv, tid, kSimtThreads);
+        stage_block(sK, Ly::LDS, pk_n, c0, C, valid, S, s0, Ly::SG, sv, tid, kSimtThreads);
         stage_block(sV, Ly::LDD, v_n, c0, C, valid, D, 0, Ly::DP, D, tid, kSimtThreads);
         stage_block(sD, Ly::LDD, do_n, c0, C, valid, D, 0, Ly::DP, D, tid, kSimtThreads);
         __syncthreads();
@@ -216,11 +226,11 @@ bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
             for (int j = 0; j < Ly::SEGLEN; ++j) {
                 const int t = seg * Ly::SEGLEN + j;
                 a += sK[t * Ly::LDS + scol];
-                const float inv = (scol < S) ? 1.f / (a + dm.eps) : 0.f;
+                const float inv = (scol < sv) ? 1.f / (a + dm.eps) : 0.f;
                 const float wv = sQ[t * Ly::LDS + scol] * inv;
                 sI[t * Ly::LDS + scol] = inv;
                 sQ[t * Ly::LDS + scol] = wv;
-                if (t < valid && scol < S) w_n[(c0 + t) * S + scol] = wv;
+                if (t < valid && scol < sv) w_n[(c0 + t) * S + s0 + scol] = wv;
             }
             if (seg == Ly::NSEG - 1) sA[(a_cur ^ 1) * Ly::SG + scol] = a;
         }
@@ -258,8 +268,8 @@ bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
                     const float dq = x[i][k] * inv;
                     const float g = -dq * wv;
                     sI[t * Ly::LDS + s] = g;          // this thread is the only reader of the entry
-                    if (t < valid && s < S) {
-                        const int64_t at = (c0 + t) * S + s;
+                    if (t < valid && s < sv) {
+                        const int64_t at = (c0 + t) * S + s0 + s;
                         if constexpr (sizeof(Tin) == 4) dpq_n[at] = dq; else dpq_n[at] = __float2bfloat16_rn(dq);
                         g_n[at] = g;
                     }
@@ -279,7 +289,7 @@ bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
         publish_state<SPT, DV>(sB, Ly::LDD, rB, ty, tx);   // every read of the old B is behind the barrier above
         __syncthreads();                                    // this chunk's tiles may now be overwritten
     }
-    store_state<SPT, DV>(ws_suffix + (n * tiles + tile) * sf, rR, g_sum, S, D, tid, ty, tx);
+    store_state<SPT, DV>(ws_suffix + (n * tiles + tile) * sf, rR, g_sum, S, D, s0, sv, tid, ty, tx);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -317,7 +327,8 @@ template <typename Tin, int SPT, int DV>
 __global__ void __launch_bounds__(kSimtThreads)
 bwd_suffix_pass(const Tin* __restrict__ pk, const Tin* __restrict__ v, const Tin* __restrict__ dout,
                 const float* __restrict__ w_in, const float* __restrict__ g_in, Tin* __restrict__ dpk,
-                Tin* __restrict__ dv_out, const float* __restrict__ ws_suffix, Dims dm, int tile_tokens) {
+                Tin* __restrict__ dv_out, const float* __restrict__ ws_suffix, Dims dm, int tile_tokens,
+                int groups) {
     using Ly = BwdLayout<SPT, DV>;
     extern __shared__ __align__(16) float smem[];
     float* sW = smem + Ly::oQ;
@@ -330,10 +341,14 @@ bwd_suffix_pass(const Tin* __restrict__ pk, const Tin* __restrict__ v, const Tin
     float* sG2 = smem + Ly::oG + C * Ly::LDG;  // triu(pK W^T)
     float* sA = smem + Ly::oA;
     float* sP = smem + Ly::oP;
+    float* sO = smem + Ly::floats;   // [C][LDD] partial dV of this bucket group, only with clusters
 
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-    const int64_t tile = blockIdx.x, tiles = gridDim.x, n = blockIdx.y;
+    const int group = blockIdx.x % groups;
+    const int64_t tile = blockIdx.x / groups, tiles = gridDim.x / groups, n = blockIdx.y;
     const int S = dm.S, D = dm.D;
+    const int s0 = group * kGroupBuckets;          // first bucket of this CTA's group
+    const int sv = min(S - s0, Ly::SG);            // buckets it owns
     const int64_t t_begin = tile * tile_tokens;
     const int64_t t_end = min(dm.T, t_begin + tile_tokens);
     const Tin* pk_n = pk + n * dm.T * S;
@@ -346,7 +361,7 @@ bwd_suffix_pass(const Tin* __restrict__ pk, const Tin* __restrict__ v, const Tin
     const int64_t sf = state_floats_per_stream(S, D);
 
     float rS[SPT][4 * DV];
-    load_state<SPT, DV>(rS, sB, Ly::LDD, sA, ws_suffix + (n * tiles + tile) * sf, S, D, tid, ty, tx);
+    load_state<SPT, DV>(rS, sB, Ly::LDD, sA, ws_suffix + (n * tiles + tile) * sf, S, D, s0, sv, tid, ty, tx);
     int a_cur = 0;
     const int seg = tid / Ly::SG, scol = tid % Ly::SG;
     const int64_t chunks = (t_end - t_begin + C - 1) / C;
@@ -354,9 +369,9 @@ bwd_suffix_pass(const Tin* __restrict__ pk, const Tin* __restrict__ v, const Tin
     for (int64_t ch = chunks - 1; ch >= 0; --ch) {
         const int64_t c0 = t_begin + ch * C;
         const int valid = (int)min((int64_t)C, t_end - c0);
-        stage_block(sW, Ly::LDS, w_n, c0, C, valid, S, 0, Ly::SG, S, tid, kSimtThreads);
-        stage_block(sI, Ly::LDS, g_n, c0, C, valid, S, 0, Ly::SG, S, tid, kSimtThreads);
-        stage_block(sK, Ly::LDS, pk_n, c0, C, valid, S, 0, Ly::SG, S, tid, kSimtThreads);
+        stage_block(sW, Ly::LDS, w_n, c0, C, valid, S, s0, Ly::SG, sv, tid, kSimtThreads);
+        stage_block(sI, Ly::LDS, g_n, c0, C, valid, S, s0, Ly::SG, sv, tid, kSimtThreads);
+        stage_block(sK, Ly::LDS, pk_n, c0, C, valid, S, s0, Ly::SG, sv, tid, kSimtThreads);
         stage_block(sV, Ly::LDD, v_n, c0, C, valid, D, 0, Ly::DP, D, tid, kSimtThreads);
         stage_block(sD, Ly::LDD, do_n, c0, C, valid, D, 0, Ly::DP, D, tid, kSimtThreads);
         __syncthreads();
@@ -411,8 +426,8 @@ bwd_suffix_pass(const Tin* __restrict__ pk, const Tin* __restrict__ v, const Tin
 #pragma unroll
                 for (int k = 0; k < SPT; ++k) {
                     const int j = ty * 2 + i, s = tx + 16 * k;
-                    if (j < valid && s < S) {
-                        const int64_t at = (c0 + j) * S + s;
+                    if (j < valid && s < sv) {
+                        const int64_t at = (c0 + j) * S + s0 + s;
                         if constexpr (sizeof(Tin) == 4) dpk_n[at] = y[i][k]; else dpk_n[at] = __float2bfloat16_rn(y[i][k]);
                     }
                 }
@@ -448,19 +463,46 @@ bwd_suffix_pass(const Tin* __restrict__ pk, const Tin* __restrict__ v, const Tin
                     o[0][dv * 4 + 3] = fmaf(g0, b.w, o[0][dv * 4 + 3]); o[1][dv * 4 + 3] = fmaf(g1, b.w, o[1][dv * 4 + 3]);
                 }
             }
+            if (groups == 1) {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int j = ty * 2 + i;
-                if (j < valid) {
+                for (int i = 0; i < 2; ++i) {
+                    const int j = ty * 2 + i;
+                    if (j < valid) {
 #pragma unroll
-                    for (int dv = 0; dv < DV; ++dv) {
-                        const int c = dv * 64 + tx * 4;
-                        if (c < D)
-                            store4_stream(dv_n + (c0 + j) * D + c,
-                                          make_float4(o[i][dv * 4], o[i][dv * 4 + 1], o[i][dv * 4 + 2], o[i][dv * 4 + 3]));
+                        for (int dv = 0; dv < DV; ++dv) {
+                            const int c = dv * 64 + tx * 4;
+                            if (c < D)
+                                store4_stream(dv_n + (c0 + j) * D + c,
+                                              make_float4(o[i][dv * 4], o[i][dv * 4 + 1], o[i][dv * 4 + 2], o[i][dv * 4 + 3]));
+                        }
                     }
                 }
+            } else {
+                // this group's share of dV -> own shared memory; the cluster adds the shares in group order
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int dv = 0; dv < DV; ++dv)
+                        *reinterpret_cast<float4*>(sO + (ty * 2 + i) * Ly::LDD + dv * 64 + tx * 4) =
+                            make_float4(o[i][dv * 4], o[i][dv * 4 + 1], o[i][dv * 4 + 2], o[i][dv * 4 + 3]);
             }
+        }
+        if (groups > 1) {
+            cg::cluster_group cluster = cg::this_cluster();
+            cluster.sync();
+            for (int idx = tid; idx < C * (Ly::DP / 4); idx += kSimtThreads) {   // rows dealt round-robin
+                const int j = idx / (Ly::DP / 4);
+                const int c = (idx % (Ly::DP / 4)) * 4;
+                if ((j % groups) != group || j >= valid || c >= D) continue;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int g = 0; g < groups; ++g) {
+                    const float* remote = cluster.map_shared_rank(sO, g);
+                    const float4 x = *reinterpret_cast<const float4*>(remote + j * Ly::LDD + c);
+                    acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+                }
+                store4_stream(dv_n + (c0 + j) * D + c, acc);
+            }
+            cluster.sync();
         }
         // ---- SB += W^T dO (registers are the master copy) ------------------------------------------
         outer_update<SPT, DV>(rS, sW, Ly::LDS, sD, Ly::LDD, ty, tx);
@@ -479,30 +521,48 @@ cudaError_t launch_bwd(const Tin* pq, const Tin* pk, const Tin* v, const Tin* do
     using Ly = BwdLayout<SPT, DV>;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const int sf = state_floats_per_stream(dm.S, dm.D);
+    const int groups = simt_groups(dm.S);
     const size_t smem = (size_t)Ly::floats * sizeof(float);
-    dim3 grid((unsigned)tiles, (unsigned)dm.N);
+    const size_t smem3 = smem + (groups > 1 ? (size_t)C * Ly::LDD * sizeof(float) : 0);
+    dim3 grid((unsigned)(tiles * groups), (unsigned)dm.N);
     auto k1 = bwd_prefix_pass<Tin, SPT, DV>;
     auto k3 = bwd_suffix_pass<Tin, SPT, DV>;
     cudaError_t err = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
-    err = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    err = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
     if (err != cudaSuccess) return err;
-    k1<<<grid, kSimtThreads, smem, stream>>>(pq, pk, v, dout, dpq, w_scr, g_scr, ws_prefix, ws_suffix, dm, tile_tokens);
+    k1<<<grid, kSimtThreads, smem, stream>>>(pq, pk, v, dout, dpq, w_scr, g_scr, ws_prefix, ws_suffix, dm, tile_tokens,
+                                             groups);
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     dim3 sgrid((unsigned)((sf + 127) / 128), (unsigned)dm.N);
     tile_scan_suffix<<<sgrid, 128, 0, stream>>>(ws_suffix, tiles, sf);
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
-    k3<<<grid, kSimtThreads, smem, stream>>>(pk, v, dout, w_scr, g_scr, dpk, dv, ws_suffix, dm, tile_tokens);
-    return cudaGetLastError();
+    // the bucket groups of a tile form one thread-block cluster: they add their shares of dV through
+    // distributed shared memory
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kSimtThreads);
+    cfg.dynamicSmemBytes = smem3;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = groups;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = groups > 1 ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k3, pk, v, dout, (const float*)w_scr, (const float*)g_scr, dpk, dv,
+                              (const float*)ws_suffix, dm, tile_tokens, groups);
 }
 
 template <typename Tin>
 cudaError_t dispatch_bwd(const void* pq, const void* pk, const void* v, const void* dout, void* dpq, void* dpk,
                          void* dv, const float* ws_prefix, float* ws_suffix, float* w_scr, float* g_scr,
                          const Dims& dm, int tile_tokens, cudaStream_t stream) {
-    const int spt = dm.S <= 16 ? 1 : (dm.S <= 32 ? 2 : 4);
+    const int sg = dm.S > kGroupBuckets ? kGroupBuckets : dm.S;
+    const int spt = sg <= 16 ? 1 : (sg <= 32 ? 2 : 4);
     const int dvn = dm.D <= 64 ? 1 : 2;
 #define RACE_BWD_CASE(SPT_, DV_)                                                                              \
     if (spt == SPT_ && dvn == DV_)                                                                            \
@@ -518,8 +578,7 @@ cudaError_t dispatch_bwd(const void* pq, const void* pk, const void* v, const vo
 }  // namespace
 
 bool causal_bwd_supported(const Dims& dm) {
-    return dm.S > 0 && dm.S <= kGroupBuckets && dm.D > 0 && dm.D <= 128 && dm.H == 1 && dm.N >= 0 && dm.N <= 65535 &&
-           dm.T >= 0;
+    return simt_supported(dm) && dm.H == 1;   // S <= 64, or a multiple of 64 up to 512 (one cluster); d_k <= 128
 }
 
 int causal_bwd_tile_tokens(const Dims& dm, int sm_count) { return simt_default_tile_tokens(dm, sm_count); }

@@ -295,7 +295,8 @@ class _RaceCausal(torch.autograd.Function):
 
 def race_causal_backward(probsQ, probsK, V, grad_out, eps: float = 1e-6):
     """(d probsQ, d probsK, d V) of ``race_causal_prefix(probsQ, probsK, V, eps)`` for the output
-    gradient ``grad_out`` [N,T,d_k] (derivative of src/race_baseline.py:45-51; L*R <= 64, d_k <= 128)."""
+    gradient ``grad_out`` [N,T,d_k] (derivative of src/race_baseline.py:45-51; L*R <= 64 or a multiple of 64
+    up to 512, d_k <= 128)."""
     N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
     if V.dim() != 3:
         raise RuntimeError("race_causal_backward takes V as [N,T,d_k]")

@@ -132,10 +132,10 @@ def test_global_form_argument_errors_without_launch():
 def test_causal_backward_argument_errors_without_launch():
     L = _lib.lib()
     call = lambda sh: L.race_b200_causal_bwd(None, None, None, None, None, None, None, None, 0, ctypes.byref(sh), None)
-    assert call(_shape(L=8, R=64)) == -2                 # S = 512: one bucket group only
+    assert call(_shape(L=3, R=32)) == -2                 # S = 96: neither <= 64 nor a multiple of 64
     assert call(_shape(dk=96 * 4)) == -2
     assert call(_shape(heads=8)) == -2
     assert call(_shape()) == -1                          # valid shape, NULL pointers
     assert call(_shape(T=0)) == 0
-    assert L.race_b200_causal_bwd_workspace_bytes(ctypes.byref(_shape(L=8, R=64))) == 0
+    assert L.race_b200_causal_bwd_workspace_bytes(ctypes.byref(_shape(L=3, R=32))) == 0
     assert L.race_b200_causal_bwd_workspace_bytes(ctypes.byref(_shape())) >= 2 * 8 * 4096 * 64 * 4

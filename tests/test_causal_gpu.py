@@ -416,6 +416,8 @@ BWD_SHAPES = [
     (2, 70, 4, 16, 64), (2, 2100, 4, 16, 64),   # config 1's geometry; the second spans many state tiles
     (1, 32, 4, 16, 64), (1, 33, 1, 32, 64),
     (3, 150, 2, 8, 32), (2, 300, 4, 16, 128), (5, 97, 2, 4, 40),
+    (2, 300, 8, 64, 128),       # config 3's bucket geometry: S = 512, a cluster of eight bucket groups
+    (1, 100, 2, 64, 64),        # S = 128: two groups
 ]
 
 
@@ -475,7 +477,7 @@ def test_causal_backward_bf16_and_autograd():
 
 def test_causal_backward_rejections():
     rk = _ops()
-    pQ, pK, V = ro.synthetic_probs(1, 40, 8, 64, 64, seed=2)      # S = 512: outside the backward's range
+    pQ, pK, V = ro.synthetic_probs(1, 40, 3, 32, 64, seed=2)      # S = 96: outside the backward's range
     with pytest.raises(RuntimeError):
         rk.race_causal_backward(pQ.cuda(), pK.cuda(), V.cuda(), torch.zeros_like(V).cuda())
     pQ, pK, V = ro.synthetic_probs(1, 40, 4, 16, 64, seed=2)
