@@ -122,6 +122,101 @@ decode_step(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Tin* _
     for (int s = tid; s < S; s += kDecodeThreads) sout[(int64_t)S * D + s] = a[s];
 }
 
+// One token per stream and a state small enough that a thread holds TWO streams' rows (S <= 4 rows per
+// thread): a CTA walks `per_cta` consecutive streams and requests the next stream's state, A, pK and pQ
+// while it works on the current one, so the chain prologue -> update -> reduction of a stream no longer
+// waits on memory.  grid = ceil(N / per_cta); d_k <= 128; shared memory as decode_step.
+template <typename Tin>
+__global__ void __launch_bounds__(kDecodeThreads, 4)
+decode_step_small(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Tin* __restrict__ v,
+                  Tin* __restrict__ out, const float* state_in, float* state_out, int64_t N, int per_cta, int S,
+                  int D, float eps, int lpr_log2) {
+    constexpr int kHalf = kDecodeDepth / 2;
+    extern __shared__ __align__(16) float sm[];
+    float* a = sm;
+    float* w = sm + S;
+    float* pks = sm + 2 * S;
+    float* red = sm + 3 * S;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int lpr = 1 << lpr_log2;
+    const int cl = lane & (lpr - 1);
+    const int rows_iter = kDecodeWarps * (32 >> lpr_log2);
+    const int row0 = warp * (32 >> lpr_log2) + (lane >> lpr_log2);
+    const int c = cl * 4;
+    const bool cv = c < D;
+    const int64_t sf = (int64_t)state_floats_per_stream(S, D);
+    const int64_t n_first = (int64_t)blockIdx.x * per_cta;
+    const int cnt = (int)min((int64_t)per_cta, N - n_first);
+
+    float4 bn[kHalf];
+    float an = 0.f, kn = 0.f, qn = 0.f;
+    auto request = [&](int64_t n) {   // state rows, A, pK, pQ of stream n -> registers
+        const float* sin = state_in ? state_in + n * sf : nullptr;
+#pragma unroll
+        for (int i = 0; i < kHalf; ++i) {
+            const int s = row0 + i * rows_iter;
+            bn[i] = (cv && s < S && sin) ? *reinterpret_cast<const float4*>(sin + (int64_t)s * D + c)
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (tid < S) {
+            an = sin ? sin[(int64_t)S * D + tid] : 0.f;
+            kn = ld1(pk + n * S + tid);
+            qn = ld1(pq + n * S + tid);
+        }
+    };
+    request(n_first);
+    for (int i = 0; i < cnt; ++i) {
+        const int64_t n = n_first + i;
+        float4 b[kHalf];
+#pragma unroll
+        for (int j = 0; j < kHalf; ++j) b[j] = bn[j];
+        const float a0 = an, k0 = kn, q0 = qn;
+        const float4 vv = cv ? load4(v + n * D + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i + 1 < cnt) request(n + 1);
+        __syncthreads();   // readers of a / w / pks / red of the previous stream are done
+        if (tid < S) {
+            const float at = a0 + k0;
+            a[tid] = at;
+            pks[tid] = k0;
+            w[tid] = q0 / (at + eps);
+        }
+        __syncthreads();
+        float* sout = state_out + n * sf;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < kHalf; ++j) {
+            const int s = row0 + j * rows_iter;
+            if (cv && s < S) {
+                const float k = pks[s], ws = w[s];
+                float4 x = b[j];
+                x.x = fmaf(k, vv.x, x.x); x.y = fmaf(k, vv.y, x.y);
+                x.z = fmaf(k, vv.z, x.z); x.w = fmaf(k, vv.w, x.w);
+                *reinterpret_cast<float4*>(sout + (int64_t)s * D + c) = x;
+                acc.x = fmaf(ws, x.x, acc.x); acc.y = fmaf(ws, x.y, acc.y);
+                acc.z = fmaf(ws, x.z, acc.z); acc.w = fmaf(ws, x.w, acc.w);
+            }
+        }
+        for (int off = lpr; off < 32; off <<= 1) {
+            acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+            acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+            acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+            acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+        }
+        if (lane < lpr) *reinterpret_cast<float4*>(red + warp * kDecodeCols + cl * 4) = acc;
+        if (tid < S) sout[(int64_t)S * D + tid] = a[tid];   // own entry, written by this thread above
+        __syncthreads();
+        if (tid < lpr && cv) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kDecodeWarps; ++j) {
+                const float4 x = *reinterpret_cast<const float4*>(red + j * kDecodeCols + tid * 4);
+                o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
+            }
+            store4_stream(out + n * D + c, o);
+        }
+    }
+}
+
 }  // namespace
 
 int decode_max_tokens() { return 64; }
@@ -133,6 +228,24 @@ cudaError_t decode_step_launch(const void* pq, const void* pk, const void* v, vo
     while ((4 << lpr_log2) < width) ++lpr_log2;
     const size_t smem = (size_t)(3 * dm.S + kDecodeWarps * kDecodeCols) * sizeof(float);
     const unsigned grid = (unsigned)dm.N;
+    const int rows_iter = kDecodeWarps * (32 >> lpr_log2);
+    if (dm.T == 1 && dm.D <= kDecodeCols && dm.S <= (kDecodeDepth / 2) * rows_iter && dm.S <= kDecodeThreads) {
+        // small states: several streams per CTA, the next stream's loads in flight (about 8 CTAs per SM's worth)
+        int sms = 148, dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int64_t per_cta = dm.N / ((int64_t)sms * 8);
+        per_cta = per_cta < 1 ? 1 : (per_cta > 16 ? 16 : per_cta);
+        const unsigned g = (unsigned)((dm.N + per_cta - 1) / per_cta);
+        if (dtype == RACE_DTYPE_BF16)
+            decode_step_small<__nv_bfloat16><<<g, kDecodeThreads, smem, stream>>>(
+                (const __nv_bfloat16*)pq, (const __nv_bfloat16*)pk, (const __nv_bfloat16*)v, (__nv_bfloat16*)out,
+                state_in, state_out, dm.N, (int)per_cta, dm.S, dm.D, dm.eps, lpr_log2);
+        else
+            decode_step_small<float><<<g, kDecodeThreads, smem, stream>>>(
+                (const float*)pq, (const float*)pk, (const float*)v, (float*)out, state_in, state_out, dm.N,
+                (int)per_cta, dm.S, dm.D, dm.eps, lpr_log2);
+        return cudaGetLastError();
+    }
     if (dtype == RACE_DTYPE_BF16)
         decode_step<__nv_bfloat16><<<grid, kDecodeThreads, smem, stream>>>(
             (const __nv_bfloat16*)pq, (const __nv_bfloat16*)pk, (const __nv_bfloat16*)v, (__nv_bfloat16*)out, state_in,

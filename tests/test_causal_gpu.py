@@ -303,6 +303,8 @@ DECODE_SHAPES = [
     (2, 100, (1, 3), 8, 64, 128),           # config 3's bucket geometry (S = 512, d_k = 128)
     (5, 33, (1, 7), 2, 8, 40),              # d_k not a multiple of the 32-column slice
     (200, 16, (1, 1), 4, 16, 64),           # more streams than SMs
+    (3001, 0, (1, 1), 4, 16, 64),           # several streams per CTA (pipelined small-state kernel), odd tail
+    (2500, 0, (1, 1), 2, 8, 32),            # the same with d_k = 32: four rows of the state per warp access
 ]
 
 
