@@ -601,9 +601,18 @@ cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const
     float* ws_suffix = (float*)((char*)ws + states);
     float* w_scr = (float*)((char*)ws + 2 * states);
     float* g_scr = (float*)((char*)ws + 2 * states + tokens);
-    // prefix state of every tile: the forward's totals pass and exclusive scan
-    cudaError_t err = causal_fwd_simt(nullptr, pk, v, nullptr, nullptr, nullptr, ws_prefix, dm, dtype, tile_tokens,
-                                      /*totals_only=*/false, stream, /*skip_output=*/true, /*skip_totals=*/false);
+    // prefix state of every tile: the forward's totals pass (on the tensor cores where that kernel covers the
+    // shape) and exclusive scan
+    cudaError_t err;
+    if (tensor_supported(dm, dtype) && tile_tokens % tensor_chunk_tokens() == 0) {
+        err = causal_fwd_tensor(nullptr, pk, v, nullptr, nullptr, nullptr, ws_prefix, dm, dtype, tile_tokens, stream,
+                                /*status=*/nullptr, kPhaseTotals);
+        if (err == cudaSuccess)
+            err = causal_scan_tiles(ws_prefix, nullptr, nullptr, dm, tile_tokens, stream, /*write_prefix=*/true);
+    } else {
+        err = causal_fwd_simt(nullptr, pk, v, nullptr, nullptr, nullptr, ws_prefix, dm, dtype, tile_tokens,
+                              /*totals_only=*/false, stream, /*skip_output=*/true, /*skip_totals=*/false);
+    }
     if (err != cudaSuccess) return err;
     if (dtype == RACE_DTYPE_F32)
         return dispatch_bwd<float>(pq, pk, v, dout, dpq, dpk, dv, ws_prefix, ws_suffix, w_scr, g_scr, dm, tile_tokens,
