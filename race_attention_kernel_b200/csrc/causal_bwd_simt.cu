@@ -67,12 +67,13 @@ __device__ __forceinline__ void dot_rows(float (&acc)[2][NK], const float* X, in
     }
 }
 
-// acc[i][k] += sum_j G[row0+i][j] * Y[j][tx+16k] over the C tokens of a chunk
+// acc[i][k] += sum_j G[row0+i][j] * Y[j][tx+16k] over the tokens [j0, j1) of a chunk (G is triangular: the
+// caller passes the range in which rows row0, row0+1 can be non-zero)
 template <int NK>
 __device__ __forceinline__ void mix_rows(float (&acc)[2][NK], const float* G, int ldg, int row0, const float* Y,
-                                         int ldy, int tx) {
+                                         int ldy, int tx, int j0, int j1) {
 #pragma unroll 4
-    for (int j = 0; j < C; ++j) {
+    for (int j = j0; j < j1; ++j) {
         const float g0 = G[row0 * ldg + j], g1 = G[(row0 + 1) * ldg + j];
 #pragma unroll
         for (int k = 0; k < NK; ++k) {
@@ -258,7 +259,7 @@ bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
 #pragma unroll
                 for (int k = 0; k < SPT; ++k) x[i][k] = 0.f;
             dot_rows<SPT>(x, sD, Ly::LDD, ty * 2, sB, Ly::LDD, tx, Ly::DP);
-            mix_rows<SPT>(x, sG, Ly::LDG, ty * 2, sK, Ly::LDS, tx);
+            mix_rows<SPT>(x, sG, Ly::LDG, ty * 2, sK, Ly::LDS, tx, 0, ty * 2 + 2);    // P is lower triangular
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -420,7 +421,7 @@ bwd_suffix_pass(const Tin* __restrict__ pk, const Tin* __restrict__ v, const Tin
 #pragma unroll
                 for (int k = 0; k < SPT; ++k) y[i][k] = sI[(ty * 2 + i) * Ly::LDS + tx + 16 * k];
             dot_rows<SPT>(y, sV, Ly::LDD, ty * 2, sB, Ly::LDD, tx, Ly::DP);
-            mix_rows<SPT>(y, sG1, Ly::LDG, ty * 2, sW, Ly::LDS, tx);
+            mix_rows<SPT>(y, sG1, Ly::LDG, ty * 2, sW, Ly::LDS, tx, ty * 2, C);       // G1 is upper triangular
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -452,7 +453,7 @@ bwd_suffix_pass(const Tin* __restrict__ pk, const Tin* __restrict__ v, const Tin
                 }
             }
 #pragma unroll 4
-            for (int t = 0; t < C; ++t) {
+            for (int t = ty * 2; t < C; ++t) {   // G2 is upper triangular
                 const float g0 = sG2[(ty * 2) * Ly::LDG + t], g1 = sG2[(ty * 2 + 1) * Ly::LDG + t];
 #pragma unroll
                 for (int dv = 0; dv < DV; ++dv) {

@@ -295,7 +295,7 @@ causal_out_simt(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
             }
         }
 #pragma unroll 4
-        for (int j = 0; j < C; ++j) {
+        for (int j = 0; j < ty * 2 + 2; ++j) {   // G is lower triangular: rows ty*2, ty*2+1 end at column ty*2+1
             const float g0 = sG[(ty * 2) * Ly::LDG + j], g1 = sG[(ty * 2 + 1) * Ly::LDG + j];
             if (GLOBAL) { den0 += g0; den1 += g1; }
 #pragma unroll
