@@ -160,7 +160,7 @@ __device__ __forceinline__ void store_state(float* slice, const float (&r)[SPT][
 // prefix pass: dPQ, scratch W and g, tile totals of the suffix quantities
 // ------------------------------------------------------------------------------------------
 template <typename Tin, int SPT, int DV>
-__global__ void __launch_bounds__(kSimtThreads)
+__global__ void __launch_bounds__(kSimtThreads, DV == 1 ? 3 : 2)
 bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Tin* __restrict__ v,
                 const Tin* __restrict__ dout, Tin* __restrict__ dpq, float* __restrict__ w_out,
                 float* __restrict__ g_out, const float* __restrict__ ws_prefix, float* __restrict__ ws_suffix,
