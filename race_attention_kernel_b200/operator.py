@@ -77,3 +77,23 @@ class BatchedACE(nn.Module):
         if host:
             out = out.cpu()
         return (out, res[1], res[2]) if return_state else out
+
+    @torch.no_grad()
+    def step(self, Khf, Vhf, Qhf, state: torch.Tensor):
+        """Token-by-token generation: outputs for the ``t`` <= 64 NEW tokens ``[M,B,t,H,d_k]`` given the
+        packed running state ``[M*B*H, S*(d_k+1)]`` of everything before them (``torch.zeros`` or
+        ``ops.pack_state(A, B)`` of a ``forward(..., return_state=True)`` prefill); ``state`` is advanced
+        in place.  Equals continuing the reference's chunked evaluation (src/race_chunked.py:54-63) by a
+        chunk of ``t`` tokens."""
+        if not (Khf.shape == Vhf.shape == Qhf.shape) or Khf.dim() != 5:
+            raise RuntimeError("expected K, V, Q of identical shape [M,B,t,H,d_k]")
+        M, B, T, H, dk = Khf.shape
+        if dk != self.d_k:
+            raise RuntimeError(f"d_k mismatch: module {self.d_k}, input {dk}")
+        if not (Khf.is_cuda and state.is_cuda):
+            raise RuntimeError("step() takes CUDA tensors (there is no CPU path)")
+        planes = self.planes_T.T.contiguous().float()
+        pK = ops.bucket_probs_streams(Khf.contiguous(), planes, self.L, self.K)
+        pQ = ops.bucket_probs_streams(Qhf.contiguous(), planes, self.L, self.K)
+        out2 = ops.race_decode_step(pQ, pK, self._streams(Vhf), state, self.eps)
+        return out2.view(M, B, H, T, dk).permute(0, 1, 3, 2, 4)

@@ -4,6 +4,8 @@ Tolerances are the ones the task fixes: rel-L2 <= 1e-4 for fp32; <= 2e-2 for bf1
 against the fp32/fp64 oracle evaluated on the same bf16-rounded inputs."""
 from __future__ import annotations
 
+import itertools
+
 import numpy as np
 import pytest
 import torch
@@ -485,3 +487,31 @@ def test_causal_backward_rejections():
     pQ, pK, V = ro.synthetic_probs(1, 40, 4, 16, 64, seed=2)
     with pytest.raises(RuntimeError):
         rk.race_causal_backward(pQ.cuda(), pK.cuda(), V.cuda(), torch.zeros(1, 39, 64).cuda())
+
+
+def test_operator_step_continues_the_reference_output(golden):
+    """Prefill with BatchedACE.forward(return_state=True), then BatchedACE.step token groups: the pieces equal
+    the reference's own BatchedACE output over the whole sequence (golden vectors)."""
+    rk = _ops()
+    for name, prefill in (("small_k4l4", 64), ("mb_k3l2_d32", 0), ("small_k6l8_d128", 17)):
+        M, B, H, dk, K, L, T, _ = (int(x) for x in golden[f"{name}/cfg"])
+        ace = rk.BatchedACE(dk, K, L, M)
+        ace.planes_T = torch.from_numpy(golden[f"{name}/planes_T"]).float()
+        ace = ace.cuda()
+        Kh, Vh, Qh = (torch.from_numpy(golden[f"{name}/{k}"]).float().cuda() for k in "KVQ")
+        ref = torch.from_numpy(golden[f"{name}/out"])
+        got = torch.empty(M, B, T, H, dk, device="cuda")
+        if prefill:
+            o, A, Bs = ace(Kh[:, :, :prefill], Vh[:, :, :prefill], Qh[:, :, :prefill], return_state=True)
+            got[:, :, :prefill] = o
+            state = rk.pack_state(A, Bs)
+        else:
+            state = torch.zeros(M * B * H, L * (1 << K) * (dk + 1), device="cuda")
+        t0 = prefill
+        for n_new in itertools.cycle((1, 3, 1, 8)):
+            if t0 >= T:
+                break
+            t1 = min(T, t0 + n_new)
+            got[:, :, t0:t1] = ace.step(Kh[:, :, t0:t1], Vh[:, :, t0:t1], Qh[:, :, t0:t1], state)
+            t0 = t1
+        assert ro.rel_l2(got, ref) <= FP32_TOL, name
