@@ -157,6 +157,18 @@ int race_b200_causal_bwd(const void* probs_q, const void* probs_k, const void* v
                          const RaceShape* shape, void* stream);
 
 /*
+ * The same backward for one chunk of a longer sequence, i.e. of race_b200_causal_fwd called with carry_in
+ * and state_out (the chunk loop of src/race_chunked.py:45-63, differentiated chunk by chunk in reverse):
+ *   carry_in     nullable; state layout; the forward's carry_in
+ *   d_state_out  nullable; state layout; gradient reaching the forward's state_out (from the chunks after)
+ *   d_carry_in   nullable; state layout; receives the gradient of carry_in (for the chunk before)
+ */
+int race_b200_causal_bwd_carry(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
+                               const float* carry_in, const float* d_state_out, void* d_probs_q, void* d_probs_k,
+                               void* d_v, float* d_carry_in, void* workspace, size_t workspace_bytes,
+                               const RaceShape* shape, void* stream);
+
+/*
  * Incremental (decode) step: race_b200_causal_fwd for a few NEW tokens per stream (seq_len <= 64,
  * typically 1) against a running state kept in device memory between calls, i.e. chunked_forward's
  * state update (src/race_chunked.py:54-63) with a chunk of seq_len tokens, costing one read and one

@@ -6,11 +6,12 @@ Public surface:
   race_tile_totals                per-stream totals (A, B) of a token range
   race_decode_step                incremental step: a few new tokens against a running state
   race_causal                     the causal forward with autograd (hand-written backward kernels)
+  race_causal_chunk               the same for one chunk of a longer sequence (state in, state out)
   race_noncausal                  non-causal forward with autograd
   bucket_probs                    bucket-probability producer
   bucket_probs_streams            the producer reading [M,B,T,H,d_k] directly (flattening fused)
 """
 from .operator import BatchedACE  # noqa: F401
 from .ops import (bucket_probs, bucket_probs_streams, is_supported, pack_state, race_causal_prefix,  # noqa: F401
-                  race_causal_prefix_host, race_causal_prefix_static, race_causal, race_causal_backward, race_decode_step, race_noncausal, race_tile_totals, select_tile_tokens,
+                  race_causal_prefix_host, race_causal_prefix_static, race_causal, race_causal_backward, race_causal_chunk, race_decode_step, race_noncausal, race_tile_totals, select_tile_tokens,
                   unpack_state)

@@ -75,7 +75,7 @@ size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile) {
 
 extern "C" {
 
-int race_b200_version(void) { return 1005; }
+int race_b200_version(void) { return 1006; }
 
 const char* race_b200_error_string(int code) {
     switch (code) {
@@ -208,19 +208,34 @@ size_t race_b200_causal_bwd_workspace_bytes(const RaceShape* shape) {
 int race_b200_causal_bwd(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
                          void* d_probs_q, void* d_probs_k, void* d_v, void* workspace, size_t workspace_bytes,
                          const RaceShape* shape, void* stream) {
+    return race_b200_causal_bwd_carry(probs_q, probs_k, v, d_out, nullptr, nullptr, d_probs_q, d_probs_k, d_v, nullptr,
+                                      workspace, workspace_bytes, shape, stream);
+}
+
+int race_b200_causal_bwd_carry(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
+                               const float* carry_in, const float* d_state_out, void* d_probs_q, void* d_probs_k,
+                               void* d_v, float* d_carry_in, void* workspace, size_t workspace_bytes,
+                               const RaceShape* shape, void* stream) {
     Dims dm;
     int rc = check_shape(shape, &dm);
     if (rc != RACE_OK) return rc;
     if (!causal_bwd_supported(dm)) return RACE_ERR_SHAPE;
-    if (dm.N == 0 || dm.T == 0) return RACE_OK;
+    if (dm.N == 0) return RACE_OK;
+    if (dm.T == 0) {   // no tokens: the state passes through, and so does its gradient
+        if (!d_carry_in) return RACE_OK;
+        const size_t sfb = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
+        return (int)(d_state_out ? cudaMemcpyAsync(d_carry_in, d_state_out, sfb, cudaMemcpyDeviceToDevice, (cudaStream_t)stream)
+                                 : cudaMemsetAsync(d_carry_in, 0, sfb, (cudaStream_t)stream));
+    }
     if (!probs_q || !probs_k || !v || !d_out || !d_probs_q || !d_probs_k || !d_v || !workspace) return RACE_ERR_NULL;
+    if (!aligned16(carry_in) || !aligned16(d_state_out) || !aligned16(d_carry_in)) return RACE_ERR_ALIGN;
     if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(d_out) || !aligned16(d_probs_q) ||
         !aligned16(d_probs_k) || !aligned16(d_v) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return RACE_ERR_ALIGN;
     const int tile = causal_bwd_tile_tokens(dm, sm_count());
     if (workspace_bytes < causal_bwd_workspace_bytes(dm, tile)) return RACE_ERR_WORKSPACE;
-    return (int)causal_bwd_simt(probs_q, probs_k, v, d_out, d_probs_q, d_probs_k, d_v, workspace, dm, shape->dtype,
-                                tile, (cudaStream_t)stream);
+    return (int)causal_bwd_simt(probs_q, probs_k, v, d_out, carry_in, d_state_out, d_probs_q, d_probs_k, d_v,
+                                d_carry_in, workspace, dm, shape->dtype, tile, (cudaStream_t)stream);
 }
 
 int race_b200_decode_step(const void* probs_q, const void* probs_k, const void* v, void* out,

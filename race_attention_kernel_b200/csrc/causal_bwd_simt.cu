@@ -296,13 +296,16 @@ bwd_prefix_pass(const Tin* __restrict__ pq, const Tin* __restrict__ pk, const Ti
 // ------------------------------------------------------------------------------------------
 // exclusive suffix scan over the tiles of a stream, one thread per state float
 // ------------------------------------------------------------------------------------------
+// d_state (nullable): gradient reaching the state after the last token, the carry of the last tile;
+// d_carry (nullable): receives the sum over all tiles + d_state, the gradient of the carried-in state
 __global__ void __launch_bounds__(128)
-tile_scan_suffix(float* __restrict__ ws, int64_t tiles, int state_floats) {
+tile_scan_suffix(float* __restrict__ ws, int64_t tiles, int state_floats, const float* __restrict__ d_state,
+                 float* __restrict__ d_carry) {
     constexpr int kInFlight = 16;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= state_floats) return;
     float* p = ws + (int64_t)blockIdx.y * tiles * state_floats + i;
-    float run = 0.f;
+    float run = d_state ? d_state[(int64_t)blockIdx.y * state_floats + i] : 0.f;
     int64_t t = tiles;
     for (; t >= kInFlight; t -= kInFlight) {
         float x[kInFlight];
@@ -319,6 +322,7 @@ tile_scan_suffix(float* __restrict__ ws, int64_t tiles, int state_floats) {
         p[(t - 1) * state_floats] = run;
         run += x;
     }
+    if (d_carry) d_carry[(int64_t)blockIdx.y * state_floats + i] = run;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -517,8 +521,8 @@ inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 template <typename Tin, int SPT, int DV>
 cudaError_t launch_bwd(const Tin* pq, const Tin* pk, const Tin* v, const Tin* dout, Tin* dpq, Tin* dpk, Tin* dv,
-                       const float* ws_prefix, float* ws_suffix, float* w_scr, float* g_scr, const Dims& dm,
-                       int tile_tokens, cudaStream_t stream) {
+                       const float* ws_prefix, float* ws_suffix, float* w_scr, float* g_scr, const float* d_state,
+                       float* d_carry, const Dims& dm, int tile_tokens, cudaStream_t stream) {
     using Ly = BwdLayout<SPT, DV>;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const int sf = state_floats_per_stream(dm.S, dm.D);
@@ -537,7 +541,7 @@ cudaError_t launch_bwd(const Tin* pq, const Tin* pk, const Tin* v, const Tin* do
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     dim3 sgrid((unsigned)((sf + 127) / 128), (unsigned)dm.N);
-    tile_scan_suffix<<<sgrid, 128, 0, stream>>>(ws_suffix, tiles, sf);
+    tile_scan_suffix<<<sgrid, 128, 0, stream>>>(ws_suffix, tiles, sf, d_state, d_carry);
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     // the bucket groups of a tile form one thread-block cluster: they add their shares of dV through
@@ -561,7 +565,7 @@ cudaError_t launch_bwd(const Tin* pq, const Tin* pk, const Tin* v, const Tin* do
 template <typename Tin>
 cudaError_t dispatch_bwd(const void* pq, const void* pk, const void* v, const void* dout, void* dpq, void* dpk,
                          void* dv, const float* ws_prefix, float* ws_suffix, float* w_scr, float* g_scr,
-                         const Dims& dm, int tile_tokens, cudaStream_t stream) {
+                         const float* d_state, float* d_carry, const Dims& dm, int tile_tokens, cudaStream_t stream) {
     const int sg = dm.S > kGroupBuckets ? kGroupBuckets : dm.S;
     const int spt = sg <= 16 ? 1 : (sg <= 32 ? 2 : 4);
     const int dvn = dm.D <= 64 ? 1 : 2;
@@ -569,7 +573,7 @@ cudaError_t dispatch_bwd(const void* pq, const void* pk, const void* v, const vo
     if (spt == SPT_ && dvn == DV_)                                                                            \
         return launch_bwd<Tin, SPT_, DV_>((const Tin*)pq, (const Tin*)pk, (const Tin*)v, (const Tin*)dout,    \
                                           (Tin*)dpq, (Tin*)dpk, (Tin*)dv, ws_prefix, ws_suffix, w_scr, g_scr, \
-                                          dm, tile_tokens, stream);
+                                          d_state, d_carry, dm, tile_tokens, stream);
     RACE_BWD_CASE(1, 1) RACE_BWD_CASE(2, 1) RACE_BWD_CASE(4, 1)
     RACE_BWD_CASE(1, 2) RACE_BWD_CASE(2, 2) RACE_BWD_CASE(4, 2)
 #undef RACE_BWD_CASE
@@ -593,8 +597,9 @@ size_t causal_bwd_workspace_bytes(const Dims& dm, int tile_tokens) {
     return 2 * states + 2 * tokens;
 }
 
-cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const void* dout, void* dpq, void* dpk,
-                            void* dv, void* ws, const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream) {
+cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const void* dout, const float* carry_in,
+                            const float* d_state, void* dpq, void* dpk, void* dv, float* d_carry, void* ws,
+                            const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream) {
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const size_t states = align256((size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float));
     const size_t tokens = align256((size_t)dm.N * dm.T * dm.S * sizeof(float));
@@ -609,17 +614,17 @@ cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const
         err = causal_fwd_tensor(nullptr, pk, v, nullptr, nullptr, nullptr, ws_prefix, dm, dtype, tile_tokens, stream,
                                 /*status=*/nullptr, kPhaseTotals);
         if (err == cudaSuccess)
-            err = causal_scan_tiles(ws_prefix, nullptr, nullptr, dm, tile_tokens, stream, /*write_prefix=*/true);
+            err = causal_scan_tiles(ws_prefix, carry_in, nullptr, dm, tile_tokens, stream, /*write_prefix=*/true);
     } else {
-        err = causal_fwd_simt(nullptr, pk, v, nullptr, nullptr, nullptr, ws_prefix, dm, dtype, tile_tokens,
+        err = causal_fwd_simt(nullptr, pk, v, nullptr, carry_in, nullptr, ws_prefix, dm, dtype, tile_tokens,
                               /*totals_only=*/false, stream, /*skip_output=*/true, /*skip_totals=*/false);
     }
     if (err != cudaSuccess) return err;
     if (dtype == RACE_DTYPE_F32)
-        return dispatch_bwd<float>(pq, pk, v, dout, dpq, dpk, dv, ws_prefix, ws_suffix, w_scr, g_scr, dm, tile_tokens,
-                                   stream);
-    return dispatch_bwd<__nv_bfloat16>(pq, pk, v, dout, dpq, dpk, dv, ws_prefix, ws_suffix, w_scr, g_scr, dm,
-                                       tile_tokens, stream);
+        return dispatch_bwd<float>(pq, pk, v, dout, dpq, dpk, dv, ws_prefix, ws_suffix, w_scr, g_scr, d_state, d_carry,
+                                   dm, tile_tokens, stream);
+    return dispatch_bwd<__nv_bfloat16>(pq, pk, v, dout, dpq, dpk, dv, ws_prefix, ws_suffix, w_scr, g_scr, d_state,
+                                       d_carry, dm, tile_tokens, stream);
 }
 
 }  // namespace race

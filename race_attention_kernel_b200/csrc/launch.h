@@ -30,8 +30,11 @@ constexpr int kPhaseTotals = 1, kPhaseOutput = 2, kPhaseAll = 3;
 bool causal_bwd_supported(const Dims& dm);
 int causal_bwd_tile_tokens(const Dims& dm, int sm_count);
 size_t causal_bwd_workspace_bytes(const Dims& dm, int tile_tokens);
-cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const void* dout, void* dpq, void* dpk,
-                            void* dv, void* ws, const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream);
+// carry_in: state before the first token (nullable); d_state: gradient reaching the state after the last token
+// (nullable); d_carry: receives the gradient of carry_in (nullable)
+cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const void* dout, const float* carry_in,
+                            const float* d_state, void* dpq, void* dpk, void* dv, float* d_carry, void* ws,
+                            const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream);
 
 // ---- non-causal path (noncausal_simt.cu) ------------------------------------------------------
 cudaError_t noncausal_query(const void* pq, const float* totals, void* out, const Dims& dm, int dtype,

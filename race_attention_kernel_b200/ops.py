@@ -293,10 +293,15 @@ class _RaceCausal(torch.autograd.Function):
         return (dpq if g[0] else None, dpk if g[1] else None, dv if g[2] else None, None)
 
 
-def race_causal_backward(probsQ, probsK, V, grad_out, eps: float = 1e-6):
+def race_causal_backward(probsQ, probsK, V, grad_out, eps: float = 1e-6, *, carry_in=None, grad_state=None,
+                         return_grad_carry: bool = False):
     """(d probsQ, d probsK, d V) of ``race_causal_prefix(probsQ, probsK, V, eps)`` for the output
     gradient ``grad_out`` [N,T,d_k] (derivative of src/race_baseline.py:45-51; L*R <= 64 or a multiple of 64
-    up to 512, d_k <= 128)."""
+    up to 512, d_k <= 128).
+
+    For one chunk of a longer sequence: ``carry_in`` is the packed state the forward was given,
+    ``grad_state`` the gradient reaching the packed state it returned, and ``return_grad_carry=True``
+    appends the gradient of ``carry_in`` to the result."""
     N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
     if V.dim() != 3:
         raise RuntimeError("race_causal_backward takes V as [N,T,d_k]")
@@ -310,10 +315,46 @@ def race_causal_backward(probsQ, probsK, V, grad_out, eps: float = 1e-6):
         dpq, dpk, dv = torch.empty_like(probsQ), torch.empty_like(probsK), torch.empty_like(V)
         ws_bytes = L_.race_b200_causal_bwd_workspace_bytes(ctypes.byref(sh))
         ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=V.device)
-        rc = L_.race_b200_causal_bwd(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(grad_out), _ptr(dpq), _ptr(dpk),
-                                     _ptr(dv), _ptr(ws), ws_bytes, ctypes.byref(sh), _stream())
-    _lib.check(rc, "race_b200_causal_bwd")
-    return dpq, dpk, dv
+        for st in (carry_in, grad_state):
+            if st is not None and (not st.is_cuda or st.dtype != torch.float32 or not st.is_contiguous()
+                                   or st.numel() != N * L * R * (dk + 1)):
+                raise RuntimeError("carry_in / grad_state must be contiguous fp32 CUDA states of N*S*(d_k+1) floats")
+        dcarry = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device) if return_grad_carry else None
+        rc = L_.race_b200_causal_bwd_carry(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(grad_out), _ptr(carry_in),
+                                           _ptr(grad_state), _ptr(dpq), _ptr(dpk), _ptr(dv), _ptr(dcarry), _ptr(ws),
+                                           ws_bytes, ctypes.byref(sh), _stream())
+    _lib.check(rc, "race_b200_causal_bwd_carry")
+    return (dpq, dpk, dv, dcarry) if return_grad_carry else (dpq, dpk, dv)
+
+
+class _RaceCausalChunk(torch.autograd.Function):
+    """One chunk of a longer sequence: (out, state_out) = forward(pQ, pK, V, state_in), differentiable in all
+    four, so that chained chunks back-propagate through the carried state."""
+
+    @staticmethod
+    def forward(ctx, probsQ, probsK, V, state, eps):
+        N, T, L, R = probsK.shape
+        out, A, B = race_causal_prefix(probsQ, probsK, V, eps, carry_in=state, return_state=True)
+        ctx.save_for_backward(probsQ, probsK, V, state)
+        ctx.eps = eps
+        return out, pack_state(A, B)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_out, grad_state):
+        probsQ, probsK, V, state = ctx.saved_tensors
+        gs = None if grad_state is None else grad_state.float().contiguous()
+        dpq, dpk, dv, dcarry = race_causal_backward(probsQ, probsK, V, grad_out, ctx.eps, carry_in=state,
+                                                    grad_state=gs, return_grad_carry=True)
+        g = ctx.needs_input_grad
+        return (dpq if g[0] else None, dpk if g[1] else None, dv if g[2] else None, dcarry if g[3] else None, None)
+
+
+def race_causal_chunk(probsQ, probsK, V, state, eps: float = 1e-6):
+    """Differentiable chunk step for sequences processed in pieces (the loop of src/race_chunked.py:45-63 with
+    gradients): returns (out, new_state); ``state`` is the packed [N, S*(d_k+1)] running state (zeros before
+    the first chunk).  Chain the calls and call ``backward`` once: autograd walks the chunks in reverse."""
+    return _RaceCausalChunk.apply(probsQ, probsK, V, state, eps)
 
 
 def race_causal(probsQ, probsK, V, eps: float = 1e-6) -> torch.Tensor:

@@ -139,3 +139,12 @@ def test_causal_backward_argument_errors_without_launch():
     assert call(_shape(T=0)) == 0
     assert L.race_b200_causal_bwd_workspace_bytes(ctypes.byref(_shape(L=3, R=32))) == 0
     assert L.race_b200_causal_bwd_workspace_bytes(ctypes.byref(_shape())) >= 2 * 8 * 4096 * 64 * 4
+
+
+def test_causal_backward_carry_argument_errors_without_launch():
+    L = _lib.lib()
+    call = lambda sh: L.race_b200_causal_bwd_carry(None, None, None, None, None, None, None, None, None, None, None, 0,
+                                                   ctypes.byref(sh), None)
+    assert call(_shape(L=3, R=32)) == -2
+    assert call(_shape()) == -1
+    assert call(_shape(T=0)) == 0        # no tokens and no d_carry_in requested: nothing to do

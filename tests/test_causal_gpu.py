@@ -515,3 +515,24 @@ def test_operator_step_continues_the_reference_output(golden):
             got[:, :, t0:t1] = ace.step(Kh[:, :, t0:t1], Vh[:, :, t0:t1], Qh[:, :, t0:t1], state)
             t0 = t1
         assert ro.rel_l2(got, ref) <= FP32_TOL, name
+
+
+@pytest.mark.parametrize("N,T,L,R,dk,cuts", [(2, 300, 4, 16, 64, (0, 100, 164, 300)), (2, 90, 2, 64, 32, (0, 1, 50, 90))])
+def test_causal_backward_through_chunks(N, T, L, R, dk, cuts):
+    """Chunks chained through the carried state (src/race_chunked.py:45-63) back-propagate to the same
+    gradients as the whole sequence at once."""
+    rk = _ops()
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=21)
+    dO = _grad_out(N, T, dk, torch.float32, 22)
+    ref = ro.causal_backward_autograd(pQ.double(), pK.double(), V.double(), dO.double())
+    q, k, v = (t.cuda().requires_grad_(True) for t in (pQ, pK, V))
+    state = torch.zeros(N, L * R * (dk + 1), device="cuda")
+    outs = []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        o, state = rk.race_causal_chunk(q[:, a:b].contiguous(), k[:, a:b].contiguous(), v[:, a:b].contiguous(), state)
+        outs.append(o)
+    out = torch.cat(outs, 1)
+    assert ro.rel_l2(out, ro.causal_prefix(pQ.double(), pK.double(), V.double())) <= FP32_TOL
+    out.backward(dO.cuda())
+    for name, g, r in zip(("dPQ", "dPK", "dV"), (q.grad, k.grad, v.grad), ref):
+        assert ro.rel_l2(g, r) <= FP32_TOL, name
