@@ -536,3 +536,16 @@ def test_causal_backward_through_chunks(N, T, L, R, dk, cuts):
     out.backward(dO.cuda())
     for name, g, r in zip(("dPQ", "dPK", "dV"), (q.grad, k.grad, v.grad), ref):
         assert ro.rel_l2(g, r) <= FP32_TOL, name
+
+
+def test_causal_backward_long_sequence():
+    """20 000 tokens (ten state tiles of 2048, suffix sums over 625 chunks): accumulated rounding stays inside
+    the fp32 bound."""
+    rk = _ops()
+    N, T, L, R, dk = 1, 20000, 4, 16, 64
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=77)
+    dO = _grad_out(N, T, dk, torch.float32, 78)
+    ref = ro.causal_backward_closed_form(pQ.double(), pK.double(), V.double(), dO.double())
+    got = rk.race_causal_backward(pQ.cuda(), pK.cuda(), V.cuda(), dO.cuda())
+    for name, g, r in zip(("dPQ", "dPK", "dV"), got, ref):
+        assert ro.rel_l2(g, r) <= FP32_TOL, name
