@@ -91,8 +91,13 @@ __device__ __forceinline__ void outer_update(float (&r)[SPT][4 * DV], const floa
 #pragma unroll 4
     for (int t = 0; t < C; ++t) {
         float kk[SPT];
+        if constexpr (SPT == 4) {   // the thread's four buckets are one 16-byte word
+            const float4 k4 = *reinterpret_cast<const float4*>(X + t * ldx + ty * 4);
+            kk[0] = k4.x; kk[1] = k4.y; kk[2] = k4.z; kk[3] = k4.w;
+        } else {
 #pragma unroll
-        for (int i = 0; i < SPT; ++i) kk[i] = X[t * ldx + ty * SPT + i];
+            for (int i = 0; i < SPT; ++i) kk[i] = X[t * ldx + ty * SPT + i];
+        }
 #pragma unroll
         for (int dv = 0; dv < DV; ++dv) {
             const float4 vv = *reinterpret_cast<const float4*>(Y + t * ldy + dv * 64 + tx * 4);
@@ -444,16 +449,22 @@ bwd_suffix_pass(const Tin* __restrict__ pk, const Tin* __restrict__ v, const Tin
             for (int i = 0; i < 2; ++i)
 #pragma unroll
                 for (int j = 0; j < 4 * DV; ++j) o[i][j] = 0.f;
-#pragma unroll 4
-            for (int s = 0; s < Ly::SG; ++s) {
-                const float w0 = sK[(ty * 2) * Ly::LDS + s], w1 = sK[(ty * 2 + 1) * Ly::LDS + s];
+#pragma unroll 2
+            for (int s4 = 0; s4 < Ly::SG; s4 += 4) {   // four buckets per 16-byte read of the two pK rows
+                const float4 wa = *reinterpret_cast<const float4*>(sK + (ty * 2) * Ly::LDS + s4);
+                const float4 wb = *reinterpret_cast<const float4*>(sK + (ty * 2 + 1) * Ly::LDS + s4);
+                const float w0s[4] = {wa.x, wa.y, wa.z, wa.w}, w1s[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-                for (int dv = 0; dv < DV; ++dv) {
-                    const float4 b = *reinterpret_cast<const float4*>(sB + s * Ly::LDD + dv * 64 + tx * 4);
-                    o[0][dv * 4 + 0] = fmaf(w0, b.x, o[0][dv * 4 + 0]); o[1][dv * 4 + 0] = fmaf(w1, b.x, o[1][dv * 4 + 0]);
-                    o[0][dv * 4 + 1] = fmaf(w0, b.y, o[0][dv * 4 + 1]); o[1][dv * 4 + 1] = fmaf(w1, b.y, o[1][dv * 4 + 1]);
-                    o[0][dv * 4 + 2] = fmaf(w0, b.z, o[0][dv * 4 + 2]); o[1][dv * 4 + 2] = fmaf(w1, b.z, o[1][dv * 4 + 2]);
-                    o[0][dv * 4 + 3] = fmaf(w0, b.w, o[0][dv * 4 + 3]); o[1][dv * 4 + 3] = fmaf(w1, b.w, o[1][dv * 4 + 3]);
+                for (int u = 0; u < 4; ++u) {
+                    const float w0 = w0s[u], w1 = w1s[u];
+#pragma unroll
+                    for (int dv = 0; dv < DV; ++dv) {
+                        const float4 b = *reinterpret_cast<const float4*>(sB + (s4 + u) * Ly::LDD + dv * 64 + tx * 4);
+                        o[0][dv * 4 + 0] = fmaf(w0, b.x, o[0][dv * 4 + 0]); o[1][dv * 4 + 0] = fmaf(w1, b.x, o[1][dv * 4 + 0]);
+                        o[0][dv * 4 + 1] = fmaf(w0, b.y, o[0][dv * 4 + 1]); o[1][dv * 4 + 1] = fmaf(w1, b.y, o[1][dv * 4 + 1]);
+                        o[0][dv * 4 + 2] = fmaf(w0, b.z, o[0][dv * 4 + 2]); o[1][dv * 4 + 2] = fmaf(w1, b.z, o[1][dv * 4 + 2]);
+                        o[0][dv * 4 + 3] = fmaf(w0, b.w, o[0][dv * 4 + 3]); o[1][dv * 4 + 3] = fmaf(w1, b.w, o[1][dv * 4 + 3]);
+                    }
                 }
             }
 #pragma unroll 4
