@@ -131,14 +131,17 @@ int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const 
  *   out[n,t,:] = (sum_s pQ[n,t,s] * B_t[n,s,:]) / (sum_s pQ[n,t,s] * A_t[n,s])
  * with the prefixes A_t, B_t of race_b200_causal_fwd; one denominator per token, shape.eps is not
  * used, and a row whose denominator is exactly 0 is written as 0 (:77-81).  carry_in / state_out /
- * workspace as in race_b200_causal_fwd with RACE_VARIANT_SIMT (the CUDA-core kernels compute this
- * form; size the workspace with that variant); heads <= 1.
+ * workspace / variant / status as in race_b200_causal_fwd (size the workspace with the same variant).
+ * RACE_VARIANT_TENSOR computes this form for fp32, S = 64, d_k = 64 (tcgen05 kernels, heads allowed);
+ * RACE_VARIANT_SIMT for every shape the CUDA-core kernels take (heads <= 1); AUTO picks the tensor
+ * kernels where they have it.  The bf16 tensor kernels do not have this form (RACE_ERR_VARIANT).
  * Replaces race_causal_forward (src/causal_v2/kernels/race_causal_fwd.h:126-130) at the
  * probabilities boundary for callers that want the reference kernels' estimator.
  */
 int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const void* v, void* out,
                                 const float* carry_in, float* state_out, void* workspace,
-                                size_t workspace_bytes, const RaceShape* shape, int tile_tokens, void* stream);
+                                size_t workspace_bytes, const RaceShape* shape, int tile_tokens, int variant,
+                                void* stream, int* status);
 
 /*
  * Backward of race_b200_causal_fwd (carry_in = none): gradients w.r.t. probsQ, probsK and V given
@@ -149,12 +152,13 @@ int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const 
  *   dPK_j[s] = sum_{t>=j} g_t[s] + (sum_{t>=j} W_t[s] dO_t).V_j,  dV_j = sum_s pK_j[s] sum_{t>=j} W_t[s] dO_t.
  * Recomputes the forward's prefix states (nothing has to be saved by the forward).  CUDA-core kernels;
  * L*R <= 64 or a multiple of 64 up to 512, d_k <= 128, heads <= 1.  workspace: 256-byte aligned, >= race_b200_causal_bwd_workspace_bytes()
- * (two fp32 [N,T,L*R] scratch arrays plus tile states).
+ * (two fp32 [N,T,L*R] scratch arrays plus tile states).  status: as in race_b200_causal_fwd (the prefix
+ * states come from the forward's tile-totals kernel, whose waits are bounded).
  */
 size_t race_b200_causal_bwd_workspace_bytes(const RaceShape* shape);
 int race_b200_causal_bwd(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
                          void* d_probs_q, void* d_probs_k, void* d_v, void* workspace, size_t workspace_bytes,
-                         const RaceShape* shape, void* stream);
+                         const RaceShape* shape, void* stream, int* status);
 
 /*
  * The same backward for one chunk of a longer sequence, i.e. of race_b200_causal_fwd called with carry_in
@@ -166,7 +170,7 @@ int race_b200_causal_bwd(const void* probs_q, const void* probs_k, const void* v
 int race_b200_causal_bwd_carry(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
                                const float* carry_in, const float* d_state_out, void* d_probs_q, void* d_probs_k,
                                void* d_v, float* d_carry_in, void* workspace, size_t workspace_bytes,
-                               const RaceShape* shape, void* stream);
+                               const RaceShape* shape, void* stream, int* status);
 
 /*
  * Incremental (decode) step: race_b200_causal_fwd for a few NEW tokens per stream (seq_len <= 64,
@@ -258,6 +262,22 @@ size_t race_b200_static_scratch_bytes(void);
 int race_b200_causal_fwd_static(const void* probs_q, const void* probs_k, const void* v, void* out,
                                 const float* carry_in, float* state_out, const RaceShape* shape,
                                 int tile_tokens, int variant, void* stream, int* status);
+
+/*
+ * Self-test of the bounded device-side waits (diagnostics; not part of the compute path).  Runs
+ * race_b200_causal_fwd with RACE_VARIANT_TENSOR (fp32, S = 64, d_k = 64) with every device-side
+ * wait limited to wait_cycles SM clock cycles (1000 .. 2^31) and with the TMA producer of the
+ * first CTA skipping the load of chunk withhold_chunk (64-token chunks of the first tile of
+ * stream 0), so that the consumer of that chunk waits in vain.  Expected behaviour, which a test
+ * asserts: the call returns, the kernels end within a few multiples of wait_cycles, *status
+ * (required) holds the code of the wait that gave up, the outputs of that CTA are unspecified,
+ * and the device stays usable.  Nothing faults and nothing spins without a limit.  The reference
+ * has no counterpart: its kernels have no device-side waits on other agents
+ * (src/causal_v2/kernels/race_causal_fwd.cu uses __syncthreads only).
+ */
+int race_b200_selftest_bounded_wait(const void* probs_q, const void* probs_k, const void* v, void* out,
+                                    void* workspace, size_t workspace_bytes, const RaceShape* shape,
+                                    int64_t wait_cycles, int withhold_chunk, void* stream, int* status);
 
 #ifdef __cplusplus
 }

@@ -5,6 +5,7 @@ Public surface:
   race_causal_prefix              probabilities-level causal forward (the hot path)
   race_tile_totals                per-stream totals (A, B) of a token range
   race_decode_step                incremental step: a few new tokens against a running state
+  DecodeStepper                   the same with shape checks and buffers hoisted out of the serving loop
   race_causal                     the causal forward with autograd (hand-written backward kernels)
   race_causal_chunk               the same for one chunk of a longer sequence (state in, state out)
   race_noncausal                  non-causal forward with autograd
@@ -12,6 +13,6 @@ Public surface:
   bucket_probs_streams            the producer reading [M,B,T,H,d_k] directly (flattening fused)
 """
 from .operator import BatchedACE  # noqa: F401
-from .ops import (bucket_probs, bucket_probs_streams, is_supported, pack_state, race_causal_prefix,  # noqa: F401
+from .ops import (DecodeStepper, bucket_probs, bucket_probs_streams, is_supported, pack_state, race_causal_prefix,  # noqa: F401
                   race_causal_prefix_host, race_causal_prefix_static, race_causal, race_causal_backward, race_causal_chunk, race_decode_step, race_noncausal, race_tile_totals, select_tile_tokens,
                   unpack_state)

@@ -26,7 +26,7 @@ EXPORTS = [
     "race_b200_bucket_probs", "race_b200_bucket_probs_streams", "race_b200_causal_fwd_host",
     "race_b200_static_scratch_bytes", "race_b200_causal_fwd_static", "race_b200_decode_step",
     "race_b200_causal_fwd_global", "race_b200_causal_bwd_workspace_bytes", "race_b200_causal_bwd",
-    "race_b200_causal_bwd_carry",
+    "race_b200_causal_bwd_carry", "race_b200_selftest_bounded_wait",
 ]
 
 
@@ -82,13 +82,15 @@ def lib() -> ctypes.CDLL:
     L.race_b200_causal_fwd_static.restype = i32
     L.race_b200_causal_fwd_static.argtypes = [vp, vp, vp, vp, vp, vp, shp, i32, i32, vp, vp]
     L.race_b200_causal_fwd_global.restype = i32
-    L.race_b200_causal_fwd_global.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, vp]
+    L.race_b200_causal_fwd_global.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, i32, vp, vp]
+    L.race_b200_selftest_bounded_wait.restype = i32
+    L.race_b200_selftest_bounded_wait.argtypes = [vp, vp, vp, vp, vp, sz, shp, i64, i32, vp, vp]
     L.race_b200_causal_bwd_workspace_bytes.restype = sz
     L.race_b200_causal_bwd_workspace_bytes.argtypes = [shp]
     L.race_b200_causal_bwd.restype = i32
-    L.race_b200_causal_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, shp, vp]
+    L.race_b200_causal_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, shp, vp, vp]
     L.race_b200_causal_bwd_carry.restype = i32
-    L.race_b200_causal_bwd_carry.argtypes = [vp] * 10 + [vp, sz, shp, vp]
+    L.race_b200_causal_bwd_carry.argtypes = [vp] * 10 + [vp, sz, shp, vp, vp]
     L.race_b200_decode_step.restype = i32
     L.race_b200_decode_step.argtypes = [vp, vp, vp, vp, vp, vp, shp, vp]
     return L

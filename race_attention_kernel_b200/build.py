@@ -21,7 +21,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--use_fast_math" if False else "-DRACE_B200", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
+    "-DRACE_B200", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
     "--expt-relaxed-constexpr",
 ]
 

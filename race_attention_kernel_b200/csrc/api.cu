@@ -75,7 +75,7 @@ size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile) {
 
 extern "C" {
 
-int race_b200_version(void) { return 1006; }
+int race_b200_version(void) { return 1007; }
 
 const char* race_b200_error_string(int code) {
     switch (code) {
@@ -130,13 +130,16 @@ size_t race_b200_causal_workspace_bytes(const RaceShape* shape, int tile_tokens,
 static int causal_entry(const void* probs_q, const void* probs_k, const void* v, void* out,
                         const float* carry_in, float* state_out, void* workspace,
                         size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
-                        int variant, void* stream, int* status, int phases, bool global_norm = false) {
+                        int variant, void* stream, int* status, int phases, bool global_norm = false,
+                        long long wait_cycles = 0, int withhold_chunk = -1) {
     Dims dm;
     int rc = check_shape(shape, &dm);
     if (rc != RACE_OK) return rc;
     const int var = resolve_variant(dm, shape->dtype, variant);
     if (var != RACE_VARIANT_SIMT && var != RACE_VARIANT_TENSOR) return RACE_ERR_VARIANT;
     if (!variant_supported(dm, shape->dtype, var)) return var == variant ? RACE_ERR_VARIANT : RACE_ERR_SHAPE;
+    // the global-normalisation form runs on the CUDA-core kernels and on the fp32 tensor kernels
+    if (global_norm && var == RACE_VARIANT_TENSOR && shape->dtype != RACE_DTYPE_F32) return RACE_ERR_VARIANT;
     if (tile_tokens < 0) return RACE_ERR_TILE;
     const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, var);
     if (tile % chunk_of(var) != 0) return RACE_ERR_TILE;
@@ -160,10 +163,10 @@ static int causal_entry(const void* probs_q, const void* probs_k, const void* v,
         !aligned16(workspace) || !aligned16(carry_in) || !aligned16(state_out))
         return RACE_ERR_ALIGN;
     if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, var, tile)) return RACE_ERR_WORKSPACE;
-    if (global_norm && var != RACE_VARIANT_SIMT) return RACE_ERR_VARIANT;
     if (var == RACE_VARIANT_TENSOR)
         return (int)causal_fwd_tensor(probs_q, probs_k, v, out, carry_in, state_out, workspace,
-                                      dm, shape->dtype, tile, st, status, phases);
+                                      dm, shape->dtype, tile, st, status, phases, global_norm, wait_cycles,
+                                      withhold_chunk);
     return (int)causal_fwd_simt(probs_q, probs_k, v, out, carry_in, state_out, (float*)workspace,
                                 dm, shape->dtype, tile, /*totals_only=*/!want_out, st,
                                 /*skip_output=*/false, /*skip_totals=*/!(phases & kPhaseTotals), global_norm);
@@ -194,9 +197,22 @@ int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const 
 
 int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const void* v, void* out,
                                 const float* carry_in, float* state_out, void* workspace,
-                                size_t workspace_bytes, const RaceShape* shape, int tile_tokens, void* stream) {
+                                size_t workspace_bytes, const RaceShape* shape, int tile_tokens, int variant,
+                                void* stream, int* status) {
+    // AUTO: the tensor kernels where they have this form (fp32, S = 64, d_k = 64), else the CUDA cores
+    if (variant == RACE_VARIANT_AUTO && shape && shape->dtype != RACE_DTYPE_F32) variant = RACE_VARIANT_SIMT;
     return causal_entry(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes, shape,
-                        tile_tokens, RACE_VARIANT_SIMT, stream, nullptr, kPhaseAll, /*global_norm=*/true);
+                        tile_tokens, variant, stream, status, kPhaseAll, /*global_norm=*/true);
+}
+
+int race_b200_selftest_bounded_wait(const void* probs_q, const void* probs_k, const void* v, void* out,
+                                    void* workspace, size_t workspace_bytes, const RaceShape* shape,
+                                    int64_t wait_cycles, int withhold_chunk, void* stream, int* status) {
+    if (!status) return RACE_ERR_NULL;
+    if (wait_cycles < 1000 || wait_cycles > (1ll << 31) || withhold_chunk < 0) return RACE_ERR_SHAPE;
+    if (!shape || shape->dtype != RACE_DTYPE_F32) return RACE_ERR_VARIANT;
+    return causal_entry(probs_q, probs_k, v, out, nullptr, nullptr, workspace, workspace_bytes, shape, 0,
+                        RACE_VARIANT_TENSOR, stream, status, kPhaseAll, false, wait_cycles, withhold_chunk);
 }
 
 size_t race_b200_causal_bwd_workspace_bytes(const RaceShape* shape) {
@@ -207,15 +223,15 @@ size_t race_b200_causal_bwd_workspace_bytes(const RaceShape* shape) {
 
 int race_b200_causal_bwd(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
                          void* d_probs_q, void* d_probs_k, void* d_v, void* workspace, size_t workspace_bytes,
-                         const RaceShape* shape, void* stream) {
+                         const RaceShape* shape, void* stream, int* status) {
     return race_b200_causal_bwd_carry(probs_q, probs_k, v, d_out, nullptr, nullptr, d_probs_q, d_probs_k, d_v, nullptr,
-                                      workspace, workspace_bytes, shape, stream);
+                                      workspace, workspace_bytes, shape, stream, status);
 }
 
 int race_b200_causal_bwd_carry(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
                                const float* carry_in, const float* d_state_out, void* d_probs_q, void* d_probs_k,
                                void* d_v, float* d_carry_in, void* workspace, size_t workspace_bytes,
-                               const RaceShape* shape, void* stream) {
+                               const RaceShape* shape, void* stream, int* status) {
     Dims dm;
     int rc = check_shape(shape, &dm);
     if (rc != RACE_OK) return rc;
@@ -235,7 +251,7 @@ int race_b200_causal_bwd_carry(const void* probs_q, const void* probs_k, const v
     const int tile = causal_bwd_tile_tokens(dm, sm_count());
     if (workspace_bytes < causal_bwd_workspace_bytes(dm, tile)) return RACE_ERR_WORKSPACE;
     return (int)causal_bwd_simt(probs_q, probs_k, v, d_out, carry_in, d_state_out, d_probs_q, d_probs_k, d_v,
-                                d_carry_in, workspace, dm, shape->dtype, tile, (cudaStream_t)stream);
+                                d_carry_in, workspace, dm, shape->dtype, tile, (cudaStream_t)stream, status);
 }
 
 int race_b200_decode_step(const void* probs_q, const void* probs_k, const void* v, void* out,

@@ -610,7 +610,7 @@ size_t causal_bwd_workspace_bytes(const Dims& dm, int tile_tokens) {
 
 cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const void* dout, const float* carry_in,
                             const float* d_state, void* dpq, void* dpk, void* dv, float* d_carry, void* ws,
-                            const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream) {
+                            const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream, int* status) {
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const size_t states = align256((size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float));
     const size_t tokens = align256((size_t)dm.N * dm.T * dm.S * sizeof(float));
@@ -623,7 +623,7 @@ cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const
     cudaError_t err;
     if (tensor_supported(dm, dtype) && tile_tokens % tensor_chunk_tokens() == 0) {
         err = causal_fwd_tensor(nullptr, pk, v, nullptr, nullptr, nullptr, ws_prefix, dm, dtype, tile_tokens, stream,
-                                /*status=*/nullptr, kPhaseTotals);
+                                status, kPhaseTotals);
         if (err == cudaSuccess)
             err = causal_scan_tiles(ws_prefix, carry_in, nullptr, dm, tile_tokens, stream, /*write_prefix=*/true);
     } else {

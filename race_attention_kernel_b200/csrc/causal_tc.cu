@@ -94,10 +94,16 @@ __device__ __forceinline__ void convert_tile(const uint8_t* stage, uint8_t* hi, 
 }
 
 // ------------------------------------------------------------------------------------------------
+// kGlobal selects the global-normalisation estimator (src/causal_v2/reference.py:106-127): W = pQ
+// without the per-bucket divide and every output row divided by den_t = pQ_t . A_t (0 -> a row of 0).
+// wait_cycles > 0 replaces the default limit of every wait; withhold_chunk >= 0 makes the TMA
+// producer of CTA (0, 0) skip the load of that chunk (the self-test of the bounded waits).
+template <bool kGlobal>
 __global__ void __launch_bounds__(kThreads, 1)
 causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, float* __restrict__ out,
-              const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int heads, int* status) {
+              const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int heads, int* status,
+              long long wait_cycles, int withhold_chunk) {
     extern __shared__ uint8_t smem_raw[];
     Ctx cx;
     cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -105,6 +111,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
     cx.bars = oBars;
     cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + oMisc + 4);
     cx.status = status;
+    if (wait_cycles > 0) cx.limit = wait_cycles;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + oMisc);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -173,6 +180,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
         uint32_t ohi[16], olo[16];   // operand limbs of W / masked G on their way to tensor memory
 
         // O of chunk c: TMEM -> global (fragment rows rbase, rbase + 8; 8-byte stores, full sectors)
+        float den[2] = {1.f, 1.f};   // global form: denominators of rows rbase, rbase + 8 of the chunk
         auto store_out = [&](int c) {
             const int64_t tok0 = t_begin + (int64_t)c * C;
             const int valid = (int)min((int64_t)C, t_end - tok0);
@@ -184,10 +192,13 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                 const int row = rbase + 8 * h;
                 if (row < valid) {
                     float* orow = out_n + (tok0 + row) * orow_stride + 2 * q;
+                    const float sc = kGlobal ? (den[h] != 0.f ? 1.f / den[h] : 0.f) : 1.f;
 #pragma unroll
-                    for (int x = 0; x < 8; ++x)
-                        __stcs(reinterpret_cast<float2*>(orow + 8 * x),
-                               make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]));
+                    for (int x = 0; x < 8; ++x) {
+                        float2 o2 = make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+                        if (kGlobal) { o2.x *= sc; o2.y *= sc; }
+                        __stcs(reinterpret_cast<float2*>(orow + 8 * x), o2);
+                    }
                 }
             }
         };
@@ -232,6 +243,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             tc_fence_after();
             tmem_ld64(lane_base + tmAG(wg), v);
             tc_fence_before();
+            if (kGlobal) den[0] = den[1] = 0.f;
 #pragma unroll
             for (int x = 0; x < 8; ++x) {
 #pragma unroll
@@ -239,8 +251,14 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
                     // packed fp32x2 arithmetic: (a0, a1) = running A + A_loc; W = pQ / (a + eps)
                     const float2 a2 = __fadd2_rn(make_float2(acar[2 * x], acar[2 * x + 1]),
                                                  make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]));
-                    const float2 d2 = __fadd2_rn(a2, make_float2(eps, eps));
-                    const float2 w2 = __fmul2_rn(pqv[2 * x + h], make_float2(__fdividef(1.f, d2.x), __fdividef(1.f, d2.y)));
+                    float2 w2;
+                    if (kGlobal) {
+                        w2 = pqv[2 * x + h];
+                        den[h] = fmaf(w2.x, a2.x, fmaf(w2.y, a2.y, den[h]));
+                    } else {
+                        const float2 d2 = __fadd2_rn(a2, make_float2(eps, eps));
+                        w2 = __fmul2_rn(pqv[2 * x + h], make_float2(__fdividef(1.f, d2.x), __fdividef(1.f, d2.y)));
+                    }
                     split2(w2.x, w2.y, ohi[2 * x + h], olo[2 * x + h]);
                     if (h == 1 && w == 3 && (lane >> 2) == 7) {
                         // row 63: the running A after this chunk, for the other group
@@ -257,6 +275,14 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             if (lane == 0) {
                 mbar_arrive(cx.bar(kWReady + wg));
                 if (w == 3) mbar_arrive(cx.bar(kAcar + (wg ^ 1)));
+            }
+            if (kGlobal) {
+                // a row's 64 buckets are spread over the four lanes of a quad, in a fixed order
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    den[h] += __shfl_xor_sync(0xffffffffu, den[h], 1);
+                    den[h] += __shfl_xor_sync(0xffffffffu, den[h], 2);
+                }
             }
 
             // -- S3: G -> causal mask -> operand tile (over W's buffer) ----------------------------
@@ -394,6 +420,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             for (int c = 0; c < nch; ++c) {
                 const int st = c & 1;
                 if (c >= 2 && !wait_bar(cx, kEmpty + st, ((c >> 1) - 1) & 1, 301)) break;
+                if (c == withhold_chunk && blockIdx.x == 0 && blockIdx.y == 0) continue;   // self-test only
                 const uint32_t dst = cx.sm_u32 + oStage + st * kStageBytes;
                 const uint32_t bar = cx.bar(kFull + st);
                 const int tok = (int)(t_begin + (int64_t)c * C);
@@ -480,7 +507,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             // everything this thread issued has to retire before TMEM is freed
             mma_commit(cx.bar(kDrain + wg));
             const long long t0 = clock64();
-            while (!mbar_try_wait(cx.bar(kDrain + wg), 0) && clock64() - t0 < kWaitCycles) {}
+            while (!mbar_try_wait(cx.bar(kDrain + wg), 0) && clock64() - t0 < cx.limit) {}
         }
     }
 
@@ -783,10 +810,13 @@ size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
 
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
                               const float* carry_in, float* state_out, void* ws, const Dims& dm,
-                              int dtype, int tile_tokens, cudaStream_t stream, int* status, int phases) {
-    if (dtype == RACE_DTYPE_BF16)
+                              int dtype, int tile_tokens, cudaStream_t stream, int* status, int phases,
+                              bool global_norm, long long wait_cycles, int withhold_chunk) {
+    if (dtype == RACE_DTYPE_BF16) {
+        if (global_norm) return cudaErrorInvalidValue;
         return causal_fwd_tensor_bf16(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream,
                                       status, phases);
+    }
     // Runtime calls first: they bind the device's primary context to the calling host thread,
     // which the driver-level tensor-map encoder needs (a thread that has made no runtime call
     // yet, e.g. an autograd worker, has no current context).
@@ -804,14 +834,19 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
     }
-    if (!(phases & kPhaseOutput))   // totals only: sum the tiles into state_out, keep the per-tile totals
+    if (!(phases & kPhaseOutput)) {
+        // totals only: sum the tiles into state_out, keep the per-tile totals (nothing to do when
+        // the caller wants the per-tile totals alone)
+        if (!state_out) return cudaSuccess;
         return causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, /*write_prefix=*/false);
+    }
     err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, /*write_prefix=*/true);
     if (err != cudaSuccess) return err;
-    err = cudaFuncSetAttribute(causal_out_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    auto kern = global_norm ? causal_out_tc<true> : causal_out_tc<false>;
+    err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return err;
-    causal_out_tc<<<grid, kThreads, kSmemBytes, stream>>>((const float*)pq, mk, mv, (float*)out, (const float*)ws, dm.T,
-                                                          tile_tokens, dm.eps, dm.H, status);
+    kern<<<grid, kThreads, kSmemBytes, stream>>>((const float*)pq, mk, mv, (float*)out, (const float*)ws, dm.T,
+                                                 tile_tokens, dm.eps, dm.H, status, wait_cycles, withhold_chunk);
     return cudaGetLastError();
 }
 

@@ -459,7 +459,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             }
             mma_commit(cx.bar(bDrain + wg));
             const long long t0 = clock64();
-            while (!mbar_try_wait(cx.bar(bDrain + wg), 0) && clock64() - t0 < kWaitCycles) {}
+            while (!mbar_try_wait(cx.bar(bDrain + wg), 0) && clock64() - t0 < cx.limit) {}
         }
     }
 
@@ -1089,7 +1089,7 @@ causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant
             if (ok && nch > 0) ok = gv(nch - 1);
             mma_commit(cx.bar(wDrain));
             const long long t0 = clock64();
-            while (!mbar_try_wait(cx.bar(wDrain), 0) && clock64() - t0 < kWaitCycles) {}
+            while (!mbar_try_wait(cx.bar(wDrain), 0) && clock64() - t0 < cx.limit) {}
         }
     }
 
@@ -1163,8 +1163,10 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
     }
-    if (!(phases & kPhaseOutput))
+    if (!(phases & kPhaseOutput)) {
+        if (!state_out) return cudaSuccess;   // the caller wants the per-tile totals alone
         return causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, false);
+    }
     err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, true);
     if (err != cudaSuccess) return err;
     if (G > 1) {

@@ -21,6 +21,7 @@ struct HostPipe {
     void* out[2] = {nullptr, nullptr};
     float* state[2] = {nullptr, nullptr};
     void* ws = nullptr;
+    int* status = nullptr;   // device word the kernels raise when a bounded wait runs out
 
     ~HostPipe() {
         for (int i = 0; i < 2; ++i) {
@@ -30,6 +31,7 @@ struct HostPipe {
             if (out_done[i]) cudaEventDestroy(out_done[i]);
         }
         cudaFree(ws);
+        cudaFree(status);
         if (s_in) cudaStreamDestroy(s_in);
         if (s_run) cudaStreamDestroy(s_run);
         if (s_out) cudaStreamDestroy(s_out);
@@ -69,7 +71,12 @@ extern "C" int race_b200_causal_fwd_host(const void* probs_q, const void* probs_
     seg = std::min<int64_t>(seg, std::max<int64_t>(T, 1));
     seg_shape.seq_len = seg;
     if (!race_b200_is_supported(&seg_shape, variant)) return RACE_ERR_SHAPE;
-    size_t ws_bytes = race_b200_causal_workspace_bytes(&seg_shape, 0, variant);
+    // one tile length for every segment: a shorter last segment launched with the automatic choice
+    // could pick a shorter tile and need more tile slices than the workspace holds
+    int tile = 0;
+    int rc0 = race_b200_select_tile_tokens(&seg_shape, variant, &tile);
+    if (rc0 != RACE_OK) return rc0;
+    size_t ws_bytes = race_b200_causal_workspace_bytes(&seg_shape, tile, variant);
 
     HostPipe p;
     RACE_TRY(cudaStreamCreateWithFlags(&p.s_in, cudaStreamNonBlocking));
@@ -86,10 +93,12 @@ extern "C" int race_b200_causal_fwd_host(const void* probs_q, const void* probs_
         RACE_TRY(cudaMalloc((void**)&p.state[i], sf_bytes));
     }
     RACE_TRY(cudaMalloc(&p.ws, std::max<size_t>(ws_bytes, 256)));
+    RACE_TRY(cudaMalloc((void**)&p.status, sizeof(int)));
 
     // state[0] holds the carry into segment 0
     if (carry_in) RACE_TRY(cudaMemcpyAsync(p.state[0], carry_in, sf_bytes, cudaMemcpyHostToDevice, p.s_run));
     else RACE_TRY(cudaMemsetAsync(p.state[0], 0, sf_bytes, p.s_run));
+    RACE_TRY(cudaMemsetAsync(p.status, 0, sizeof(int), p.s_run));
 
     const int64_t nseg = (T + seg - 1) / seg;
     for (int64_t i = 0; i < nseg; ++i) {
@@ -113,7 +122,7 @@ extern "C" int race_b200_causal_fwd_host(const void* probs_q, const void* probs_
         if (i >= 2) RACE_TRY(cudaStreamWaitEvent(p.s_run, p.out_done[b], 0));
         seg_shape.seq_len = len;
         int rc = race_b200_causal_fwd(p.pq[b], p.pk[b], p.v[b], p.out[b], p.state[b], p.state[b ^ 1],
-                                      p.ws, ws_bytes, &seg_shape, 0, variant, (void*)p.s_run, nullptr);
+                                      p.ws, ws_bytes, &seg_shape, tile, variant, (void*)p.s_run, p.status);
         if (rc != RACE_OK) { cudaDeviceSynchronize(); return rc; }
         RACE_TRY(cudaEventRecord(p.run_done[b], p.s_run));
 
@@ -126,8 +135,10 @@ extern "C" int race_b200_causal_fwd_host(const void* probs_q, const void* probs_
     }
     if (state_out)
         RACE_TRY(cudaMemcpyAsync(state_out, p.state[nseg & 1], sf_bytes, cudaMemcpyDeviceToHost, p.s_run));
+    int waited = 0;
+    RACE_TRY(cudaMemcpyAsync(&waited, p.status, sizeof(int), cudaMemcpyDeviceToHost, p.s_run));
     RACE_TRY(cudaStreamSynchronize(p.s_in));
     RACE_TRY(cudaStreamSynchronize(p.s_run));
     RACE_TRY(cudaStreamSynchronize(p.s_out));
-    return RACE_OK;
+    return waited ? RACE_ERR_DEVICE_WAIT : RACE_OK;
 }

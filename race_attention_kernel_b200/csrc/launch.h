@@ -34,7 +34,7 @@ size_t causal_bwd_workspace_bytes(const Dims& dm, int tile_tokens);
 // (nullable); d_carry: receives the gradient of carry_in (nullable)
 cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const void* dout, const float* carry_in,
                             const float* d_state, void* dpq, void* dpk, void* dv, float* d_carry, void* ws,
-                            const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream);
+                            const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream, int* status = nullptr);
 
 // ---- non-causal path (noncausal_simt.cu) ------------------------------------------------------
 cudaError_t noncausal_query(const void* pq, const float* totals, void* out, const Dims& dm, int dtype,
@@ -73,7 +73,8 @@ size_t tensor_workspace_bytes(const Dims& dm, int dtype, int tile_tokens);
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
                               const float* carry_in, float* state_out, void* ws, const Dims& dm,
                               int dtype, int tile_tokens, cudaStream_t stream, int* status,
-                              int phases = kPhaseAll);
+                              int phases = kPhaseAll, bool global_norm = false, long long wait_cycles = 0,
+                              int withhold_chunk = -1);
 
 // bf16 tensor path (causal_tc_bf16.cu): S a multiple of 64 (1, 2, 4 or 8 bucket groups), d_k 64 or 128
 bool tensor_bf16_supported(const Dims& dm);

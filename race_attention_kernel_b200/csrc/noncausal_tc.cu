@@ -235,7 +235,7 @@ nc_rows_tc(const NcArgs args, const float* __restrict__ totals, const float* __r
             // products still in flight have to retire before TMEM is freed (bounded)
             mma_commit(cx.bar(0));
             const long long t0 = clock64();
-            while (!mbar_try_wait(cx.bar(0), parity) && clock64() - t0 < kWaitCycles) {}
+            while (!mbar_try_wait(cx.bar(0), parity) && clock64() - t0 < cx.limit) {}
         }
         __syncwarp();
         tc_fence_after();

@@ -14,6 +14,11 @@
 // streams, or different host threads) race on it; the caller has to order them.  The array keeps
 // whatever the previous call left in it; nothing in it has to start at zero, because the tile
 // totals pass overwrites every slice the later passes read.
+//
+// Limits that follow from the per-device address cache below: the device that is current when the
+// entry point is called must be the device the stream belongs to (the array of the current device
+// is the one handed to the kernels); the cached address is not refreshed after cudaDeviceReset, so
+// a process that resets a device must not call this entry point on it afterwards.
 #include "launch.h"
 
 namespace {
@@ -58,7 +63,8 @@ int race_b200_causal_fwd_static(const void* probs_q, const void* probs_k, const 
                                 int tile_tokens, int variant, void* stream, int* status) {
     if (!shape) return RACE_ERR_NULL;
     if (!race_b200_is_supported(shape, variant)) return RACE_ERR_SHAPE;
-    // size check first: it needs no device and gives the caller a definite answer
+    // size check first, before any device memory is touched: the caller gets a definite answer (the
+    // automatic tile length behind it reads the current device's SM count, 148 if there is none)
     const size_t need = race_b200_causal_workspace_bytes(shape, tile_tokens, variant);
     if (need > kScratchBytes) return RACE_ERR_SCRATCH;
     void* scratch = nullptr;

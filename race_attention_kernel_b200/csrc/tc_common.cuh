@@ -11,7 +11,7 @@
 namespace race {
 namespace {
 
-constexpr long long kWaitCycles = 1ll << 31;   // ~1 s: bound of every device-side wait
+constexpr long long kWaitCycles = 1ll << 31;   // ~1 s: default bound of every device-side wait
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -216,6 +216,7 @@ struct Ctx {
     volatile int* abort_flag;
     int* status;
     int bars;           // byte offset of the mbarrier array
+    long long limit = kWaitCycles;   // clock cycles after which a wait gives up
     __device__ __forceinline__ uint32_t bar(int i) const { return sm_u32 + bars + i * 8; }
 };
 
@@ -227,7 +228,7 @@ __device__ __forceinline__ bool wait_bar(const Ctx& cx, int bar, uint32_t parity
     while (!mbar_try_wait(cx.bar(bar), parity)) {
         if ((++spins & 63) == 0) {
             if (*cx.abort_flag) { RACE_TRACE_STUCK(code, bar, parity); return false; }
-            if (clock64() - t0 > kWaitCycles) {
+            if (clock64() - t0 > cx.limit) {
                 *cx.abort_flag = 1;
                 if (cx.status) atomicCAS(cx.status, 0, code);
                 RACE_TRACE_STUCK(code, bar, parity);
@@ -251,7 +252,7 @@ __device__ __forceinline__ bool wait_bar2(const Ctx& cx, int bar_a, uint32_t par
         if (a && b) return true;
         if ((++spins & 63) == 0) {
             if (*cx.abort_flag) { RACE_TRACE_STUCK(code, a ? bar_b : bar_a, 0); return false; }
-            if (clock64() - t0 > kWaitCycles) {
+            if (clock64() - t0 > cx.limit) {
                 *cx.abort_flag = 1;
                 if (cx.status) atomicCAS(cx.status, 0, code);
                 RACE_TRACE_STUCK(code, a ? bar_b : bar_a, 0);

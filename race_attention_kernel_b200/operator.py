@@ -9,6 +9,12 @@
 The forward runs on the GPU only: bucket probabilities come from the producer kernel and the
 cumsum/divide/bmm of the reference is replaced by the prefix kernel.  Host tensors are
 accepted and streamed through the device; there is no CPU compute path.
+
+Gradients: the reference module is differentiable through K, V and Q (plain autograd over
+src/race_baseline.py:41-51).  Here, when autograd is recording and an input requires a gradient,
+``forward`` forms the bucket probabilities with differentiable torch ops on the GPU (the producer
+kernel has no backward) and runs the prefix path through ``ops.race_causal`` -- the same forward
+kernels with the hand-written backward kernels.  Without gradients it is the pure kernel path.
 """
 from __future__ import annotations
 
@@ -44,13 +50,39 @@ class BatchedACE(nn.Module):
         planes = self.planes_T.T.contiguous().float()
         return ops.bucket_probs(x2, planes, self.L, self.K)
 
-    @torch.no_grad()
+    def _probs_autograd(self, x2: torch.Tensor) -> torch.Tensor:
+        """src/race_baseline.py:41-44 with torch ops (differentiable); x2 [N,T,d_k] on the GPU."""
+        N, T, dk = x2.shape
+        proj = (x2.float() @ self.planes_T.float()).view(N, T, self.L, self.K)
+        logits = proj.tanh().div(dk ** 0.5) @ self.protos_T.float()
+        return torch.softmax(logits, dim=-1).to(x2.dtype)
+
+    def _forward_autograd(self, Khf, Vhf, Qhf):
+        M, B, T, H, dk = Khf.shape
+        dev = self.planes_T.device if self.planes_T.is_cuda else torch.device("cuda", torch.cuda.current_device())
+        K2, V2, Q2 = (self._streams(t.to(dev)) for t in (Khf, Vhf, Qhf))
+        out2 = ops.race_causal(self._probs_autograd(Q2), self._probs_autograd(K2), V2, self.eps)
+        out = out2.view(M, B, H, T, dk).permute(0, 1, 3, 2, 4)
+        return out if Khf.is_cuda else out.cpu()
+
     def forward(self, Khf, Vhf, Qhf, *, carry_in=None, return_state=False):
         if not (Khf.shape == Vhf.shape == Qhf.shape) or Khf.dim() != 5:
             raise RuntimeError("expected K, V, Q of identical shape [M,B,T,H,d_k]")
         M, B, T, H, dk = Khf.shape
         if dk != self.d_k:
             raise RuntimeError(f"d_k mismatch: module {self.d_k}, input {dk}")
+        if torch.is_grad_enabled() and (Khf.requires_grad or Vhf.requires_grad or Qhf.requires_grad):
+            if carry_in is not None or return_state:
+                raise RuntimeError("carry_in / return_state are inference-only; chain ops.race_causal_chunk "
+                                   "for differentiable chunked sequences")
+            if Khf.dtype not in (torch.float32, torch.bfloat16):
+                raise RuntimeError("fp32 or bf16 inputs only")
+            return self._forward_autograd(Khf, Vhf, Qhf)
+        with torch.no_grad():
+            return self._forward_kernels(Khf, Vhf, Qhf, carry_in, return_state)
+
+    def _forward_kernels(self, Khf, Vhf, Qhf, carry_in, return_state):
+        M, B, T, H, dk = Khf.shape
         host = not Khf.is_cuda
         dev = self.planes_T.device if self.planes_T.is_cuda else torch.device("cuda", torch.cuda.current_device())
         if host:

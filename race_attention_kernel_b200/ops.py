@@ -37,6 +37,27 @@ def _status_word(device: torch.device) -> torch.Tensor:
     return _STATUS[idx]
 
 
+def prepare(device=None) -> None:
+    """Create the per-device status word now.  Callers that must not allocate later (stream capture,
+    ``race_causal_prefix_static``) call this once per device at start-up; without it the static wrapper
+    runs without a status word rather than allocating one."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _status_word(dev)
+
+
+def _existing_status(device: torch.device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return _STATUS.get(idx)
+
+
+def _check_state(name, st, V, n_floats):
+    if st is None:
+        return
+    if (not isinstance(st, torch.Tensor) or not st.is_cuda or st.device != V.device or st.dtype != torch.float32
+            or not st.is_contiguous() or st.numel() != n_floats):
+        raise RuntimeError(f"{name} must be a contiguous fp32 CUDA state of N*S*(d_k+1) floats on V's device")
+
+
 def device_status(device=None, reset: bool = True) -> int:
     """Synchronise and return the status word of `device` (0 = every kernel ran to completion;
     non-zero = code of the first wait that gave up).  Reading it costs a device sync, so the
@@ -47,6 +68,14 @@ def device_status(device=None, reset: bool = True) -> int:
     if reset and val:
         word.zero_()
     return val
+
+
+def _raise_on_wait(device, what: str) -> None:
+    """With RACE_B200_CHECK_STATUS=1 (the test-suite sets it): synchronise and raise if a kernel gave up a wait."""
+    if os.environ.get("RACE_B200_CHECK_STATUS") == "1":
+        code = device_status(device)
+        if code:
+            raise RuntimeError(f"{what}: a bounded device-side wait ran out (code {code})")
 
 
 def _check_inputs(probsQ, probsK, V, need_q=True):
@@ -126,8 +155,9 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
     after the last token.  tile_tokens / variant are test hooks (0 / "auto" = automatic).
 
     normalization="global" computes the global-normalisation estimator instead (one denominator per
-    token, no eps: out_t = (pQ_t . B_t) / (pQ_t . A_t), src/causal_v2/reference.py:106-127) on the
-    CUDA-core kernels; states and carries are the same quantities in both forms.
+    token, no eps: out_t = (pQ_t . B_t) / (pQ_t . A_t), src/causal_v2/reference.py:106-127): on the
+    tcgen05 kernels for fp32, S = 64, d_k = 64, else on the CUDA-core kernels; states and carries are the
+    same quantities in both forms.
     """
     N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
     if variant not in _lib.VARIANTS:
@@ -139,15 +169,14 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
         raise RuntimeError(f"unknown normalization {normalization!r}")
     glob = normalization == "global"
     if glob:
-        if variant == "tensor" or totals_workspace is not None or V.dim() != 3:
-            raise RuntimeError("normalization='global' runs on the CUDA-core kernels with V [N,T,d_k] only")
-        var = _lib.VARIANTS["simt"]
+        if totals_workspace is not None or V.dim() != 3:
+            raise RuntimeError("normalization='global' takes V [N,T,d_k] and no totals_workspace")
+        if V.dtype != torch.float32 and variant == "auto":
+            var = _lib.VARIANTS["simt"]     # the bf16 tensor kernels do not have this form
     carry = None
     if carry_in is not None:
         carry = pack_state(*carry_in) if isinstance(carry_in, (tuple, list)) else carry_in
-        if (not carry.is_cuda or carry.dtype != torch.float32 or not carry.is_contiguous()
-                or carry.numel() != N * L * R * (dk + 1)):
-            raise RuntimeError("carry_in must be a contiguous fp32 CUDA state of N*S*(d_k+1) floats")
+        _check_state("carry_in", carry, V, N * L * R * (dk + 1))
     with torch.cuda.device(V.device):
         if out is None:
             out = torch.empty_like(V)
@@ -166,16 +195,13 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
         if glob:
             rc = L_.race_b200_causal_fwd_global(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry),
                                                 _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh), tile_tokens,
-                                                _stream())
+                                                var, _stream(), _ptr(_status_word(V.device)))
         else:
             rc = entry(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry),
                        _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh),
                        tile_tokens, var, _stream(), _ptr(_status_word(V.device)))
     _lib.check(rc, "race_b200_causal_fwd")
-    if os.environ.get("RACE_B200_CHECK_STATUS") == "1":
-        code = device_status(V.device)
-        if code:
-            raise RuntimeError(f"race_b200_causal_fwd: a bounded device-side wait ran out (code {code})")
+    _raise_on_wait(V.device, "race_b200_causal_fwd")
     if return_state:
         A, B = unpack_state(state, L, R, dk)
         return out, A, B
@@ -204,6 +230,49 @@ def race_decode_step(probsQ, probsK, V, state: torch.Tensor, eps: float = 1e-6, 
                                               _ptr(dst), ctypes.byref(sh), _stream())
     _lib.check(rc, "race_b200_decode_step")
     return out
+
+
+class DecodeStepper:
+    """``race_decode_step`` for a serving loop: shape, dtype and device are fixed and checked once, the
+    output buffer is allocated once, and a call is little more than the C-ABI call itself (the general
+    wrapper spends most of a one-token step on Python-side validation).
+
+        step = DecodeStepper(N, L, R, d_k, torch.float32, device)
+        out = step(pQ_t, pK_t, V_t, state)      # [N, tokens, d_k]; `state` advanced in place
+
+    The returned tensor is the stepper's own buffer: it is overwritten by the next call."""
+
+    def __init__(self, N: int, L: int, R: int, dk: int, dtype=torch.float32, device=None, tokens: int = 1,
+                 eps: float = 1e-6):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.shape = make_shape(N, tokens, L, R, dk, dtype, eps)
+        self._shape_ref = ctypes.byref(self.shape)
+        self._fn = _lib.lib().race_b200_decode_step
+        self._probs = (N, tokens, L, R)
+        self._v = (N, tokens, dk)
+        self._state_floats = N * L * R * (dk + 1)
+        self._dtype = dtype
+        self.out = torch.empty(N, tokens, dk, dtype=dtype, device=self.device)
+        # one validated call-through of the general wrapper's checks, on zeros
+        z = torch.zeros(N, tokens, L, R, dtype=dtype, device=self.device)
+        race_decode_step(z, z, torch.zeros(N, tokens, dk, dtype=dtype, device=self.device),
+                         torch.zeros(N, L * R * (dk + 1), device=self.device))
+
+    def __call__(self, probsQ, probsK, V, state):
+        if (probsQ.shape != self._probs or probsK.shape != self._probs or V.shape != self._v
+                or state.numel() != self._state_floats or state.dtype != torch.float32
+                or probsQ.dtype != self._dtype or probsK.dtype != self._dtype or V.dtype != self._dtype
+                or probsQ.device != self.device or probsK.device != self.device or V.device != self.device
+                or state.device != self.device
+                or not (probsQ.is_contiguous() and probsK.is_contiguous() and V.is_contiguous()
+                        and state.is_contiguous())):
+            raise RuntimeError("DecodeStepper: tensors do not match the shape/dtype/device it was built for")
+        sp = state.data_ptr()
+        rc = self._fn(probsQ.data_ptr(), probsK.data_ptr(), V.data_ptr(), self.out.data_ptr(), sp, sp,
+                      self._shape_ref, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc:
+            _lib.check(rc, "race_b200_decode_step")
+        return self.out
 
 
 def race_tile_totals(probsK, V, *, tile_tokens: int = 0, variant: str = "auto",
@@ -322,8 +391,9 @@ def race_causal_backward(probsQ, probsK, V, grad_out, eps: float = 1e-6, *, carr
         dcarry = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device) if return_grad_carry else None
         rc = L_.race_b200_causal_bwd_carry(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(grad_out), _ptr(carry_in),
                                            _ptr(grad_state), _ptr(dpq), _ptr(dpk), _ptr(dv), _ptr(dcarry), _ptr(ws),
-                                           ws_bytes, ctypes.byref(sh), _stream())
+                                           ws_bytes, ctypes.byref(sh), _stream(), _ptr(_status_word(V.device)))
     _lib.check(rc, "race_b200_causal_bwd_carry")
+    _raise_on_wait(V.device, "race_b200_causal_bwd_carry")
     return (dpq, dpk, dv, dcarry) if return_grad_carry else (dpq, dpk, dv)
 
 
@@ -372,6 +442,8 @@ class _RaceNonCausal(torch.autograd.Function):
     @staticmethod
     def forward(ctx, probsQ, probsK, V, eps):
         N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
+        if V.dim() != 3:
+            raise RuntimeError("race_noncausal takes V as [N,T,d_k]")
         L_ = _lib.lib()
         sh = make_shape(N, T, L, R, dk, V.dtype, eps)
         with torch.cuda.device(V.device):
@@ -462,15 +534,47 @@ def race_causal_prefix_static(probsQ, probsK, V, out, eps: float = 1e-6, *, carr
     packed state, and the kernels' workspace is the 16 MiB array built into the library.
     Shapes that need more raise ``RuntimeError`` (RACE_ERR_SCRATCH).  All calls share that array:
     issue them on one stream or order them with events.  Make the first call on each device
-    outside of stream capture (it looks up the array's device address)."""
+    outside of stream capture (it looks up the array's device address).  The kernels report a
+    wait that ran out through the per-device status word only if that word already exists
+    (``prepare(device)`` at start-up, or any other operator of this module called before): this
+    wrapper does not create it."""
     N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
-    if out.shape != V.shape or out.dtype != V.dtype or not out.is_contiguous() or out.device != V.device:
+    if (not isinstance(out, torch.Tensor) or out.shape != V.shape or out.dtype != V.dtype
+            or not out.is_contiguous() or out.device != V.device):
         raise RuntimeError("out must be a contiguous tensor like V")
-    sh = make_shape(N, T, L, R, dk, V.dtype, eps)
+    if variant not in _lib.VARIANTS:
+        raise RuntimeError(f"unknown variant {variant!r}")
+    _check_state("carry_in", carry_in, V, N * L * R * (dk + 1))
+    _check_state("state_out", state_out, V, N * L * R * (dk + 1))
+    sh = make_shape(N, T, L, R, dk, V.dtype, eps, _heads(V))
     with torch.cuda.device(V.device):
         rc = _lib.lib().race_b200_causal_fwd_static(
             _ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(carry_in), _ptr(state_out),
             ctypes.byref(sh), tile_tokens, _lib.VARIANTS[variant], _stream(),
-            _ptr(_status_word(V.device)))
+            _ptr(_existing_status(V.device)))
     _lib.check(rc, "race_b200_causal_fwd_static")
     return out
+
+
+def selftest_bounded_wait(probsQ, probsK, V, wait_cycles: int = 2_000_000, withhold_chunk: int = 1):
+    """Diagnostics: run the fp32 tensor forward with every device-side wait limited to ``wait_cycles``
+    SM cycles while the first CTA's load of one chunk is withheld (``race_b200_selftest_bounded_wait``).
+    Returns ``(out, code)``: ``code`` is the status the kernels raised (non-zero when the wait ran out as
+    designed); the rows of ``out`` that belong to the first tile of stream 0 are unspecified."""
+    N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
+    if V.dim() != 3:
+        raise RuntimeError("selftest_bounded_wait takes V as [N,T,d_k]")
+    L_ = _lib.lib()
+    sh = make_shape(N, T, L, R, dk, V.dtype, 1e-6)
+    var = _lib.VARIANTS["tensor"]
+    with torch.cuda.device(V.device):
+        out = torch.empty_like(V)
+        word = torch.zeros(1, dtype=torch.int32, device=V.device)
+        ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), 0, var)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
+        rc = L_.race_b200_selftest_bounded_wait(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(ws), ws_bytes,
+                                                ctypes.byref(sh), int(wait_cycles), int(withhold_chunk), _stream(),
+                                                _ptr(word))
+        _lib.check(rc, "race_b200_selftest_bounded_wait")
+        code = int(word.item())
+    return out, code

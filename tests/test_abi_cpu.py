@@ -121,17 +121,21 @@ def test_decode_step_argument_errors_without_launch():
 
 def test_global_form_argument_errors_without_launch():
     L = _lib.lib()
-    call = lambda sh: L.race_b200_causal_fwd_global(None, None, None, None, None, None, None, 0, ctypes.byref(sh),
-                                                    0, None)
-    assert call(_shape(heads=8)) == -6                  # the heads layout is read by the fp32 tensor kernels only
-    assert call(_shape(dk=96 * 4)) == -6                # outside the CUDA-core kernels' range
+    call = lambda sh, variant=0: L.race_b200_causal_fwd_global(None, None, None, None, None, None, None, 0,
+                                                               ctypes.byref(sh), 0, variant, None, None)
+    assert call(_shape(heads=8), 1) == -6               # the heads layout is read by the fp32 tensor kernels only
+    assert call(_shape(heads=8)) == -1                  # ... which AUTO picks: valid shape, NULL pointers
+    assert call(_shape(dk=96 * 4), 1) == -6             # outside the CUDA-core kernels' range
+    assert call(_shape(dk=96 * 4)) == -2                # no kernel family takes it
+    assert call(_shape(dtype=1), 2) == -6               # the bf16 tensor kernels do not have this form
     assert call(_shape()) == -1                         # valid shape, NULL pointers
     assert call(_shape(T=0)) == 0                       # nothing to launch
 
 
 def test_causal_backward_argument_errors_without_launch():
     L = _lib.lib()
-    call = lambda sh: L.race_b200_causal_bwd(None, None, None, None, None, None, None, None, 0, ctypes.byref(sh), None)
+    call = lambda sh: L.race_b200_causal_bwd(None, None, None, None, None, None, None, None, 0, ctypes.byref(sh), None,
+                                             None)
     assert call(_shape(L=3, R=32)) == -2                 # S = 96: neither <= 64 nor a multiple of 64
     assert call(_shape(dk=96 * 4)) == -2
     assert call(_shape(heads=8)) == -2
@@ -144,7 +148,19 @@ def test_causal_backward_argument_errors_without_launch():
 def test_causal_backward_carry_argument_errors_without_launch():
     L = _lib.lib()
     call = lambda sh: L.race_b200_causal_bwd_carry(None, None, None, None, None, None, None, None, None, None, None, 0,
-                                                   ctypes.byref(sh), None)
+                                                   ctypes.byref(sh), None, None)
     assert call(_shape(L=3, R=32)) == -2
     assert call(_shape()) == -1
     assert call(_shape(T=0)) == 0        # no tokens and no d_carry_in requested: nothing to do
+
+
+def test_bounded_wait_selftest_argument_errors_without_launch():
+    L = _lib.lib()
+    call = lambda sh, cycles=2_000_000, chunk=1, status=256: L.race_b200_selftest_bounded_wait(
+        None, None, None, None, None, 0, ctypes.byref(sh), cycles, chunk, None, status)
+    assert call(_shape(), status=None) == -1             # the status word is required
+    assert call(_shape(), cycles=10) == -2               # limit below the accepted range
+    assert call(_shape(), chunk=-1) == -2
+    assert call(_shape(dtype=1)) == -6                   # fp32 tensor kernels only
+    assert call(_shape(L=3, R=32)) == -6                 # S = 96: not a tensor-kernel shape
+    assert call(_shape()) == -1                          # valid arguments, NULL tensors

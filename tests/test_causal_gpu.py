@@ -246,6 +246,26 @@ def test_host_entry_matches_device_entry():
     assert ro.rel_l2(out1, ref) <= FP32_TOL
 
 
+@pytest.mark.parametrize("variant", ["simt", "tensor"])
+def test_host_entry_short_last_segment(variant):
+    """A last segment much shorter than the others must run with the tile length (and inside the
+    workspace) chosen for the full segments: 8 streams, segments of 32 768 tokens, 4 108 tokens left over."""
+    rk = _ops()
+    N, L, R, dk, seg = 8, 4, 16, 64, 32768
+    T = seg + 4108
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=77)
+    out, A, B = rk.race_causal_prefix_host(pQ.pin_memory(), pK.pin_memory(), V.pin_memory(), return_state=True,
+                                           segment_tokens=seg, variant=variant)
+    w = 2048
+    A0, B0 = ro.tile_totals(pK[:, : T - w].double(), V[:, : T - w].double())
+    ref, A1, B1 = ro.causal_prefix(pQ[-1:, T - w:].double(), pK[-1:, T - w:].double(), V[-1:, T - w:].double(),
+                                   carry=(A0[-1:], B0[-1:]), return_state=True)
+    assert ro.rel_l2(out[-1:, T - w:], ref) <= FP32_TOL
+    assert ro.rel_l2(A[-1:], A1) <= 1e-5 and ro.rel_l2(B[-1:], B1) <= 1e-4
+    head = ro.causal_prefix(pQ[:1, :1024].double(), pK[:1, :1024].double(), V[:1, :1024].double())
+    assert ro.rel_l2(out[:1, :1024], head) <= FP32_TOL
+
+
 def test_long_sequence_spot_check():
     # T = 2^18 per stream: the oracle runs on a window of one stream, fed with the true carry
     # (the method of the reference's 2^31-element test, test_forward_cuda.py:306-318)
@@ -370,9 +390,15 @@ def test_global_form_matches_reference_vectors(golden_global, name):
     (src/causal_v2/reference.py:106-127) on the features that function computed."""
     rk = _ops()
     pQ, pK, V, ref = global_case(golden_global, name)
-    out = rk.race_causal_prefix(pQ.float().cuda(), pK.float().cuda(), V.float().cuda(), normalization="global")
-    assert ro.rel_l2(out, ref) <= FP32_TOL
-    assert torch.isfinite(out).all()
+    N, T, L, R = pK.shape
+    variants = _variants(N, T, L, R, V.shape[-1], torch.float32)
+    if name == "g_k4l4":
+        assert "tensor" in variants      # the reference kernels' own geometry runs on the tcgen05 kernels too
+    for variant in variants:
+        out = rk.race_causal_prefix(pQ.float().cuda(), pK.float().cuda(), V.float().cuda(), normalization="global",
+                                    variant=variant)
+        assert ro.rel_l2(out, ref) <= FP32_TOL, variant
+        assert torch.isfinite(out).all()
 
 
 @pytest.mark.parametrize("N,T,L,R,dk,dtype,tol", [
@@ -389,28 +415,33 @@ def test_global_form_parity_and_carry(N, T, L, R, dk, dtype, tol):
     pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=11 * N + T, dtype=dtype)
     ref, A_ref, B_ref = ro.causal_prefix_global(pQ.double(), pK.double(), V.double(), return_state=True)
     q, k, v = pQ.cuda(), pK.cuda(), V.cuda()
-    out, A, B = rk.race_causal_prefix(q, k, v, normalization="global", return_state=True)
-    assert ro.rel_l2(out, ref) <= tol
-    assert ro.rel_l2(A, A_ref) <= tol and ro.rel_l2(B, B_ref) <= tol
-    # two calls with the carried state equal one call; small tiles exercise the scan
-    h = T // 3
-    o1, A1, B1 = rk.race_causal_prefix(q[:, :h].contiguous(), k[:, :h].contiguous(), v[:, :h].contiguous(),
-                                       normalization="global", return_state=True, tile_tokens=32)
-    o2 = rk.race_causal_prefix(q[:, h:].contiguous(), k[:, h:].contiguous(), v[:, h:].contiguous(),
-                               normalization="global", carry_in=(A1, B1), tile_tokens=64)
-    assert ro.rel_l2(torch.cat([o1, o2], 1), ref) <= tol
+    variants = ["simt"] + (["tensor"] if dtype == torch.float32 and "tensor" in _variants(N, T, L, R, dk, dtype) else [])
+    for variant in variants:
+        out, A, B = rk.race_causal_prefix(q, k, v, normalization="global", return_state=True, variant=variant)
+        assert ro.rel_l2(out, ref) <= tol, variant
+        assert ro.rel_l2(A, A_ref) <= tol and ro.rel_l2(B, B_ref) <= tol
+        # two calls with the carried state equal one call; small tiles exercise the scan
+        h = T // 3
+        t1, t2 = (32, 64) if variant == "simt" else (64, 128)
+        o1, A1, B1 = rk.race_causal_prefix(q[:, :h].contiguous(), k[:, :h].contiguous(), v[:, :h].contiguous(),
+                                           normalization="global", return_state=True, tile_tokens=t1, variant=variant)
+        o2 = rk.race_causal_prefix(q[:, h:].contiguous(), k[:, h:].contiguous(), v[:, h:].contiguous(),
+                                   normalization="global", carry_in=(A1, B1), tile_tokens=t2, variant=variant)
+        assert ro.rel_l2(torch.cat([o1, o2], 1), ref) <= tol, variant
 
 
 def test_global_form_zero_denominator_and_rejections():
     rk = _ops()
     pQ, pK, V = ro.synthetic_probs(2, 64, 4, 16, 64, seed=3)
     pK[0, :10] = 0          # stream 0 has no key mass for its first ten tokens: those rows are 0
-    out = rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="global")
     ref = ro.causal_prefix_global(pQ.double(), pK.double(), V.double())
-    assert not out[0, :10].any() and torch.isfinite(out).all()
-    assert ro.rel_l2(out, ref) <= FP32_TOL
-    with pytest.raises(RuntimeError):
-        rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="global", variant="tensor")
+    for variant in ("simt", "tensor", "auto"):
+        out = rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="global", variant=variant)
+        assert not out[0, :10].any() and torch.isfinite(out).all(), variant
+        assert ro.rel_l2(out, ref) <= FP32_TOL, variant
+    with pytest.raises(RuntimeError):     # the bf16 tensor kernels do not have this form
+        rk.race_causal_prefix(pQ.bfloat16().cuda(), pK.bfloat16().cuda(), V.bfloat16().cuda(),
+                              normalization="global", variant="tensor")
     with pytest.raises(RuntimeError):
         rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="paper")
 
@@ -549,3 +580,77 @@ def test_causal_backward_long_sequence():
     got = rk.race_causal_backward(pQ.cuda(), pK.cuda(), V.cuda(), dO.cuda())
     for name, g, r in zip(("dPQ", "dPK", "dV"), got, ref):
         assert ro.rel_l2(g, r) <= FP32_TOL, name
+
+
+def test_bounded_wait_runs_out_and_device_stays_usable():
+    """A wait that nothing satisfies must end by its limit: the producer of the first CTA withholds one
+    chunk's load, every wait is limited to about a millisecond, and the kernel has to return with the
+    status word set -- after which an ordinary forward on the same device is bit-identical to one run
+    before.  No memory fault and no unbounded spin is involved."""
+    rk = _ops()
+    N, T, L, R, dk = 2, 32768, 4, 16, 64
+    assert rk.select_tile_tokens(N, T, L, R, dk, variant="tensor") >= 6 * 64      # chunks 0, 1 and 5 exist in a tile
+    pQ, pK, V = (t.cuda() for t in ro.synthetic_probs(N, T, L, R, dk, seed=99))
+    before = rk.race_causal_prefix(pQ, pK, V, variant="tensor")
+    assert rk.ops.device_status() == 0
+    for chunk in (0, 1, 5):
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        out, code = rk.ops.selftest_bounded_wait(pQ, pK, V, wait_cycles=2_000_000, withhold_chunk=chunk)
+        t1.record()
+        torch.cuda.synchronize()
+        assert code != 0, "the withheld load went unnoticed"
+        assert 100 <= code < 500, code                    # one of the kernels' wait codes
+        assert t0.elapsed_time(t1) < 1000.0               # ended by the limit (~1 ms), not by the default (~1 s)
+        # tiles of the other stream never depended on the withheld chunk
+        assert torch.equal(out[1], before[1])
+        assert rk.ops.device_status() == 0                # the self-test used its own status word
+        again = rk.race_causal_prefix(pQ, pK, V, variant="tensor")
+        assert torch.equal(again, before)
+    # a chunk index beyond the tile: nothing is withheld, nothing runs out
+    out, code = rk.ops.selftest_bounded_wait(pQ, pK, V, wait_cycles=2_000_000, withhold_chunk=10_000)
+    assert code == 0 and torch.equal(out, before)
+
+
+def test_operator_gradients_match_reference():
+    """BatchedACE under autograd: gradients w.r.t. K, V, Q against the reference module's own autograd
+    gradients (tests/golden/make_golden_grad.py, fp64), through the forward and backward kernels."""
+    import os
+
+    import numpy as np
+    rk = _ops()
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "race_grad_golden.npz"))
+    for name in ("grad_k4l4", "grad_k3l2_d32"):
+        M, B, H, dk, K, L, T = (int(x) for x in g[f"{name}/cfg"])
+        ace = rk.BatchedACE(dk, K, L, M)
+        ace.planes_T = torch.from_numpy(g[f"{name}/planes_T"]).float()
+        ace = ace.cuda()
+        Kh, Vh, Qh = (torch.from_numpy(g[f"{name}/{k}"]).float().cuda().requires_grad_(True) for k in "KVQ")
+        out = ace(Kh, Vh, Qh)
+        assert out.requires_grad
+        assert ro.rel_l2(out, torch.from_numpy(g[f"{name}/out"])) <= FP32_TOL
+        out.backward(torch.from_numpy(g[f"{name}/dO"]).float().cuda())
+        for t, key in ((Kh, "dK"), (Vh, "dV"), (Qh, "dQ")):
+            assert ro.rel_l2(t.grad, torch.from_numpy(g[f"{name}/{key}"])) <= 5e-4, (name, key)
+        # without gradients the same call takes the pure kernel path and agrees
+        with torch.no_grad():
+            plain = ace(Kh, Vh, Qh)
+        assert not plain.requires_grad and ro.rel_l2(plain, out) <= 1e-5
+
+
+def test_decode_stepper_matches_general_wrapper():
+    rk = _ops()
+    N, L, R, dk = 8, 4, 16, 64
+    pQ, pK, V = (t.cuda() for t in ro.synthetic_probs(N, 40, L, R, dk, seed=21))
+    step = rk.DecodeStepper(N, L, R, dk, torch.float32, torch.device("cuda", torch.cuda.current_device()))
+    s1 = torch.zeros(N, L * R * (dk + 1), device="cuda")
+    s2 = torch.zeros_like(s1)
+    for t in range(40):
+        q, k, v = (x[:, t:t + 1].contiguous() for x in (pQ, pK, V))
+        a = step(q, k, v, s1).clone()
+        b = rk.race_decode_step(q, k, v, s2)
+        assert torch.equal(a, b)
+    assert torch.equal(s1, s2)
+    with pytest.raises(RuntimeError):
+        step(pQ[:, :2].contiguous(), pK[:, :2].contiguous(), V[:, :2].contiguous(), s1)

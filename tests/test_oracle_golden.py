@@ -158,3 +158,19 @@ def test_causal_closed_form_matches_autograd(N, T, L, R, dk):
     ref = ro.causal_backward_autograd(pQ, pK, V, dO)
     for g, r in zip(got, ref):
         assert ro.rel_l2(g, r) <= 1e-12
+
+
+@pytest.mark.parametrize("name", ["grad_k4l4", "grad_k3l2_d32"])
+def test_oracle_gradients_match_reference_autograd(name):
+    """The restated operator under torch.autograd reproduces the reference module's own gradients
+    w.r.t. K, V, Q (fixture written by tests/golden/make_golden_grad.py, fp64)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "race_grad_golden.npz"))
+    M, B, H, dk, K, L, T = (int(x) for x in g[f"{name}/cfg"])
+    planes_T = torch.from_numpy(g[f"{name}/planes_T"])
+    Kh, Vh, Qh = (torch.from_numpy(g[f"{name}/{k}"]).requires_grad_(True) for k in "KVQ")
+    out = ro.batched_ace_forward(planes_T, ro.make_protos(K, torch.float64), Kh, Vh, Qh, L, K)
+    assert (out - torch.from_numpy(g[f"{name}/out"])).abs().max().item() <= 1e-12
+    out.backward(torch.from_numpy(g[f"{name}/dO"]))
+    for t, key in ((Kh, "dK"), (Vh, "dV"), (Qh, "dQ")):
+        assert ro.rel_l2(t.grad, torch.from_numpy(g[f"{name}/{key}"])) <= 1e-12, key

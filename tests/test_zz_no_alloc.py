@@ -70,3 +70,36 @@ def test_static_scratch_matches_ordinary_entry_twice():
                 carry=None if carry is None else (A0.double().cpu(), B0.double().cpu()))
             assert ro.rel_l2(out, want) <= 1e-4
     assert rk.ops.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_static_wrapper_allocates_nothing_as_first_call():
+    """The Python wrapper must not create the per-device status word on the fly: with the word absent
+    (a process whose first operator call is the allocation-free one) the call still allocates nothing."""
+    import race_attention_kernel_b200 as rk
+    from race_attention_kernel_b200 import ops
+
+    torch.cuda.set_device(0)
+    N, T, L, R, dk = 2, 1000, 4, 16, 64
+    pQ, pK, V = (t.cuda() for t in ro.synthetic_probs(N, T, L, R, dk, seed=5))
+    ref = rk.race_causal_prefix(pQ, pK, V)
+    out = torch.full_like(V, float("nan"))
+    saved = dict(ops._STATUS)
+    ops._STATUS.clear()
+    try:
+        before = torch.cuda.memory_allocated()
+        rk.race_causal_prefix_static(pQ, pK, V, out)
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before
+        assert not ops._STATUS                      # still absent: nothing was created behind the caller's back
+    finally:
+        ops._STATUS.update(saved)
+    assert torch.equal(out, ref)
+    # bad carry / state arguments are refused before they reach the device
+    with pytest.raises(RuntimeError):
+        rk.race_causal_prefix_static(pQ, pK, V, out, carry_in=torch.zeros(N, L * R * (dk + 1)))          # host tensor
+    with pytest.raises(RuntimeError):
+        rk.race_causal_prefix_static(pQ, pK, V, out, state_out=torch.zeros(N, 8, device="cuda"))           # too short
+    with pytest.raises(RuntimeError):
+        rk.race_causal_prefix_static(pQ, pK, V, out, carry_in=torch.zeros(N, L * R * (dk + 1), device="cuda",
+                                                                          dtype=torch.float64))
