@@ -13,9 +13,16 @@ One step = one forward over all streams.  Metric: M tokens/s = streams*T / secon
   roofline  algorithmic bytes elt*(2S+2d_k) per token-stream / measured forward time, against the
             measured HBM copy peak (MEASURED_PEAKS.json) or the stated fallback
   cpu_baseline   the CPU oracle (port of the reference's path) on this box's host cores
+  c4, c3    sub-records of the same line: the sequence-sharded configuration (N=8, T=4,194,304 fp32 cut
+            over the ranks, carry chain over NCCL send/recv) and the bf16 configuration (256 streams,
+            T=262,144, S=512, d_k=128, split over the ranks, walked in batches of 32 streams)
 
 With N > 1 (torchrun) every rank runs its own N=8 streams: streams are independent, so ranks
 share nothing on the data path ("weak" scaling); only timing uses a collective.
+
+Parity gates (a kernel that fails one is not timed): the first 1024 tokens of stream 0, the LAST 2048
+tokens of the last stream against the oracle fed the true fp64 carry of everything before them, and the
+returned final state of every stream against fp64 totals -- at the full headline length.
 """
 from __future__ import annotations
 
@@ -47,6 +54,7 @@ def parse():
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-sub", action="store_true", help="skip the c4 / c3 sub-records")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c4", "c5", "operator", "next"],
                     help="c2 (default): the contract line; the others print extra measurement lines")
@@ -142,50 +150,173 @@ def _time_ms(fn, warmup, steps):
     return e0.elapsed_time(e1) / steps
 
 
+def fp64_state(pK_n, V_n, upto: int, block: int = 1 << 19):
+    """fp64 (A [L,R], B [L,R,d_k]) over tokens [0, upto) of ONE stream (pK_n [T,L,R], V_n [T,d_k] on the
+    device), accumulated block by block so that the fp64 temporaries stay small."""
+    Tn, L, R = pK_n.shape
+    dk = V_n.shape[-1]
+    A = torch.zeros(L * R, dtype=torch.float64, device=pK_n.device)
+    B = torch.zeros(L * R, dk, dtype=torch.float64, device=pK_n.device)
+    for t0 in range(0, upto, block):
+        t1 = min(upto, t0 + block)
+        k = pK_n[t0:t1].reshape(t1 - t0, L * R).double()
+        A += k.sum(0)
+        B += k.T @ V_n[t0:t1].double()
+    return A.view(L, R), B.view(L, R, dk)
+
+
+def window_parity(ro, pQ, pK, V, out, A=None, B=None, window: int = 2048, carry=None):
+    """rel-L2 of the last `window` tokens of the last stream against the oracle fed the fp64 state of all
+    tokens before them (+ `carry`, the fp64 state before this tensor's first token), and, when the final
+    state (A, B) is given, its worst rel-L2 over the streams against fp64 totals.  The method of the
+    reference's large-tensor test (src/causal_v2/tests/test_forward_cuda.py:306-318)."""
+    N, T = pK.shape[0], pK.shape[1]
+    n, w = N - 1, min(window, T)
+    A0, B0 = fp64_state(pK[n], V[n], T - w)
+    if carry is not None:
+        A0, B0 = A0 + carry[0], B0 + carry[1]
+    ref, A1, B1 = ro.causal_prefix(pQ[n:, T - w:].double().cpu(), pK[n:, T - w:].double().cpu(),
+                                   V[n:, T - w:].double().cpu(), carry=(A0.cpu()[None], B0.cpu()[None]),
+                                   return_state=True)
+    tail = ro.rel_l2(out[n:, T - w:], ref)
+    state = None
+    if A is not None:
+        state = max(ro.rel_l2(A[n:], A1), ro.rel_l2(B[n:], B1))
+        for m in range(N - 1):
+            Am, Bm = fp64_state(pK[m], V[m], T)
+            state = max(state, ro.rel_l2(A[m], Am), ro.rel_l2(B[m], Bm))
+    return tail, state
+
+
+def _probs_on_device(N, T, L, R, dtype, g, dev):
+    # generated stream by stream to bound the fp32 temporaries
+    out = torch.empty(N, T, L, R, dtype=dtype, device=dev)
+    for n in range(N):
+        out[n] = torch.softmax(torch.randn(T, L, R, device=dev, generator=g), -1).to(dtype)
+    return out
+
+
+def sub_c4(rk, ro, dev, rank, world, steps=5, warmup=2):
+    """Sequence-sharded configuration on the ranks of this run: N=8, T=4,194,304 fp32, contiguous T/world tokens
+    per rank; local totals, carry chain (NCCL send/recv of N*S*(d_k+1) floats per hop), output pass with
+    the received carry.  Strong scaling: the total work is fixed."""
+    import torch.distributed as dist
+
+    from race_attention_kernel_b200 import multigpu as mg
+    N, L, R, dk, T = 8, 4, 16, 64, 4194304
+
+    def reduce_max(x):
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    def run(q, k, v):
+        if world > 1:
+            return mg.sequence_sharded_prefix(q, k, v, mode="chain")
+        return rk.race_causal_prefix(q, k, v)
+
+    # gate 1: a short sequence, the same inputs on every rank, each rank's slice against the oracle
+    Ts = 20000
+    pQ, pK, V = ro.synthetic_probs(N, Ts, L, R, dk, seed=3)
+    sl = mg.shard_tokens(Ts, world, rank)
+    ref = ro.causal_prefix_chunked(pQ.double(), pK.double(), V.double(), chunk=512)[:, sl]
+    err_short = reduce_max(ro.rel_l2(run(pQ[:, sl].contiguous().to(dev), pK[:, sl].contiguous().to(dev),
+                                         V[:, sl].contiguous().to(dev)), ref))
+    if not err_short <= 1e-4:
+        raise SystemExit(f"c4 parity gate failed: rel-L2 {err_short:.3e}")
+    Tl = T // world
+    g = torch.Generator(device=dev).manual_seed(4000 + rank)
+    q = _probs_on_device(N, Tl, L, R, torch.float32, g, dev)
+    k = _probs_on_device(N, Tl, L, R, torch.float32, g, dev)
+    v = torch.randn(N, Tl, dk, device=dev, generator=g)
+    # gate 2, at full size: the last 2048 tokens of the last stream on the LAST rank, against the oracle fed
+    # the fp64 state of all tokens before them on every rank
+    out = run(q, k, v)
+    A_own, B_own = fp64_state(k[N - 1], v[N - 1], Tl)
+    packed = torch.cat([A_own.reshape(-1), B_own.reshape(-1)])
+    parts = [torch.empty_like(packed) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(parts, packed)
+    err_tail = 0.0
+    if rank == world - 1:
+        carry = torch.zeros_like(packed)
+        for r in range(world - 1):
+            carry += parts[r]
+        cA, cB = carry[: L * R].view(L, R), carry[L * R:].view(L, R, dk)
+        err_tail, _ = window_parity(ro, q, k, v, out, carry=(cA, cB))
+    err_tail = reduce_max(err_tail)
+    if not err_tail <= 1e-4:
+        raise SystemExit(f"c4 tail parity gate failed: rel-L2 {err_tail:.3e}")
+    del out
+    if world > 1:
+        dist.barrier()
+    ms = reduce_max(_time_ms(lambda: run(q, k, v), warmup, steps))
+    return {"workload": f"C4 causal fwd f32 N={N} T={T} sharded over {world} rank(s), carry chain send/recv",
+            "ranks": world, "tokens_per_rank": Tl, "ms_per_step": ms, "value": N * T / ms / 1e3, "unit": "Mtok/s",
+            "scaling": "strong", "steps": steps, "warmup": warmup, "carry_bytes_per_hop": N * L * R * (dk + 1) * 4,
+            "parity_rel_l2": max(err_short, err_tail), "parity_short_rel_l2": err_short,
+            "parity_tail_rel_l2": err_tail}
+
+
+def sub_c3(rk, ro, dev, rank, world, peak, steps=2, warmup=1):
+    """bf16 configuration: 256 streams of T=262,144 tokens, S=512 (L=8, R=64), d_k=128, split over the ranks with
+    no communication; a rank walks its streams in batches of 32 through one set of device buffers (all
+    256 streams are 172 GB of probabilities and do not fit one GPU)."""
+    import torch.distributed as dist
+
+    from race_attention_kernel_b200 import multigpu as mg
+    L, R, dk, T, N_total, batch = 8, 64, 128, 262144, 256, 32
+    mine = mg.shard_streams(N_total, world, rank)
+    n_mine = mine.stop - mine.start
+    # gate: a small case of the same geometry through the same kernels against the fp64 oracle
+    pQ, pK, V = (t.bfloat16() for t in ro.synthetic_probs(2, 300, L, R, dk, seed=33))
+    ref = ro.causal_prefix_chunked(pQ.double(), pK.double(), V.double(), chunk=128)
+    err = ro.rel_l2(rk.race_causal_prefix(pQ.to(dev), pK.to(dev), V.to(dev)), ref)
+    if not err <= 2e-2:
+        raise SystemExit(f"c3 parity gate failed: rel-L2 {err:.3e}")
+    g = torch.Generator(device=dev).manual_seed(3000 + rank)
+    nb = min(batch, n_mine)
+    q = _probs_on_device(nb, T, L, R, torch.bfloat16, g, dev)
+    k = _probs_on_device(nb, T, L, R, torch.bfloat16, g, dev)
+    v = torch.randn(nb, T, dk, device=dev, generator=g).bfloat16()
+    out = torch.empty_like(v)
+    batches = (n_mine + nb - 1) // nb
+
+    def step():
+        for _ in range(batches):
+            rk.race_causal_prefix(q, k, v, out=out)
+
+    if world > 1:
+        dist.barrier()
+    ms = _time_ms(step, warmup, steps)
+    t = torch.tensor([ms, err], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, err = t[0].item(), t[1].item()
+    gbs = n_mine * T * 2 * (2 * L * R + 2 * dk) / (ms * 1e-3) / 1e9     # this rank's algorithmic bytes
+    return {"workload": f"C3 causal fwd bf16 {N_total} streams T={T} d_k={dk} L={L} R={R}, streams split over "
+                        f"{world} rank(s), batches of {nb}",
+            "ranks": world, "streams_per_rank": n_mine, "batches_per_step": batches, "ms_per_step": ms,
+            "value": N_total * T / ms / 1e3, "unit": "Mtok/s", "scaling": "strong", "steps": steps, "warmup": warmup,
+            "GB_s_per_gpu": gbs, "frac": gbs / peak, "parity_rel_l2": err}
+
+
 def workload_c4(args):
-    """Single ultra-long sequence configuration: one long sequence per stream (N=8, T=4,194,304, fp32) sharded contiguously
-    over the ranks (run under torchrun); carry chain over NCCL send/recv."""
+    """The sequence-sharded configuration alone (run under torchrun for more than one rank)."""
     import torch.distributed as dist
 
     import race_attention_kernel_b200 as rk
     from oracle import race_oracle as ro
-    from race_attention_kernel_b200 import multigpu as mg
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    N, L, R, dk, T = 8, 4, 16, 64, 4194304
-
-    def reduce_max(x):
-        t = torch.tensor([x], device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return t.item()
-
-    # parity on a short sequence first: every rank builds the same inputs and takes its slice
-    Ts = 20000
-    pQ, pK, V = ro.synthetic_probs(N, Ts, L, R, dk, seed=3)
-    sl = mg.shard_tokens(Ts, world, rank)
-    ref = ro.causal_prefix_chunked(pQ.double(), pK.double(), V.double(), chunk=512)[:, sl]
-    run = (lambda q, k, v, mode: mg.sequence_sharded_prefix(q, k, v, mode=mode)) if world > 1 else \
-          (lambda q, k, v, mode: rk.race_causal_prefix(q, k, v))
-    err = reduce_max(ro.rel_l2(run(pQ[:, sl].contiguous().cuda(), pK[:, sl].contiguous().cuda(),
-                                   V[:, sl].contiguous().cuda(), "chain"), ref))
-    if not err <= 1e-4:
-        raise SystemExit(f"parity gate failed: rel-L2 {err:.3e}")
-    Tl = T // world
-    g = torch.Generator(device=dev).manual_seed(rank)
-    q = torch.softmax(torch.randn(N, Tl, L, R, device=dev, generator=g), -1)
-    k = torch.softmax(torch.randn(N, Tl, L, R, device=dev, generator=g), -1)
-    v = torch.randn(N, Tl, dk, device=dev, generator=g)
-    for mode in (("chain", "allgather") if world > 1 else ("single",)):
-        ms = reduce_max(_time_ms(lambda: run(q, k, v, mode), args.warmup, args.steps))
-        if rank == 0:
-            print(json.dumps({"workload": "c4", "mode": mode, "n_gpus": world, "N": N, "T": T,
-                              "ms_per_step": round(ms, 3), "Mtok_s": round(N * T / ms / 1e3, 1),
-                              "scaling": "strong", "parity_rel_l2": err}), flush=True)
+    rec = sub_c4(rk, ro, dev, rank, world, steps=args.steps, warmup=args.warmup)
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -220,6 +351,9 @@ def extra_workloads(args):
                 V = torch.randn(N, T, dk, device=dev, generator=g)
                 out = torch.empty_like(V)
                 ms = _time_ms(lambda: rk.race_causal_prefix(pQ, pK, V, out=out), 3, 10 if T <= (1 << 21) else 3)
+                # parity spot check at this length: last window of the last stream with the fp64 carry
+                from oracle import race_oracle as ro
+                tail, _ = window_parity(ro, pQ, pK, V, out)
             except (torch.OutOfMemoryError, RuntimeError) as e:
                 print(json.dumps({"workload": "sweep", "T": T, "failed": str(e)[:80]}), flush=True)
                 break
@@ -228,7 +362,10 @@ def extra_workloads(args):
                               "Mtok_s": round(N * T / ms / 1e3, 1), "GB_s": round(gbs, 1),
                               "frac_measured_peak": round(gbs / peak, 4),
                               "peak_GiB": round(torch.cuda.max_memory_allocated() / 2**30, 2),
+                              "parity_tail_rel_l2": tail, "parity_ok": bool(tail <= 1e-4),
                               "status": rk.ops.device_status(dev)}), flush=True)
+            if not tail <= 1e-4:
+                break
             del pQ, pK, V, out
             torch.cuda.empty_cache()
             torch.cuda.reset_peak_memory_stats()
@@ -287,6 +424,24 @@ def extra_workloads(args):
                               "frac_measured_peak": round(byts / ms / 1e6 / peak, 4),
                               "Mtok_s": round(N / ms / 1e3, 2)}), flush=True)
             del pQ, pK, V, state
+        # launch path of a one-token step at N=8 streams: general wrapper vs the pre-validated stepper
+        N, L, R, dk = 8, 4, 16, 64
+        pQ, pK = probs(N, 1, L, R, torch.float32, g), probs(N, 1, L, R, torch.float32, g)
+        V = torch.randn(N, 1, dk, device=dev, generator=g)
+        state = torch.rand(N, L * R * (dk + 1), device=dev)
+        stepper = rk.DecodeStepper(N, L, R, dk, torch.float32, dev)
+        for name, fn in (("race_decode_step", lambda: rk.race_decode_step(pQ, pK, V, state)),
+                         ("DecodeStepper", lambda: stepper(pQ, pK, V, state))):
+            for _ in range(20):
+                fn()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(2000):
+                fn()
+            torch.cuda.synchronize()
+            print(json.dumps({"workload": "decode_step_launch_path", "api": name, "N": N,
+                              "us_per_call": round((time.perf_counter() - t0) / 2000 * 1e6, 2)}), flush=True)
+        del pQ, pK, V, state
         N, T, L, R, dk = 8, 131072, 4, 16, 64
         pQ, pK = probs(N, T, L, R, torch.float32, g), probs(N, T, L, R, torch.float32, g)
         V = torch.randn(N, T, dk, device=dev, generator=g)
@@ -321,6 +476,31 @@ def extra_workloads(args):
             torch.cuda.empty_cache()
 
 
+# DRAM traffic of one forward per algorithmic byte, by kernel, from the ncu capture summarised under
+# profiles/ (causal_out_tc_N8_T131072_ncu_full.md: T=131072, 1073.7 MB of algorithmic bytes per launch set;
+# traffic grows in proportion to the tokens processed).  Update together with that file.
+TRAFFIC_MB_PER_1073_7 = {"causal_out_tc": 1053.7, "tile_totals_tc": 547.9, "tile_scan": 17.0}
+
+
+def reference_arm(args, workload):
+    """The reference's own CPU path for this workload -- its memory-light chunked restatement
+    (src/race_chunked.py), which it uses as the timing baseline for long T -- as restated by the oracle, on
+    the box's host cores with all threads, at the FULL sequence length of the workload.  A full-size step
+    takes about a minute, so the step counts actually run (and printed) are small: 1 warm-up + 2 timed."""
+    T = args.seq_len
+    steps, warmup = min(args.steps, 2), min(args.warmup, 1)
+    res = cpu_run(T, steps, warmup)
+    return {"impl": "reference", "metric": "causal_fwd_tokens_per_s", "value": res["value"],
+            "unit": "Mtok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "ms_per_step": res["seconds_per_step"] * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload},
+            "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": res["value"], "unit": "Mtok/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+
+
 def main():
     args = parse()
     if args.workload != "c2":
@@ -334,26 +514,14 @@ def main():
     workload = f"C2 causal fwd {args.dtype} N={N}/GPU T={T} d_k={dk} L={L} R={R} (probs-in)"
 
     if args.impl == "reference":
-        # the reference's own CPU path (its memory-light chunked restatement, which it uses as the
-        # timing baseline for long T) on a bounded sample of the same workload; rank 0 only
-        if rank != 0:
-            return
-        T_s = min(T, 32768)
-        res = cpu_run(T_s, max(1, min(args.steps, 3)), max(1, min(args.warmup, 1)))
-        line = {"impl": "reference", "metric": "causal_fwd_tokens_per_s", "value": res["value"],
-                "unit": "Mtok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": res["seconds_per_step"] * 1e3, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": workload, "sample_T": T_s},
-                "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
-                "e2e": {"value": res["value"], "unit": "Mtok/s", "h2d_bytes_per_step": 0,
-                        "d2h_bytes_per_step": 0}}
-        print(json.dumps(line), flush=True)
+        if rank == 0:      # rank 0 alone runs the CPU arm; the other ranks have nothing to do
+            print(json.dumps(reference_arm(args, workload)), flush=True)
         return
 
     import torch.distributed as dist
 
     import race_attention_kernel_b200 as rk
+    from oracle import race_oracle as ro
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -361,6 +529,13 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     tdtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
     elt = 4 if args.dtype == "f32" else 2
+    tol = 1e-4 if args.dtype == "f32" else 2e-2
+    peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+        peak_src = "measured"
+    except Exception:
+        pass
 
     # synthetic inputs generated on the device for the resident-input leg (8.6 GB at T=2^20)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
@@ -377,16 +552,17 @@ def main():
     def step():
         rk.race_causal_prefix(pQ, pK, V, variant=variant, out=out)
 
-    # parity gate on a window before timing: a wrong kernel is not timed
-    from oracle import race_oracle as ro
-    step()
+    # parity gates before timing, at the full length: a wrong kernel is not timed
+    _, A_fin, B_fin = rk.race_causal_prefix(pQ, pK, V, variant=variant, out=out, return_state=True)
     torch.cuda.synchronize()
     w = min(T, 1024)
     ref = ro.causal_prefix(pQ[:1, :w].double().cpu(), pK[:1, :w].double().cpu(), V[:1, :w].double().cpu())
-    err = ro.rel_l2(out[:1, :w], ref)
-    tol = 1e-4 if args.dtype == "f32" else 2e-2
-    if not err <= tol:
-        raise SystemExit(f"parity gate failed: rel-L2 {err:.3e} > {tol}")
+    err_head = ro.rel_l2(out[:1, :w], ref)
+    err_tail, err_state = window_parity(ro, pQ, pK, V, out, A_fin, B_fin)
+    del A_fin, B_fin
+    if not (err_head <= tol and err_tail <= tol and err_state <= tol):
+        raise SystemExit(f"parity gate failed: rel-L2 head {err_head:.3e} tail {err_tail:.3e} "
+                         f"state {err_state:.3e} > {tol}")
 
     for _ in range(args.warmup):
         step()
@@ -415,26 +591,30 @@ def main():
 
     # roofline of the forward: algorithmic bytes / measured time of one forward on this rank
     alg_bytes = N * T * elt * (2 * S + 2 * dk)
-    peak, peak_src = FALLBACK_HBM_GBS, "fallback"
-    try:
-        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
-        peak_src = "measured"
-    except Exception:
-        pass
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
-    # DRAM traffic of one forward from the ncu capture in profiles/ (T=131072: output pass 1053.7 MB,
-    # totals pass 547.9 MB, scan 17 MB per 1073.7 MB of algorithmic bytes), scaled by tokens
-    traffic = alg_bytes * (1053.7 + 547.9 + 17.0) / 1073.7 if (variant == "tensor" and args.dtype == "f32") else None
+    traffic = (alg_bytes * sum(TRAFFIC_MB_PER_1073_7.values()) / 1073.7
+               if (variant == "tensor" and args.dtype == "f32") else None)
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                 "kernel": "causal forward (tile_totals_tc + tile_scan + causal_out_tc of one step)",
                 "algorithmic_bytes_per_launch": alg_bytes}
+    del pQ, pK, V, out
+    torch.cuda.empty_cache()
+
+    # sub-records: the sequence-sharded and the bf16 configuration on the same ranks
+    c4 = c3 = None
+    if not args.no_sub and args.dtype == "f32" and T == (1 << 20):
+        c4 = sub_c4(rk, ro, dev, rank, world)
+        torch.cuda.empty_cache()
+        c3 = sub_c3(rk, ro, dev, rank, world, peak)
+        torch.cuda.empty_cache()
+        code = rk.ops.device_status(dev)
+        if code:
+            raise SystemExit(f"a bounded device-side wait ran out in a sub-record (code {code})")
 
     # e2e: host buffers through the C-ABI host entry point
     e2e = None
     if not args.no_e2e:
-        del pQ, pK, V, out
-        torch.cuda.empty_cache()
         gh = torch.Generator().manual_seed(rank)
         hq = torch.softmax(torch.randn(N, T, L, R, generator=gh), -1).to(tdtype).pin_memory()
         hk = torch.softmax(torch.randn(N, T, L, R, generator=gh), -1).to(tdtype).pin_memory()
@@ -447,18 +627,45 @@ def main():
         for _ in range(args.e2e_steps):
             rk.race_causal_prefix_host(hq, hk, hv, out=ho, variant=variant, device=local)
         dt = (time.perf_counter() - t0) / args.e2e_steps
+        # the floor of that step: the same bytes moved by plain pinned copies, both directions at once
+        dq, dk_, dv = (torch.empty_like(t, device=dev) for t in (hq, hk, hv))
+        do = torch.empty_like(hv, device=dev)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+        def copies():
+            with torch.cuda.stream(s_in):
+                dq.copy_(hq, non_blocking=True)
+                dk_.copy_(hk, non_blocking=True)
+                dv.copy_(hv, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                ho.copy_(do, non_blocking=True)
+            s_in.synchronize()
+            s_out.synchronize()
+        copies()
         if world > 1:
-            t = torch.tensor([dt], device=dev)
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            copies()
+        dt_copy = (time.perf_counter() - t0) / args.e2e_steps
+        if world > 1:
+            t = torch.tensor([dt, dt_copy], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = t.item()
+            dt, dt_copy = t[0].item(), t[1].item()
+        h2d, d2h = N * T * elt * (2 * S + dk), N * T * elt * dk
         e2e = {"value": tokens_total / dt / 1e6, "unit": "Mtok/s",
-               "h2d_bytes_per_step": N * T * elt * (2 * S + dk), "d2h_bytes_per_step": N * T * elt * dk,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "ms_per_step": dt * 1e3, "steps": args.e2e_steps,
-               "api": "race_b200_causal_fwd_host (pinned host tensors, segmented copy/compute pipeline)"}
+               "copy_only_ms_per_step": dt_copy * 1e3,
+               "copy_only_GB_s_per_rank": (h2d + d2h) / dt_copy / 1e9,
+               "frac_of_copy_only": dt_copy / dt,
+               "api": "race_b200_causal_fwd_host (pinned host tensors, segmented copy/compute pipeline); "
+                      "copy_only = the same bytes as plain pinned cudaMemcpyAsync, both directions at once"}
+        del dq, dk_, dv, do, hq, hk, hv, ho
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        res = cpu_run(min(T, 32768), 3, 1)
+        res = cpu_run(min(T, 65536), 3, 1)
         cpu = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
     if rank == 0:
@@ -467,8 +674,12 @@ def main():
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": args.dtype, "data": "synthetic",
                 "config": {"workload": workload, "variant": variant, "l2": "inputs larger than L2",
-                           "parity_gate_rel_l2": err},
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+                           "parity_gate_rel_l2": max(err_head, err_tail),
+                           "parity_head_rel_l2": err_head, "parity_tail_rel_l2": err_tail,
+                           "parity_state_rel_l2": err_state,
+                           "parity_gate": "first 1024 tokens of stream 0; last 2048 tokens of the last stream vs the "
+                                          "oracle with the fp64 carry; final state of every stream vs fp64 totals"},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "c4": c4, "c3": c3,
                 "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}
         print(json.dumps(line), flush=True)
     if world > 1:
