@@ -81,9 +81,21 @@ size_t race_b200_state_floats(const RaceShape* shape);
  * Replaces race_causal_select_tile_tokens (src/causal_v2/kernels/race_causal_fwd.h:89-90). */
 int race_b200_select_tile_tokens(const RaceShape* shape, int variant, int* tile_tokens);
 
-/* Bytes of workspace race_b200_causal_fwd / race_b200_tile_totals need for this tile length
- * (tile_tokens = 0: the automatic one).  Replaces workspace_floats (:99). */
+/* Bytes of workspace race_b200_causal_fwd / race_b200_tile_totals want for this tile length
+ * (tile_tokens = 0: the automatic one).  Replaces workspace_floats (:99).
+ * For the fp32 tensor variant this is what the single-pass form of the forward takes (one
+ * persistent kernel: per tile its totals and its inclusive prefix, a carry slot per CTA, the
+ * look-back flags and the tile ticket; the launcher zeroes flags and ticket on the caller's stream). */
 size_t race_b200_causal_workspace_bytes(const RaceShape* shape, int tile_tokens, int variant);
+
+/* The smallest workspace the same call runs in: one state per tile, which selects the three-launch
+ * form of the forward (tile totals, scan over tiles, output pass).  race_b200_causal_fwd picks the
+ * form from workspace_bytes: >= race_b200_causal_workspace_bytes -> single pass, >= this -> three
+ * launches, less -> RACE_ERR_WORKSPACE.  Both forms give bit-identical results.
+ * race_b200_tile_totals and race_b200_causal_fwd_resume need only this much.
+ * Equal to race_b200_causal_workspace_bytes for every other variant.  No counterpart in the
+ * reference, whose launcher has one form (src/causal_v2/kernels/race_causal_fwd.h:99). */
+size_t race_b200_causal_workspace_bytes_min(const RaceShape* shape, int tile_tokens, int variant);
 
 /*
  * Causal per-bucket prefix forward:

@@ -26,7 +26,7 @@ EXPORTS = [
     "race_b200_bucket_probs", "race_b200_bucket_probs_streams", "race_b200_causal_fwd_host",
     "race_b200_static_scratch_bytes", "race_b200_causal_fwd_static", "race_b200_decode_step",
     "race_b200_causal_fwd_global", "race_b200_causal_bwd_workspace_bytes", "race_b200_causal_bwd",
-    "race_b200_causal_bwd_carry", "race_b200_selftest_bounded_wait",
+    "race_b200_causal_bwd_carry", "race_b200_selftest_bounded_wait", "race_b200_causal_workspace_bytes_min",
 ]
 
 
@@ -59,6 +59,8 @@ def lib() -> ctypes.CDLL:
     L.race_b200_select_tile_tokens.argtypes = [shp, i32, ctypes.POINTER(i32)]
     L.race_b200_causal_workspace_bytes.restype = sz
     L.race_b200_causal_workspace_bytes.argtypes = [shp, i32, i32]
+    L.race_b200_causal_workspace_bytes_min.restype = sz
+    L.race_b200_causal_workspace_bytes_min.argtypes = [shp, i32, i32]
     L.race_b200_causal_fwd.restype = i32
     L.race_b200_causal_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, i32, vp, vp]
     L.race_b200_tile_totals.restype = i32

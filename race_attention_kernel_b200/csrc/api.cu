@@ -64,9 +64,10 @@ int pick_tile(const Dims& dm, int dtype, int variant) {
     return simt_default_tile_tokens(dm, sm_count());
 }
 
-size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile) {
+size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile, bool minimum = false) {
     if (dm.T == 0 || dm.N == 0) return 0;
-    if (variant == RACE_VARIANT_TENSOR) return tensor_workspace_bytes(dm, dtype, tile);
+    if (variant == RACE_VARIANT_TENSOR)
+        return minimum ? tensor_workspace_bytes_min(dm, dtype, tile) : tensor_workspace_bytes(dm, dtype, tile);
     const int64_t tiles = (dm.T + tile - 1) / tile;
     return (size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
 }
@@ -127,6 +128,15 @@ size_t race_b200_causal_workspace_bytes(const RaceShape* shape, int tile_tokens,
     return workspace_bytes_for(dm, shape->dtype, var, tile);
 }
 
+size_t race_b200_causal_workspace_bytes_min(const RaceShape* shape, int tile_tokens, int variant) {
+    Dims dm;
+    if (check_shape(shape, &dm) != RACE_OK) return 0;
+    const int var = resolve_variant(dm, shape->dtype, variant);
+    if (!variant_supported(dm, shape->dtype, var)) return 0;
+    const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, var);
+    return workspace_bytes_for(dm, shape->dtype, var, tile, /*minimum=*/true);
+}
+
 static int causal_entry(const void* probs_q, const void* probs_k, const void* v, void* out,
                         const float* carry_in, float* state_out, void* workspace,
                         size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
@@ -162,9 +172,9 @@ static int causal_entry(const void* probs_q, const void* probs_k, const void* v,
     if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(out) ||
         !aligned16(workspace) || !aligned16(carry_in) || !aligned16(state_out))
         return RACE_ERR_ALIGN;
-    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, var, tile)) return RACE_ERR_WORKSPACE;
+    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, var, tile, /*minimum=*/true)) return RACE_ERR_WORKSPACE;
     if (var == RACE_VARIANT_TENSOR)
-        return (int)causal_fwd_tensor(probs_q, probs_k, v, out, carry_in, state_out, workspace,
+        return (int)causal_fwd_tensor(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes,
                                       dm, shape->dtype, tile, st, status, phases, global_norm, wait_cycles,
                                       withhold_chunk);
     return (int)causal_fwd_simt(probs_q, probs_k, v, out, carry_in, state_out, (float*)workspace,

@@ -24,9 +24,15 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
+
+#ifndef RACE_FUSED_STAGGER_PER_CHUNK
+#define RACE_FUSED_STAGGER_PER_CHUNK 5000
+#endif
 
 namespace race {
 namespace {
@@ -94,37 +100,12 @@ __device__ __forceinline__ void convert_tile(const uint8_t* stage, uint8_t* hi, 
 }
 
 // ------------------------------------------------------------------------------------------------
-// kGlobal selects the global-normalisation estimator (src/causal_v2/reference.py:106-127): W = pQ
-// without the per-bucket divide and every output row divided by den_t = pQ_t . A_t (0 -> a row of 0).
-// wait_cycles > 0 replaces the default limit of every wait; withhold_chunk >= 0 makes the TMA
-// producer of CTA (0, 0) skip the load of that chunk (the self-test of the bounded waits).
-template <bool kGlobal>
-__global__ void __launch_bounds__(kThreads, 1)
-causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
-              const __grid_constant__ CUtensorMap map_v, float* __restrict__ out,
-              const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int heads, int* status,
-              long long wait_cycles, int withhold_chunk) {
-    extern __shared__ uint8_t smem_raw[];
-    Ctx cx;
-    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    cx.sm_u32 = smem_u32(cx.sm);
-    cx.bars = oBars;
-    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + oMisc + 4);
-    cx.status = status;
-    if (wait_cycles > 0) cx.limit = wait_cycles;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + oMisc);
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int64_t tiles = gridDim.x;
-    const int64_t tile = blockIdx.x, n = blockIdx.y;
-    const int64_t t_begin = tile * tile_tokens;
-    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
-    const int nch = (int)((t_end - t_begin + C - 1) / C);
-    const float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
-
-    // ---- set-up: barriers, TMEM, the constant lower-triangular ones tile -----------------------
-    if (tid == 0) {
-        *cx.abort_flag = 0;
+// Barriers of the output phase (one thread; the caller orders this against their use).  With
+// `again` the objects held a previous tile's phases and are invalidated first.
+__device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again) {
+    if (again)
+        for (int i = 0; i < kNumBars; ++i) mbar_inval(cx.bar(i));
+    {
         for (int i = 0; i < 2; ++i) {
             mbar_init(cx.bar(kFull + i), 1);
             mbar_init(cx.bar(kEmpty + i), 4);
@@ -149,16 +130,22 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
         mbar_init(cx.bar(kDrain + 1), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kMmaWarp) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(cx.sm_u32 + oMisc), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
+}
+
+// Output phase of one (stream n, tokens [t_begin, t_end)) tile whose carry (state before its first
+// token, state layout) is at `slice`.  Called by all 15 warps with barriers initialised and 512 TMEM
+// columns at `tmem`; ends with every issued product retired, before the caller's __syncthreads.
+// kGlobal selects the global-normalisation estimator (src/causal_v2/reference.py:106-127): W = pQ
+// without the per-bucket divide and every output row divided by den_t = pQ_t . A_t (0 -> a row of 0).
+// withhold (self-test of the bounded waits): the TMA producer skips the load of chunk withhold_chunk.
+template <bool kGlobal>
+__device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, const float* __restrict__ pq,
+                                          const CUtensorMap* map_k, const CUtensorMap* map_v,
+                                          float* __restrict__ out, const float* __restrict__ slice, int64_t T,
+                                          const int64_t t_begin, const int64_t t_end, const int64_t n, float eps,
+                                          int heads, int withhold_chunk) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nch = (int)((t_end - t_begin + C - 1) / C);
     const uint32_t tmB = tmem;                               // B accumulator, columns [0, 64)
     auto tmAG = [&](int wg) { return tmem + 64 + wg * 128; };      // A_loc, then G
     auto tmO = [&](int wg) { return tmem + 64 + wg * 128 + 64; };  // O
@@ -344,8 +331,8 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
         for (int x = 0; x < 8; ++x)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const float2 b2 = *reinterpret_cast<const float2*>(
-                    slice + (rbase + 8 * h) * D + 8 * x + 2 * q);
+                const float2 b2 = __ldcg(reinterpret_cast<const float2*>(
+                    slice + (rbase + 8 * h) * D + 8 * x + 2 * q));
                 v[4 * x + 2 * h] = b2.x; v[4 * x + 2 * h + 1] = b2.y;
             }
         {   // tril[t][j] = (j <= t), exact in bf16, as an A operand in tensor memory
@@ -363,8 +350,8 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
         tc_fence_before();
         if (warp == 8) {
             float* ac = reinterpret_cast<float*>(cx.sm + oAcar);
-            ac[lane] = slice[S * D + lane];
-            ac[lane + 32] = slice[S * D + lane + 32];
+            ac[lane] = __ldcg(slice + S * D + lane);
+            ac[lane + 32] = __ldcg(slice + S * D + lane + 32);
         }
         __syncwarp();
         if (lane == 0) {
@@ -420,15 +407,15 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             for (int c = 0; c < nch; ++c) {
                 const int st = c & 1;
                 if (c >= 2 && !wait_bar(cx, kEmpty + st, ((c >> 1) - 1) & 1, 301)) break;
-                if (c == withhold_chunk && blockIdx.x == 0 && blockIdx.y == 0) continue;   // self-test only
+                if (c == withhold_chunk) continue;   // self-test only
                 const uint32_t dst = cx.sm_u32 + oStage + st * kStageBytes;
                 const uint32_t bar = cx.bar(kFull + st);
                 const int tok = (int)(t_begin + (int64_t)c * C);
                 mbar_arrive_expect_tx(bar, kStageBytes);
-                tma_load_4d(dst, &map_k, bar, 0, tok, 0, (int)n);
-                tma_load_4d(dst + 8192, &map_k, bar, 0, tok, 1, (int)n);
-                tma_load_5d(dst + kTileF32, &map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
-                tma_load_5d(dst + kTileF32 + 8192, &map_v, bar, 0, tok, 1, (int)(n % heads), (int)(n / heads));
+                tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
+                tma_load_4d(dst + 8192, map_k, bar, 0, tok, 1, (int)n);
+                tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                tma_load_5d(dst + kTileF32 + 8192, map_v, bar, 0, tok, 1, (int)(n % heads), (int)(n / heads));
                 issued = c + 1;
             }
             if (*cx.abort_flag) {
@@ -510,12 +497,56 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
             while (!mbar_try_wait(cx.bar(kDrain + wg), 0) && clock64() - t0 < cx.limit) {}
         }
     }
+}
 
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_u32, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_u32), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t tmem, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(cols) : "memory");
+}
+
+// The output pass as a kernel of its own (second half of a forward whose per-tile prefixes are
+// already in the workspace): one CTA per (tile, stream).  wait_cycles > 0 replaces the default limit
+// of every wait; withhold_chunk >= 0 makes the producer of CTA (0, 0) skip that chunk's load.
+template <bool kGlobal>
+__global__ void __launch_bounds__(kThreads, 1)
+causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
+              const __grid_constant__ CUtensorMap map_v, float* __restrict__ out,
+              const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int heads, int* status,
+              long long wait_cycles, int withhold_chunk) {
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cx;
+    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cx.sm_u32 = smem_u32(cx.sm);
+    cx.bars = oBars;
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + oMisc + 4);
+    cx.status = status;
+    if (wait_cycles > 0) cx.limit = wait_cycles;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + oMisc);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int64_t tiles = gridDim.x, tile = blockIdx.x, n = blockIdx.y;
+    const int64_t t_begin = tile * tile_tokens;
+    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
+    const float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+    if (tid == 0) {
+        *cx.abort_flag = 0;
+        out_phase_init_bars(cx, false);
+    }
+    if (warp == kMmaWarp) tmem_alloc(cx.sm_u32 + oMisc, kTmemCols);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    out_phase<kGlobal>(cx, tmem, pq, &map_k, &map_v, out, slice, T, t_begin, t_end, n, eps, heads,
+                       (tile == 0 && n == 0) ? withhold_chunk : -1);
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        tmem_dealloc(tmem, kTmemCols);
     }
 }
 
@@ -562,27 +593,11 @@ __device__ __forceinline__ void convert_tile_sum(const uint8_t* stage, uint8_t* 
     }
 }
 
-__global__ void __launch_bounds__(kT1Threads, 1)
-tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-               float* __restrict__ ws, int64_t T, int tile_tokens, int heads, int* status) {
-    extern __shared__ uint8_t smem_raw[];
-    Ctx cx;
-    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    cx.sm_u32 = smem_u32(cx.sm);
-    cx.bars = o1Bars;
-    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + o1Misc + 4);
-    cx.status = status;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + o1Misc);
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int64_t tiles = gridDim.x, tile = blockIdx.x, n = blockIdx.y;
-    const int64_t t_begin = tile * tile_tokens;
-    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
-    const int nch = (int)((t_end - t_begin + C - 1) / C);
-    float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
-
-    if (tid == 0) {
-        *cx.abort_flag = 0;
+constexpr int kT1NumBars = 13;
+__device__ __forceinline__ void totals_phase_init_bars(const Ctx& cx, bool again) {
+    if (again)
+        for (int i = 0; i < kT1NumBars; ++i) mbar_inval(cx.bar(i));
+    {
         for (int i = 0; i < kT1Stages; ++i) {
             mbar_init(cx.bar(k1Full + i), 1);
             mbar_init(cx.bar(k1Empty + i), 4);
@@ -594,15 +609,16 @@ tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         mbar_init(cx.bar(k1Done), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(cx.sm_u32 + o1Misc), "r"(64u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
+}
+
+// Totals phase of one (stream n, tokens [t_begin, t_end)) tile into `slice` (state layout).  Called
+// by at least 10 warps (warps 0-7 convert, 8 issues TMA, 9 issues the products; further warps only
+// take part in the block-wide barriers) with barriers initialised and 64 TMEM columns at `tmem`.
+__device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem, const CUtensorMap* map_k,
+                                             const CUtensorMap* map_v, float* __restrict__ slice,
+                                             const int64_t t_begin, const int64_t t_end, const int64_t n, int heads) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nch = (int)((t_end - t_begin + C - 1) / C);
 
     if (warp < 8) {
         const int wg = warp >> 2, w = warp & 3, wtid = tid & 127;
@@ -647,10 +663,10 @@ tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 const uint32_t bar = cx.bar(k1Full + st);
                 const int tok = (int)(t_begin + (int64_t)c * C);
                 mbar_arrive_expect_tx(bar, kT1StageBytes);
-                tma_load_4d(dst, &map_k, bar, 0, tok, 0, (int)n);
-                tma_load_4d(dst + 8192, &map_k, bar, 0, tok, 1, (int)n);
-                tma_load_5d(dst + kTileF32, &map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
-                tma_load_5d(dst + kTileF32 + 8192, &map_v, bar, 0, tok, 1, (int)(n % heads), (int)(n / heads));
+                tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
+                tma_load_4d(dst + 8192, map_k, bar, 0, tok, 1, (int)n);
+                tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                tma_load_5d(dst + kTileF32 + 8192, map_v, bar, 0, tok, 1, (int)(n % heads), (int)(n / heads));
                 issued = c + 1;
             }
             if (*cx.abort_flag) {
@@ -661,7 +677,7 @@ tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 }
             }
         }
-    } else {
+    } else if (warp == 9) {
         if (lane == 0) {
             bool ok = true;
             for (int c = 0; c < nch && ok; ++c) {
@@ -714,11 +730,236 @@ tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(kT1Threads, 1)
+tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+               float* __restrict__ ws, int64_t T, int tile_tokens, int heads, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cx;
+    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cx.sm_u32 = smem_u32(cx.sm);
+    cx.bars = o1Bars;
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + o1Misc + 4);
+    cx.status = status;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + o1Misc);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int64_t tiles = gridDim.x, tile = blockIdx.x, n = blockIdx.y;
+    const int64_t t_begin = tile * tile_tokens;
+    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
+    float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+    if (tid == 0) {
+        *cx.abort_flag = 0;
+        totals_phase_init_bars(cx, false);
+    }
+    if (warp == 9) tmem_alloc(cx.sm_u32 + o1Misc, 64u);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    totals_phase(cx, tmem, &map_k, &map_v, slice, t_begin, t_end, n, heads);
     tc_fence_before();
     __syncthreads();
     if (warp == 9) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(64u) : "memory");
+        tmem_dealloc(tmem, 64u);
+    }
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Single-pass forward: one persistent kernel, tiles taken from an atomic ticket.  For its tile a CTA
+//   1. reduces the tile to its totals (totals_phase) and publishes them (flag 1);
+//   2. looks back over the tiles before it in the stream -- all of them hold smaller tickets, so
+//      their CTAs are running or done -- for the nearest one whose inclusive prefix is published
+//      (flag 2), adds the totals of the tiles after that one IN TILE ORDER (so the sum is the same
+//      left-to-right fp32 sum whichever tile the look-back stopped at, and equal to tile_scan's),
+//      publishes its own inclusive prefix (flag 2);
+//   3. runs the output phase with that carry; pK and V of the tile are re-read from L2 (the tiles in
+//      flight on all SMs are 148 x 1024 tokens x 512 B = 74 MB).
+// CTAs drift apart, so the DRAM-bound step 1 of some overlaps the latency-bound step 3 of others.
+// Every spin is bounded (cx.limit): a flag that never comes raises the status word and the CTA
+// stops taking tickets; nothing is in flight at that point.
+// ------------------------------------------------------------------------------------------------
+constexpr int kSF = S * (D + 1);                  // floats of one state
+constexpr int kFusedMaxGrid = 160;                // per-CTA carry slots in the workspace
+constexpr int kLookbackDepth = 24;                // tiles whose totals a look-back adds at most
+constexpr int oFusedMisc = (oMisc > o1Misc ? oMisc : o1Misc) + 16;   // tmem base, abort, ticket, j
+constexpr int kFusedSmemBytes = oFusedMisc + 32 + 1024;
+
+struct FusedArgs {
+    const float* pq;
+    float* out;
+    float* agg;                   // [N][tiles][kSF] totals of every tile
+    float* incl;                  // [N][tiles][kSF] state after every tile
+    float* cta_carry;             // [grid][kSF]     state before the tile a CTA is working on
+    int* flags;                   // [N * tiles]     0 nothing, 1 totals, 2 inclusive prefix
+    unsigned long long* ticket;
+    const float* carry_in;        // nullable [N][kSF]
+    float* state_out;             // nullable [N][kSF]
+    int64_t T, N, tiles;
+    int tile_tokens;
+    float eps;
+    int heads;
+    int* status;
+    long long wait_cycles;
+    int withhold_chunk;
+    long long stagger_cycles;     // start of the last CTA's first tile relative to the first CTA's
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <bool kGlobal>
+__global__ void __launch_bounds__(kThreads, 1)
+causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                const __grid_constant__ FusedArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cxA, cxB;   // the two phases keep their barriers at their own offsets
+    cxA.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cxA.sm_u32 = smem_u32(cxA.sm);
+    cxA.bars = o1Bars;
+    cxA.abort_flag = reinterpret_cast<volatile int*>(cxA.sm + oFusedMisc + 4);
+    cxA.status = a.status;
+    if (a.wait_cycles > 0) cxA.limit = a.wait_cycles;
+    cxB = cxA;
+    cxB.bars = oBars;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cxA.sm + oFusedMisc);
+    volatile unsigned long long* ticket_slot = reinterpret_cast<volatile unsigned long long*>(cxA.sm + oFusedMisc + 8);
+    volatile int* j_slot = reinterpret_cast<volatile int*>(cxA.sm + oFusedMisc + 16);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const unsigned long long total = (unsigned long long)a.N * (unsigned long long)a.tiles;
+
+    if (tid == 0) *cxA.abort_flag = 0;
+    if (warp == kMmaWarp) tmem_alloc(cxA.sm_u32 + oFusedMisc, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (a.stagger_cycles > 0 && tid == 0) {
+        // spread the CTAs' first tiles over one tile time, so that consecutive tiles of a stream
+        // reach their look-back one after the other instead of all at once
+        const long long delay = a.stagger_cycles * (long long)blockIdx.x / (long long)gridDim.x;
+        const long long t0 = clock64();
+        while (clock64() - t0 < delay) __nanosleep(256);
+    }
+
+    bool first = true;
+    for (;;) {
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();                      // nobody still uses the previous tile's shared memory
+        tc_fence_after();
+        // a CTA that gave up a wait takes no further tile (a tile taken but not finished would make
+        // the tiles after it wait in vain)
+        if (tid == 0) *ticket_slot = *cxA.abort_flag ? ~0ull : atomicAdd(a.ticket, 1ull);
+        __syncthreads();
+        const unsigned long long t = *ticket_slot;
+        if (t >= total) break;
+        const int64_t n = (int64_t)(t % (unsigned long long)a.N), tile = (int64_t)(t / (unsigned long long)a.N);
+        const int64_t t_begin = tile * a.tile_tokens;
+        const int64_t t_end = min(a.T, t_begin + (int64_t)a.tile_tokens);
+        float* agg_n = a.agg + n * a.tiles * kSF;
+        float* incl_n = a.incl + n * a.tiles * kSF;
+        int* flags_n = a.flags + n * a.tiles;
+
+        // ---- 1. totals of the tile ----------------------------------------------------------------
+        if (tid == 0) totals_phase_init_bars(cxA, !first);
+        __syncthreads();
+        totals_phase(cxA, tmem, &map_k, &map_v, agg_n + tile * kSF, t_begin, t_end, n, a.heads);
+        __threadfence();
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+        if (*cxA.abort_flag) break;
+        if (tid == 0) st_release_gpu(flags_n + tile, 1);
+
+        // ---- 2. look-back: carry of the tile, inclusive prefix published -----------------------------
+        if (tid == 0) {
+            int j = -1;                       // -1: the sum starts from carry_in
+            if (tile > 0) {
+                int64_t m = tile - 1;
+                int depth = 0;
+                const long long t0 = clock64();
+                for (;;) {
+                    const int f = ld_acquire_gpu(flags_n + m);
+                    if (f == 2) { j = (int)m; break; }
+                    if (f == 1 && depth < kLookbackDepth) {
+                        if (m == 0) break;    // totals of every earlier tile are there
+                        --m; ++depth;
+                        continue;
+                    }
+                    if (clock64() - t0 > cxA.limit) {
+                        *cxA.abort_flag = 1;
+                        if (a.status) atomicCAS(a.status, 0, 501);
+                        break;
+                    }
+                    __nanosleep(64);
+                }
+            }
+            *j_slot = j;
+        }
+        __syncthreads();
+        if (*cxA.abort_flag) break;
+        {
+            const int j = *j_slot;
+            float* mine = a.cta_carry + (int64_t)blockIdx.x * kSF;
+            constexpr int kPer = (kSF + kThreads - 1) / kThreads;
+            float x[kPer];
+#pragma unroll
+            for (int k = 0; k < kPer; ++k) {
+                const int e = tid + k * kThreads;
+                x[k] = 0.f;
+                if (e < kSF) {
+                    if (j >= 0) x[k] = __ldcg(incl_n + (int64_t)j * kSF + e);
+                    else if (a.carry_in) x[k] = a.carry_in[n * kSF + e];
+                }
+            }
+            for (int64_t m = j + 1; m < tile; ++m) {
+                float y[kPer];
+#pragma unroll
+                for (int k = 0; k < kPer; ++k) {
+                    const int e = tid + k * kThreads;
+                    y[k] = e < kSF ? __ldcg(agg_n + m * kSF + e) : 0.f;
+                }
+#pragma unroll
+                for (int k = 0; k < kPer; ++k) x[k] += y[k];
+            }
+            const bool last = tile == a.tiles - 1;
+#pragma unroll
+            for (int k = 0; k < kPer; ++k) {
+                const int e = tid + k * kThreads;
+                if (e < kSF) {
+                    mine[e] = x[k];
+                    const float inc = x[k] + __ldcg(agg_n + tile * kSF + e);
+                    incl_n[tile * kSF + e] = inc;
+                    if (last && a.state_out) a.state_out[n * kSF + e] = inc;
+                }
+            }
+            __threadfence();
+        }
+        if (tid == 0) out_phase_init_bars(cxB, !first);
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) st_release_gpu(flags_n + tile, 2);
+
+        // ---- 3. outputs of the tile ---------------------------------------------------------------
+        out_phase<kGlobal>(cxB, tmem, a.pq, &map_k, &map_v, a.out, a.cta_carry + (int64_t)blockIdx.x * kSF, a.T,
+                           t_begin, t_end, n, a.eps, a.heads, (tile == 0 && n == 0) ? a.withhold_chunk : -1);
+        first = false;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
     }
 }
 
@@ -784,7 +1025,16 @@ bool tensor_supported(const Dims& dm, int dtype) {
 
 int tensor_chunk_tokens() { return C; }
 
-int tensor_default_tile_tokens(const Dims& dm, int, int sm_count) {
+int tensor_default_tile_tokens(const Dims& dm, int dtype, int sm_count) {
+    if (dtype == RACE_DTYPE_F32) {
+        // The fp32 forward is one persistent kernel that hands tiles to the SMs as they become free and reads
+        // pK and V of a tile twice: 1024 tokens keep the tiles in flight on all SMs (sm_count x 512 KB) inside
+        // the L2.  Short inputs get shorter tiles, about one per SM.
+        const int64_t sms = sm_count > 0 ? sm_count : 148;
+        const int64_t per_sm = (dm.N * dm.T + sms - 1) / sms;
+        const int64_t tile = (per_sm + C - 1) / C * C;
+        return (int)(tile < C ? C : (tile > 1024 ? 1024 : tile));
+    }
     // One CTA per SM (and per bucket group) at a time: the CTAs run in waves of sm_count, so the tile
     // length (a multiple of the chunk, at most 2048 tokens) is chosen to fill the last wave:
     // cost = waves x (tokens per tile + the set-up of a CTA, about one and a half chunks).  For long
@@ -803,13 +1053,35 @@ int tensor_default_tile_tokens(const Dims& dm, int, int sm_count) {
     return best;
 }
 
-size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
+// fp32 single-pass kernel: [totals of every tile | inclusive prefix of every tile | carry slot per CTA | flags, ticket]
+struct FusedLayout {
+    size_t states, off_incl, off_carry, off_flags, flag_bytes, total;
+};
+static FusedLayout fused_layout(const Dims& dm, int tile_tokens) {
+    const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
+    FusedLayout l;
+    l.states = (size_t)dm.N * tiles * kSF * sizeof(float);
+    l.off_incl = l.states;
+    l.off_carry = 2 * l.states;
+    l.off_flags = l.off_carry + (size_t)kFusedMaxGrid * kSF * sizeof(float);
+    l.flag_bytes = ((size_t)dm.N * tiles * sizeof(int) + 15) / 16 * 16 + 16;   // + the ticket counter
+    l.total = l.off_flags + l.flag_bytes;
+    return l;
+}
+
+size_t tensor_workspace_bytes(const Dims& dm, int dtype, int tile_tokens) {
+    if (dtype == RACE_DTYPE_F32) return fused_layout(dm, tile_tokens).total;
+    return tensor_workspace_bytes_min(dm, dtype, tile_tokens);
+}
+
+// what the three-launch form (totals, scan, outputs) needs: one state per tile
+size_t tensor_workspace_bytes_min(const Dims& dm, int, int tile_tokens) {
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     return (size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
 }
 
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
-                              const float* carry_in, float* state_out, void* ws, const Dims& dm,
+                              const float* carry_in, float* state_out, void* ws, size_t ws_bytes, const Dims& dm,
                               int dtype, int tile_tokens, cudaStream_t stream, int* status, int phases,
                               bool global_norm, long long wait_cycles, int withhold_chunk) {
     if (dtype == RACE_DTYPE_BF16) {
@@ -827,6 +1099,41 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
     if (!make_map(&mk, pk, dm.N, dm.T, dm.S) || !make_map_heads(&mv, v, dm.N, dm.T, dm.D, dm.H))
         return cudaErrorInvalidValue;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
+    const FusedLayout lay = fused_layout(dm, tile_tokens);
+    if (phases == kPhaseAll && ws_bytes >= lay.total) {
+        // the whole forward as one persistent kernel (a smaller workspace selects the three launches below)
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const unsigned long long items = (unsigned long long)dm.N * (unsigned long long)tiles;
+        const unsigned grid_f = (unsigned)std::min<unsigned long long>(items, (unsigned long long)std::min(sms > 0 ? sms : 148, kFusedMaxGrid));
+        char* base = (char*)ws;
+        err = cudaMemsetAsync(base + lay.off_flags, 0, lay.flag_bytes, stream);
+        if (err != cudaSuccess) return err;
+        FusedArgs fa;
+        fa.pq = (const float*)pq;
+        fa.out = (float*)out;
+        fa.agg = (float*)base;
+        fa.incl = (float*)(base + lay.off_incl);
+        fa.cta_carry = (float*)(base + lay.off_carry);
+        fa.flags = (int*)(base + lay.off_flags);
+        fa.ticket = (unsigned long long*)(base + lay.off_flags + lay.flag_bytes - 16);
+        fa.carry_in = carry_in;
+        fa.state_out = state_out;
+        fa.T = dm.T; fa.N = dm.N; fa.tiles = tiles;
+        fa.tile_tokens = tile_tokens;
+        fa.eps = dm.eps;
+        fa.heads = dm.H;
+        fa.status = status;
+        fa.wait_cycles = wait_cycles;
+        fa.withhold_chunk = withhold_chunk;
+        // more tiles than CTAs: start the CTAs spread over one tile time (about 5k cycles per 64-token chunk)
+        fa.stagger_cycles = items > grid_f ? (long long)(tile_tokens / C) * RACE_FUSED_STAGGER_PER_CHUNK : 0;
+        auto kern = global_norm ? causal_fused_tc<true> : causal_fused_tc<false>;
+        err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBytes);
+        if (err != cudaSuccess) return err;
+        kern<<<grid_f, kThreads, kFusedSmemBytes, stream>>>(mk, mv, fa);
+        return cudaGetLastError();
+    }
     dim3 grid((unsigned)tiles, (unsigned)dm.N);
     // 1. tile totals (tensor cores)  2. exclusive scan over tiles  3. output pass
     if (phases & kPhaseTotals) {

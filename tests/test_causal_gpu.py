@@ -601,7 +601,7 @@ def test_bounded_wait_runs_out_and_device_stays_usable():
         t1.record()
         torch.cuda.synchronize()
         assert code != 0, "the withheld load went unnoticed"
-        assert 100 <= code < 500, code                    # one of the kernels' wait codes
+        assert 100 <= code < 600, code                    # one of the kernels' wait codes
         assert t0.elapsed_time(t1) < 1000.0               # ended by the limit (~1 ms), not by the default (~1 s)
         # tiles of the other stream never depended on the withheld chunk
         assert torch.equal(out[1], before[1])
