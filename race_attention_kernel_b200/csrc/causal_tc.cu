@@ -102,6 +102,21 @@ __device__ __forceinline__ void convert_tile(const uint8_t* stage, uint8_t* hi, 
 // ------------------------------------------------------------------------------------------------
 // Barriers of the output phase (one thread; the caller orders this against their use).  With
 // `again` the objects held a previous tile's phases and are invalidated first.
+// arrival count of output-phase barrier i (the table restates out_phase_init_bars)
+__device__ __forceinline__ uint32_t out_bar_count(int i) {
+    // bit i set: four arrivals (one per warp of a group), else one
+    constexpr uint64_t kFour = (3ull << kEmpty) | (3ull << kKvReady) | (3ull << kWReady) | (3ull << kGtReady) |
+                               (3ull << kBaccFree) | (3ull << kBtReady) | (3ull << kAcarFree) | (3ull << kVReady);
+    return ((kFour >> i) & 1ull) ? 4u : 1u;
+}
+// The same from the lanes of one warp (re-initialisation between the tiles of the persistent kernel).
+__device__ __forceinline__ void out_phase_reinit_bars_warp(const Ctx& cx, int lane, bool again) {
+    for (int i = lane; i < kNumBars; i += 32) {
+        if (again) mbar_inval(cx.bar(i));
+        mbar_init(cx.bar(i), out_bar_count(i));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
 __device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again) {
     if (again)
         for (int i = 0; i < kNumBars; ++i) mbar_inval(cx.bar(i));
@@ -138,12 +153,15 @@ __device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again) {
 // kGlobal selects the global-normalisation estimator (src/causal_v2/reference.py:106-127): W = pQ
 // without the per-bucket divide and every output row divided by den_t = pQ_t . A_t (0 -> a row of 0).
 // withhold (self-test of the bounded waits): the TMA producer skips the load of chunk withhold_chunk.
+// pf_chunks > 0: while it walks this tile the producer also prefetches, chunk by chunk, pK and V of the
+// tile (stream pf_n, first token pf_begin) this CTA works on next into the L2.
 template <bool kGlobal>
 __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, const float* __restrict__ pq,
                                           const CUtensorMap* map_k, const CUtensorMap* map_v,
                                           float* __restrict__ out, const float* __restrict__ slice, int64_t T,
                                           const int64_t t_begin, const int64_t t_end, const int64_t n, float eps,
-                                          int heads, int withhold_chunk) {
+                                          int heads, int withhold_chunk, const int64_t pf_begin = 0,
+                                          const int64_t pf_n = 0, const int pf_chunks = 0) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nch = (int)((t_end - t_begin + C - 1) / C);
     const uint32_t tmB = tmem;                               // B accumulator, columns [0, 64)
@@ -417,6 +435,14 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
                 tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
                 tma_load_5d(dst + kTileF32 + 8192, map_v, bar, 0, tok, 1, (int)(n % heads), (int)(n / heads));
                 issued = c + 1;
+                for (int pc = c; pc < pf_chunks && (pc == c || c == nch - 1); ++pc) {
+                    // the same chunk of the next tile (all that is left of it, from this tile's last chunk)
+                    const int ptok = (int)(pf_begin + (int64_t)pc * C);
+                    tma_prefetch_4d(map_k, 0, ptok, 0, (int)pf_n);
+                    tma_prefetch_4d(map_k, 0, ptok, 1, (int)pf_n);
+                    tma_prefetch_5d(map_v, 0, ptok, 0, (int)(pf_n % heads), (int)(pf_n / heads));
+                    tma_prefetch_5d(map_v, 0, ptok, 1, (int)(pf_n % heads), (int)(pf_n / heads));
+                }
             }
             if (*cx.abort_flag) {
                 // copies still in flight must land before the CTA may exit
@@ -561,8 +587,8 @@ constexpr int kT1Threads = 10 * 32;
 constexpr int kT1Stages = 4;
 constexpr int kT1StageBytes = 2 * kTileF32;            // pK | V
 constexpr int o1Stage = 0;
-constexpr int o1Kt = o1Stage + kT1Stages * kT1StageBytes;   // [2 wg][hi|lo]
-constexpr int o1Vt = o1Kt + 4 * kOpTile;
+constexpr int o1Kt = o1Stage + kT1Stages * kT1StageBytes;   // [2 wg][hi | lo]
+constexpr int o1Vt = o1Kt + 4 * kOpTile;               // [2 wg][hi | lo]
 constexpr int o1Red = o1Vt + 4 * kOpTile;              // [8 warps][4][8] fp32 column-sum partials
 constexpr int o1Bars = o1Red + 8 * 32 * 4;
 constexpr int o1Misc = o1Bars + 16 * 8;
@@ -594,6 +620,13 @@ __device__ __forceinline__ void convert_tile_sum(const uint8_t* stage, uint8_t* 
 }
 
 constexpr int kT1NumBars = 13;
+__device__ __forceinline__ void totals_phase_reinit_bars_warp(const Ctx& cx, int lane, bool again) {
+    if (lane < kT1NumBars) {
+        if (again) mbar_inval(cx.bar(lane));
+        mbar_init(cx.bar(lane), (lane >= k1Empty && lane < k1KvFree) ? 4u : 1u);   // k1Empty, k1KvReady: 4 warps
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
 __device__ __forceinline__ void totals_phase_init_bars(const Ctx& cx, bool again) {
     if (again)
         for (int i = 0; i < kT1NumBars; ++i) mbar_inval(cx.bar(i));
@@ -614,6 +647,7 @@ __device__ __forceinline__ void totals_phase_init_bars(const Ctx& cx, bool again
 // Totals phase of one (stream n, tokens [t_begin, t_end)) tile into `slice` (state layout).  Called
 // by at least 10 warps (warps 0-7 convert, 8 issues TMA, 9 issues the products; further warps only
 // take part in the block-wide barriers) with barriers initialised and 64 TMEM columns at `tmem`.
+// Two converter groups take alternate chunks from a four-stage TMA ring.
 __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem, const CUtensorMap* map_k,
                                              const CUtensorMap* map_v, float* __restrict__ slice,
                                              const int64_t t_begin, const int64_t t_end, const int64_t n, int heads) {
@@ -621,9 +655,7 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
     const int nch = (int)((t_end - t_begin + C - 1) / C);
 
     if (warp < 8) {
-        const int wg = warp >> 2, w = warp & 3, wtid = tid & 127;
-        uint8_t* kt_hi = cx.sm + o1Kt + wg * 2 * kOpTile;
-        uint8_t* vt_hi = cx.sm + o1Vt + wg * 2 * kOpTile;
+        const int wg = warp >> 2, wtid = tid & 127;
         float asum[4][8];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -632,6 +664,8 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
         bool ok = true;
         for (int c = wg; c < nch && ok; c += 2) {
             const int st = c % kT1Stages;
+            uint8_t* kt_hi = cx.sm + o1Kt + wg * 2 * kOpTile;
+            uint8_t* vt_hi = cx.sm + o1Vt + wg * 2 * kOpTile;
             if (!(ok = wait_bar_warp(cx, k1Full + st, (c / kT1Stages) & 1, 111))) break;
             if (c >= 2 && !(ok = wait_bar_warp(cx, k1KvFree + wg, ((c >> 1) - 1) & 1, 112))) break;
             const uint8_t* stage = cx.sm + o1Stage + st * kT1StageBytes;
@@ -652,7 +686,6 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
                 for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
                 if (lane == 0) red[i * 8 + e] = x;
             }
-        (void)w;
     } else if (warp == 8) {
         if (lane == 0) {
             int issued = 0;
@@ -678,23 +711,24 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
             }
         }
     } else if (warp == 9) {
-        if (lane == 0) {
+        // every operand of the issuing thread derives from warp-uniform values (cheap descriptor arithmetic)
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
+        constexpr uint32_t kLimb = kOpTile >> 4;
+        constexpr uint32_t kId = kIdescBase | kAmn | kBmn;
+        if (elect_one()) {
             bool ok = true;
             for (int c = 0; c < nch && ok; ++c) {
                 const int wg = c & 1;
                 if (!(ok = wait_bar(cx, k1KvReady + wg, (c >> 1) & 1, 411))) break;
                 tc_fence_after();
-                const uint32_t kt = cx.sm_u32 + o1Kt + wg * 2 * kOpTile;
-                const uint32_t vt = cx.sm_u32 + o1Vt + wg * 2 * kOpTile;
-#pragma unroll
-                for (int pass = 0; pass < 3; ++pass) {
-                    const uint32_t a = kt + (pass == 2 ? kOpTile : 0);
-                    const uint32_t b = vt + (pass == 1 ? kOpTile : 0);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        mma_bf16(tmem, make_desc(a + k * 2048, 1024, 128), make_desc(b + k * 2048, 1024, 128),
-                                 kIdescBase | kAmn | kBmn, (c | pass | k) ? 1u : 0u);
-                }
+                const uint32_t kt = lo_mn(smb + o1Kt + wg * 2 * kOpTile);
+                const uint32_t vt = lo_mn(smb + o1Vt + wg * 2 * kOpTile);
+                // pK_hi.V_hi + pK_hi.V_lo + pK_lo.V_hi; the first product of the tile starts the accumulator
+                if (c == 0) mma_k64<true, kHiMN, 128, kHiMN, 128>(tm, kt, vt, kId);
+                else mma_k64<false, kHiMN, 128, kHiMN, 128>(tm, kt, vt, kId);
+                mma_k64<false, kHiMN, 128, kHiMN, 128>(tm, kt, vt + kLimb, kId);
+                mma_k64<false, kHiMN, 128, kHiMN, 128>(tm, kt + kLimb, vt, kId);
                 mma_commit(cx.bar(k1KvFree + wg));
             }
             mma_commit(cx.bar(k1Done));
@@ -816,6 +850,16 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
     asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+#ifdef RACE_FUSED_PROF
+// per-CTA cycle counters of the single-pass kernel (profiling builds only): totals phase, wait for
+// the look-back flags, prefix sum, output phase, tiles taken
+__device__ long long g_fused_prof[kFusedMaxGrid][8];
+#define RACE_PROF_ADD(slot, t_from)                                                   \
+    do { if (tid == 0) { const long long now_ = clock64(); g_fused_prof[blockIdx.x][slot] += now_ - (t_from); (t_from) = now_; } } while (0)
+#else
+#define RACE_PROF_ADD(slot, t_from) do {} while (0)
+#endif
+
 template <bool kGlobal>
 __global__ void __launch_bounds__(kThreads, 1)
 causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -851,17 +895,14 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         while (clock64() - t0 < delay) __nanosleep(256);
     }
 
+    // tiles are taken one ahead: the ticket of the next tile is drawn before the output phase of the current
+    // one, which prefetches the next tile's pK and V into the L2 as it goes
+    if (tid == 0) *ticket_slot = atomicAdd(a.ticket, 1ull);
+    __syncthreads();
+    unsigned long long t_next = *ticket_slot;
     bool first = true;
     for (;;) {
-        fence_proxy_async();
-        tc_fence_before();
-        __syncthreads();                      // nobody still uses the previous tile's shared memory
-        tc_fence_after();
-        // a CTA that gave up a wait takes no further tile (a tile taken but not finished would make
-        // the tiles after it wait in vain)
-        if (tid == 0) *ticket_slot = *cxA.abort_flag ? ~0ull : atomicAdd(a.ticket, 1ull);
-        __syncthreads();
-        const unsigned long long t = *ticket_slot;
+        const unsigned long long t = t_next;
         if (t >= total) break;
         const int64_t n = (int64_t)(t % (unsigned long long)a.N), tile = (int64_t)(t / (unsigned long long)a.N);
         const int64_t t_begin = tile * a.tile_tokens;
@@ -871,15 +912,18 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         int* flags_n = a.flags + n * a.tiles;
 
         // ---- 1. totals of the tile ----------------------------------------------------------------
-        if (tid == 0) totals_phase_init_bars(cxA, !first);
+        long long tp = clock64();
+        (void)tp;
+        if (warp == 0) totals_phase_reinit_bars_warp(cxA, tid, !first);
         __syncthreads();
         totals_phase(cxA, tmem, &map_k, &map_v, agg_n + tile * kSF, t_begin, t_end, n, a.heads);
-        __threadfence();
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
         if (*cxA.abort_flag) break;
+        // the release store is cumulative over the block's writes that the barrier ordered before it
         if (tid == 0) st_release_gpu(flags_n + tile, 1);
+        RACE_PROF_ADD(0, tp);
 
         // ---- 2. look-back: carry of the tile, inclusive prefix published -----------------------------
         if (tid == 0) {
@@ -907,12 +951,18 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
             *j_slot = j;
         }
         __syncthreads();
+        RACE_PROF_ADD(1, tp);
         if (*cxA.abort_flag) break;
         {
             const int j = *j_slot;
             float* mine = a.cta_carry + (int64_t)blockIdx.x * kSF;
             constexpr int kPer = (kSF + kThreads - 1) / kThreads;
-            float x[kPer];
+            float x[kPer], own[kPer];
+#pragma unroll
+            for (int k = 0; k < kPer; ++k) {
+                const int e = tid + k * kThreads;
+                own[k] = e < kSF ? __ldcg(agg_n + tile * kSF + e) : 0.f;
+            }
 #pragma unroll
             for (int k = 0; k < kPer; ++k) {
                 const int e = tid + k * kThreads;
@@ -938,22 +988,43 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                 const int e = tid + k * kThreads;
                 if (e < kSF) {
                     mine[e] = x[k];
-                    const float inc = x[k] + __ldcg(agg_n + tile * kSF + e);
+                    const float inc = x[k] + own[k];
                     incl_n[tile * kSF + e] = inc;
                     if (last && a.state_out) a.state_out[n * kSF + e] = inc;
                 }
             }
-            __threadfence();
         }
-        if (tid == 0) out_phase_init_bars(cxB, !first);
+        if (warp == 1) out_phase_reinit_bars_warp(cxB, tid & 31, !first);
+        if (tid == 0) *ticket_slot = atomicAdd(a.ticket, 1ull);
         fence_proxy_async();
         __syncthreads();
         if (tid == 0) st_release_gpu(flags_n + tile, 2);
+        t_next = *ticket_slot;
+        int64_t pf_n = 0, pf_begin = 0;
+        int pf_chunks = 0;
+        if (t_next < total) {
+            pf_n = (int64_t)(t_next % (unsigned long long)a.N);
+            pf_begin = (int64_t)(t_next / (unsigned long long)a.N) * a.tile_tokens;
+            pf_chunks = (int)((min(a.T, pf_begin + (int64_t)a.tile_tokens) - pf_begin + C - 1) / C);
+        }
+        RACE_PROF_ADD(2, tp);
+#ifdef RACE_FUSED_PROF
+        if (tid == 0) { g_fused_prof[blockIdx.x][4] += 1; g_fused_prof[blockIdx.x][5] += tile - 1 - *j_slot; }
+#endif
 
         // ---- 3. outputs of the tile ---------------------------------------------------------------
         out_phase<kGlobal>(cxB, tmem, a.pq, &map_k, &map_v, a.out, a.cta_carry + (int64_t)blockIdx.x * kSF, a.T,
-                           t_begin, t_end, n, a.eps, a.heads, (tile == 0 && n == 0) ? a.withhold_chunk : -1);
+                           t_begin, t_end, n, a.eps, a.heads, (tile == 0 && n == 0) ? a.withhold_chunk : -1,
+                           pf_begin, pf_n, pf_chunks);
         first = false;
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();                      // nobody still uses this tile's shared memory or tensor memory
+        tc_fence_after();
+        RACE_PROF_ADD(3, tp);
+        // a CTA that gave up a wait stops here (the tile it drew ahead stays undone: the tiles after it in that
+        // stream run into their own limits)
+        if (*cxA.abort_flag) break;
     }
     tc_fence_before();
     __syncthreads();
@@ -1156,6 +1227,17 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
                                                  tile_tokens, dm.eps, dm.H, status, wait_cycles, withhold_chunk);
     return cudaGetLastError();
 }
+
+#ifdef RACE_FUSED_PROF
+extern "C" int race_b200_debug_fused_prof(long long* host_out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(host_out, g_fused_prof, sizeof(long long) * kFusedMaxGrid * 8);
+    if (e == cudaSuccess && reset) {
+        static long long zeros[kFusedMaxGrid * 8] = {};
+        e = cudaMemcpyToSymbol(g_fused_prof, zeros, sizeof(zeros));
+    }
+    return (int)e;
+}
+#endif
 
 #ifdef RACE_TC_TRACE
 extern "C" int race_b200_debug_set_trace(long long* buf) {
