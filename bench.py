@@ -480,6 +480,9 @@ def extra_workloads(args):
 # profiles/ (causal_out_tc_N8_T131072_ncu_full.md: T=131072, 1073.7 MB of algorithmic bytes per launch set;
 # traffic grows in proportion to the tokens processed).  Update together with that file.
 TRAFFIC_MB_PER_1073_7 = {"causal_out_tc": 1053.7, "tile_totals_tc": 547.9, "tile_scan": 17.0}
+# the single-pass kernel in the same units (profiles/causal_fused_tc_N8_T131072_ncu.md): 851.7 MB read + 272.9 MB
+# written per 1073.7 MB
+TRAFFIC_SINGLE_PASS_PER_ALG = (851.7 + 272.9) / 1073.7
 
 
 def reference_arm(args, workload):
@@ -598,6 +601,27 @@ def main():
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                 "kernel": "causal forward (tile_totals_tc + tile_scan + causal_out_tc of one step)",
                 "algorithmic_bytes_per_launch": alg_bytes}
+    # the same workload through the single-pass form of the forward (one persistent kernel, decoupled look-back,
+    # second read of a tile from L2), gated bitwise against the form timed above
+    single = None
+    if variant == "tensor" and args.dtype == "f32" and not args.no_sub:
+        tile_sp = rk.select_tile_tokens(N, T, L, R, dk, tdtype, "tensor_single_pass")
+        same = torch.equal(rk.race_causal_prefix(pQ, pK, V, variant="tensor_single_pass", tile_tokens=tile_sp),
+                           rk.race_causal_prefix(pQ, pK, V, variant="tensor", tile_tokens=tile_sp, out=out))
+        if not same:
+            raise SystemExit("single-pass form differs from the three launches at the same tile length")
+        out_sp = torch.empty_like(V)
+        ms_sp = _time_ms(lambda: rk.race_causal_prefix(pQ, pK, V, variant="tensor_single_pass", out=out_sp),
+                         args.warmup, args.steps)
+        if world > 1:
+            t = torch.tensor([ms_sp], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_sp = t.item()
+        single = {"variant": "tensor_single_pass", "tile_tokens": tile_sp, "ms_per_step": ms_sp,
+                  "value": tokens_total / ms_sp / 1e3, "unit": "Mtok/s", "bitwise_equal_to_three_launches": True,
+                  "frac": alg_bytes / (ms_sp * 1e-3) / 1e9 / peak,
+                  "traffic": alg_bytes * TRAFFIC_SINGLE_PASS_PER_ALG, "gpu_launches": args.steps}
+        del out_sp
     del pQ, pK, V, out
     torch.cuda.empty_cache()
 
@@ -679,7 +703,7 @@ def main():
                            "parity_state_rel_l2": err_state,
                            "parity_gate": "first 1024 tokens of stream 0; last 2048 tokens of the last stream vs the "
                                           "oracle with the fp64 carry; final state of every stream vs fp64 totals"},
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "c4": c4, "c3": c3,
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "c4": c4, "c3": c3, "single_pass": single,
                 "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -37,8 +37,17 @@ extern "C" {
 
 enum { RACE_DTYPE_F32 = 0, RACE_DTYPE_BF16 = 1 };
 
-/* kernel families: AUTO picks TENSOR when the shape is supported by it, else SIMT */
-enum { RACE_VARIANT_AUTO = 0, RACE_VARIANT_SIMT = 1, RACE_VARIANT_TENSOR = 2 };
+/* kernel families: AUTO picks TENSOR when the shape is supported by it, else SIMT.
+ * TENSOR_SINGLE_PASS is the fp32 tensor family with the causal forward as ONE persistent kernel
+ * (tiles handed out by an atomic ticket; per tile: totals, decoupled look-back over the earlier
+ * tiles of the stream, outputs with the tile's pK and V read the second time from L2) instead of
+ * the three launches (tile totals, scan over tiles, output pass) of TENSOR.  Same arithmetic in
+ * the same order: for equal tile_tokens the two forms give bit-identical results.  It moves
+ * about 1.05x the algorithmic bytes through DRAM where the three launches move 1.5x, and wants
+ * a larger workspace (race_b200_causal_workspace_bytes with this variant; the launcher zeroes the
+ * look-back flags and the tile ticket in it on the caller's stream).  For race_b200_tile_totals
+ * and race_b200_causal_fwd_resume it means the same as TENSOR. */
+enum { RACE_VARIANT_AUTO = 0, RACE_VARIANT_SIMT = 1, RACE_VARIANT_TENSOR = 2, RACE_VARIANT_TENSOR_SINGLE_PASS = 3 };
 
 enum {
     RACE_OK = 0,
@@ -81,21 +90,11 @@ size_t race_b200_state_floats(const RaceShape* shape);
  * Replaces race_causal_select_tile_tokens (src/causal_v2/kernels/race_causal_fwd.h:89-90). */
 int race_b200_select_tile_tokens(const RaceShape* shape, int variant, int* tile_tokens);
 
-/* Bytes of workspace race_b200_causal_fwd / race_b200_tile_totals want for this tile length
- * (tile_tokens = 0: the automatic one).  Replaces workspace_floats (:99).
- * For the fp32 tensor variant this is what the single-pass form of the forward takes (one
- * persistent kernel: per tile its totals and its inclusive prefix, a carry slot per CTA, the
- * look-back flags and the tile ticket; the launcher zeroes flags and ticket on the caller's stream). */
+/* Bytes of workspace race_b200_causal_fwd / race_b200_tile_totals need for this tile length
+ * (tile_tokens = 0: the automatic one of the variant).  Replaces workspace_floats (:99).
+ * One state per tile; RACE_VARIANT_TENSOR_SINGLE_PASS: per tile its totals and its inclusive
+ * prefix, a carry slot per CTA, the look-back flags and the tile ticket. */
 size_t race_b200_causal_workspace_bytes(const RaceShape* shape, int tile_tokens, int variant);
-
-/* The smallest workspace the same call runs in: one state per tile, which selects the three-launch
- * form of the forward (tile totals, scan over tiles, output pass).  race_b200_causal_fwd picks the
- * form from workspace_bytes: >= race_b200_causal_workspace_bytes -> single pass, >= this -> three
- * launches, less -> RACE_ERR_WORKSPACE.  Both forms give bit-identical results.
- * race_b200_tile_totals and race_b200_causal_fwd_resume need only this much.
- * Equal to race_b200_causal_workspace_bytes for every other variant.  No counterpart in the
- * reference, whose launcher has one form (src/causal_v2/kernels/race_causal_fwd.h:99). */
-size_t race_b200_causal_workspace_bytes_min(const RaceShape* shape, int tile_tokens, int variant);
 
 /*
  * Causal per-bucket prefix forward:
@@ -249,10 +248,15 @@ int race_b200_bucket_probs_streams(const void* x, const float* planes, void* pro
  * the sequence through them in segments (copy-in, kernel and copy-out overlapped on three
  * streams, the carry staying on the device between segments) and SYNCHRONISES before
  * returning.  segment_tokens = 0 picks a default.  device = CUDA ordinal to run on.
+ * Returns RACE_ERR_DEVICE_WAIT if a kernel gave up a bounded wait.  The staging buffers (about
+ * 2 x 260 MB at the default segment), streams and events of a device are kept for the next call;
+ * race_b200_host_release(device) frees them.  Calls on one device are serialised.
+ * Role of the reference's chunk loop around its carried state (src/race_chunked.py:41-63).
  */
 int race_b200_causal_fwd_host(const void* probs_q, const void* probs_k, const void* v, void* out,
                               const float* carry_in, float* state_out, const RaceShape* shape,
                               int64_t segment_tokens, int variant, int device);
+int race_b200_host_release(int device);
 
 /*
  * race_b200_causal_fwd without a caller-provided workspace, for callers that cannot allocate
@@ -277,10 +281,11 @@ int race_b200_causal_fwd_static(const void* probs_q, const void* probs_k, const 
 
 /*
  * Self-test of the bounded device-side waits (diagnostics; not part of the compute path).  Runs
- * race_b200_causal_fwd with RACE_VARIANT_TENSOR (fp32, S = 64, d_k = 64) with every device-side
- * wait limited to wait_cycles SM clock cycles (1000 .. 2^31) and with the TMA producer of the
- * first CTA skipping the load of chunk withhold_chunk (64-token chunks of the first tile of
- * stream 0), so that the consumer of that chunk waits in vain.  Expected behaviour, which a test
+ * race_b200_causal_fwd with variant RACE_VARIANT_TENSOR or RACE_VARIANT_TENSOR_SINGLE_PASS (fp32,
+ * S = 64, d_k = 64) with every device-side wait limited to wait_cycles SM clock cycles
+ * (1000 .. 2^31) and with the TMA producer of the CTA that works on the first tile of stream 0
+ * skipping the load of chunk withhold_chunk (64-token chunks), so that the consumer of that chunk
+ * waits in vain.  Expected behaviour, which a test
  * asserts: the call returns, the kernels end within a few multiples of wait_cycles, *status
  * (required) holds the code of the wait that gave up, the outputs of that CTA are unspecified,
  * and the device stays usable.  Nothing faults and nothing spins without a limit.  The reference
@@ -288,7 +293,7 @@ int race_b200_causal_fwd_static(const void* probs_q, const void* probs_k, const 
  * (src/causal_v2/kernels/race_causal_fwd.cu uses __syncthreads only).
  */
 int race_b200_selftest_bounded_wait(const void* probs_q, const void* probs_k, const void* v, void* out,
-                                    void* workspace, size_t workspace_bytes, const RaceShape* shape,
+                                    void* workspace, size_t workspace_bytes, const RaceShape* shape, int variant,
                                     int64_t wait_cycles, int withhold_chunk, void* stream, int* status);
 
 #ifdef __cplusplus

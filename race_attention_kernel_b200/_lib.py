@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "librace_b200.so")
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
-VARIANTS = {"auto": 0, "simt": 1, "tensor": 2}
+VARIANTS = {"auto": 0, "simt": 1, "tensor": 2, "tensor_single_pass": 3}
 
 EXPORTS = [
     "race_b200_version", "race_b200_error_string", "race_b200_is_supported",
@@ -26,7 +26,7 @@ EXPORTS = [
     "race_b200_bucket_probs", "race_b200_bucket_probs_streams", "race_b200_causal_fwd_host",
     "race_b200_static_scratch_bytes", "race_b200_causal_fwd_static", "race_b200_decode_step",
     "race_b200_causal_fwd_global", "race_b200_causal_bwd_workspace_bytes", "race_b200_causal_bwd",
-    "race_b200_causal_bwd_carry", "race_b200_selftest_bounded_wait", "race_b200_causal_workspace_bytes_min",
+    "race_b200_causal_bwd_carry", "race_b200_selftest_bounded_wait", "race_b200_host_release",
 ]
 
 
@@ -59,8 +59,6 @@ def lib() -> ctypes.CDLL:
     L.race_b200_select_tile_tokens.argtypes = [shp, i32, ctypes.POINTER(i32)]
     L.race_b200_causal_workspace_bytes.restype = sz
     L.race_b200_causal_workspace_bytes.argtypes = [shp, i32, i32]
-    L.race_b200_causal_workspace_bytes_min.restype = sz
-    L.race_b200_causal_workspace_bytes_min.argtypes = [shp, i32, i32]
     L.race_b200_causal_fwd.restype = i32
     L.race_b200_causal_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, i32, vp, vp]
     L.race_b200_tile_totals.restype = i32
@@ -79,6 +77,8 @@ def lib() -> ctypes.CDLL:
     L.race_b200_bucket_probs_streams.argtypes = [vp, vp, vp, i64, i64, i32, i32, i32, i32, i32, i32, vp]
     L.race_b200_causal_fwd_host.restype = i32
     L.race_b200_causal_fwd_host.argtypes = [vp, vp, vp, vp, vp, vp, shp, i64, i32, i32]
+    L.race_b200_host_release.restype = i32
+    L.race_b200_host_release.argtypes = [i32]
     L.race_b200_static_scratch_bytes.restype = sz
     L.race_b200_static_scratch_bytes.argtypes = []
     L.race_b200_causal_fwd_static.restype = i32
@@ -86,7 +86,7 @@ def lib() -> ctypes.CDLL:
     L.race_b200_causal_fwd_global.restype = i32
     L.race_b200_causal_fwd_global.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, i32, vp, vp]
     L.race_b200_selftest_bounded_wait.restype = i32
-    L.race_b200_selftest_bounded_wait.argtypes = [vp, vp, vp, vp, vp, sz, shp, i64, i32, vp, vp]
+    L.race_b200_selftest_bounded_wait.argtypes = [vp, vp, vp, vp, vp, sz, shp, i32, i64, i32, vp, vp]
     L.race_b200_causal_bwd_workspace_bytes.restype = sz
     L.race_b200_causal_bwd_workspace_bytes.argtypes = [shp]
     L.race_b200_causal_bwd.restype = i32

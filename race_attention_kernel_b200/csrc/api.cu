@@ -42,6 +42,10 @@ int sm_count() {
     return sms > 0 ? sms : 148;
 }
 
+// the single-pass form exists for the fp32 tensor kernels; everything else about it is the TENSOR family
+inline bool is_single_pass(int variant) { return variant == RACE_VARIANT_TENSOR_SINGLE_PASS; }
+inline int family(int variant) { return is_single_pass(variant) ? RACE_VARIANT_TENSOR : variant; }
+
 int resolve_variant(const Dims& dm, int dtype, int variant) {
     if (variant == RACE_VARIANT_AUTO)
         return (tensor_supported(dm, dtype) && (dm.H == 1 || dtype == RACE_DTYPE_F32)) ? RACE_VARIANT_TENSOR
@@ -51,23 +55,25 @@ int resolve_variant(const Dims& dm, int dtype, int variant) {
 
 bool variant_supported(const Dims& dm, int dtype, int variant) {
     // the heads layout of V / out is read by the fp32 tensor kernels only
-    if (dm.H > 1 && !(variant == RACE_VARIANT_TENSOR && dtype == RACE_DTYPE_F32)) return false;
+    if (dm.H > 1 && !(family(variant) == RACE_VARIANT_TENSOR && dtype == RACE_DTYPE_F32)) return false;
     if (variant == RACE_VARIANT_SIMT) return simt_supported(dm);
     if (variant == RACE_VARIANT_TENSOR) return tensor_supported(dm, dtype);
+    if (is_single_pass(variant)) return dtype == RACE_DTYPE_F32 && tensor_supported(dm, dtype);
     return false;
 }
 
-int chunk_of(int variant) { return variant == RACE_VARIANT_TENSOR ? tensor_chunk_tokens() : kSimtChunk; }
+int chunk_of(int variant) { return family(variant) == RACE_VARIANT_TENSOR ? tensor_chunk_tokens() : kSimtChunk; }
 
 int pick_tile(const Dims& dm, int dtype, int variant) {
+    if (is_single_pass(variant)) return tensor_single_pass_tile_tokens(dm, sm_count());
     if (variant == RACE_VARIANT_TENSOR) return tensor_default_tile_tokens(dm, dtype, sm_count());
     return simt_default_tile_tokens(dm, sm_count());
 }
 
-size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile, bool minimum = false) {
+size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile, bool totals_or_resume = false) {
     if (dm.T == 0 || dm.N == 0) return 0;
-    if (variant == RACE_VARIANT_TENSOR)
-        return minimum ? tensor_workspace_bytes_min(dm, dtype, tile) : tensor_workspace_bytes(dm, dtype, tile);
+    if (is_single_pass(variant) && !totals_or_resume) return tensor_single_pass_workspace_bytes(dm, tile);
+    if (family(variant) == RACE_VARIANT_TENSOR) return tensor_workspace_bytes(dm, dtype, tile);
     const int64_t tiles = (dm.T + tile - 1) / tile;
     return (size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
 }
@@ -128,15 +134,6 @@ size_t race_b200_causal_workspace_bytes(const RaceShape* shape, int tile_tokens,
     return workspace_bytes_for(dm, shape->dtype, var, tile);
 }
 
-size_t race_b200_causal_workspace_bytes_min(const RaceShape* shape, int tile_tokens, int variant) {
-    Dims dm;
-    if (check_shape(shape, &dm) != RACE_OK) return 0;
-    const int var = resolve_variant(dm, shape->dtype, variant);
-    if (!variant_supported(dm, shape->dtype, var)) return 0;
-    const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, var);
-    return workspace_bytes_for(dm, shape->dtype, var, tile, /*minimum=*/true);
-}
-
 static int causal_entry(const void* probs_q, const void* probs_k, const void* v, void* out,
                         const float* carry_in, float* state_out, void* workspace,
                         size_t workspace_bytes, const RaceShape* shape, int tile_tokens,
@@ -146,10 +143,10 @@ static int causal_entry(const void* probs_q, const void* probs_k, const void* v,
     int rc = check_shape(shape, &dm);
     if (rc != RACE_OK) return rc;
     const int var = resolve_variant(dm, shape->dtype, variant);
-    if (var != RACE_VARIANT_SIMT && var != RACE_VARIANT_TENSOR) return RACE_ERR_VARIANT;
+    if (var != RACE_VARIANT_SIMT && var != RACE_VARIANT_TENSOR && !is_single_pass(var)) return RACE_ERR_VARIANT;
     if (!variant_supported(dm, shape->dtype, var)) return var == variant ? RACE_ERR_VARIANT : RACE_ERR_SHAPE;
     // the global-normalisation form runs on the CUDA-core kernels and on the fp32 tensor kernels
-    if (global_norm && var == RACE_VARIANT_TENSOR && shape->dtype != RACE_DTYPE_F32) return RACE_ERR_VARIANT;
+    if (global_norm && family(var) == RACE_VARIANT_TENSOR && shape->dtype != RACE_DTYPE_F32) return RACE_ERR_VARIANT;
     if (tile_tokens < 0) return RACE_ERR_TILE;
     const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, var);
     if (tile % chunk_of(var) != 0) return RACE_ERR_TILE;
@@ -172,9 +169,11 @@ static int causal_entry(const void* probs_q, const void* probs_k, const void* v,
     if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(out) ||
         !aligned16(workspace) || !aligned16(carry_in) || !aligned16(state_out))
         return RACE_ERR_ALIGN;
-    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, var, tile, /*minimum=*/true)) return RACE_ERR_WORKSPACE;
-    if (var == RACE_VARIANT_TENSOR)
-        return (int)causal_fwd_tensor(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes,
+    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, var, tile, /*totals_or_resume=*/phases != kPhaseAll))
+        return RACE_ERR_WORKSPACE;
+    if (family(var) == RACE_VARIANT_TENSOR)
+        return (int)causal_fwd_tensor(probs_q, probs_k, v, out, carry_in, state_out, workspace,
+                                      /*single_pass=*/is_single_pass(var) && phases == kPhaseAll,
                                       dm, shape->dtype, tile, st, status, phases, global_norm, wait_cycles,
                                       withhold_chunk);
     return (int)causal_fwd_simt(probs_q, probs_k, v, out, carry_in, state_out, (float*)workspace,
@@ -216,13 +215,13 @@ int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const 
 }
 
 int race_b200_selftest_bounded_wait(const void* probs_q, const void* probs_k, const void* v, void* out,
-                                    void* workspace, size_t workspace_bytes, const RaceShape* shape,
+                                    void* workspace, size_t workspace_bytes, const RaceShape* shape, int variant,
                                     int64_t wait_cycles, int withhold_chunk, void* stream, int* status) {
     if (!status) return RACE_ERR_NULL;
     if (wait_cycles < 1000 || wait_cycles > (1ll << 31) || withhold_chunk < 0) return RACE_ERR_SHAPE;
-    if (!shape || shape->dtype != RACE_DTYPE_F32) return RACE_ERR_VARIANT;
+    if (!shape || shape->dtype != RACE_DTYPE_F32 || family(variant) != RACE_VARIANT_TENSOR) return RACE_ERR_VARIANT;
     return causal_entry(probs_q, probs_k, v, out, nullptr, nullptr, workspace, workspace_bytes, shape, 0,
-                        RACE_VARIANT_TENSOR, stream, status, kPhaseAll, false, wait_cycles, withhold_chunk);
+                        variant, stream, status, kPhaseAll, false, wait_cycles, withhold_chunk);
 }
 
 size_t race_b200_causal_bwd_workspace_bytes(const RaceShape* shape) {

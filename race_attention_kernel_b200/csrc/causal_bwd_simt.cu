@@ -622,7 +622,7 @@ cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const
     // shape) and exclusive scan
     cudaError_t err;
     if (tensor_supported(dm, dtype) && tile_tokens % tensor_chunk_tokens() == 0) {
-        err = causal_fwd_tensor(nullptr, pk, v, nullptr, nullptr, nullptr, ws_prefix, 0, dm, dtype, tile_tokens, stream,
+        err = causal_fwd_tensor(nullptr, pk, v, nullptr, nullptr, nullptr, ws_prefix, false, dm, dtype, tile_tokens, stream,
                                 status, kPhaseTotals);
         if (err == cudaSuccess)
             err = causal_scan_tiles(ws_prefix, carry_in, nullptr, dm, tile_tokens, stream, /*write_prefix=*/true);

@@ -30,8 +30,11 @@
 #include "launch.h"
 #include "tc_common.cuh"
 
+#ifndef RACE_FUSED_PREFETCH
+#define RACE_FUSED_PREFETCH 0
+#endif
 #ifndef RACE_FUSED_STAGGER_PER_CHUNK
-#define RACE_FUSED_STAGGER_PER_CHUNK 5000
+#define RACE_FUSED_STAGGER_PER_CHUNK 0
 #endif
 
 namespace race {
@@ -79,15 +82,25 @@ enum Bar {
 };
 
 // fp32 staged tile (two 128B-swizzled halves of 32 columns) -> bf16 hi/lo operand tiles
-__device__ __forceinline__ void convert_tile(const uint8_t* stage, uint8_t* hi, uint8_t* lo, int tid) {
+__device__ __forceinline__ void convert_tile(const uint8_t* __restrict__ stage, uint8_t* __restrict__ hi,
+                                             uint8_t* __restrict__ lo, int tid) {
+    // all loads first: the staged tile and the operand tiles are different buffers, but only loads issued
+    // ahead of the stores overlap their latencies
+    float4 av[4], bv[4];
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
         const int idx = it * 128 + tid;
         const int j = idx >> 6, r = idx & 63;            // 8-column group, token row
         const uint8_t* src = stage + (j >> 2) * 8192 + r * 128;
         const int jj = j & 3;
-        const float4 a = *reinterpret_cast<const float4*>(src + (((2 * jj) ^ (r & 7)) << 4));
-        const float4 b = *reinterpret_cast<const float4*>(src + (((2 * jj + 1) ^ (r & 7)) << 4));
+        av[it] = *reinterpret_cast<const float4*>(src + (((2 * jj) ^ (r & 7)) << 4));
+        bv[it] = *reinterpret_cast<const float4*>(src + (((2 * jj + 1) ^ (r & 7)) << 4));
+    }
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int idx = it * 128 + tid;
+        const int j = idx >> 6, r = idx & 63;
+        const float4 a = av[it], b = bv[it];
         uint4 h, l;
         split2(a.x, a.y, h.x, l.x);
         split2(a.z, a.w, h.y, l.y);
@@ -153,15 +166,18 @@ __device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again) {
 // kGlobal selects the global-normalisation estimator (src/causal_v2/reference.py:106-127): W = pQ
 // without the per-bucket divide and every output row divided by den_t = pQ_t . A_t (0 -> a row of 0).
 // withhold (self-test of the bounded waits): the TMA producer skips the load of chunk withhold_chunk.
-// pf_chunks > 0: while it walks this tile the producer also prefetches, chunk by chunk, pK and V of the
-// tile (stream pf_n, first token pf_begin) this CTA works on next into the L2.
+// l2_last_use: this is the second read of the tile's pK and V (single-pass kernel), so their lines are loaded
+// with the evict-first priority and leave the L2 to the tiles still waiting for their second read.
+// pf_chunks > 0: while it walks this tile the producer also prefetches, chunk by chunk and with the evict-last
+// priority, pK and V of the tile this CTA works on next (stream pf_n, first token pf_begin) into the L2: what a
+// CTA keeps in the L2 stays one tile's worth (the rest of this tile plus the start of the next).
 template <bool kGlobal>
 __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, const float* __restrict__ pq,
                                           const CUtensorMap* map_k, const CUtensorMap* map_v,
                                           float* __restrict__ out, const float* __restrict__ slice, int64_t T,
                                           const int64_t t_begin, const int64_t t_end, const int64_t n, float eps,
-                                          int heads, int withhold_chunk, const int64_t pf_begin = 0,
-                                          const int64_t pf_n = 0, const int pf_chunks = 0) {
+                                          int heads, int withhold_chunk, const bool l2_last_use = false,
+                                          const int64_t pf_begin = 0, const int64_t pf_n = 0, const int pf_chunks = 0) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nch = (int)((t_end - t_begin + C - 1) / C);
     const uint32_t tmB = tmem;                               // B accumulator, columns [0, 64)
@@ -422,6 +438,8 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
         // =========================== TMA producer ==============================================
         if (lane == 0) {
             int issued = 0;
+            const uint64_t pol = l2_policy_evict_first();
+            const uint64_t pol_keep = l2_policy_evict_last();
             for (int c = 0; c < nch; ++c) {
                 const int st = c & 1;
                 if (c >= 2 && !wait_bar(cx, kEmpty + st, ((c >> 1) - 1) & 1, 301)) break;
@@ -430,18 +448,19 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
                 const uint32_t bar = cx.bar(kFull + st);
                 const int tok = (int)(t_begin + (int64_t)c * C);
                 mbar_arrive_expect_tx(bar, kStageBytes);
-                tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
-                tma_load_4d(dst + 8192, map_k, bar, 0, tok, 1, (int)n);
-                tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
-                tma_load_5d(dst + kTileF32 + 8192, map_v, bar, 0, tok, 1, (int)(n % heads), (int)(n / heads));
+                if (l2_last_use) {
+                    tma_load_4d_hint(dst, map_k, bar, 0, tok, 0, (int)n, pol);
+                    tma_load_5d_hint(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads), pol);
+                } else {
+                    tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
+                    tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                }
                 issued = c + 1;
-                for (int pc = c; pc < pf_chunks && (pc == c || c == nch - 1); ++pc) {
+                for (int pc = c; RACE_FUSED_PREFETCH && pc < pf_chunks && (pc == c || c == nch - 1); ++pc) {
                     // the same chunk of the next tile (all that is left of it, from this tile's last chunk)
                     const int ptok = (int)(pf_begin + (int64_t)pc * C);
-                    tma_prefetch_4d(map_k, 0, ptok, 0, (int)pf_n);
-                    tma_prefetch_4d(map_k, 0, ptok, 1, (int)pf_n);
-                    tma_prefetch_5d(map_v, 0, ptok, 0, (int)(pf_n % heads), (int)(pf_n / heads));
-                    tma_prefetch_5d(map_v, 0, ptok, 1, (int)(pf_n % heads), (int)(pf_n / heads));
+                    tma_prefetch_4d_hint(map_k, 0, ptok, 0, (int)pf_n, pol_keep);
+                    tma_prefetch_5d_hint(map_v, 0, ptok, 0, (int)(pf_n % heads), (int)(pf_n / heads), pol_keep);
                 }
             }
             if (*cx.abort_flag) {
@@ -577,35 +596,72 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
 }
 
 
+#ifdef RACE_FUSED_PROF
+// per-CTA cycle counters of the single-pass kernel (profiling builds only): totals phase, wait for
+// the look-back flags, prefix sum, output phase, tiles taken
+__device__ long long g_fused_prof[160][16];
+#define RACE_PROF_ADD(slot, t_from)                                                   \
+    do { if (tid == 0) { const long long now_ = clock64(); g_fused_prof[blockIdx.x][slot] += now_ - (t_from); (t_from) = now_; } } while (0)
+#else
+#define RACE_PROF_ADD(slot, t_from) do {} while (0)
+#endif
+
+#ifdef RACE_FUSED_PROF
+#define RACE_PROF_T(var) long long var = clock64()
+#define RACE_PROF_LANE(slot, t_from) do { const long long now_ = clock64(); g_fused_prof[blockIdx.x][slot] += now_ - (t_from); (t_from) = now_; } while (0)
+#else
+#define RACE_PROF_T(var) do {} while (0)
+#define RACE_PROF_LANE(slot, t_from) do {} while (0)
+#endif
+
 // ------------------------------------------------------------------------------------------------
 // Tile totals on the tensor cores: B_tile = sum_t pK^T V (tcgen05.mma into one TMEM accumulator),
 // A_tile = sum_t pK (fp32 adds while the keys are split into limbs).  A streaming kernel: two
 // converter warpgroups take alternate chunks from a four-stage TMA ring; nothing but the
 // accumulator is carried from chunk to chunk.
 // ------------------------------------------------------------------------------------------------
-constexpr int kT1Threads = 10 * 32;
+// kT1Groups converter warpgroups take the chunks c = g (mod kT1Groups), each with its own operand tiles, from a
+// TMA ring of kT1Stages stages.  The stage count is a multiple of the group count so that a stage always goes
+// to the same group: a group that saw only every other phase of a stage's barrier could not tell a refilled
+// stage from the one it read two fills ago by the parity (which made a 3-stage ring with two groups run ahead
+// of the copies and overflow its barriers' arrival counts under load).
+constexpr int kT1Groups = 2;
 constexpr int kT1Stages = 4;
+static_assert(kT1Stages % kT1Groups == 0, "a stage must stay with one converter group");
+constexpr int kT1ProducerWarp = 4 * kT1Groups, kT1MmaWarp = 4 * kT1Groups + 1;
+constexpr int kT1Threads = (4 * kT1Groups + 2) * 32;    // converters, TMA producer, MMA issuer
 constexpr int kT1StageBytes = 2 * kTileF32;            // pK | V
 constexpr int o1Stage = 0;
-constexpr int o1Kt = o1Stage + kT1Stages * kT1StageBytes;   // [2 wg][hi | lo]
-constexpr int o1Vt = o1Kt + 4 * kOpTile;               // [2 wg][hi | lo]
-constexpr int o1Red = o1Vt + 4 * kOpTile;              // [8 warps][4][8] fp32 column-sum partials
-constexpr int o1Bars = o1Red + 8 * 32 * 4;
+constexpr int o1Kt = o1Stage + kT1Stages * kT1StageBytes;   // [group][hi | lo]
+constexpr int o1Vt = o1Kt + kT1Groups * 2 * kOpTile;        // [group][hi | lo]
+constexpr int o1Red = o1Vt + kT1Groups * 2 * kOpTile;       // [12 warps][4][8] fp32 column-sum partials
+constexpr int o1Bars = o1Red + 4 * kT1Groups * 32 * 4;
 constexpr int o1Misc = o1Bars + 16 * 8;
 constexpr int kT1SmemBytes = o1Misc + 16 + 1024;
-enum Bar1 { k1Full = 0, k1Empty = 4, k1KvReady = 8, k1KvFree = 10, k1Done = 12 };
+enum Bar1 {
+    k1Full = 0, k1Empty = kT1Stages, k1KvReady = 2 * kT1Stages, k1KvFree = 2 * kT1Stages + kT1Groups,
+    k1Done = 2 * kT1Stages + 2 * kT1Groups
+};
+static_assert(kT1Threads <= kThreads, "the single-pass kernel runs the totals phase with its own warps");
 
 // like convert_tile, and adds each thread's 8 values per item into asum[item][8]
-__device__ __forceinline__ void convert_tile_sum(const uint8_t* stage, uint8_t* hi, uint8_t* lo, int tid,
-                                                 float (&asum)[4][8]) {
+__device__ __forceinline__ void convert_tile_sum(const uint8_t* __restrict__ stage, uint8_t* __restrict__ hi,
+                                                 uint8_t* __restrict__ lo, int tid, float (&asum)[4][8]) {
+    float4 av[4], bv[4];
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
         const int idx = it * 128 + tid;
         const int j = idx >> 6, r = idx & 63;
         const uint8_t* src = stage + (j >> 2) * 8192 + r * 128;
         const int jj = j & 3;
-        const float4 a = *reinterpret_cast<const float4*>(src + (((2 * jj) ^ (r & 7)) << 4));
-        const float4 b = *reinterpret_cast<const float4*>(src + (((2 * jj + 1) ^ (r & 7)) << 4));
+        av[it] = *reinterpret_cast<const float4*>(src + (((2 * jj) ^ (r & 7)) << 4));
+        bv[it] = *reinterpret_cast<const float4*>(src + (((2 * jj + 1) ^ (r & 7)) << 4));
+    }
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int idx = it * 128 + tid;
+        const int j = idx >> 6, r = idx & 63;
+        const float4 a = av[it], b = bv[it];
         asum[it][0] += a.x; asum[it][1] += a.y; asum[it][2] += a.z; asum[it][3] += a.w;
         asum[it][4] += b.x; asum[it][5] += b.y; asum[it][6] += b.z; asum[it][7] += b.w;
         uint4 h, l;
@@ -619,7 +675,8 @@ __device__ __forceinline__ void convert_tile_sum(const uint8_t* stage, uint8_t* 
     }
 }
 
-constexpr int kT1NumBars = 13;
+constexpr int kT1NumBars = k1Done + 1;
+static_assert(kT1NumBars <= 16, "barrier array of the totals phase");
 __device__ __forceinline__ void totals_phase_reinit_bars_warp(const Ctx& cx, int lane, bool again) {
     if (lane < kT1NumBars) {
         if (again) mbar_inval(cx.bar(lane));
@@ -635,7 +692,7 @@ __device__ __forceinline__ void totals_phase_init_bars(const Ctx& cx, bool again
             mbar_init(cx.bar(k1Full + i), 1);
             mbar_init(cx.bar(k1Empty + i), 4);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kT1Groups; ++i) {
             mbar_init(cx.bar(k1KvReady + i), 4);
             mbar_init(cx.bar(k1KvFree + i), 1);
         }
@@ -645,62 +702,75 @@ __device__ __forceinline__ void totals_phase_init_bars(const Ctx& cx, bool again
 }
 
 // Totals phase of one (stream n, tokens [t_begin, t_end)) tile into `slice` (state layout).  Called
-// by at least 10 warps (warps 0-7 convert, 8 issues TMA, 9 issues the products; further warps only
+// by at least kT1Threads / 32 warps (the first 4 * kT1Groups convert, the next issues TMA, the next the products; further warps only
 // take part in the block-wide barriers) with barriers initialised and 64 TMEM columns at `tmem`.
-// Two converter groups take alternate chunks from a four-stage TMA ring.
+// l2_keep: pK and V of the tile are read again soon (single-pass kernel): load them with the evict-last priority.
 __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem, const CUtensorMap* map_k,
                                              const CUtensorMap* map_v, float* __restrict__ slice,
-                                             const int64_t t_begin, const int64_t t_end, const int64_t n, int heads) {
+                                             const int64_t t_begin, const int64_t t_end, const int64_t n, int heads,
+                                             const bool l2_keep = false) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nch = (int)((t_end - t_begin + C - 1) / C);
 
-    if (warp < 8) {
+    if (warp < 4 * kT1Groups) {
         const int wg = warp >> 2, wtid = tid & 127;
+        uint8_t* kt_hi = cx.sm + o1Kt + wg * 2 * kOpTile;
+        uint8_t* vt_hi = cx.sm + o1Vt + wg * 2 * kOpTile;
         float asum[4][8];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int e = 0; e < 8; ++e) asum[i][e] = 0.f;
         bool ok = true;
-        for (int c = wg; c < nch && ok; c += 2) {
+        int i = 0;   // the group's i-th chunk
+        RACE_PROF_T(tq);
+        for (int c = wg; c < nch && ok; c += kT1Groups, ++i) {
             const int st = c % kT1Stages;
-            uint8_t* kt_hi = cx.sm + o1Kt + wg * 2 * kOpTile;
-            uint8_t* vt_hi = cx.sm + o1Vt + wg * 2 * kOpTile;
-            if (!(ok = wait_bar_warp(cx, k1Full + st, (c / kT1Stages) & 1, 111))) break;
-            if (c >= 2 && !(ok = wait_bar_warp(cx, k1KvFree + wg, ((c >> 1) - 1) & 1, 112))) break;
             const uint8_t* stage = cx.sm + o1Stage + st * kT1StageBytes;
+            if (!(ok = wait_bar_warp(cx, k1Full + st, (uint32_t)((c / kT1Stages) & 1), 111))) break;
+            if (tid == 0) RACE_PROF_LANE(8, tq);
+            if (i >= 1 && !(ok = wait_bar_warp(cx, k1KvFree + wg, (uint32_t)((i - 1) & 1), 112))) break;
+            if (tid == 0) RACE_PROF_LANE(9, tq);
             convert_tile_sum(stage, kt_hi, kt_hi + kOpTile, wtid, asum);
             convert_tile(stage + kTileF32, vt_hi, vt_hi + kOpTile, wtid);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) { mbar_arrive(cx.bar(k1KvReady + wg)); mbar_arrive(cx.bar(k1Empty + st)); }
+            if (tid == 0) RACE_PROF_LANE(10, tq);
         }
         // column sums: lanes of a warp hold different token rows of the same 8 columns
         float* red = reinterpret_cast<float*>(cx.sm + o1Red) + warp * 32;
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int it = 0; it < 4; ++it)
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                float x = asum[i][e];
+                float x = asum[it][e];
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
-                if (lane == 0) red[i * 8 + e] = x;
+                if (lane == 0) red[it * 8 + e] = x;
             }
-    } else if (warp == 8) {
+    } else if (warp == kT1ProducerWarp) {
         if (lane == 0) {
             int issued = 0;
+            const uint64_t pol = l2_policy_evict_last();
+            RACE_PROF_T(tq);
             for (int c = 0; c < nch; ++c) {
-                const int st = c % kT1Stages;
-                if (c >= kT1Stages && !wait_bar(cx, k1Empty + st, ((c / kT1Stages) - 1) & 1, 311)) break;
+                const int st = c % kT1Stages, i = c / kT1Stages;
+                if (i >= 1 && !wait_bar(cx, k1Empty + st, (uint32_t)((i - 1) & 1), 311)) break;
+                RACE_PROF_LANE(11, tq);
                 const uint32_t dst = cx.sm_u32 + o1Stage + st * kT1StageBytes;
                 const uint32_t bar = cx.bar(k1Full + st);
                 const int tok = (int)(t_begin + (int64_t)c * C);
                 mbar_arrive_expect_tx(bar, kT1StageBytes);
-                tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
-                tma_load_4d(dst + 8192, map_k, bar, 0, tok, 1, (int)n);
-                tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
-                tma_load_5d(dst + kTileF32 + 8192, map_v, bar, 0, tok, 1, (int)(n % heads), (int)(n / heads));
+                if (l2_keep) {
+                    tma_load_4d_hint(dst, map_k, bar, 0, tok, 0, (int)n, pol);
+                    tma_load_5d_hint(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads), pol);
+                } else {
+                    tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
+                    tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                }
                 issued = c + 1;
+                RACE_PROF_LANE(12, tq);
             }
             if (*cx.abort_flag) {
                 for (int c = max(0, issued - kT1Stages); c < issued; ++c) {
@@ -710,7 +780,7 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == kT1MmaWarp) {
         // every operand of the issuing thread derives from warp-uniform values (cheap descriptor arithmetic)
         const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
         const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
@@ -718,9 +788,11 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
         constexpr uint32_t kId = kIdescBase | kAmn | kBmn;
         if (elect_one()) {
             bool ok = true;
+            RACE_PROF_T(tq);
             for (int c = 0; c < nch && ok; ++c) {
-                const int wg = c & 1;
-                if (!(ok = wait_bar(cx, k1KvReady + wg, (c >> 1) & 1, 411))) break;
+                const int wg = c % kT1Groups, i = c / kT1Groups;
+                if (!(ok = wait_bar(cx, k1KvReady + wg, (uint32_t)(i & 1), 411))) break;
+                RACE_PROF_LANE(13, tq);
                 tc_fence_after();
                 const uint32_t kt = lo_mn(smb + o1Kt + wg * 2 * kOpTile);
                 const uint32_t vt = lo_mn(smb + o1Vt + wg * 2 * kOpTile);
@@ -730,6 +802,7 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
                 mma_k64<false, kHiMN, 128, kHiMN, 128>(tm, kt, vt + kLimb, kId);
                 mma_k64<false, kHiMN, 128, kHiMN, 128>(tm, kt + kLimb, vt, kId);
                 mma_commit(cx.bar(k1KvFree + wg));
+                RACE_PROF_LANE(14, tq);
             }
             mma_commit(cx.bar(k1Done));
         }
@@ -756,7 +829,7 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
                 const float* red = reinterpret_cast<const float*>(cx.sm + o1Red);
                 float a = 0.f;
 #pragma unroll
-                for (int g = 0; g < 2; ++g)
+                for (int g = 0; g < kT1Groups; ++g)
 #pragma unroll
                     for (int half = 0; half < 2; ++half)
                         a += red[(g * 4 + wh + half) * 32 + it * 8 + e];
@@ -786,7 +859,7 @@ tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         *cx.abort_flag = 0;
         totals_phase_init_bars(cx, false);
     }
-    if (warp == 9) tmem_alloc(cx.sm_u32 + o1Misc, 64u);
+    if (warp == kT1MmaWarp) tmem_alloc(cx.sm_u32 + o1Misc, 64u);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -794,7 +867,7 @@ tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     totals_phase(cx, tmem, &map_k, &map_v, slice, t_begin, t_end, n, heads);
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kT1MmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem, 64u);
     }
@@ -850,16 +923,6 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
     asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-#ifdef RACE_FUSED_PROF
-// per-CTA cycle counters of the single-pass kernel (profiling builds only): totals phase, wait for
-// the look-back flags, prefix sum, output phase, tiles taken
-__device__ long long g_fused_prof[kFusedMaxGrid][8];
-#define RACE_PROF_ADD(slot, t_from)                                                   \
-    do { if (tid == 0) { const long long now_ = clock64(); g_fused_prof[blockIdx.x][slot] += now_ - (t_from); (t_from) = now_; } } while (0)
-#else
-#define RACE_PROF_ADD(slot, t_from) do {} while (0)
-#endif
-
 template <bool kGlobal>
 __global__ void __launch_bounds__(kThreads, 1)
 causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -880,7 +943,11 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     const int tid = threadIdx.x, warp = tid >> 5;
     const unsigned long long total = (unsigned long long)a.N * (unsigned long long)a.tiles;
 
-    if (tid == 0) *cxA.abort_flag = 0;
+    if (tid == 0) {
+        *cxA.abort_flag = 0;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    }
     if (warp == kMmaWarp) tmem_alloc(cxA.sm_u32 + oFusedMisc, kTmemCols);
     tc_fence_before();
     __syncthreads();
@@ -895,7 +962,7 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         while (clock64() - t0 < delay) __nanosleep(256);
     }
 
-    // tiles are taken one ahead: the ticket of the next tile is drawn before the output phase of the current
+    // tiles are drawn one ahead: the ticket of the next tile is taken before the output phase of the current
     // one, which prefetches the next tile's pK and V into the L2 as it goes
     if (tid == 0) *ticket_slot = atomicAdd(a.ticket, 1ull);
     __syncthreads();
@@ -916,7 +983,7 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         (void)tp;
         if (warp == 0) totals_phase_reinit_bars_warp(cxA, tid, !first);
         __syncthreads();
-        totals_phase(cxA, tmem, &map_k, &map_v, agg_n + tile * kSF, t_begin, t_end, n, a.heads);
+        totals_phase(cxA, tmem, &map_k, &map_v, agg_n + tile * kSF, t_begin, t_end, n, a.heads, /*l2_keep=*/true);
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
@@ -1015,7 +1082,7 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         // ---- 3. outputs of the tile ---------------------------------------------------------------
         out_phase<kGlobal>(cxB, tmem, a.pq, &map_k, &map_v, a.out, a.cta_carry + (int64_t)blockIdx.x * kSF, a.T,
                            t_begin, t_end, n, a.eps, a.heads, (tile == 0 && n == 0) ? a.withhold_chunk : -1,
-                           pf_begin, pf_n, pf_chunks);
+                           /*l2_last_use=*/true, pf_begin, pf_n, pf_chunks);
         first = false;
         fence_proxy_async();
         tc_fence_before();
@@ -1057,15 +1124,15 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }
 
 // V in the layout [N/heads, T, heads, width] (heads = 1: [N, T, width]) viewed as (32 values, T tokens,
-// width/32 column blocks, heads, N/heads); one box = 32 values x 64 tokens (128-byte rows, 128B swizzle);
-// tokens past T read as zero
+// width/32 column blocks, heads, N/heads); one box = 32 values x 64 tokens x both column blocks (128-byte rows,
+// 128B swizzle; the box lands as two consecutive 8 KB tiles, one per column block); tokens past T read as zero
 bool make_map_heads(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width, int heads) {
     auto fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[5] = {32, (cuuint64_t)T, (cuuint64_t)(width / 32), (cuuint64_t)heads, (cuuint64_t)(N / heads)};
     cuuint64_t strides[4] = {(cuuint64_t)heads * width * 4, 128, (cuuint64_t)width * 4,
                              (cuuint64_t)T * heads * width * 4};
-    cuuint32_t box[5] = {32, (cuuint32_t)C, 1, 1, 1};
+    cuuint32_t box[5] = {32, (cuuint32_t)C, (cuuint32_t)(width / 32), 1, 1};
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1078,7 +1145,7 @@ bool make_map(CUtensorMap* map, const void* base, int64_t N, int64_t T, int widt
     if (!fn) return false;
     cuuint64_t dims[4] = {32, (cuuint64_t)T, (cuuint64_t)(width / 32), (cuuint64_t)N};
     cuuint64_t strides[3] = {(cuuint64_t)width * 4, 128, (cuuint64_t)T * width * 4};
-    cuuint32_t box[4] = {32, (cuuint32_t)C, 1, 1};
+    cuuint32_t box[4] = {32, (cuuint32_t)C, (cuuint32_t)(width / 32), 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1096,16 +1163,17 @@ bool tensor_supported(const Dims& dm, int dtype) {
 
 int tensor_chunk_tokens() { return C; }
 
-int tensor_default_tile_tokens(const Dims& dm, int dtype, int sm_count) {
-    if (dtype == RACE_DTYPE_F32) {
-        // The fp32 forward is one persistent kernel that hands tiles to the SMs as they become free and reads
-        // pK and V of a tile twice: 1024 tokens keep the tiles in flight on all SMs (sm_count x 512 KB) inside
-        // the L2.  Short inputs get shorter tiles, about one per SM.
-        const int64_t sms = sm_count > 0 ? sm_count : 148;
-        const int64_t per_sm = (dm.N * dm.T + sms - 1) / sms;
-        const int64_t tile = (per_sm + C - 1) / C * C;
-        return (int)(tile < C ? C : (tile > 1024 ? 1024 : tile));
-    }
+int tensor_single_pass_tile_tokens(const Dims& dm, int sm_count) {
+    // The persistent kernel hands tiles to the SMs as they become free and reads pK and V of a tile twice:
+    // 1024 tokens keep the tiles in flight on all SMs (sm_count x 512 KB) inside the L2.  Short inputs get
+    // shorter tiles, about one per SM.
+    const int64_t sms = sm_count > 0 ? sm_count : 148;
+    const int64_t per_sm = (dm.N * dm.T + sms - 1) / sms;
+    const int64_t tile = (per_sm + C - 1) / C * C;
+    return (int)(tile < C ? C : (tile > 1024 ? 1024 : tile));
+}
+
+int tensor_default_tile_tokens(const Dims& dm, int, int sm_count) {
     // One CTA per SM (and per bucket group) at a time: the CTAs run in waves of sm_count, so the tile
     // length (a multiple of the chunk, at most 2048 tokens) is chosen to fill the last wave:
     // cost = waves x (tokens per tile + the set-up of a CTA, about one and a half chunks).  For long
@@ -1140,19 +1208,16 @@ static FusedLayout fused_layout(const Dims& dm, int tile_tokens) {
     return l;
 }
 
-size_t tensor_workspace_bytes(const Dims& dm, int dtype, int tile_tokens) {
-    if (dtype == RACE_DTYPE_F32) return fused_layout(dm, tile_tokens).total;
-    return tensor_workspace_bytes_min(dm, dtype, tile_tokens);
-}
+size_t tensor_single_pass_workspace_bytes(const Dims& dm, int tile_tokens) { return fused_layout(dm, tile_tokens).total; }
 
-// what the three-launch form (totals, scan, outputs) needs: one state per tile
-size_t tensor_workspace_bytes_min(const Dims& dm, int, int tile_tokens) {
+// the three launches (totals, scan, outputs): one state per tile
+size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     return (size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
 }
 
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
-                              const float* carry_in, float* state_out, void* ws, size_t ws_bytes, const Dims& dm,
+                              const float* carry_in, float* state_out, void* ws, bool single_pass, const Dims& dm,
                               int dtype, int tile_tokens, cudaStream_t stream, int* status, int phases,
                               bool global_norm, long long wait_cycles, int withhold_chunk) {
     if (dtype == RACE_DTYPE_BF16) {
@@ -1171,8 +1236,8 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
         return cudaErrorInvalidValue;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const FusedLayout lay = fused_layout(dm, tile_tokens);
-    if (phases == kPhaseAll && ws_bytes >= lay.total) {
-        // the whole forward as one persistent kernel (a smaller workspace selects the three launches below)
+    if (single_pass && phases == kPhaseAll) {
+        // the whole forward as one persistent kernel
         int dev = 0, sms = 148;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const unsigned long long items = (unsigned long long)dm.N * (unsigned long long)tiles;
@@ -1230,9 +1295,9 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
 
 #ifdef RACE_FUSED_PROF
 extern "C" int race_b200_debug_fused_prof(long long* host_out, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(host_out, g_fused_prof, sizeof(long long) * kFusedMaxGrid * 8);
+    cudaError_t e = cudaMemcpyFromSymbol(host_out, g_fused_prof, sizeof(long long) * 160 * 16);
     if (e == cudaSuccess && reset) {
-        static long long zeros[kFusedMaxGrid * 8] = {};
+        static long long zeros[160 * 16] = {};
         e = cudaMemcpyToSymbol(g_fused_prof, zeros, sizeof(zeros));
     }
     return (int)e;

@@ -70,12 +70,12 @@ bool tensor_supported(const Dims& dm, int dtype);
 int tensor_chunk_tokens();
 int tensor_default_tile_tokens(const Dims& dm, int dtype, int sm_count);
 size_t tensor_workspace_bytes(const Dims& dm, int dtype, int tile_tokens);
-// the smallest workspace a forward runs in (the three-launch form); tensor_workspace_bytes is what
-// the single-pass kernel of the fp32 path wants
-size_t tensor_workspace_bytes_min(const Dims& dm, int dtype, int tile_tokens);
-// ws_bytes selects the form of the fp32 forward: >= tensor_workspace_bytes -> one persistent kernel
+// the single-pass form of the fp32 forward (one persistent kernel): its tile length and its workspace
+int tensor_single_pass_tile_tokens(const Dims& dm, int sm_count);
+size_t tensor_single_pass_workspace_bytes(const Dims& dm, int tile_tokens);
+// single_pass: the fp32 forward as one persistent kernel (needs phases == kPhaseAll and its larger workspace)
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
-                              const float* carry_in, float* state_out, void* ws, size_t ws_bytes, const Dims& dm,
+                              const float* carry_in, float* state_out, void* ws, bool single_pass, const Dims& dm,
                               int dtype, int tile_tokens, cudaStream_t stream, int* status,
                               int phases = kPhaseAll, bool global_norm = false, long long wait_cycles = 0,
                               int withhold_chunk = -1);

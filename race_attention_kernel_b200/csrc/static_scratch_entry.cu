@@ -65,8 +65,7 @@ int race_b200_causal_fwd_static(const void* probs_q, const void* probs_k, const 
     if (!race_b200_is_supported(shape, variant)) return RACE_ERR_SHAPE;
     // size check first, before any device memory is touched: the caller gets a definite answer (the
     // automatic tile length behind it reads the current device's SM count, 148 if there is none)
-    // the single-pass form of the forward when its workspace fits the array, else the three-launch form
-    const size_t need = race_b200_causal_workspace_bytes_min(shape, tile_tokens, variant);
+    const size_t need = race_b200_causal_workspace_bytes(shape, tile_tokens, variant);
     if (need > kScratchBytes) return RACE_ERR_SCRATCH;
     void* scratch = nullptr;
     if (shape->n_streams > 0 && shape->seq_len > 0) {

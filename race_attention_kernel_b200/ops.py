@@ -152,7 +152,10 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
 
     carry_in: None, a packed state [N, S*d_k+S] or a tuple (A [N,L,R], B [N,L,R,d_k]) holding the
     sums over tokens before this call's first token.  return_state=True also returns (A, B)
-    after the last token.  tile_tokens / variant are test hooks (0 / "auto" = automatic).
+    after the last token.  tile_tokens / variant are test hooks (0 / "auto" = automatic);
+    variant="tensor_single_pass" runs the fp32 tensor forward as one persistent kernel (tile tickets, decoupled
+    look-back, second read of a tile from L2: 1.05x instead of 1.5x the algorithmic DRAM traffic), bit-identical
+    to "tensor" for equal tile_tokens.
 
     normalization="global" computes the global-normalisation estimator instead (one denominator per
     token, no eps: out_t = (pQ_t . B_t) / (pQ_t . A_t), src/causal_v2/reference.py:106-127): on the
@@ -556,7 +559,8 @@ def race_causal_prefix_static(probsQ, probsK, V, out, eps: float = 1e-6, *, carr
     return out
 
 
-def selftest_bounded_wait(probsQ, probsK, V, wait_cycles: int = 2_000_000, withhold_chunk: int = 1):
+def selftest_bounded_wait(probsQ, probsK, V, wait_cycles: int = 2_000_000, withhold_chunk: int = 1,
+                          variant: str = "tensor"):
     """Diagnostics: run the fp32 tensor forward with every device-side wait limited to ``wait_cycles``
     SM cycles while the first CTA's load of one chunk is withheld (``race_b200_selftest_bounded_wait``).
     Returns ``(out, code)``: ``code`` is the status the kernels raised (non-zero when the wait ran out as
@@ -566,14 +570,14 @@ def selftest_bounded_wait(probsQ, probsK, V, wait_cycles: int = 2_000_000, withh
         raise RuntimeError("selftest_bounded_wait takes V as [N,T,d_k]")
     L_ = _lib.lib()
     sh = make_shape(N, T, L, R, dk, V.dtype, 1e-6)
-    var = _lib.VARIANTS["tensor"]
+    var = _lib.VARIANTS[variant]
     with torch.cuda.device(V.device):
         out = torch.empty_like(V)
         word = torch.zeros(1, dtype=torch.int32, device=V.device)
         ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), 0, var)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
         rc = L_.race_b200_selftest_bounded_wait(_ptr(probsQ), _ptr(probsK), _ptr(V), _ptr(out), _ptr(ws), ws_bytes,
-                                                ctypes.byref(sh), int(wait_cycles), int(withhold_chunk), _stream(),
+                                                ctypes.byref(sh), var, int(wait_cycles), int(withhold_chunk), _stream(),
                                                 _ptr(word))
         _lib.check(rc, "race_b200_selftest_bounded_wait")
         code = int(word.item())

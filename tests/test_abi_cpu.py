@@ -156,11 +156,32 @@ def test_causal_backward_carry_argument_errors_without_launch():
 
 def test_bounded_wait_selftest_argument_errors_without_launch():
     L = _lib.lib()
-    call = lambda sh, cycles=2_000_000, chunk=1, status=256: L.race_b200_selftest_bounded_wait(
-        None, None, None, None, None, 0, ctypes.byref(sh), cycles, chunk, None, status)
+    call = lambda sh, cycles=2_000_000, chunk=1, status=256, variant=2: L.race_b200_selftest_bounded_wait(
+        None, None, None, None, None, 0, ctypes.byref(sh), variant, cycles, chunk, None, status)
     assert call(_shape(), status=None) == -1             # the status word is required
     assert call(_shape(), cycles=10) == -2               # limit below the accepted range
     assert call(_shape(), chunk=-1) == -2
     assert call(_shape(dtype=1)) == -6                   # fp32 tensor kernels only
     assert call(_shape(L=3, R=32)) == -6                 # S = 96: not a tensor-kernel shape
     assert call(_shape()) == -1                          # valid arguments, NULL tensors
+    assert call(_shape(), variant=3) == -1               # the single-pass form too
+    assert call(_shape(), variant=1) == -6               # not a tensor-kernel family
+
+
+def test_single_pass_variant_sizes():
+    L = _lib.lib()
+    sh = _shape(T=1 << 20)
+    three = L.race_b200_causal_workspace_bytes(ctypes.byref(sh), 1024, 2)
+    single = L.race_b200_causal_workspace_bytes(ctypes.byref(sh), 1024, 3)
+    tiles = 8 * 1024
+    assert three == tiles * 64 * 65 * 4
+    assert single >= 2 * three + tiles * 4 + 8           # totals + inclusive prefixes + flags + ticket
+    assert L.race_b200_is_supported(ctypes.byref(sh), 3) == 1
+    assert L.race_b200_is_supported(ctypes.byref(_shape(dtype=1)), 3) == 0      # fp32 only
+    assert L.race_b200_is_supported(ctypes.byref(_shape(L=8, R=64, dk=128)), 3) == 0
+    tile = ctypes.c_int(0)
+    assert L.race_b200_select_tile_tokens(ctypes.byref(sh), 3, ctypes.byref(tile)) == 0
+    assert tile.value == 1024                            # tiles in flight on all SMs stay inside the L2
+    # too small a workspace for the single-pass form is refused, not silently switched
+    rc = L.race_b200_causal_fwd(256, 256, 256, 256, None, None, 256, three, ctypes.byref(sh), 1024, 3, None, None)
+    assert rc == -4

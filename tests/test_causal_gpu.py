@@ -26,7 +26,7 @@ def _ops():
 
 def _variants(N, T, L, R, dk, dtype):
     rk = _ops()
-    return [v for v in ("simt", "tensor") if rk.is_supported(N, max(T, 1), L, R, dk, dtype, v)]
+    return [v for v in ("simt", "tensor", "tensor_single_pass") if rk.is_supported(N, max(T, 1), L, R, dk, dtype, v)]
 
 
 def _oracle(pQ, pK, V, **kw):
@@ -85,7 +85,7 @@ def test_forced_tile_lengths_agree(tile):
     pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=11)
     ref = _oracle(pQ, pK, V)
     for variant in _variants(N, T, L, R, dk, torch.float32):
-        chunk = 32 if variant == "simt" else rk.select_tile_tokens(1, 1, L, R, dk, variant=variant)
+        chunk = 32 if variant == "simt" else 64
         if tile % chunk:
             continue
         out = rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), variant=variant, tile_tokens=tile)
@@ -415,7 +415,8 @@ def test_global_form_parity_and_carry(N, T, L, R, dk, dtype, tol):
     pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=11 * N + T, dtype=dtype)
     ref, A_ref, B_ref = ro.causal_prefix_global(pQ.double(), pK.double(), V.double(), return_state=True)
     q, k, v = pQ.cuda(), pK.cuda(), V.cuda()
-    variants = ["simt"] + (["tensor"] if dtype == torch.float32 and "tensor" in _variants(N, T, L, R, dk, dtype) else [])
+    variants = ["simt"] + (["tensor", "tensor_single_pass"]
+                           if dtype == torch.float32 and "tensor" in _variants(N, T, L, R, dk, dtype) else [])
     for variant in variants:
         out, A, B = rk.race_causal_prefix(q, k, v, normalization="global", return_state=True, variant=variant)
         assert ro.rel_l2(out, ref) <= tol, variant
@@ -435,7 +436,7 @@ def test_global_form_zero_denominator_and_rejections():
     pQ, pK, V = ro.synthetic_probs(2, 64, 4, 16, 64, seed=3)
     pK[0, :10] = 0          # stream 0 has no key mass for its first ten tokens: those rows are 0
     ref = ro.causal_prefix_global(pQ.double(), pK.double(), V.double())
-    for variant in ("simt", "tensor", "auto"):
+    for variant in ("simt", "tensor", "tensor_single_pass", "auto"):
         out = rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="global", variant=variant)
         assert not out[0, :10].any() and torch.isfinite(out).all(), variant
         assert ro.rel_l2(out, ref) <= FP32_TOL, variant
@@ -589,15 +590,23 @@ def test_bounded_wait_runs_out_and_device_stays_usable():
     before.  No memory fault and no unbounded spin is involved."""
     rk = _ops()
     N, T, L, R, dk = 2, 32768, 4, 16, 64
-    assert rk.select_tile_tokens(N, T, L, R, dk, variant="tensor") >= 6 * 64      # chunks 0, 1 and 5 exist in a tile
     pQ, pK, V = (t.cuda() for t in ro.synthetic_probs(N, T, L, R, dk, seed=99))
-    before = rk.race_causal_prefix(pQ, pK, V, variant="tensor")
+    for variant in ("tensor", "tensor_single_pass"):
+        _bounded_wait_case(rk, pQ, pK, V, variant)
+
+
+def _bounded_wait_case(rk, pQ, pK, V, variant):
+    N, T, L, R = pK.shape
+    dk = V.shape[-1]
+    assert rk.select_tile_tokens(N, T, L, R, dk, variant=variant) >= 6 * 64      # chunks 0, 1 and 5 exist in a tile
+    before = rk.race_causal_prefix(pQ, pK, V, variant=variant)
     assert rk.ops.device_status() == 0
     for chunk in (0, 1, 5):
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
-        out, code = rk.ops.selftest_bounded_wait(pQ, pK, V, wait_cycles=2_000_000, withhold_chunk=chunk)
+        out, code = rk.ops.selftest_bounded_wait(pQ, pK, V, wait_cycles=2_000_000, withhold_chunk=chunk,
+                                                 variant=variant)
         t1.record()
         torch.cuda.synchronize()
         assert code != 0, "the withheld load went unnoticed"
@@ -606,10 +615,10 @@ def test_bounded_wait_runs_out_and_device_stays_usable():
         # tiles of the other stream never depended on the withheld chunk
         assert torch.equal(out[1], before[1])
         assert rk.ops.device_status() == 0                # the self-test used its own status word
-        again = rk.race_causal_prefix(pQ, pK, V, variant="tensor")
+        again = rk.race_causal_prefix(pQ, pK, V, variant=variant)
         assert torch.equal(again, before)
     # a chunk index beyond the tile: nothing is withheld, nothing runs out
-    out, code = rk.ops.selftest_bounded_wait(pQ, pK, V, wait_cycles=2_000_000, withhold_chunk=10_000)
+    out, code = rk.ops.selftest_bounded_wait(pQ, pK, V, wait_cycles=2_000_000, withhold_chunk=10_000, variant=variant)
     assert code == 0 and torch.equal(out, before)
 
 
@@ -654,3 +663,29 @@ def test_decode_stepper_matches_general_wrapper():
     assert torch.equal(s1, s2)
     with pytest.raises(RuntimeError):
         step(pQ[:, :2].contiguous(), pK[:, :2].contiguous(), V[:, :2].contiguous(), s1)
+
+
+@pytest.mark.parametrize("N,T", [(8, 20000), (3, 4097), (2, 1 << 16), (1, 100)])
+def test_single_pass_equals_three_launches_bitwise(N, T):
+    """The persistent single-pass kernel (tile tickets, decoupled look-back in tile order, tile re-read from L2)
+    and the three launches (totals, scan, outputs) run the same arithmetic in the same order: for equal tile
+    lengths outputs and final states are bit-identical, with and without a carried state; and the single-pass
+    form meets the oracle at its own automatic tile length."""
+    rk = _ops()
+    L, R, dk = 4, 16, 64
+    pQ, pK, V = (t.cuda() for t in ro.synthetic_probs(N, T, L, R, dk, seed=T))
+    carry = rk.pack_state(torch.rand(N, L, R, device="cuda") * 5, torch.randn(N, L, R, dk, device="cuda"))
+    for tile in (64, 512, 1024, 2048):
+        for cin in (None, carry):
+            a, Aa, Ba = rk.race_causal_prefix(pQ, pK, V, carry_in=cin, return_state=True, variant="tensor",
+                                              tile_tokens=tile)
+            b, Ab, Bb = rk.race_causal_prefix(pQ, pK, V, carry_in=cin, return_state=True,
+                                              variant="tensor_single_pass", tile_tokens=tile)
+            assert torch.equal(a, b), (tile, cin is None)
+            assert torch.equal(Aa, Ab) and torch.equal(Ba, Bb)
+    out = rk.race_causal_prefix(pQ, pK, V, variant="tensor_single_pass")
+    ref = _oracle(pQ.cpu(), pK.cpu(), V.cpu())
+    assert ro.rel_l2(out, ref) <= FP32_TOL
+    # run to run: the look-back may stop at different tiles, the sum is the same
+    again = rk.race_causal_prefix(pQ, pK, V, variant="tensor_single_pass")
+    assert torch.equal(out, again)

@@ -39,7 +39,7 @@ def test_static_scratch_matches_ordinary_entry_twice():
     torch.cuda.set_device(0)
     # second call: other sizes, fewer tiles, a carry-in and the final state
     cases = [(8, 20000, 4, 16, 64, False), (3, 4097, 4, 16, 64, True)]
-    for variant in ("simt", "tensor"):
+    for variant in ("simt", "tensor", "tensor_single_pass"):
         for N, T, L, R, dk, with_state in cases:
             if not rk.is_supported(N, T, L, R, dk, torch.float32, variant):
                 continue
