@@ -451,6 +451,18 @@ def extra_workloads(args):
         print(json.dumps({"workload": "causal_bwd", "dtype": "f32", "N": N, "T": T, "ms": round(ms, 3),
                           "Mtok_s": round(N * T / ms / 1e3, 1), "GB_s": round(bb / ms / 1e6, 1),
                           "frac_measured_peak": round(bb / ms / 1e6 / peak, 4)}), flush=True)
+        # the global-normalisation form on the tcgen05 kernels at the size the reference quotes its own tensor-core
+        # kernel on (bf16, d=64, N*T = 16.8 M token-streams: 14.7 ms on H100, benchmarks/h100_run.md:47)
+        for dt in (torch.float32, torch.bfloat16):
+            N2, T2 = 8, 1 << 21
+            q2, k2 = probs(N2, T2, L, R, dt, g), probs(N2, T2, L, R, dt, g)
+            v2 = torch.randn(N2, T2, dk, device=dev, generator=g).to(dt)
+            o2 = torch.empty_like(v2)
+            for norm in ("bucket", "global"):
+                ms2 = _time_ms(lambda: rk.race_causal_prefix(q2, k2, v2, variant="tensor", normalization=norm, out=o2), 3, 10)
+                print(json.dumps({"workload": "causal_fwd_tcgen05", "normalization": norm, "dtype": str(dt), "N": N2,
+                                  "T": T2, "ms": round(ms2, 3), "Mtok_s": round(N2 * T2 / ms2 / 1e3, 1)}), flush=True)
+            del q2, k2, v2, o2
         for norm in ("bucket", "global"):
             ms = _time_ms(lambda: rk.race_causal_prefix(pQ, pK, V, variant="simt", normalization=norm), 3, 10)
             print(json.dumps({"workload": "causal_fwd_cuda_cores", "normalization": norm, "N": N, "T": T,

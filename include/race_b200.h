@@ -143,9 +143,10 @@ int race_b200_causal_fwd_resume(const void* probs_q, const void* probs_k, const 
  * with the prefixes A_t, B_t of race_b200_causal_fwd; one denominator per token, shape.eps is not
  * used, and a row whose denominator is exactly 0 is written as 0 (:77-81).  carry_in / state_out /
  * workspace / variant / status as in race_b200_causal_fwd (size the workspace with the same variant).
- * RACE_VARIANT_TENSOR computes this form for fp32, S = 64, d_k = 64 (tcgen05 kernels, heads allowed);
+ * RACE_VARIANT_TENSOR (and _SINGLE_PASS) computes this form for fp32, S = 64, d_k = 64 (heads allowed) and for
+ * bf16 with S = 64, d_k = 64 or 128 (the geometry of the reference's own tensor-core kernel);
  * RACE_VARIANT_SIMT for every shape the CUDA-core kernels take (heads <= 1); AUTO picks the tensor
- * kernels where they have it.  The bf16 tensor kernels do not have this form (RACE_ERR_VARIANT).
+ * kernels where they have it.  The wider bf16 tensor kernel (S > 64) does not have it (RACE_ERR_VARIANT).
  * Replaces race_causal_forward (src/causal_v2/kernels/race_causal_fwd.h:126-130) at the
  * probabilities boundary for callers that want the reference kernels' estimator.
  */

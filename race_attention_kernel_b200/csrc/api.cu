@@ -146,7 +146,9 @@ static int causal_entry(const void* probs_q, const void* probs_k, const void* v,
     if (var != RACE_VARIANT_SIMT && var != RACE_VARIANT_TENSOR && !is_single_pass(var)) return RACE_ERR_VARIANT;
     if (!variant_supported(dm, shape->dtype, var)) return var == variant ? RACE_ERR_VARIANT : RACE_ERR_SHAPE;
     // the global-normalisation form runs on the CUDA-core kernels and on the fp32 tensor kernels
-    if (global_norm && family(var) == RACE_VARIANT_TENSOR && shape->dtype != RACE_DTYPE_F32) return RACE_ERR_VARIANT;
+    // the global-normalisation form: CUDA-core kernels, fp32 tensor kernels, bf16 tensor kernels with one bucket group
+    if (global_norm && family(var) == RACE_VARIANT_TENSOR && shape->dtype != RACE_DTYPE_F32 && dm.S != 64)
+        return RACE_ERR_VARIANT;
     if (tile_tokens < 0) return RACE_ERR_TILE;
     const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, var);
     if (tile % chunk_of(var) != 0) return RACE_ERR_TILE;
@@ -208,8 +210,10 @@ int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const 
                                 const float* carry_in, float* state_out, void* workspace,
                                 size_t workspace_bytes, const RaceShape* shape, int tile_tokens, int variant,
                                 void* stream, int* status) {
-    // AUTO: the tensor kernels where they have this form (fp32, S = 64, d_k = 64), else the CUDA cores
-    if (variant == RACE_VARIANT_AUTO && shape && shape->dtype != RACE_DTYPE_F32) variant = RACE_VARIANT_SIMT;
+    // AUTO: the tensor kernels where they have this form (fp32 S = 64, d_k = 64; bf16 S = 64), else the CUDA cores
+    if (variant == RACE_VARIANT_AUTO && shape && shape->dtype != RACE_DTYPE_F32 &&
+        shape->n_tables * shape->n_buckets != 64)
+        variant = RACE_VARIANT_SIMT;
     return causal_entry(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes, shape,
                         tile_tokens, variant, stream, status, kPhaseAll, /*global_norm=*/true);
 }

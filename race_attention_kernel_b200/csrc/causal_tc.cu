@@ -1220,11 +1220,9 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
                               const float* carry_in, float* state_out, void* ws, bool single_pass, const Dims& dm,
                               int dtype, int tile_tokens, cudaStream_t stream, int* status, int phases,
                               bool global_norm, long long wait_cycles, int withhold_chunk) {
-    if (dtype == RACE_DTYPE_BF16) {
-        if (global_norm) return cudaErrorInvalidValue;
+    if (dtype == RACE_DTYPE_BF16)
         return causal_fwd_tensor_bf16(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream,
-                                      status, phases);
-    }
+                                      status, phases, global_norm);
     // Runtime calls first: they bind the device's primary context to the calling host thread,
     // which the driver-level tensor-map encoder needs (a thread that has made no runtime call
     // yet, e.g. an autograd worker, has no current context).

@@ -95,7 +95,10 @@ __device__ __forceinline__ void copy_tile(const uint8_t* stage, uint8_t* dst, in
 // ------------------------------------------------------------------------------------------------
 // output pass
 // ------------------------------------------------------------------------------------------------
-template <int D>
+// kGlobal: the global-normalisation estimator (src/causal_v2/reference.py:106-127): W = pQ as given (bf16 inputs
+// need no rounding then, so numerator and normaliser see the same values) and each output row divided by
+// den_t = pQ_t . A_t (a zero denominator gives a row of zeros).
+template <int D, bool kGlobal>
 __global__ void __launch_bounds__(kThreads, 1)
 causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -183,6 +186,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
         const __nv_bfloat16* pq_n = pq + n * T * S + g * SG;
         float v[32];
         uint32_t ov[16];   // W / masked G pairs on their way to tensor memory (d_k = 64)
+        float den[2] = {1.f, 1.f};   // global form: denominators of rows rbase, rbase + 8 of the chunk
         uint32_t ph = 0;
         bool ok = true;
         for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
@@ -217,6 +221,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             tc_fence_after();
             tmem_ld64(lane_base + tmAG(wg), v);
             tc_fence_before();
+            if (kGlobal) den[0] = den[1] = 0.f;
 #pragma unroll
             for (int x = 0; x < 8; ++x) {
 #pragma unroll
@@ -225,7 +230,13 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                     const float2 pq2 = unpack_bf16(pqv[2 * x + h]);
                     const float a0 = acar[2 * x] + v[4 * x + 2 * h];
                     const float a1 = acar[2 * x + 1] + v[4 * x + 2 * h + 1];
-                    const uint32_t wp = pack_bf16(__fdividef(pq2.x, a0 + eps), __fdividef(pq2.y, a1 + eps));
+                    uint32_t wp;
+                    if (kGlobal) {
+                        wp = pqv[2 * x + h];
+                        den[h] = fmaf(pq2.x, a0, fmaf(pq2.y, a1, den[h]));
+                    } else {
+                        wp = pack_bf16(__fdividef(pq2.x, a0 + eps), __fdividef(pq2.y, a1 + eps));
+                    }
                     if constexpr (kTA) ov[2 * x + h] = wp;
                     else *reinterpret_cast<uint32_t*>(wt + off_w<64>(row, 8 * x + 2 * q)) = wp;
                     if (h == 1 && w == 3 && (lane >> 2) == 7) {
@@ -245,6 +256,14 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             if (lane == 0) {
                 mbar_arrive(cx.bar(bWReady + wg));
                 if (w == 3) mbar_arrive(cx.bar(bAcar + (wg ^ 1)));
+            }
+            if (kGlobal) {
+                // a row's 64 buckets are spread over the four lanes of a quad
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    den[h] += __shfl_xor_sync(0xffffffffu, den[h], 1);
+                    den[h] += __shfl_xor_sync(0xffffffffu, den[h], 2);
+                }
             }
             // ---- causal mask of G (over W's tile) ----------------------------------------------
             if (!(ok = wait_bar_warp(cx, bGReady + wg, ph, 104))) break;
@@ -285,10 +304,11 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                     const int row = rbase + 8 * h;
                     if (row < valid) {
                         __nv_bfloat16* orow = out_n + (tok0 + row) * D + dh * 64 + 2 * q;
+                        const float sc = kGlobal ? (den[h] != 0.f ? 1.f / den[h] : 0.f) : 1.f;
 #pragma unroll
                         for (int x = 0; x < 8; ++x)
                             *reinterpret_cast<uint32_t*>(orow + 8 * x) =
-                                pack_bf16(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+                                pack_bf16(v[4 * x + 2 * h] * sc, v[4 * x + 2 * h + 1] * sc);
                     }
                 }
             }
@@ -1146,10 +1166,11 @@ bool make_map_bf16_slice(CUtensorMap* map, const void* base, int64_t N, int64_t 
 template <int D>
 cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out, const float* carry_in,
                         float* state_out, void* ws, const Dims& dm, int tile_tokens, cudaStream_t stream,
-                        int* status, int phases) {
+                        int* status, int phases, bool global_norm) {
     const int G = dm.S / SG;
+    if (global_norm && G > 1) return cudaErrorInvalidValue;   // the one-group kernel has the global form
     auto k1 = tile_totals_tc_bf16<D>;
-    auto k3 = causal_out_tc_bf16<D>;
+    auto k3 = global_norm ? causal_out_tc_bf16<D, true> : causal_out_tc_bf16<D, false>;
     // runtime call first: binds the primary context to this host thread for the map encoder
     cudaError_t err = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay1<D>::kSmem);
     if (err != cudaSuccess) return err;
@@ -1198,10 +1219,12 @@ bool tensor_bf16_supported(const Dims& dm) {
 
 cudaError_t causal_fwd_tensor_bf16(const void* pq, const void* pk, const void* v, void* out,
                                    const float* carry_in, float* state_out, void* ws, const Dims& dm,
-                                   int tile_tokens, cudaStream_t stream, int* status, int phases) {
+                                   int tile_tokens, cudaStream_t stream, int* status, int phases, bool global_norm) {
     if (dm.D == 64)
-        return launch_bf16<64>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream, status, phases);
-    return launch_bf16<128>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream, status, phases);
+        return launch_bf16<64>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream, status, phases,
+                               global_norm);
+    return launch_bf16<128>(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream, status, phases,
+                            global_norm);
 }
 
 #ifdef RACE_TC_TRACE

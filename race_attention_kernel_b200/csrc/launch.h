@@ -84,6 +84,7 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
 bool tensor_bf16_supported(const Dims& dm);
 cudaError_t causal_fwd_tensor_bf16(const void* pq, const void* pk, const void* v, void* out,
                                    const float* carry_in, float* state_out, void* ws, const Dims& dm,
-                                   int tile_tokens, cudaStream_t stream, int* status, int phases);
+                                   int tile_tokens, cudaStream_t stream, int* status, int phases,
+                                   bool global_norm = false);
 
 }  // namespace race

@@ -159,8 +159,8 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
 
     normalization="global" computes the global-normalisation estimator instead (one denominator per
     token, no eps: out_t = (pQ_t . B_t) / (pQ_t . A_t), src/causal_v2/reference.py:106-127): on the
-    tcgen05 kernels for fp32, S = 64, d_k = 64, else on the CUDA-core kernels; states and carries are the
-    same quantities in both forms.
+    tcgen05 kernels for fp32 S = 64, d_k = 64 and for bf16 S = 64, else on the CUDA-core kernels; states and
+    carries are the same quantities in both forms.
     """
     N, T, L, R, dk = _check_inputs(probsQ, probsK, V)
     if variant not in _lib.VARIANTS:
@@ -174,8 +174,8 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
     if glob:
         if totals_workspace is not None or V.dim() != 3:
             raise RuntimeError("normalization='global' takes V [N,T,d_k] and no totals_workspace")
-        if V.dtype != torch.float32 and variant == "auto":
-            var = _lib.VARIANTS["simt"]     # the bf16 tensor kernels do not have this form
+        if V.dtype != torch.float32 and variant == "auto" and L * R != 64:
+            var = _lib.VARIANTS["simt"]     # the wide bf16 tensor kernel does not have this form
     carry = None
     if carry_in is not None:
         carry = pack_state(*carry_in) if isinstance(carry_in, (tuple, list)) else carry_in

@@ -127,7 +127,8 @@ def test_global_form_argument_errors_without_launch():
     assert call(_shape(heads=8)) == -1                  # ... which AUTO picks: valid shape, NULL pointers
     assert call(_shape(dk=96 * 4), 1) == -6             # outside the CUDA-core kernels' range
     assert call(_shape(dk=96 * 4)) == -2                # no kernel family takes it
-    assert call(_shape(dtype=1), 2) == -6               # the bf16 tensor kernels do not have this form
+    assert call(_shape(dtype=1, L=8, R=64, dk=128), 2) == -6   # the wide bf16 tensor kernel does not have this form
+    assert call(_shape(dtype=1), 2) == -1               # bf16, S = 64: valid, NULL pointers
     assert call(_shape()) == -1                         # valid shape, NULL pointers
     assert call(_shape(T=0)) == 0                       # nothing to launch
 

@@ -408,6 +408,7 @@ def test_global_form_matches_reference_vectors(golden_global, name):
     (1, 100, 2, 64, 64, torch.float32, FP32_TOL),
     (3, 150, 2, 8, 32, torch.float32, FP32_TOL),
     (2, 1000, 4, 16, 64, torch.bfloat16, BF16_TOL),
+    (2, 700, 4, 16, 128, torch.bfloat16, BF16_TOL),
     (2, 300, 8, 64, 128, torch.bfloat16, BF16_TOL),
 ])
 def test_global_form_parity_and_carry(N, T, L, R, dk, dtype, tol):
@@ -417,6 +418,8 @@ def test_global_form_parity_and_carry(N, T, L, R, dk, dtype, tol):
     q, k, v = pQ.cuda(), pK.cuda(), V.cuda()
     variants = ["simt"] + (["tensor", "tensor_single_pass"]
                            if dtype == torch.float32 and "tensor" in _variants(N, T, L, R, dk, dtype) else [])
+    if dtype == torch.bfloat16 and L * R == 64:
+        variants.append("tensor")        # the one-group bf16 tensor kernel has this form too
     for variant in variants:
         out, A, B = rk.race_causal_prefix(q, k, v, normalization="global", return_state=True, variant=variant)
         assert ro.rel_l2(out, ref) <= tol, variant
@@ -440,9 +443,9 @@ def test_global_form_zero_denominator_and_rejections():
         out = rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="global", variant=variant)
         assert not out[0, :10].any() and torch.isfinite(out).all(), variant
         assert ro.rel_l2(out, ref) <= FP32_TOL, variant
-    with pytest.raises(RuntimeError):     # the bf16 tensor kernels do not have this form
-        rk.race_causal_prefix(pQ.bfloat16().cuda(), pK.bfloat16().cuda(), V.bfloat16().cuda(),
-                              normalization="global", variant="tensor")
+    pQw, pKw, Vw = (t.bfloat16().cuda() for t in ro.synthetic_probs(2, 64, 8, 64, 128, seed=4))
+    with pytest.raises(RuntimeError):     # the wide bf16 tensor kernel does not have this form
+        rk.race_causal_prefix(pQw, pKw, Vw, normalization="global", variant="tensor")
     with pytest.raises(RuntimeError):
         rk.race_causal_prefix(pQ.cuda(), pK.cuda(), V.cuda(), normalization="paper")
 
