@@ -30,12 +30,6 @@
 #include "launch.h"
 #include "tc_common.cuh"
 
-#ifndef RACE_FUSED_PREFETCH
-#define RACE_FUSED_PREFETCH 0
-#endif
-#ifndef RACE_FUSED_STAGGER_PER_CHUNK
-#define RACE_FUSED_STAGGER_PER_CHUNK 0
-#endif
 
 namespace race {
 namespace {
@@ -168,16 +162,12 @@ __device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again) {
 // withhold (self-test of the bounded waits): the TMA producer skips the load of chunk withhold_chunk.
 // l2_last_use: this is the second read of the tile's pK and V (single-pass kernel), so their lines are loaded
 // with the evict-first priority and leave the L2 to the tiles still waiting for their second read.
-// pf_chunks > 0: while it walks this tile the producer also prefetches, chunk by chunk and with the evict-last
-// priority, pK and V of the tile this CTA works on next (stream pf_n, first token pf_begin) into the L2: what a
-// CTA keeps in the L2 stays one tile's worth (the rest of this tile plus the start of the next).
 template <bool kGlobal>
 __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, const float* __restrict__ pq,
                                           const CUtensorMap* map_k, const CUtensorMap* map_v,
                                           float* __restrict__ out, const float* __restrict__ slice, int64_t T,
                                           const int64_t t_begin, const int64_t t_end, const int64_t n, float eps,
-                                          int heads, int withhold_chunk, const bool l2_last_use = false,
-                                          const int64_t pf_begin = 0, const int64_t pf_n = 0, const int pf_chunks = 0) {
+                                          int heads, int withhold_chunk, const bool l2_last_use = false) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nch = (int)((t_end - t_begin + C - 1) / C);
     const uint32_t tmB = tmem;                               // B accumulator, columns [0, 64)
@@ -439,7 +429,6 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
         if (lane == 0) {
             int issued = 0;
             const uint64_t pol = l2_policy_evict_first();
-            const uint64_t pol_keep = l2_policy_evict_last();
             for (int c = 0; c < nch; ++c) {
                 const int st = c & 1;
                 if (c >= 2 && !wait_bar(cx, kEmpty + st, ((c >> 1) - 1) & 1, 301)) break;
@@ -456,12 +445,6 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
                     tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
                 }
                 issued = c + 1;
-                for (int pc = c; RACE_FUSED_PREFETCH && pc < pf_chunks && (pc == c || c == nch - 1); ++pc) {
-                    // the same chunk of the next tile (all that is left of it, from this tile's last chunk)
-                    const int ptok = (int)(pf_begin + (int64_t)pc * C);
-                    tma_prefetch_4d_hint(map_k, 0, ptok, 0, (int)pf_n, pol_keep);
-                    tma_prefetch_5d_hint(map_v, 0, ptok, 0, (int)(pf_n % heads), (int)(pf_n / heads), pol_keep);
-                }
             }
             if (*cx.abort_flag) {
                 // copies still in flight must land before the CTA may exit
@@ -911,7 +894,6 @@ struct FusedArgs {
     int* status;
     long long wait_cycles;
     int withhold_chunk;
-    long long stagger_cycles;     // start of the last CTA's first tile relative to the first CTA's
 };
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
@@ -954,16 +936,9 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (a.stagger_cycles > 0 && tid == 0) {
-        // spread the CTAs' first tiles over one tile time, so that consecutive tiles of a stream
-        // reach their look-back one after the other instead of all at once
-        const long long delay = a.stagger_cycles * (long long)blockIdx.x / (long long)gridDim.x;
-        const long long t0 = clock64();
-        while (clock64() - t0 < delay) __nanosleep(256);
-    }
 
-    // tiles are drawn one ahead: the ticket of the next tile is taken before the output phase of the current
-    // one, which prefetches the next tile's pK and V into the L2 as it goes
+    // tiles are drawn one ahead (the ticket of the next tile is taken before the output phase of the current one),
+    // which keeps the round trip of the atomic out of the path between two tiles
     if (tid == 0) *ticket_slot = atomicAdd(a.ticket, 1ull);
     __syncthreads();
     unsigned long long t_next = *ticket_slot;
@@ -1067,13 +1042,6 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         __syncthreads();
         if (tid == 0) st_release_gpu(flags_n + tile, 2);
         t_next = *ticket_slot;
-        int64_t pf_n = 0, pf_begin = 0;
-        int pf_chunks = 0;
-        if (t_next < total) {
-            pf_n = (int64_t)(t_next % (unsigned long long)a.N);
-            pf_begin = (int64_t)(t_next / (unsigned long long)a.N) * a.tile_tokens;
-            pf_chunks = (int)((min(a.T, pf_begin + (int64_t)a.tile_tokens) - pf_begin + C - 1) / C);
-        }
         RACE_PROF_ADD(2, tp);
 #ifdef RACE_FUSED_PROF
         if (tid == 0) { g_fused_prof[blockIdx.x][4] += 1; g_fused_prof[blockIdx.x][5] += tile - 1 - *j_slot; }
@@ -1082,7 +1050,7 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         // ---- 3. outputs of the tile ---------------------------------------------------------------
         out_phase<kGlobal>(cxB, tmem, a.pq, &map_k, &map_v, a.out, a.cta_carry + (int64_t)blockIdx.x * kSF, a.T,
                            t_begin, t_end, n, a.eps, a.heads, (tile == 0 && n == 0) ? a.withhold_chunk : -1,
-                           /*l2_last_use=*/true, pf_begin, pf_n, pf_chunks);
+                           /*l2_last_use=*/true);
         first = false;
         fence_proxy_async();
         tc_fence_before();
@@ -1260,8 +1228,6 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
         fa.status = status;
         fa.wait_cycles = wait_cycles;
         fa.withhold_chunk = withhold_chunk;
-        // more tiles than CTAs: start the CTAs spread over one tile time (about 5k cycles per 64-token chunk)
-        fa.stagger_cycles = items > grid_f ? (long long)(tile_tokens / C) * RACE_FUSED_STAGGER_PER_CHUNK : 0;
         auto kern = global_norm ? causal_fused_tc<true> : causal_fused_tc<false>;
         err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBytes);
         if (err != cudaSuccess) return err;

@@ -31,20 +31,11 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-#ifdef RACE_WAIT_HINT_NS
-    // with a suspend-time hint the waiting thread may sleep in hardware up to that long instead of re-polling
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(bar), "r"(parity), "r"((uint32_t)RACE_WAIT_HINT_NS) : "memory");
-#else
     asm volatile(
         "{\n.reg .pred p;\n"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-#endif
     return ok != 0;
 }
 // true in exactly one lane of a converged warp
@@ -100,17 +91,6 @@ __device__ __forceinline__ void tma_load_5d_hint(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
         "[%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "l"(policy) : "memory");
-}
-// L2 prefetch of one box of a tiled tensor map with an eviction-priority hint (no shared-memory destination,
-// no barrier)
-__device__ __forceinline__ void tma_prefetch_4d_hint(const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t policy) {
-    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile.L2::cache_hint [%0, {%1, %2, %3, %4}], %5;"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_5d_hint(const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
-                                                     uint64_t policy) {
-    asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile.L2::cache_hint [%0, {%1, %2, %3, %4, %5}], %6;"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
                                          uint32_t idesc, uint32_t accumulate) {
