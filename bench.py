@@ -451,6 +451,18 @@ def extra_workloads(args):
         print(json.dumps({"workload": "causal_bwd", "dtype": "f32", "N": N, "T": T, "ms": round(ms, 3),
                           "Mtok_s": round(N * T / ms / 1e3, 1), "GB_s": round(bb / ms / 1e6, 1),
                           "frac_measured_peak": round(bb / ms / 1e6 / peak, 4)}), flush=True)
+        # the same at the headline length
+        Tb = 1 << 20
+        qb, kb = probs(N, Tb, L, R, torch.float32, g), probs(N, Tb, L, R, torch.float32, g)
+        vb = torch.randn(N, Tb, dk, device=dev, generator=g)
+        dob = torch.randn(N, Tb, dk, device=dev, generator=g)
+        ms = _time_ms(lambda: rk.race_causal_backward(qb, kb, vb, dob), 2, 5)
+        bb2 = N * Tb * 4 * (4 * 64 + 3 * 64)
+        print(json.dumps({"workload": "causal_bwd", "dtype": "f32", "N": N, "T": Tb, "ms": round(ms, 3),
+                          "Mtok_s": round(N * Tb / ms / 1e3, 1), "GB_s": round(bb2 / ms / 1e6, 1),
+                          "frac_measured_peak": round(bb2 / ms / 1e6 / peak, 4)}), flush=True)
+        del qb, kb, vb, dob
+        torch.cuda.empty_cache()
         # the global-normalisation form on the tcgen05 kernels at the size the reference quotes its own tensor-core
         # kernel on (bf16, d=64, N*T = 16.8 M token-streams: 14.7 ms on H100, benchmarks/h100_run.md:47)
         for dt in (torch.float32, torch.bfloat16):

@@ -231,7 +231,7 @@ int race_b200_selftest_bounded_wait(const void* probs_q, const void* probs_k, co
 size_t race_b200_causal_bwd_workspace_bytes(const RaceShape* shape) {
     Dims dm;
     if (check_shape(shape, &dm) != RACE_OK || !causal_bwd_supported(dm)) return 0;
-    return causal_bwd_workspace_bytes(dm, causal_bwd_tile_tokens(dm, sm_count()));
+    return causal_bwd_workspace_bytes(dm, shape->dtype, causal_bwd_tile_tokens(dm, shape->dtype, sm_count()));
 }
 
 int race_b200_causal_bwd(const void* probs_q, const void* probs_k, const void* v, const void* d_out,
@@ -261,8 +261,8 @@ int race_b200_causal_bwd_carry(const void* probs_q, const void* probs_k, const v
     if (!aligned16(probs_q) || !aligned16(probs_k) || !aligned16(v) || !aligned16(d_out) || !aligned16(d_probs_q) ||
         !aligned16(d_probs_k) || !aligned16(d_v) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return RACE_ERR_ALIGN;
-    const int tile = causal_bwd_tile_tokens(dm, sm_count());
-    if (workspace_bytes < causal_bwd_workspace_bytes(dm, tile)) return RACE_ERR_WORKSPACE;
+    const int tile = causal_bwd_tile_tokens(dm, shape->dtype, sm_count());
+    if (workspace_bytes < causal_bwd_workspace_bytes(dm, shape->dtype, tile)) return RACE_ERR_WORKSPACE;
     return (int)causal_bwd_simt(probs_q, probs_k, v, d_out, carry_in, d_state_out, d_probs_q, d_probs_k, d_v,
                                 d_carry_in, workspace, dm, shape->dtype, tile, (cudaStream_t)stream, status);
 }

@@ -597,11 +597,15 @@ bool causal_bwd_supported(const Dims& dm) {
     return simt_supported(dm) && dm.H == 1;   // S <= 64, or a multiple of 64 up to 512 (one cluster); d_k <= 128
 }
 
-int causal_bwd_tile_tokens(const Dims& dm, int sm_count) { return simt_default_tile_tokens(dm, sm_count); }
+int causal_bwd_tile_tokens(const Dims& dm, int dtype, int sm_count) {
+    if (causal_bwd_tensor_supported(dm, dtype)) return causal_bwd_tensor_tile_tokens(dm, sm_count);
+    return simt_default_tile_tokens(dm, sm_count);
+}
 
 // [prefix tile states | suffix tile states | W | g], each part 256-byte aligned
-size_t causal_bwd_workspace_bytes(const Dims& dm, int tile_tokens) {
+size_t causal_bwd_workspace_bytes(const Dims& dm, int dtype, int tile_tokens) {
     if (dm.N == 0 || dm.T == 0) return 0;
+    if (causal_bwd_tensor_supported(dm, dtype)) return causal_bwd_tensor_workspace_bytes(dm, tile_tokens);
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const size_t states = align256((size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float));
     const size_t tokens = align256((size_t)dm.N * dm.T * dm.S * sizeof(float));
@@ -611,6 +615,10 @@ size_t causal_bwd_workspace_bytes(const Dims& dm, int tile_tokens) {
 cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const void* dout, const float* carry_in,
                             const float* d_state, void* dpq, void* dpk, void* dv, float* d_carry, void* ws,
                             const Dims& dm, int dtype, int tile_tokens, cudaStream_t stream, int* status) {
+    // fp32, S = 64, d_k = 64: the backward as passes of the tcgen05 forward kernels
+    if (causal_bwd_tensor_supported(dm, dtype))
+        return causal_bwd_tensor(pq, pk, v, dout, carry_in, d_state, dpq, dpk, dv, d_carry, ws, dm, tile_tokens,
+                                 stream, status);
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const size_t states = align256((size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float));
     const size_t tokens = align256((size_t)dm.N * dm.T * dm.S * sizeof(float));

@@ -132,27 +132,29 @@ tile_totals_simt(const Tin* __restrict__ pk, const Tin* __restrict__ v, float* _
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
 tile_scan(float* __restrict__ ws, const float* __restrict__ carry_in, float* __restrict__ state_out,
-          int64_t tiles, int state_floats, int write_prefix) {
+          int64_t tiles, int state_floats, int write_prefix, int reverse) {
     constexpr int kInFlight = 32;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= state_floats) return;
     const int64_t n = blockIdx.y;
     float run = carry_in ? carry_in[n * state_floats + i] : 0.f;
     float* p = ws + n * tiles * state_floats + i;
+    // reverse: exclusive SUFFIX sums -- slot t gets carry + the totals of the tiles after t (last tile first)
+    auto at = [&](int64_t t) { return (reverse ? tiles - 1 - t : t) * state_floats; };
     int64_t t = 0;
     for (; t + kInFlight <= tiles; t += kInFlight) {
         float x[kInFlight];
 #pragma unroll
-        for (int j = 0; j < kInFlight; ++j) x[j] = p[(t + j) * state_floats];
+        for (int j = 0; j < kInFlight; ++j) x[j] = p[at(t + j)];
 #pragma unroll
         for (int j = 0; j < kInFlight; ++j) {
-            if (write_prefix) p[(t + j) * state_floats] = run;
+            if (write_prefix) p[at(t + j)] = run;
             run += x[j];
         }
     }
     for (; t < tiles; ++t) {
-        const float x = p[t * state_floats];
-        if (write_prefix) p[t * state_floats] = run;
+        const float x = p[at(t)];
+        if (write_prefix) p[at(t)] = run;
         run += x;
     }
     if (state_out) state_out[n * state_floats + i] = run;
@@ -415,7 +417,7 @@ cudaError_t launch_simt(const Tin* pq, const Tin* pk, const Tin* v, Tin* out, co
     }
 
     dim3 sgrid((unsigned)((sf + 127) / 128), (unsigned)dm.N);
-    tile_scan<<<sgrid, 128, 0, stream>>>(ws, carry_in, state_out, tiles, sf, totals_only ? 0 : 1);
+    tile_scan<<<sgrid, 128, 0, stream>>>(ws, carry_in, state_out, tiles, sf, totals_only ? 0 : 1, 0);
     err = cudaGetLastError();
     if (err != cudaSuccess || totals_only || skip_output) return err;
 
@@ -461,13 +463,13 @@ cudaError_t dispatch_simt(const void* pq, const void* pk, const void* v, void* o
 }  // namespace
 
 cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out, const Dims& dm,
-                              int tile_tokens, cudaStream_t stream, bool write_prefix) {
+                              int tile_tokens, cudaStream_t stream, bool write_prefix, bool reverse) {
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const int sf = state_floats_per_stream(dm.S, dm.D);
     if (tiles == 1 && !carry_in && !write_prefix && state_out)   // one tile per stream: its totals are the state
         return cudaMemcpyAsync(state_out, ws, (size_t)dm.N * sf * sizeof(float), cudaMemcpyDeviceToDevice, stream);
     dim3 sgrid((unsigned)((sf + 127) / 128), (unsigned)dm.N);
-    tile_scan<<<sgrid, 128, 0, stream>>>(ws, carry_in, state_out, tiles, sf, write_prefix ? 1 : 0);
+    tile_scan<<<sgrid, 128, 0, stream>>>(ws, carry_in, state_out, tiles, sf, write_prefix ? 1 : 0, reverse ? 1 : 0);
     return cudaGetLastError();
 }
 

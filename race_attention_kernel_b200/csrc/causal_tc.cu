@@ -157,19 +157,27 @@ __device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again) {
 // Output phase of one (stream n, tokens [t_begin, t_end)) tile whose carry (state before its first
 // token, state layout) is at `slice`.  Called by all 15 warps with barriers initialised and 512 TMEM
 // columns at `tmem`; ends with every issued product retired, before the caller's __syncthreads.
-// kGlobal selects the global-normalisation estimator (src/causal_v2/reference.py:106-127): W = pQ
-// without the per-bucket divide and every output row divided by den_t = pQ_t . A_t (0 -> a row of 0).
+// kMode: kModeBucket is the per-bucket estimator; kModeGlobal the global-normalisation estimator
+// (src/causal_v2/reference.py:106-127): W = pQ without the per-bucket divide and every output row divided by
+// den_t = pQ_t . A_t (0 -> a row of 0); kModeRaw the plain causal product O = pQ . B + tril(pQ pK^T) . V without any
+// normalisation (the building block of the backward passes, where pQ / pK / V stand for other tensors).
+// kReverse walks the tile from its last chunk to its first with an upper-triangular mask: out_t sums over
+// j >= t, and the carry is the state of everything AFTER the tile (the suffix sums of the backward).
 // withhold (self-test of the bounded waits): the TMA producer skips the load of chunk withhold_chunk.
 // l2_last_use: this is the second read of the tile's pK and V (single-pass kernel), so their lines are loaded
 // with the evict-first priority and leave the L2 to the tiles still waiting for their second read.
-template <bool kGlobal>
+constexpr int kModeBucket = 0, kModeGlobal = 1, kModeRaw = 2;
+template <int kMode, bool kReverse = false>
 __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, const float* __restrict__ pq,
                                           const CUtensorMap* map_k, const CUtensorMap* map_v,
                                           float* __restrict__ out, const float* __restrict__ slice, int64_t T,
                                           const int64_t t_begin, const int64_t t_end, const int64_t n, float eps,
                                           int heads, int withhold_chunk, const bool l2_last_use = false) {
+    constexpr bool kGlobal = kMode == kModeGlobal;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nch = (int)((t_end - t_begin + C - 1) / C);
+    // first token of the chunk that is processed c-th
+    auto chunk_tok0 = [&](int c) { return t_begin + (int64_t)(kReverse ? nch - 1 - c : c) * C; };
     const uint32_t tmB = tmem;                               // B accumulator, columns [0, 64)
     auto tmAG = [&](int wg) { return tmem + 64 + wg * 128; };      // A_loc, then G
     auto tmO = [&](int wg) { return tmem + 64 + wg * 128 + 64; };  // O
@@ -193,7 +201,7 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
         // O of chunk c: TMEM -> global (fragment rows rbase, rbase + 8; 8-byte stores, full sectors)
         float den[2] = {1.f, 1.f};   // global form: denominators of rows rbase, rbase + 8 of the chunk
         auto store_out = [&](int c) {
-            const int64_t tok0 = t_begin + (int64_t)c * C;
+            const int64_t tok0 = chunk_tok0(c);
             const int valid = (int)min((int64_t)C, t_end - tok0);
             tc_fence_after();
             tmem_ld64(lane_base + tmO(wg), v);
@@ -217,7 +225,7 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
         uint32_t ph = 0;   // parity of this group's per-chunk barriers (one use per chunk)
         bool ok = true;
         for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
-            const int64_t tok0 = t_begin + (int64_t)c * C;
+            const int64_t tok0 = chunk_tok0(c);
             const int valid = (int)min((int64_t)C, t_end - tok0);
             // pQ of this chunk in the accumulator-fragment layout, straight from global memory,
             // issued first so that the wait for the running-sum product hides the latency
@@ -234,8 +242,10 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             RACE_TRACE(wg, c, 0);
 
             // -- S2: W = pQ / (A + A_loc + eps) ----------------------------------------------------
-            if (!(ok = wait_bar_warp(cx, kAcar + wg, ph, 102))) break;
+            // (the plain product needs no running sum: W = pQ goes to the tensor cores as it is)
             float acar[16];
+            if (kMode != kModeRaw) {
+            if (!(ok = wait_bar_warp(cx, kAcar + wg, ph, 102))) break;
             {
                 const float* ac = reinterpret_cast<const float*>(cx.sm + oAcar) + wg * 64;
 #pragma unroll
@@ -254,15 +264,21 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             tc_fence_after();
             tmem_ld64(lane_base + tmAG(wg), v);
             tc_fence_before();
+            }
             if (kGlobal) den[0] = den[1] = 0.f;
 #pragma unroll
             for (int x = 0; x < 8; ++x) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
+                    float2 w2;
+                    if (kMode == kModeRaw) {
+                        w2 = pqv[2 * x + h];
+                        split2(w2.x, w2.y, ohi[2 * x + h], olo[2 * x + h]);
+                        continue;
+                    }
                     // packed fp32x2 arithmetic: (a0, a1) = running A + A_loc; W = pQ / (a + eps)
                     const float2 a2 = __fadd2_rn(make_float2(acar[2 * x], acar[2 * x + 1]),
                                                  make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]));
-                    float2 w2;
                     if (kGlobal) {
                         w2 = pqv[2 * x + h];
                         den[h] = fmaf(w2.x, a2.x, fmaf(w2.y, a2.y, den[h]));
@@ -285,7 +301,7 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(cx.bar(kWReady + wg));
-                if (w == 3) mbar_arrive(cx.bar(kAcar + (wg ^ 1)));
+                if (kMode != kModeRaw && w == 3) mbar_arrive(cx.bar(kAcar + (wg ^ 1)));
             }
             if (kGlobal) {
                 // a row's 64 buckets are spread over the four lanes of a quad, in a fixed order
@@ -308,8 +324,8 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int row = rbase + 8 * h, col = 8 * x + 2 * q;
-                    const float g0 = col <= row ? v[4 * x + 2 * h] : 0.f;
-                    const float g1 = col + 1 <= row ? v[4 * x + 2 * h + 1] : 0.f;
+                    const float g0 = (kReverse ? col >= row : col <= row) ? v[4 * x + 2 * h] : 0.f;
+                    const float g1 = (kReverse ? col + 1 >= row : col + 1 <= row) ? v[4 * x + 2 * h + 1] : 0.f;
                     split2(g0, g1, ohi[2 * x + h], olo[2 * x + h]);
                 }
             }
@@ -435,7 +451,7 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
                 if (c == withhold_chunk) continue;   // self-test only
                 const uint32_t dst = cx.sm_u32 + oStage + st * kStageBytes;
                 const uint32_t bar = cx.bar(kFull + st);
-                const int tok = (int)(t_begin + (int64_t)c * C);
+                const int tok = (int)chunk_tok0(c);
                 mbar_arrive_expect_tx(bar, kStageBytes);
                 if (l2_last_use) {
                     tma_load_4d_hint(dst, map_k, bar, 0, tok, 0, (int)n, pol);
@@ -480,9 +496,11 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
                 if (!(ok = wait_bar(cx, kKvReady + wg, ph, 401))) break;
                 tc_fence_after();
                 RACE_TRACE(4, c, 0);
-                mma_k64_ta<true, kHiMN, 128>(dAG, a_tril, kt_mn, kIdescBase | kBmn);
-                mma_k64_ta<false, kHiMN, 128>(dAG, a_tril, kt_mn + kLimb, kIdescBase | kBmn);
-                mma_commit(cx.bar(kXReady + wg));
+                if (kMode != kModeRaw) {
+                    mma_k64_ta<true, kHiMN, 128>(dAG, a_tril, kt_mn, kIdescBase | kBmn);
+                    mma_k64_ta<false, kHiMN, 128>(dAG, a_tril, kt_mn + kLimb, kIdescBase | kBmn);
+                    mma_commit(cx.bar(kXReady + wg));
+                }
                 RACE_TRACE(4, c, 1);
                 // B += pK^T . V, in chunk order: the accumulator is free once the state after
                 // chunk c - 1 has been read out
@@ -538,7 +556,7 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t tmem, uint32_t cols) {
 // The output pass as a kernel of its own (second half of a forward whose per-tile prefixes are
 // already in the workspace): one CTA per (tile, stream).  wait_cycles > 0 replaces the default limit
 // of every wait; withhold_chunk >= 0 makes the producer of CTA (0, 0) skip that chunk's load.
-template <bool kGlobal>
+template <int kMode, bool kReverse>
 __global__ void __launch_bounds__(kThreads, 1)
 causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, float* __restrict__ out,
@@ -568,7 +586,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    out_phase<kGlobal>(cx, tmem, pq, &map_k, &map_v, out, slice, T, t_begin, t_end, n, eps, heads,
+    out_phase<kMode, kReverse>(cx, tmem, pq, &map_k, &map_v, out, slice, T, t_begin, t_end, n, eps, heads,
                        (tile == 0 && n == 0) ? withhold_chunk : -1);
     tc_fence_before();
     __syncthreads();
@@ -1048,7 +1066,7 @@ causal_fused_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
 #endif
 
         // ---- 3. outputs of the tile ---------------------------------------------------------------
-        out_phase<kGlobal>(cxB, tmem, a.pq, &map_k, &map_v, a.out, a.cta_carry + (int64_t)blockIdx.x * kSF, a.T,
+        out_phase<kGlobal ? kModeGlobal : kModeBucket>(cxB, tmem, a.pq, &map_k, &map_v, a.out, a.cta_carry + (int64_t)blockIdx.x * kSF, a.T,
                            t_begin, t_end, n, a.eps, a.heads, (tile == 0 && n == 0) ? a.withhold_chunk : -1,
                            /*l2_last_use=*/true);
         first = false;
@@ -1184,6 +1202,11 @@ size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
     return (size_t)dm.N * tiles * state_floats_per_stream(dm.S, dm.D) * sizeof(float);
 }
 
+static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void* v, void* out,
+                                     const float* carry_in, float* state_out, void* ws, bool single_pass,
+                                     const Dims& dm, int tile_tokens, cudaStream_t stream, int* status, int phases,
+                                     int mode, bool reverse, long long wait_cycles, int withhold_chunk);
+
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
                               const float* carry_in, float* state_out, void* ws, bool single_pass, const Dims& dm,
                               int dtype, int tile_tokens, cudaStream_t stream, int* status, int phases,
@@ -1191,6 +1214,25 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
     if (dtype == RACE_DTYPE_BF16)
         return causal_fwd_tensor_bf16(pq, pk, v, out, carry_in, state_out, ws, dm, tile_tokens, stream,
                                       status, phases, global_norm);
+    return tensor_f32_launch(pq, pk, v, out, carry_in, state_out, ws, single_pass, dm, tile_tokens, stream, status,
+                             phases, global_norm ? kModeGlobal : kModeBucket, false, wait_cycles, withhold_chunk);
+}
+
+// The plain causal (or, with reverse, anti-causal) product out_t = sum_{j <= t} (q_t . k_j) v_j + q_t . carry over
+// fp32 [N, T, 64] tensors on the same three launches: what the backward passes are made of.  State layout as
+// everywhere: carry[s][c] = sum_j k_j[s] v_j[c] (the A part is carried along and ignored).
+cudaError_t causal_raw_tensor(const void* q, const void* k, const void* v, void* out, const float* carry_in,
+                              float* state_out, void* ws, const Dims& dm, int tile_tokens, bool reverse,
+                              cudaStream_t stream, int* status, int phases) {
+    return tensor_f32_launch(q, k, v, out, carry_in, state_out, ws, false, dm, tile_tokens, stream, status, phases,
+                             kModeRaw, reverse, 0, -1);
+}
+
+static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void* v, void* out,
+                                     const float* carry_in, float* state_out, void* ws, bool single_pass,
+                                     const Dims& dm, int tile_tokens, cudaStream_t stream, int* status, int phases,
+                                     int mode, bool reverse, long long wait_cycles, int withhold_chunk) {
+    const bool global_norm = mode == kModeGlobal;
     // Runtime calls first: they bind the device's primary context to the calling host thread,
     // which the driver-level tensor-map encoder needs (a thread that has made no runtime call
     // yet, e.g. an autograd worker, has no current context).
@@ -1247,9 +1289,10 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
         if (!state_out) return cudaSuccess;
         return causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, /*write_prefix=*/false);
     }
-    err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, /*write_prefix=*/true);
+    err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, /*write_prefix=*/true, reverse);
     if (err != cudaSuccess) return err;
-    auto kern = global_norm ? causal_out_tc<true> : causal_out_tc<false>;
+    auto kern = mode == kModeRaw ? (reverse ? causal_out_tc<kModeRaw, true> : causal_out_tc<kModeRaw, false>)
+                                 : (global_norm ? causal_out_tc<kModeGlobal, false> : causal_out_tc<kModeBucket, false>);
     err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return err;
     kern<<<grid, kThreads, kSmemBytes, stream>>>((const float*)pq, mk, mv, (float*)out, (const float*)ws, dm.T,

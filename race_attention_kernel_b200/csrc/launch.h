@@ -20,16 +20,17 @@ cudaError_t causal_fwd_simt(const void* pq, const void* pk, const void* v, void*
                             bool skip_output = false, bool skip_totals = false, bool global_norm = false);
 
 // in-place exclusive scan over the per-tile totals in ws (+ carry_in), inclusive total to state_out
+// (reverse: exclusive SUFFIX sums, last tile first -- the scans of the backward)
 cudaError_t causal_scan_tiles(float* ws, const float* carry_in, float* state_out, const Dims& dm,
-                              int tile_tokens, cudaStream_t stream, bool write_prefix = true);
+                              int tile_tokens, cudaStream_t stream, bool write_prefix = true, bool reverse = false);
 
 // which passes of a causal forward to run: totals (per-tile sums into ws) and/or scan + outputs
 constexpr int kPhaseTotals = 1, kPhaseOutput = 2, kPhaseAll = 3;
 
 // ---- causal backward (causal_bwd_simt.cu): S <= 64, d_k <= 128 ---------------------------------
 bool causal_bwd_supported(const Dims& dm);
-int causal_bwd_tile_tokens(const Dims& dm, int sm_count);
-size_t causal_bwd_workspace_bytes(const Dims& dm, int tile_tokens);
+int causal_bwd_tile_tokens(const Dims& dm, int dtype, int sm_count);
+size_t causal_bwd_workspace_bytes(const Dims& dm, int dtype, int tile_tokens);
 // carry_in: state before the first token (nullable); d_state: gradient reaching the state after the last token
 // (nullable); d_carry: receives the gradient of carry_in (nullable)
 cudaError_t causal_bwd_simt(const void* pq, const void* pk, const void* v, const void* dout, const float* carry_in,
@@ -79,6 +80,20 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
                               int dtype, int tile_tokens, cudaStream_t stream, int* status,
                               int phases = kPhaseAll, bool global_norm = false, long long wait_cycles = 0,
                               int withhold_chunk = -1);
+
+// out_t = sum_{j <= t} (q_t . k_j) v_j + q_t . carry (reverse: j >= t, carry = state of the tokens after the call)
+// on fp32 [N, T, 64] tensors with the three launches of the fp32 tensor forward, no normalisation
+cudaError_t causal_raw_tensor(const void* q, const void* k, const void* v, void* out, const float* carry_in,
+                              float* state_out, void* ws, const Dims& dm, int tile_tokens, bool reverse,
+                              cudaStream_t stream, int* status, int phases = kPhaseAll);
+
+// ---- causal backward on the tensor kernels (causal_bwd_tc.cu): fp32, S = 64, d_k = 64 ----------
+bool causal_bwd_tensor_supported(const Dims& dm, int dtype);
+int causal_bwd_tensor_tile_tokens(const Dims& dm, int sm_count);
+size_t causal_bwd_tensor_workspace_bytes(const Dims& dm, int tile_tokens);
+cudaError_t causal_bwd_tensor(const void* pq, const void* pk, const void* v, const void* dout, const float* carry_in,
+                              const float* d_state, void* dpq, void* dpk, void* dv, float* d_carry, void* ws,
+                              const Dims& dm, int tile_tokens, cudaStream_t stream, int* status);
 
 // bf16 tensor path (causal_tc_bf16.cu): S a multiple of 64 (1, 2, 4 or 8 bucket groups), d_k 64 or 128
 bool tensor_bf16_supported(const Dims& dm);
