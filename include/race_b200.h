@@ -162,8 +162,9 @@ int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const 
  * docs/causal_v2_design.md:689-741); this is the derivative of src/race_baseline.py:45-51:
  *   X_t[s] = B_t[s,:].dO_t, dPQ_t = X_t/(A_t+eps), g_t = -X_t*W_t/(A_t+eps), W_t = pQ_t/(A_t+eps),
  *   dPK_j[s] = sum_{t>=j} g_t[s] + (sum_{t>=j} W_t[s] dO_t).V_j,  dV_j = sum_s pK_j[s] sum_{t>=j} W_t[s] dO_t.
- * Recomputes the forward's prefix states (nothing has to be saved by the forward).  CUDA-core kernels;
- * L*R <= 64 or a multiple of 64 up to 512, d_k <= 128, heads <= 1.  workspace: 256-byte aligned, >= race_b200_causal_bwd_workspace_bytes()
+ * Recomputes the forward's prefix states (nothing has to be saved by the forward).  fp32 with L*R = 64, d_k = 64
+ * runs as three plain causal / anti-causal passes of the forward's tcgen05 kernels plus two streaming kernels;
+ * every other shape (L*R <= 64 or a multiple of 64 up to 512, d_k <= 128, bf16) on CUDA-core kernels; heads <= 1.  workspace: 256-byte aligned, >= race_b200_causal_bwd_workspace_bytes()
  * (two fp32 [N,T,L*R] scratch arrays plus tile states).  status: as in race_b200_causal_fwd (the prefix
  * states come from the forward's tile-totals kernel, whose waits are bounded).
  */
