@@ -53,8 +53,10 @@ class BatchedACE(nn.Module):
     def _probs_autograd(self, x2: torch.Tensor) -> torch.Tensor:
         """src/race_baseline.py:41-44 with torch ops (differentiable); x2 [N,T,d_k] on the GPU."""
         N, T, dk = x2.shape
-        proj = (x2.float() @ self.planes_T.float()).view(N, T, self.L, self.K)
-        logits = proj.tanh().div(dk ** 0.5) @ self.protos_T.float()
+        planes_T = self.planes_T.to(device=x2.device, dtype=torch.float32)
+        protos_T = self.protos_T.to(device=x2.device, dtype=torch.float32)
+        proj = (x2.float() @ planes_T).view(N, T, self.L, self.K)
+        logits = proj.tanh().div(dk ** 0.5) @ protos_T
         return torch.softmax(logits, dim=-1).to(x2.dtype)
 
     def _forward_autograd(self, Khf, Vhf, Qhf):
