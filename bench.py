@@ -76,7 +76,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -86,7 +86,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def mark(self):
+        """Host time stamp to bracket the timed region with (summary(t0, t1) keeps the samples in between)."""
+        return time.time()
 
     def __exit__(self, *a):
         if self.proc:
@@ -94,10 +98,19 @@ class ClockSampler:
             self.proc.terminate()
             self.thread.join(timeout=2)
 
-    def summary(self):
+    def _window(self, t0, t1):
+        # a sample describes the period before it arrives, so the window is widened by one period and a bit
+        return [r for ts, r in self.rows if t0 is None or t0 <= ts <= t1 + 0.03]
+
+    def count(self, t0, t1):
+        return len(self._window(t0, t1))
+
+    def summary(self, t0=None, t1=None):
+        """Median SM clock and the throttle reasons seen in the samples that arrived during [t0, t1]."""
+        rows = self._window(t0, t1)
         sm, mx, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in rows:
             try:
                 sm.append(float(r[0]))
                 mx = max(mx, float(r[1]))
@@ -591,19 +604,32 @@ def main():
         raise SystemExit(f"parity gate failed: rel-L2 head {err_head:.3e} tail {err_tail:.3e} "
                          f"state {err_state:.3e} > {tol}")
 
-    for _ in range(args.warmup):
-        step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clk:
+    with ClockSampler(local) as clk:      # sampling starts before the warm-up: nvidia-smi needs a moment to come up
+        for _ in range(args.warmup):
+            step()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t_wall0 = clk.mark()
         e0.record()
         for _ in range(args.steps):
             step()
         e1.record()
         torch.cuda.synchronize()
+        t_wall1 = clk.mark()
+        # the timed region lasts tens of milliseconds, a few sampling periods: where fewer than three samples fell
+        # inside it, the same steps go on (untimed) for a quarter of a second and their samples are counted too
+        t_wall2 = t_wall1
+        if clk.count(t_wall0, t_wall1) < 3:
+            while time.time() - t_wall1 < 0.25:
+                step()
+            torch.cuda.synchronize()
+            t_wall2 = clk.mark()
+    clocks = clk.summary(t_wall0, t_wall2)
+    clocks["window"] = ("timed region" if t_wall2 == t_wall1
+                        else "timed region and the same steps repeated for 0.25 s after it")
     ms = e0.elapsed_time(e1)
     code = rk.ops.device_status(dev)
     if code:
@@ -728,7 +754,7 @@ def main():
                            "parity_gate": "first 1024 tokens of stream 0; last 2048 tokens of the last stream vs the "
                                           "oracle with the fp64 carry; final state of every stream vs fp64 totals"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "c4": c4, "c3": c3, "single_pass": single,
-                "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}
+                "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
