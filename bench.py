@@ -494,21 +494,35 @@ def extra_workloads(args):
                               "ms": round(ms, 3), "Mtok_s": round(N * T / ms / 1e3, 1),
                               "frac_measured_peak": round(N * T * 1024 / ms / 1e6 / peak, 4)}), flush=True)
     elif args.workload == "operator":
-        # the drop-in operator end to end on the device: BatchedACE.forward(K, V, Q) = stream flattening +
-        # bucket-probability producer (probabilities written to HBM) + causal prefix kernels; fp32,
-        # M=1, B=1, H=8, d_k=64, K=4, L=4 (the reference CPU configuration at longer T)
+        # the drop-in operator end to end on the device: BatchedACE.forward(K, V, Q); fp32, M=1, B=1, H=8, d_k=64,
+        # K=4, L=4 (the reference CPU configuration at longer T).  "fused": the prefix kernels form the bucket
+        # probabilities themselves (Q, K, V in, out back: 4 d_k elt = 1024 B per token-stream, the same
+        # algorithmic bytes as the probabilities-level path); "two_step": producer kernel writes the
+        # probabilities to HBM, the prefix kernels read them back.  A parity gate against the oracle of the
+        # whole operator (first 512 tokens of stream 0) runs before the timing.
+        from oracle import race_oracle as ro
         M, B, H, dk, K, L = 1, 1, 8, 64, 4, 4
         for T in (4096, 131072, 1048576):
             torch.manual_seed(1234)
             ace = rk.BatchedACE(dk, K, L, M, device=dev)
             Kh, Vh, Qh = (torch.randn(M, B, T, H, dk, device=dev, generator=g) for _ in range(3))
-            with torch.no_grad():
-                ms = _time_ms(lambda: ace(Kh, Vh, Qh), 3, 10)
             n_tok = M * B * H * T
-            print(json.dumps({"workload": "operator", "M,B,H": [M, B, H], "T": T, "ms": round(ms, 4),
-                              "Mtok_s": round(n_tok / ms / 1e3, 1),
-                              "qkvo_GB_s": round(n_tok * 4 * dk * 4 / ms / 1e6, 1),
-                              "peak_GiB": round(torch.cuda.max_memory_allocated() / 2**30, 2)}), flush=True)
+            w = min(T, 512)
+            ref = ro.batched_ace_forward(ace.planes_T.cpu().double(), ace.protos_T.cpu().double(),
+                                         *(t[:, :, :w, :1].cpu().double() for t in (Kh, Vh, Qh)), L, K)
+            for mode in ("fused", "two_step"):
+                ace.fuse_producer = mode == "fused"
+                with torch.no_grad():
+                    err = ro.rel_l2(ace(Kh, Vh, Qh)[:, :, :w, :1], ref)
+                    if not err <= 1e-4:
+                        raise SystemExit(f"operator parity gate failed ({mode}): rel-L2 {err:.3e}")
+                    ms = _time_ms(lambda: ace(Kh, Vh, Qh), 3, 10)
+                print(json.dumps({"workload": "operator", "mode": mode, "M,B,H": [M, B, H], "T": T,
+                                  "ms": round(ms, 4), "Mtok_s": round(n_tok / ms / 1e3, 1),
+                                  "qkvo_GB_s": round(n_tok * 4 * dk * 4 / ms / 1e6, 1),
+                                  "frac_measured_peak": round(n_tok * 4 * dk * 4 / ms / 1e6 / peak, 4),
+                                  "parity_rel_l2": err,
+                                  "peak_GiB": round(torch.cuda.max_memory_allocated() / 2**30, 2)}), flush=True)
             del Kh, Vh, Qh
             torch.cuda.empty_cache()
 

@@ -156,6 +156,29 @@ int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const 
                                 void* stream, int* status);
 
 /*
+ * Causal forward from Q, K, V and the hyperplanes: the bucket probabilities of BatchedACE.forward
+ * (src/race_baseline.py:41-44: projections on the L*K planes, tanh / sqrt(d_k), softmax over the 2^K sign corners)
+ * are formed inside the prefix kernels, in registers and shared memory, bit-identical to what
+ * race_b200_bucket_probs_streams writes; neither probsQ nor probsK exists in device memory and the forward moves
+ * Q, K, V and out through HBM and nothing else.  The counterpart of the reference's race_causal_forward, which
+ * also takes q, k, v and planes (src/causal_v2/kernels/race_causal_fwd.h:126-130; its in-kernel feature phases:
+ * src/causal_v2/kernels/race_causal_fwd_tc.cu:562-642).
+ *   q, k, v, out  [N/H, T, H, d_k] with H = shape.heads (0 or 1: [N, T, d_k]), fp32
+ *   planes        [L*K, d_k] fp32, row p = l*K + k (the transpose of BatchedACE.planes_T)
+ *   n_planes      K; shape.n_buckets must be 2^K
+ *   global_norm   0: the per-bucket estimator of race_b200_causal_fwd; 1: that of race_b200_causal_fwd_global
+ * Supported (race_b200_qkv_is_supported): fp32, d_k = 64, L = 4, K = 4 -- the geometry of the tcgen05 fp32
+ * kernels; other shapes return RACE_ERR_VARIANT and go through race_b200_bucket_probs_streams +
+ * race_b200_causal_fwd.  carry_in / state_out / status as in race_b200_causal_fwd; workspace >=
+ * race_b200_causal_workspace_bytes(shape, tile_tokens, RACE_VARIANT_TENSOR).
+ */
+int race_b200_qkv_is_supported(const RaceShape* shape, int n_planes);
+int race_b200_causal_fwd_qkv(const void* q, const void* k, const void* v, const float* planes, void* out,
+                             const float* carry_in, float* state_out, void* workspace, size_t workspace_bytes,
+                             const RaceShape* shape, int n_planes, int tile_tokens, int global_norm, void* stream,
+                             int* status);
+
+/*
  * Backward of race_b200_causal_fwd (carry_in = none): gradients w.r.t. probsQ, probsK and V given
  * d_out [N,T,d_k]; d_probs_q / d_probs_k / d_v have the layouts and dtype of their primals.  The
  * reference has no causal backward (its design note only outlines one for the global form,

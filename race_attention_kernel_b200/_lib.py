@@ -27,6 +27,7 @@ EXPORTS = [
     "race_b200_static_scratch_bytes", "race_b200_causal_fwd_static", "race_b200_decode_step",
     "race_b200_causal_fwd_global", "race_b200_causal_bwd_workspace_bytes", "race_b200_causal_bwd",
     "race_b200_causal_bwd_carry", "race_b200_selftest_bounded_wait", "race_b200_host_release",
+    "race_b200_qkv_is_supported", "race_b200_causal_fwd_qkv",
 ]
 
 
@@ -85,6 +86,10 @@ def lib() -> ctypes.CDLL:
     L.race_b200_causal_fwd_static.argtypes = [vp, vp, vp, vp, vp, vp, shp, i32, i32, vp, vp]
     L.race_b200_causal_fwd_global.restype = i32
     L.race_b200_causal_fwd_global.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, i32, vp, vp]
+    L.race_b200_qkv_is_supported.restype = i32
+    L.race_b200_qkv_is_supported.argtypes = [shp, i32]
+    L.race_b200_causal_fwd_qkv.restype = i32
+    L.race_b200_causal_fwd_qkv.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, shp, i32, i32, i32, vp, vp]
     L.race_b200_selftest_bounded_wait.restype = i32
     L.race_b200_selftest_bounded_wait.argtypes = [vp, vp, vp, vp, vp, sz, shp, i32, i64, i32, vp, vp]
     L.race_b200_causal_bwd_workspace_bytes.restype = sz

@@ -82,7 +82,7 @@ size_t workspace_bytes_for(const Dims& dm, int dtype, int variant, int tile, boo
 
 extern "C" {
 
-int race_b200_version(void) { return 1007; }
+int race_b200_version(void) { return 1008; }
 
 const char* race_b200_error_string(int code) {
     switch (code) {
@@ -216,6 +216,46 @@ int race_b200_causal_fwd_global(const void* probs_q, const void* probs_k, const 
         variant = RACE_VARIANT_SIMT;
     return causal_entry(probs_q, probs_k, v, out, carry_in, state_out, workspace, workspace_bytes, shape,
                         tile_tokens, variant, stream, status, kPhaseAll, /*global_norm=*/true);
+}
+
+int race_b200_qkv_is_supported(const RaceShape* shape, int n_planes) {
+    Dims dm;
+    if (check_shape(shape, &dm) != RACE_OK) return 0;
+    return (n_planes == 4 && shape->n_buckets == (1 << n_planes) &&
+            tensor_qkv_supported(dm, shape->dtype, shape->n_tables, shape->n_buckets)) ? 1 : 0;
+}
+
+int race_b200_causal_fwd_qkv(const void* q, const void* k, const void* v, const float* planes, void* out,
+                             const float* carry_in, float* state_out, void* workspace, size_t workspace_bytes,
+                             const RaceShape* shape, int n_planes, int tile_tokens, int global_norm, void* stream,
+                             int* status) {
+    Dims dm;
+    int rc = check_shape(shape, &dm);
+    if (rc != RACE_OK) return rc;
+    if (n_planes <= 0 || n_planes > 12 || shape->n_buckets != (1 << n_planes)) return RACE_ERR_SHAPE;
+    if (!tensor_qkv_supported(dm, shape->dtype, shape->n_tables, shape->n_buckets)) return RACE_ERR_VARIANT;
+    if (tile_tokens < 0) return RACE_ERR_TILE;
+    const int tile = tile_tokens > 0 ? tile_tokens : pick_tile(dm, shape->dtype, RACE_VARIANT_TENSOR);
+    if (tile % tensor_chunk_tokens() != 0) return RACE_ERR_TILE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t sf = (size_t)dm.N * state_floats_per_stream(dm.S, dm.D);
+    if (dm.N == 0) return RACE_OK;
+    if (dm.T == 0) {
+        if (state_out) {
+            cudaError_t e = carry_in
+                ? cudaMemcpyAsync(state_out, carry_in, sf * sizeof(float), cudaMemcpyDeviceToDevice, st)
+                : cudaMemsetAsync(state_out, 0, sf * sizeof(float), st);
+            return (int)e;
+        }
+        return RACE_OK;
+    }
+    if (!q || !k || !v || !planes || !out || !workspace) return RACE_ERR_NULL;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(planes) ||
+        !aligned16(workspace) || !aligned16(carry_in) || !aligned16(state_out))
+        return RACE_ERR_ALIGN;
+    if (workspace_bytes < workspace_bytes_for(dm, shape->dtype, RACE_VARIANT_TENSOR, tile)) return RACE_ERR_WORKSPACE;
+    return (int)causal_fwd_qkv_tensor(q, k, v, planes, out, carry_in, state_out, workspace, dm, tile, st, status,
+                                      kPhaseAll, global_norm != 0);
 }
 
 int race_b200_selftest_bounded_wait(const void* probs_q, const void* probs_k, const void* v, void* out,

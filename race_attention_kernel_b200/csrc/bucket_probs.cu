@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "launch.h"
+#include "probs_frag.cuh"
 
 namespace race {
 namespace {
@@ -45,13 +46,6 @@ template <> struct Vec4<__nv_bfloat16> {
         __stcs(reinterpret_cast<uint2*>(p), u);
     }
 };
-
-// tanh(a) = sign(a) (1 - e)/(1 + e), e = exp(-2|a|): absolute error ~1e-7, which is what the logits
-// need (they are tanh/sqrt(d_k), and the projections of unit-variance rows mostly saturate)
-__device__ __forceinline__ float fast_tanh(float a) {
-    const float e = __expf(-2.f * fabsf(a));
-    return copysignf(__fdividef(1.f - e, 1.f + e), a);
-}
 
 // kXReg: d <= 64, the thread's row lives in registers; the tile is then free for the outputs, which go
 // through it (stage_out) when a row of L*R values fits, and straight from registers otherwise
@@ -210,37 +204,14 @@ bucket_probs_kernel(const Tx* __restrict__ x, const float* __restrict__ planes, 
 // holds four projections of each of its two rows; the quad exchanges them by shuffles so that lane t owns
 // table t, and writes that table's 16 probabilities with 16-byte stores.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void split_pair(float a, float b, uint32_t& hi, uint32_t& lo) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    hi = *reinterpret_cast<uint32_t*>(&h);
-    __nv_bfloat162 l = __floats2bfloat162_rn(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xffff0000u));
-    lo = *reinterpret_cast<uint32_t*>(&l);
-}
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-                 "{%0, %1, %2, %3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
 constexpr int kFastThreads = 128;
 __global__ void __launch_bounds__(kFastThreads, 4)
 bucket_probs_mma_d64_l4k4(const float* __restrict__ x, const float* __restrict__ planes, float* __restrict__ probs,
                           int64_t rows, int64_t T, int heads) {
-    constexpr int D = 64, K = 4, R = 16, LR = 64;
+    constexpr int D = 64, R = 16, LR = 64;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    // plane fragments (B operand, 16 planes x 64 features): for k-step j and plane block nt the lane holds
-    // planes[8 nt + g][16 j + 2t, +1] and [16 j + 8 + 2t, +1], as hi and lo limbs
-    uint32_t bhi[4][2][2], blo[4][2][2];
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const float2 p = __ldg(reinterpret_cast<const float2*>(planes + (8 * nt + g) * D + 16 * j + 8 * half + 2 * t));
-                split_pair(p.x, p.y, bhi[j][nt][half], blo[j][nt][half]);
-            }
+    PlaneFrags pf;
+    load_plane_frags(planes, lane, pf);
     const float inv_scale = rsqrtf((float)D);
     const int64_t blocks = (rows + 15) / 16;
     const int64_t warp_global = (int64_t)blockIdx.x * (kFastThreads / 32) + (threadIdx.x >> 5);
@@ -248,7 +219,7 @@ bucket_probs_mma_d64_l4k4(const float* __restrict__ x, const float* __restrict__
     for (int64_t blk = warp_global; blk < blocks; blk += warps_total) {
         const int64_t r0 = blk * 16;
         // the lane's two rows: r0 + g and r0 + g + 8 (rows past the end read as zero and are not written)
-        float2 raw[2][8];
+        float2 raw[16];
         bool live[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -260,63 +231,20 @@ bucket_probs_mma_d64_l4k4(const float* __restrict__ x, const float* __restrict__
             const float* src = x + ((mb * T + tok) * heads + hd) * D + 2 * t;
 #pragma unroll
             for (int u = 0; u < 8; ++u)
-                raw[h][u] = live[h] ? __ldcs(reinterpret_cast<const float2*>(src + 8 * u)) : make_float2(0.f, 0.f);
+                raw[2 * u + h] = live[h] ? __ldcs(reinterpret_cast<const float2*>(src + 8 * u)) : make_float2(0.f, 0.f);
         }
         float c[2][4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) c[nt][i] = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            // A fragment of k-step j: {row g cols 2t; row g+8 cols 2t; row g cols 8+2t; row g+8 cols 8+2t}
-            uint32_t ahi[4], alo[4];
-            split_pair(raw[0][2 * j].x, raw[0][2 * j].y, ahi[0], alo[0]);
-            split_pair(raw[1][2 * j].x, raw[1][2 * j].y, ahi[1], alo[1]);
-            split_pair(raw[0][2 * j + 1].x, raw[0][2 * j + 1].y, ahi[2], alo[2]);
-            split_pair(raw[1][2 * j + 1].x, raw[1][2 * j + 1].y, ahi[3], alo[3]);
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                mma_bf16_16816(c[nt], ahi, bhi[j][nt][0], bhi[j][nt][1]);
-                mma_bf16_16816(c[nt], ahi, blo[j][nt][0], blo[j][nt][1]);
-                mma_bf16_16816(c[nt], alo, bhi[j][nt][0], bhi[j][nt][1]);
-            }
-        }
-        // c[nt][2h + e] = projection of row (g + 8h) on plane 8 nt + 2t + e.  Table l needs planes 4l .. 4l+3:
-        // lane t takes table t, whose planes sit in block nt = t >> 1 of the lanes 2 (t & 1) and 2 (t & 1) + 1
-        const int src_a = (lane & ~3) + 2 * (t & 1), src_b = src_a + 1;
+        project_rows(raw, pf, c);
+        float vals[2][R];
+        table_probs(c, lane, inv_scale, vals);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            float th[K];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const float a0 = __shfl_sync(0xffffffffu, c[0][2 * h + e], src_a);
-                const float a1 = __shfl_sync(0xffffffffu, c[1][2 * h + e], src_a);
-                const float b0 = __shfl_sync(0xffffffffu, c[0][2 * h + e], src_b);
-                const float b1 = __shfl_sync(0xffffffffu, c[1][2 * h + e], src_b);
-                th[e] = (t >> 1) ? a1 : a0;
-                th[2 + e] = (t >> 1) ? b1 : b0;
-            }
-            float vals[R];
-            vals[0] = 1.f;
-#pragma unroll
-            for (int k = 0; k < K; ++k) {
-                const float tk = fast_tanh(th[k]) * inv_scale;
-                const float e = __expf(-2.f * tk);
-                const float p1 = 1.f / (1.f + e);
-                const float p0 = e * p1;
-#pragma unroll
-                for (int i = (1 << k) - 1; i >= 0; --i) {
-                    const float b = vals[i];
-                    vals[2 * i] = b * p0;
-                    vals[2 * i + 1] = b * p1;
-                }
-            }
             if (live[h]) {
                 float* dst = probs + (r0 + g + 8 * h) * LR + t * R;
 #pragma unroll
                 for (int i = 0; i < R; i += 4)
-                    __stcs(reinterpret_cast<float4*>(dst + i), make_float4(vals[i], vals[i + 1], vals[i + 2], vals[i + 3]));
+                    __stcs(reinterpret_cast<float4*>(dst + i),
+                           make_float4(vals[h][i], vals[h][i + 1], vals[h][i + 2], vals[h][i + 3]));
             }
         }
     }

@@ -25,9 +25,11 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 #include "launch.h"
+#include "probs_frag.cuh"
 #include "tc_common.cuh"
 
 
@@ -54,7 +56,8 @@ constexpr int oAcar = oBt + 4 * kOpTile;                // [2][64] fp32
 constexpr int oBars = oAcar + 2 * 64 * 4;
 constexpr int kNumBars = 34;
 constexpr int oMisc = oBars + kNumBars * 8;             // tmem base, abort flag
-constexpr int kSmemBytes = oMisc + 16 + 1024;           // + slack for manual alignment
+constexpr int oPlaneTab = oMisc + 16;                   // plane fragments (kernels that form the probabilities)
+constexpr int kSmemBytes = oPlaneTab + kPlaneTabWords * 4 + 1024;   // + slack for manual alignment
 
 enum Bar {
     kFull = 0,      // [2] stage filled by TMA
@@ -106,6 +109,58 @@ __device__ __forceinline__ void convert_tile(const uint8_t* __restrict__ stage, 
     }
 }
 
+// Staged fp32 K tile (64 tokens x 64 features, the same two swizzled halves) -> bucket probabilities -> bf16 hi/lo
+// operand tiles, by the four warps of a converter group: warp w takes the tokens 16 w .. 16 w + 15, a lane the rows
+// g and g + 8 of them (probs_frag.cuh), and ends up with table t = lane % 4 of both rows, i.e. the 8-column groups
+// 2 t and 2 t + 1 of the operand tile.  Rows >= valid (past the end of the sequence) become zero, like the rows the
+// TMA unit fills for a probabilities tile.  kSum adds the lane's probabilities into asum[16] (column 16 t + i).
+template <bool kSum>
+__device__ __forceinline__ void produce_tile(const uint8_t* __restrict__ stage, uint8_t* __restrict__ hi,
+                                             uint8_t* __restrict__ lo, const uint32_t* ptab, int w, int lane,
+                                             int valid, float (&asum)[16]) {
+    const int g = lane >> 2, t = lane & 3;
+    float2 raw[16];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = 16 * w + g + 8 * h;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint8_t* src = stage + (u >> 2) * 8192 + r * 128;
+            const int unit = 2 * (u & 3) + (t >> 1);       // 16-byte unit of columns 8 u + 2 t, + 1 within the half
+            raw[2 * u + h] = *reinterpret_cast<const float2*>(src + ((unit ^ (r & 7)) << 4) + ((t & 1) << 3));
+        }
+    }
+    PlaneFrags pf;
+    load_plane_frags_tab(ptab, lane, pf);
+    float c[2][4];
+    project_rows(raw, pf, c);
+    float vals[2][16];
+    table_probs(c, lane, 0.125f, vals);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = 16 * w + g + 8 * h;
+        if (r >= valid) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) vals[h][i] = 0.f;
+        }
+        if (kSum) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) asum[i] += vals[h][i];
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            uint4 hv, lv;
+            split2(vals[h][8 * half], vals[h][8 * half + 1], hv.x, lv.x);
+            split2(vals[h][8 * half + 2], vals[h][8 * half + 3], hv.y, lv.y);
+            split2(vals[h][8 * half + 4], vals[h][8 * half + 5], hv.z, lv.z);
+            split2(vals[h][8 * half + 6], vals[h][8 * half + 7], hv.w, lv.w);
+            const uint32_t off = (uint32_t)((((r >> 3) * 8 + 2 * t + half) << 7) + ((r & 7) << 4));
+            *reinterpret_cast<uint4*>(hi + off) = hv;
+            *reinterpret_cast<uint4*>(lo + off) = lv;
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Barriers of the output phase (one thread; the caller orders this against their use).  With
 // `again` the objects held a previous tile's phases and are invalidated first.
@@ -124,13 +179,15 @@ __device__ __forceinline__ void out_phase_reinit_bars_warp(const Ctx& cx, int la
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
-__device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again) {
+// empty_arrivals: warps that release a stage (4: the converter group reads pK and V; 8: the worker group reads its
+// K tile itself and the converter group V)
+__device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again, uint32_t empty_arrivals = 4) {
     if (again)
         for (int i = 0; i < kNumBars; ++i) mbar_inval(cx.bar(i));
     {
         for (int i = 0; i < 2; ++i) {
             mbar_init(cx.bar(kFull + i), 1);
-            mbar_init(cx.bar(kEmpty + i), 4);
+            mbar_init(cx.bar(kEmpty + i), empty_arrivals);
             mbar_init(cx.bar(kKvReady + i), 4);
             mbar_init(cx.bar(kXReady + i), 1);
             mbar_init(cx.bar(kWReady + i), 4);
@@ -166,13 +223,20 @@ __device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again) {
 // withhold (self-test of the bounded waits): the TMA producer skips the load of chunk withhold_chunk.
 // l2_last_use: this is the second read of the tile's pK and V (single-pass kernel), so their lines are loaded
 // with the evict-first priority and leave the L2 to the tiles still waiting for their second read.
+// kProj: the kernel forms the bucket probabilities itself (d_k = 64, L = 4 tables of R = 16 buckets;
+// src/race_baseline.py:41-44): `pq` is Q and map_k covers K, both in the layout of V ([N/heads, T, heads, 64]); the
+// worker warps turn their rows of Q into probabilities in the accumulator-fragment layout, the converter group turns
+// the staged K tile into the pK operand tiles; ptab = the plane fragments in shared memory (build_plane_tab).
+// kWorkerK: the pK operand tile of a chunk is written by the warps of the chunk's own worker group (at the start of
+// their work on the chunk) instead of the converter group, which then only converts V and copies the running B.
 constexpr int kModeBucket = 0, kModeGlobal = 1, kModeRaw = 2;
-template <int kMode, bool kReverse = false>
+template <int kMode, bool kReverse = false, bool kProj = false, bool kWorkerK = kProj>
 __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, const float* __restrict__ pq,
                                           const CUtensorMap* map_k, const CUtensorMap* map_v,
                                           float* __restrict__ out, const float* __restrict__ slice, int64_t T,
                                           const int64_t t_begin, const int64_t t_end, const int64_t n, float eps,
-                                          int heads, int withhold_chunk, const bool l2_last_use = false) {
+                                          int heads, int withhold_chunk, const bool l2_last_use = false,
+                                          const uint32_t* ptab = nullptr) {
     constexpr bool kGlobal = kMode == kModeGlobal;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nch = (int)((t_end - t_begin + C - 1) / C);
@@ -194,7 +258,9 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
         // V and out are [N/heads, T, heads, D]: stream n = outer * heads + h (heads = 1: plain [N, T, D])
         const int64_t orow_stride = (int64_t)heads * D;
         float* out_n = out + ((n / heads) * T * heads + (n % heads)) * D;
-        const float* pq_n = pq + n * T * S;
+        // probabilities [N, T, S]; with kProj the rows of Q in the layout of V
+        const float* pq_n = kProj ? pq + ((n / heads) * T * heads + (n % heads)) * D : pq + n * T * S;
+        const int64_t pq_stride = kProj ? orow_stride : (int64_t)S;
         float v[32];
         uint32_t ohi[16], olo[16];   // operand limbs of W / masked G on their way to tensor memory
 
@@ -222,23 +288,72 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             }
         };
 
-        uint32_t ph = 0;   // parity of this group's per-chunk barriers (one use per chunk)
-        bool ok = true;
-        for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
+        // pQ (kProj: the rows of Q) of chunk c in the accumulator-fragment layout, straight from global memory
+        float2 pqv[16];
+        auto load_pq = [&](int c) {
             const int64_t tok0 = chunk_tok0(c);
             const int valid = (int)min((int64_t)C, t_end - tok0);
-            // pQ of this chunk in the accumulator-fragment layout, straight from global memory,
-            // issued first so that the wait for the running-sum product hides the latency
-            float2 pqv[16];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int row = rbase + 8 * h;
-                const float* prow = pq_n + (tok0 + row) * S + 2 * q;
+                const float* prow = pq_n + (tok0 + row) * pq_stride + 2 * q;
 #pragma unroll
                 for (int x = 0; x < 8; ++x)
                     pqv[2 * x + h] = row < valid ? __ldcs(reinterpret_cast<const float2*>(prow + 8 * x))
                                                  : make_float2(0.f, 0.f);
             }
+        };
+        if (kProj && wg < nch) load_pq(wg);
+        // kWorkerK: the pK operand tile of chunk c from the group's stage (convert, or with kProj form the
+        // probabilities), into buffer (c >> 1) & 1 of the group, last read by the products of the group's chunk c - 4
+        auto write_kt = [&](int c) {
+            const int kb = (c >> 1) & 1;
+            uint8_t* kt_hi = cx.sm + oKt + (wg * 2 + kb) * 2 * kOpTile;
+            const uint8_t* stage = cx.sm + oStage + wg * kStageBytes;
+            if (kProj) {
+                float unused[16];
+                produce_tile<false>(stage, kt_hi, kt_hi + kOpTile, ptab, w, lane,
+                                    (int)min((int64_t)C, t_end - chunk_tok0(c)), unused);
+            } else {
+                convert_tile(stage, kt_hi, kt_hi + kOpTile, tid & 127);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(kKvReady + wg)); mbar_arrive(cx.bar(kEmpty + wg)); }
+        };
+        // kProj: the rows of Q in pqv -> the probabilities of chunk c, in place (rows past the end stay zero)
+        auto q_to_probs = [&](int c) {
+            const int valid = (int)min((int64_t)C, t_end - chunk_tok0(c));
+            PlaneFrags pf;
+            load_plane_frags_tab(ptab, lane, pf);
+            float cp[2][4];
+            project_rows(pqv, pf, cp);
+            fragment_probs(cp, lane, 0.125f, pqv);
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (rbase + 8 * h >= valid) {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) pqv[2 * x + h] = make_float2(0.f, 0.f);
+                }
+        };
+        uint32_t ph = 0;   // parity of this group's per-chunk barriers (one use per chunk)
+        bool ok = true;
+        for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
+            const int64_t tok0 = chunk_tok0(c);
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+            // probabilities: issued first so that the wait for the running-sum product hides the latency; the
+            // rows of Q were requested a chunk ahead (after the W stage of the group's previous chunk), because the
+            // projection needs them at once
+            if (!kProj) load_pq(c);
+            // Both at the start of the chunk, where the group would otherwise idle until the running A of the other
+            // group's chunk arrives.  (Done during the waits for this group's own products instead, they delayed the
+            // reaction to those products by more than they saved.)
+            if (kWorkerK) {
+                if (c >= 4 && !(ok = wait_bar_warp(cx, kKtFree + wg * 2 + (int)ph, (uint32_t)(((c >> 2) - 1) & 1), 108))) break;
+                if (!(ok = wait_bar_warp(cx, kFull + wg, ph, 109))) break;
+                write_kt(c);
+            }
+            if (kProj) q_to_probs(c);
             RACE_TRACE(wg, c, 0);
 
             // -- S2: W = pQ / (A + A_loc + eps) ----------------------------------------------------
@@ -303,6 +418,7 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
                 mbar_arrive(cx.bar(kWReady + wg));
                 if (kMode != kModeRaw && w == 3) mbar_arrive(cx.bar(kAcar + (wg ^ 1)));
             }
+            if (kProj && c + 2 < nch) load_pq(c + 2);
             if (kGlobal) {
                 // a row's 64 buckets are spread over the four lanes of a quad, in a fixed order
 #pragma unroll
@@ -335,7 +451,6 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(cx.bar(kGtReady + wg));
-
             // -- S4: O -> global --------------------------------------------------------------------
             if (!(ok = wait_bar_warp(cx, kOReady + wg, ph, 105))) break;
             RACE_TRACE(wg, c, 3);
@@ -410,13 +525,22 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             uint8_t* vt_hi = cx.sm + oVt + wg * 2 * kOpTile;
             // pK buffer: last read by the products of chunk c - 4
             RACE_TRACE(2, c, 0);
-            if (c >= 4 && !(ok = wait_bar_warp(cx, kKtFree + wg * 2 + kb, (uint32_t)(((c >> 2) - 1) & 1), 203))) break;
+            if (!kWorkerK && c >= 4 &&
+                !(ok = wait_bar_warp(cx, kKtFree + wg * 2 + kb, (uint32_t)(((c >> 2) - 1) & 1), 203))) break;
             if (!(ok = wait_bar_warp(cx, kFull + wg, ph, 201))) break;
             RACE_TRACE(2, c, 1);
-            convert_tile(stage, kt_hi, kt_hi + kOpTile, wtid);
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(cx.bar(kKvReady + wg));
+            if (!kWorkerK) {
+                if (kProj) {
+                    float unused[16];
+                    produce_tile<false>(stage, kt_hi, kt_hi + kOpTile, ptab, w, lane,
+                                        (int)min((int64_t)C, t_end - chunk_tok0(c)), unused);
+                } else {
+                    convert_tile(stage, kt_hi, kt_hi + kOpTile, wtid);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(cx.bar(kKvReady + wg));
+            }
             RACE_TRACE(2, c, 2);
             if (c >= 1) {
                 // state after chunk c - 1 -> operand buffer c & 1 (read by W.B of chunk c; last read
@@ -457,7 +581,8 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
                     tma_load_4d_hint(dst, map_k, bar, 0, tok, 0, (int)n, pol);
                     tma_load_5d_hint(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads), pol);
                 } else {
-                    tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
+                    if (kProj) tma_load_5d(dst, map_k, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                    else tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
                     tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
                 }
                 issued = c + 1;
@@ -556,12 +681,13 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t tmem, uint32_t cols) {
 // The output pass as a kernel of its own (second half of a forward whose per-tile prefixes are
 // already in the workspace): one CTA per (tile, stream).  wait_cycles > 0 replaces the default limit
 // of every wait; withhold_chunk >= 0 makes the producer of CTA (0, 0) skip that chunk's load.
-template <int kMode, bool kReverse>
+// kProj: pq is Q, map_k covers K and `planes` [16][64] are the hyperplanes (out_phase).
+template <int kMode, bool kReverse, bool kProj>
 __global__ void __launch_bounds__(kThreads, 1)
 causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, float* __restrict__ out,
               const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int heads, int* status,
-              long long wait_cycles, int withhold_chunk) {
+              long long wait_cycles, int withhold_chunk, const float* __restrict__ planes) {
     extern __shared__ uint8_t smem_raw[];
     Ctx cx;
     cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -576,18 +702,23 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
     const int64_t t_begin = tile * tile_tokens;
     const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
     const float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+    // The worker groups write their own pK tile only where forming the probabilities makes that tile expensive: with
+    // probabilities in, leaving it to the converter group measured 3 % faster.
+    constexpr bool kWorkerK = kProj;
     if (tid == 0) {
         *cx.abort_flag = 0;
-        out_phase_init_bars(cx, false);
+        out_phase_init_bars(cx, false, kWorkerK ? 8u : 4u);
     }
+    uint32_t* ptab = reinterpret_cast<uint32_t*>(cx.sm + oPlaneTab);
+    if (kProj) build_plane_tab(planes, ptab, tid, kThreads);
     if (warp == kMmaWarp) tmem_alloc(cx.sm_u32 + oMisc, kTmemCols);
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    out_phase<kMode, kReverse>(cx, tmem, pq, &map_k, &map_v, out, slice, T, t_begin, t_end, n, eps, heads,
-                       (tile == 0 && n == 0) ? withhold_chunk : -1);
+    out_phase<kMode, kReverse, kProj, kWorkerK>(cx, tmem, pq, &map_k, &map_v, out, slice, T, t_begin, t_end, n, eps,
+                                                heads, (tile == 0 && n == 0) ? withhold_chunk : -1, false, ptab);
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) {
@@ -626,24 +757,34 @@ __device__ long long g_fused_prof[160][16];
 // to the same group: a group that saw only every other phase of a stage's barrier could not tell a refilled
 // stage from the one it read two fills ago by the parity (which made a 3-stage ring with two groups run ahead
 // of the copies and overflow its barriers' arrival counts under load).
-constexpr int kT1Groups = 2;
-constexpr int kT1Stages = 4;
-static_assert(kT1Stages % kT1Groups == 0, "a stage must stay with one converter group");
-constexpr int kT1ProducerWarp = 4 * kT1Groups, kT1MmaWarp = 4 * kT1Groups + 1;
-constexpr int kT1Threads = (4 * kT1Groups + 2) * 32;    // converters, TMA producer, MMA issuer
 constexpr int kT1StageBytes = 2 * kTileF32;            // pK | V
-constexpr int o1Stage = 0;
-constexpr int o1Kt = o1Stage + kT1Stages * kT1StageBytes;   // [group][hi | lo]
-constexpr int o1Vt = o1Kt + kT1Groups * 2 * kOpTile;        // [group][hi | lo]
-constexpr int o1Red = o1Vt + kT1Groups * 2 * kOpTile;       // [12 warps][4][8] fp32 column-sum partials
-constexpr int o1Bars = o1Red + 4 * kT1Groups * 32 * 4;
-constexpr int o1Misc = o1Bars + 16 * 8;
-constexpr int kT1SmemBytes = o1Misc + 16 + 1024;
-enum Bar1 {
-    k1Full = 0, k1Empty = kT1Stages, k1KvReady = 2 * kT1Stages, k1KvFree = 2 * kT1Stages + kT1Groups,
-    k1Done = 2 * kT1Stages + 2 * kT1Groups
+template <int kGroupsT, int kStagesT>
+struct TotalsLayout {
+    static constexpr int kGroups = kGroupsT, kStages = kStagesT;
+    static_assert(kStages % kGroups == 0, "a stage must stay with one converter group");
+    static constexpr int kProducerWarp = 4 * kGroups, kMmaWarp = 4 * kGroups + 1;
+    static constexpr int kThreads = (4 * kGroups + 2) * 32;    // converters, TMA producer, MMA issuer
+    static constexpr int oStage = 0;
+    static constexpr int oKt = oStage + kStages * kT1StageBytes;   // [group][hi | lo]
+    static constexpr int oVt = oKt + kGroups * 2 * kOpTile;        // [group][hi | lo]
+    static constexpr int oRed = oVt + kGroups * 2 * kOpTile;       // [converter warps][64] fp32 column-sum partials
+    static constexpr int oBars = oRed + 4 * kGroups * 64 * 4;
+    static constexpr int oMisc = oBars + 16 * 8;
+    static constexpr int oPlaneTab = oMisc + 16;                   // plane fragments (kProj)
+    static constexpr int kSmemBytes = oPlaneTab + kPlaneTabWords * 4 + 1024;
+    static constexpr int kFull = 0, kEmpty = kStages, kKvReady = 2 * kStages, kKvFree = 2 * kStages + kGroups,
+                         kDone = 2 * kStages + 2 * kGroups, kNumBars = kDone + 1;
+    static_assert(kNumBars <= 16, "barrier array of the totals phase");
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory of the totals phase");
 };
-static_assert(kT1Threads <= kThreads, "the single-pass kernel runs the totals phase with its own warps");
+// Two groups and four stages: with probabilities in, a streaming, DRAM-bound kernel, which wants many bytes in
+// flight; forming the probabilities, the converter groups are the bound, but a third group (with three stages, which
+// is what then fits) measured the same.
+using T1 = TotalsLayout<2, 4>;
+using T1P = TotalsLayout<2, 4>;
+static_assert(T1::kThreads <= kThreads, "the single-pass kernel runs the totals phase with its own warps");
+// names of the default layout, as the single-pass kernel uses them
+constexpr int o1Misc = T1::oMisc, o1Bars = T1::oBars;
 
 // like convert_tile, and adds each thread's 8 values per item into asum[item][8]
 __device__ __forceinline__ void convert_tile_sum(const uint8_t* __restrict__ stage, uint8_t* __restrict__ hi,
@@ -676,40 +817,47 @@ __device__ __forceinline__ void convert_tile_sum(const uint8_t* __restrict__ sta
     }
 }
 
-constexpr int kT1NumBars = k1Done + 1;
-static_assert(kT1NumBars <= 16, "barrier array of the totals phase");
+template <typename TL = T1>
 __device__ __forceinline__ void totals_phase_reinit_bars_warp(const Ctx& cx, int lane, bool again) {
-    if (lane < kT1NumBars) {
+    if (lane < TL::kNumBars) {
         if (again) mbar_inval(cx.bar(lane));
-        mbar_init(cx.bar(lane), (lane >= k1Empty && lane < k1KvFree) ? 4u : 1u);   // k1Empty, k1KvReady: 4 warps
+        mbar_init(cx.bar(lane), (lane >= TL::kEmpty && lane < TL::kKvFree) ? 4u : 1u);   // kEmpty, kKvReady: 4 warps
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+template <typename TL = T1>
 __device__ __forceinline__ void totals_phase_init_bars(const Ctx& cx, bool again) {
     if (again)
-        for (int i = 0; i < kT1NumBars; ++i) mbar_inval(cx.bar(i));
+        for (int i = 0; i < TL::kNumBars; ++i) mbar_inval(cx.bar(i));
     {
-        for (int i = 0; i < kT1Stages; ++i) {
-            mbar_init(cx.bar(k1Full + i), 1);
-            mbar_init(cx.bar(k1Empty + i), 4);
+        for (int i = 0; i < TL::kStages; ++i) {
+            mbar_init(cx.bar(TL::kFull + i), 1);
+            mbar_init(cx.bar(TL::kEmpty + i), 4);
         }
-        for (int i = 0; i < kT1Groups; ++i) {
-            mbar_init(cx.bar(k1KvReady + i), 4);
-            mbar_init(cx.bar(k1KvFree + i), 1);
+        for (int i = 0; i < TL::kGroups; ++i) {
+            mbar_init(cx.bar(TL::kKvReady + i), 4);
+            mbar_init(cx.bar(TL::kKvFree + i), 1);
         }
-        mbar_init(cx.bar(k1Done), 1);
+        mbar_init(cx.bar(TL::kDone), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 }
 
 // Totals phase of one (stream n, tokens [t_begin, t_end)) tile into `slice` (state layout).  Called
-// by at least kT1Threads / 32 warps (the first 4 * kT1Groups convert, the next issues TMA, the next the products; further warps only
-// take part in the block-wide barriers) with barriers initialised and 64 TMEM columns at `tmem`.
+// by at least TL::kThreads / 32 warps (the first 4 * TL::kGroups convert, the next issues TMA, the next the products;
+// further warps only take part in the block-wide barriers) with barriers initialised and 64 TMEM columns at `tmem`.
 // l2_keep: pK and V of the tile are read again soon (single-pass kernel): load them with the evict-last priority.
+// kProj: map_k covers K in the layout of V and the converter groups form pK themselves (out_phase); ptab = the
+// plane fragments in shared memory.
+template <bool kProj = false, typename TL = T1>
 __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem, const CUtensorMap* map_k,
                                              const CUtensorMap* map_v, float* __restrict__ slice,
                                              const int64_t t_begin, const int64_t t_end, const int64_t n, int heads,
-                                             const bool l2_keep = false) {
+                                             const bool l2_keep = false, const uint32_t* ptab = nullptr) {
+    constexpr int kT1Groups = TL::kGroups, kT1Stages = TL::kStages, kT1ProducerWarp = TL::kProducerWarp,
+                  kT1MmaWarp = TL::kMmaWarp, o1Stage = TL::oStage, o1Kt = TL::oKt, o1Vt = TL::oVt, o1Red = TL::oRed,
+                  k1Full = TL::kFull, k1Empty = TL::kEmpty, k1KvReady = TL::kKvReady, k1KvFree = TL::kKvFree,
+                  k1Done = TL::kDone;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nch = (int)((t_end - t_begin + C - 1) / C);
 
@@ -722,6 +870,9 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int e = 0; e < 8; ++e) asum[i][e] = 0.f;
+        float psum[16];   // kProj: the lane's table (columns 16 (lane % 4) + i), rows lane / 4 and lane / 4 + 8
+#pragma unroll
+        for (int i = 0; i < 16; ++i) psum[i] = 0.f;
         bool ok = true;
         int i = 0;   // the group's i-th chunk
         RACE_PROF_T(tq);
@@ -732,24 +883,39 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
             if (tid == 0) RACE_PROF_LANE(8, tq);
             if (i >= 1 && !(ok = wait_bar_warp(cx, k1KvFree + wg, (uint32_t)((i - 1) & 1), 112))) break;
             if (tid == 0) RACE_PROF_LANE(9, tq);
-            convert_tile_sum(stage, kt_hi, kt_hi + kOpTile, wtid, asum);
+            if (kProj)
+                produce_tile<true>(stage, kt_hi, kt_hi + kOpTile, ptab, warp & 3, lane,
+                                   (int)min((int64_t)C, t_end - (t_begin + (int64_t)c * C)), psum);
+            else
+                convert_tile_sum(stage, kt_hi, kt_hi + kOpTile, wtid, asum);
             convert_tile(stage + kTileF32, vt_hi, vt_hi + kOpTile, wtid);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) { mbar_arrive(cx.bar(k1KvReady + wg)); mbar_arrive(cx.bar(k1Empty + st)); }
             if (tid == 0) RACE_PROF_LANE(10, tq);
         }
-        // column sums: lanes of a warp hold different token rows of the same 8 columns
-        float* red = reinterpret_cast<float*>(cx.sm + o1Red) + warp * 32;
+        float* red = reinterpret_cast<float*>(cx.sm + o1Red) + warp * 64;
+        if (kProj) {
+            // column sums: the eight lanes with the same lane % 4 hold different token rows of one table
 #pragma unroll
-        for (int it = 0; it < 4; ++it)
+            for (int i = 0; i < 16; ++i) {
+                float x = psum[i];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                float x = asum[it][e];
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
-                if (lane == 0) red[it * 8 + e] = x;
+                for (int off = 16; off >= 4; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+                if (lane < 4) red[16 * lane + i] = x;
             }
+        } else {
+            // column sums: lanes of a warp hold different token rows of the same 8 columns
+#pragma unroll
+            for (int it = 0; it < 4; ++it)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float x = asum[it][e];
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+                    if (lane == 0) red[it * 8 + e] = x;
+                }
+        }
     } else if (warp == kT1ProducerWarp) {
         if (lane == 0) {
             int issued = 0;
@@ -767,7 +933,8 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
                     tma_load_4d_hint(dst, map_k, bar, 0, tok, 0, (int)n, pol);
                     tma_load_5d_hint(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads), pol);
                 } else {
-                    tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
+                    if (kProj) tma_load_5d(dst, map_k, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                    else tma_load_4d(dst, map_k, bar, 0, tok, 0, (int)n);
                     tma_load_5d(dst + kTileF32, map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
                 }
                 issued = c + 1;
@@ -824,33 +991,43 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
                     *reinterpret_cast<float2*>(slice + (rbase + 8 * h) * D + 8 * x + 2 * q) =
                         make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
             if (tid < 64) {
-                // column s = 8 j + e with j = 2 item + (warp_in_group >> 1); partials from both
-                // groups and both row halves, added in a fixed order
-                const int j = tid >> 3, e = tid & 7, it = j >> 1, wh = (j & 1) * 2;
                 const float* red = reinterpret_cast<const float*>(cx.sm + o1Red);
                 float a = 0.f;
+                if (kProj) {
+                    // every converter warp holds a partial of every column; added in warp order
 #pragma unroll
-                for (int g = 0; g < kT1Groups; ++g)
+                    for (int wv = 0; wv < 4 * kT1Groups; ++wv) a += red[wv * 64 + tid];
+                } else {
+                    // column s = 8 j + e with j = 2 item + (warp_in_group >> 1); partials from both
+                    // groups and both row halves, added in a fixed order
+                    const int j = tid >> 3, e = tid & 7, it = j >> 1, wh = (j & 1) * 2;
 #pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                        a += red[(g * 4 + wh + half) * 32 + it * 8 + e];
+                    for (int g = 0; g < kT1Groups; ++g)
+#pragma unroll
+                        for (int half = 0; half < 2; ++half)
+                            a += red[(g * 4 + wh + half) * 64 + it * 8 + e];
+                }
                 slice[S * D + tid] = a;
             }
         }
     }
 }
 
-__global__ void __launch_bounds__(kT1Threads, 1)
+template <bool kProj> using TotalsLayoutOf = std::conditional_t<kProj, T1P, T1>;
+template <bool kProj>
+__global__ void __launch_bounds__(TotalsLayoutOf<kProj>::kThreads, 1)
 tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-               float* __restrict__ ws, int64_t T, int tile_tokens, int heads, int* status) {
+               float* __restrict__ ws, int64_t T, int tile_tokens, int heads, int* status,
+               const float* __restrict__ planes) {
     extern __shared__ uint8_t smem_raw[];
     Ctx cx;
     cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     cx.sm_u32 = smem_u32(cx.sm);
-    cx.bars = o1Bars;
-    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + o1Misc + 4);
+    using TL = TotalsLayoutOf<kProj>;
+    cx.bars = TL::oBars;
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + TL::oMisc + 4);
     cx.status = status;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + o1Misc);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + TL::oMisc);
     const int tid = threadIdx.x, warp = tid >> 5;
     const int64_t tiles = gridDim.x, tile = blockIdx.x, n = blockIdx.y;
     const int64_t t_begin = tile * tile_tokens;
@@ -858,17 +1035,19 @@ tile_totals_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
     if (tid == 0) {
         *cx.abort_flag = 0;
-        totals_phase_init_bars(cx, false);
+        totals_phase_init_bars<TL>(cx, false);
     }
-    if (warp == kT1MmaWarp) tmem_alloc(cx.sm_u32 + o1Misc, 64u);
+    uint32_t* ptab = reinterpret_cast<uint32_t*>(cx.sm + TL::oPlaneTab);
+    if (kProj) build_plane_tab(planes, ptab, tid, TL::kThreads);
+    if (warp == TL::kMmaWarp) tmem_alloc(cx.sm_u32 + TL::oMisc, 64u);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    totals_phase(cx, tmem, &map_k, &map_v, slice, t_begin, t_end, n, heads);
+    totals_phase<kProj, TL>(cx, tmem, &map_k, &map_v, slice, t_begin, t_end, n, heads, false, ptab);
     tc_fence_before();
     __syncthreads();
-    if (warp == kT1MmaWarp) {
+    if (warp == TL::kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem, 64u);
     }
@@ -1205,7 +1384,8 @@ size_t tensor_workspace_bytes(const Dims& dm, int, int tile_tokens) {
 static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void* v, void* out,
                                      const float* carry_in, float* state_out, void* ws, bool single_pass,
                                      const Dims& dm, int tile_tokens, cudaStream_t stream, int* status, int phases,
-                                     int mode, bool reverse, long long wait_cycles, int withhold_chunk);
+                                     int mode, bool reverse, long long wait_cycles, int withhold_chunk,
+                                     const float* planes = nullptr);
 
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
                               const float* carry_in, float* state_out, void* ws, bool single_pass, const Dims& dm,
@@ -1218,6 +1398,21 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
                              phases, global_norm ? kModeGlobal : kModeBucket, false, wait_cycles, withhold_chunk);
 }
 
+// The causal forward from Q, K, V and the hyperplanes (fp32, d_k = 64, L = 4, R = 16; Q, K, V and out in the layout
+// [N/heads, T, heads, 64]): the kernels form the bucket probabilities of src/race_baseline.py:41-44 in registers and
+// shared memory, so the forward moves Q, K, V and out through HBM and nothing else.  The role of the reference's
+// race_causal_forward (src/causal_v2/kernels/race_causal_fwd.h:126-130), which also takes q, k, v and planes.
+bool tensor_qkv_supported(const Dims& dm, int dtype, int L, int R) {
+    return dtype == RACE_DTYPE_F32 && L == 4 && R == 16 && tensor_supported(dm, dtype);
+}
+cudaError_t causal_fwd_qkv_tensor(const void* q, const void* k, const void* v, const float* planes, void* out,
+                                  const float* carry_in, float* state_out, void* ws, const Dims& dm, int tile_tokens,
+                                  cudaStream_t stream, int* status, int phases, bool global_norm) {
+    if (!planes) return cudaErrorInvalidValue;
+    return tensor_f32_launch(q, k, v, out, carry_in, state_out, ws, false, dm, tile_tokens, stream, status, phases,
+                             global_norm ? kModeGlobal : kModeBucket, false, 0, -1, planes);
+}
+
 // The plain causal (or, with reverse, anti-causal) product out_t = sum_{j <= t} (q_t . k_j) v_j + q_t . carry over
 // fp32 [N, T, 64] tensors on the same three launches: what the backward passes are made of.  State layout as
 // everywhere: carry[s][c] = sum_j k_j[s] v_j[c] (the A part is carried along and ignored).
@@ -1228,19 +1423,26 @@ cudaError_t causal_raw_tensor(const void* q, const void* k, const void* v, void*
                              kModeRaw, reverse, 0, -1);
 }
 
+// planes != nullptr: pq and pk are Q and K in the layout of V and the kernels form the probabilities (the
+// three-launch form of the two estimators only).
 static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void* v, void* out,
                                      const float* carry_in, float* state_out, void* ws, bool single_pass,
                                      const Dims& dm, int tile_tokens, cudaStream_t stream, int* status, int phases,
-                                     int mode, bool reverse, long long wait_cycles, int withhold_chunk) {
+                                     int mode, bool reverse, long long wait_cycles, int withhold_chunk,
+                                     const float* planes) {
     const bool global_norm = mode == kModeGlobal;
+    const bool proj = planes != nullptr;
+    if (proj && (single_pass || reverse || mode == kModeRaw)) return cudaErrorInvalidValue;
     // Runtime calls first: they bind the device's primary context to the calling host thread,
     // which the driver-level tensor-map encoder needs (a thread that has made no runtime call
     // yet, e.g. an autograd worker, has no current context).
-    cudaError_t err = cudaFuncSetAttribute(tile_totals_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           kT1SmemBytes);
+    auto totals_kern = proj ? tile_totals_tc<true> : tile_totals_tc<false>;
+    const int totals_smem = proj ? T1P::kSmemBytes : T1::kSmemBytes, totals_threads = proj ? T1P::kThreads : T1::kThreads;
+    cudaError_t err = cudaFuncSetAttribute(totals_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, totals_smem);
     if (err != cudaSuccess) return err;
     CUtensorMap mk, mv;
-    if (!make_map(&mk, pk, dm.N, dm.T, dm.S) || !make_map_heads(&mv, v, dm.N, dm.T, dm.D, dm.H))
+    if (!(proj ? make_map_heads(&mk, pk, dm.N, dm.T, dm.D, dm.H) : make_map(&mk, pk, dm.N, dm.T, dm.S)) ||
+        !make_map_heads(&mv, v, dm.N, dm.T, dm.D, dm.H))
         return cudaErrorInvalidValue;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     const FusedLayout lay = fused_layout(dm, tile_tokens);
@@ -1279,7 +1481,8 @@ static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void*
     dim3 grid((unsigned)tiles, (unsigned)dm.N);
     // 1. tile totals (tensor cores)  2. exclusive scan over tiles  3. output pass
     if (phases & kPhaseTotals) {
-        tile_totals_tc<<<grid, kT1Threads, kT1SmemBytes, stream>>>(mk, mv, (float*)ws, dm.T, tile_tokens, dm.H, status);
+        totals_kern<<<grid, totals_threads, totals_smem, stream>>>(mk, mv, (float*)ws, dm.T, tile_tokens, dm.H, status,
+                                                                planes);
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
     }
@@ -1291,12 +1494,15 @@ static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void*
     }
     err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, /*write_prefix=*/true, reverse);
     if (err != cudaSuccess) return err;
-    auto kern = mode == kModeRaw ? (reverse ? causal_out_tc<kModeRaw, true> : causal_out_tc<kModeRaw, false>)
-                                 : (global_norm ? causal_out_tc<kModeGlobal, false> : causal_out_tc<kModeBucket, false>);
+    auto kern = mode == kModeRaw
+                    ? (reverse ? causal_out_tc<kModeRaw, true, false> : causal_out_tc<kModeRaw, false, false>)
+                    : proj ? (global_norm ? causal_out_tc<kModeGlobal, false, true> : causal_out_tc<kModeBucket, false, true>)
+                           : (global_norm ? causal_out_tc<kModeGlobal, false, false>
+                                          : causal_out_tc<kModeBucket, false, false>);
     err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return err;
     kern<<<grid, kThreads, kSmemBytes, stream>>>((const float*)pq, mk, mv, (float*)out, (const float*)ws, dm.T,
-                                                 tile_tokens, dm.eps, dm.H, status, wait_cycles, withhold_chunk);
+                                                 tile_tokens, dm.eps, dm.H, status, wait_cycles, withhold_chunk, planes);
     return cudaGetLastError();
 }
 

@@ -83,6 +83,12 @@ cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, voi
 
 // out_t = sum_{j <= t} (q_t . k_j) v_j + q_t . carry (reverse: j >= t, carry = state of the tokens after the call)
 // on fp32 [N, T, 64] tensors with the three launches of the fp32 tensor forward, no normalisation
+// The causal forward from Q, K, V and the hyperplanes [16][64] on the fp32 tensor kernels (d_k = 64, L = 4, R = 16);
+// Q, K, V, out in the layout [N/heads, T, heads, 64]; workspace as for the three-launch form.
+bool tensor_qkv_supported(const Dims& dm, int dtype, int L, int R);
+cudaError_t causal_fwd_qkv_tensor(const void* q, const void* k, const void* v, const float* planes, void* out,
+                                  const float* carry_in, float* state_out, void* ws, const Dims& dm, int tile_tokens,
+                                  cudaStream_t stream, int* status, int phases, bool global_norm);
 cudaError_t causal_raw_tensor(const void* q, const void* k, const void* v, void* out, const float* carry_in,
                               float* state_out, void* ws, const Dims& dm, int tile_tokens, bool reverse,
                               cudaStream_t stream, int* status, int phases = kPhaseAll);

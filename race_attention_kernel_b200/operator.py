@@ -40,6 +40,9 @@ class BatchedACE(nn.Module):
         self.register_buffer("protos_T", corners.T)
         self.eps = 1e-6
         self.variant = "auto"
+        # form the bucket probabilities inside the prefix kernels where that path exists (fp32, d_k = 64, L = 4,
+        # K = 4); False keeps the producer kernel and the probabilities in device memory
+        self.fuse_producer = True
 
     def _streams(self, x: torch.Tensor) -> torch.Tensor:
         M, B, T, H, dk = x.shape
@@ -91,9 +94,17 @@ class BatchedACE(nn.Module):
             Khf, Vhf, Qhf = (t.to(dev, non_blocking=True) for t in (Khf, Vhf, Qhf))
         if Khf.dtype not in (torch.float32, torch.bfloat16):
             raise RuntimeError("fp32 or bf16 inputs only")
+        planes = self.planes_T.T.contiguous().float()
+        if self.fuse_producer and self.variant == "auto" and ops.qkv_is_supported(M * B * H, T, self.L, self.K, dk, Khf.dtype, heads=H):
+            # the prefix kernels form the bucket probabilities themselves: Q, K, V in, out back, nothing else
+            res = ops.race_causal_qkv(Qhf.contiguous(), Khf.contiguous(), Vhf.contiguous(), planes, self.L, self.K,
+                                      self.eps, carry_in=carry_in, return_state=return_state)
+            out = res[0] if return_state else res
+            if host:
+                out = out.cpu()
+            return (out, res[1], res[2]) if return_state else out
         # K and Q are only read by the producer, which flattens [M,B,T,H,d_k] -> streams on the fly;
         # V is consumed by the prefix kernels as [N,T,d_k] and is copied once
-        planes = self.planes_T.T.contiguous().float()
         pK = ops.bucket_probs_streams(Khf.contiguous(), planes, self.L, self.K)
         pQ = ops.bucket_probs_streams(Qhf.contiguous(), planes, self.L, self.K)
         N, S_l, S_r = M * B * H, self.L, 1 << self.K

@@ -211,6 +211,64 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
     return out
 
 
+def qkv_is_supported(N, T, L, K, dk, dtype=torch.float32, heads: int = 0) -> bool:
+    """Whether ``race_causal_qkv`` takes this geometry (fp32, d_k = 64, L = 4, K = 4)."""
+    sh = make_shape(N, T, L, 1 << K, dk, dtype, 1e-6, heads)
+    return bool(_lib.lib().race_b200_qkv_is_supported(ctypes.byref(sh), K))
+
+
+def race_causal_qkv(Q, K, V, planes, L: int, n_planes: int, eps: float = 1e-6, *, carry_in=None,
+                    return_state: bool = False, tile_tokens: int = 0, out: torch.Tensor | None = None,
+                    normalization: str = "bucket"):
+    """The causal forward of ``BatchedACE`` from Q, K, V and the hyperplanes (src/race_baseline.py:41-51) with the
+    bucket probabilities formed inside the prefix kernels: they never exist in device memory.
+
+    Q, K, V: fp32 CUDA tensors of one shape, [N,T,d_k] or the operator's layout [M,B,T,H,d_k] (stream
+    n = (m*B+b)*H + h); planes: fp32 [L*n_planes, d_k] (``planes_T.T``).  Geometry: ``qkv_is_supported``.
+    carry_in / return_state / normalization as in ``race_causal_prefix``; the output has the layout of V."""
+    if not (Q.shape == K.shape == V.shape) or V.dim() not in (3, 5):
+        raise RuntimeError("Q, K, V must have one shape, [N,T,d_k] or [M,B,T,H,d_k]")
+    for name, t in (("Q", Q), ("K", K), ("V", V)):
+        if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous() or t.device != V.device:
+            raise RuntimeError(f"{name} must be a contiguous fp32 CUDA tensor on V's device")
+    if normalization not in ("bucket", "global"):
+        raise RuntimeError(f"unknown normalization {normalization!r}")
+    dk, R = V.shape[-1], 1 << n_planes
+    if V.dim() == 5:
+        M, B, T, H, _ = V.shape
+        N = M * B * H
+    else:
+        (N, T, _), H = V.shape, 0
+    planes = planes.to(device=V.device, dtype=torch.float32).contiguous()
+    if planes.shape != (L * n_planes, dk):
+        raise RuntimeError(f"planes must be [L*K, d_k] = [{L * n_planes}, {dk}]")
+    L_ = _lib.lib()
+    sh = make_shape(N, T, L, R, dk, V.dtype, eps, H)
+    if not L_.race_b200_qkv_is_supported(ctypes.byref(sh), n_planes):
+        raise RuntimeError("race_causal_qkv: geometry not supported (fp32, d_k = 64, L = 4, K = 4); use "
+                           "bucket_probs_streams + race_causal_prefix")
+    carry = None
+    if carry_in is not None:
+        carry = pack_state(*carry_in) if isinstance(carry_in, (tuple, list)) else carry_in
+        _check_state("carry_in", carry, V, N * L * R * (dk + 1))
+    with torch.cuda.device(V.device):
+        if out is None:
+            out = torch.empty_like(V)
+        state = torch.empty(N, L * R * (dk + 1), dtype=torch.float32, device=V.device) if return_state else None
+        ws_bytes = L_.race_b200_causal_workspace_bytes(ctypes.byref(sh), tile_tokens, _lib.VARIANTS["tensor"])
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=V.device)
+        rc = L_.race_b200_causal_fwd_qkv(_ptr(Q), _ptr(K), _ptr(V), _ptr(planes), _ptr(out), _ptr(carry),
+                                         _ptr(state), _ptr(ws), ws_bytes, ctypes.byref(sh), n_planes, tile_tokens,
+                                         1 if normalization == "global" else 0, _stream(),
+                                         _ptr(_status_word(V.device)))
+    _lib.check(rc, "race_b200_causal_fwd_qkv")
+    _raise_on_wait(V.device, "race_b200_causal_fwd_qkv")
+    if return_state:
+        A, B = unpack_state(state, L, R, dk)
+        return out, A, B
+    return out
+
+
 def race_decode_step(probsQ, probsK, V, state: torch.Tensor, eps: float = 1e-6, *,
                      state_out: torch.Tensor | None = None) -> torch.Tensor:
     """Incremental step: outputs of T <= 64 new tokens per stream (typically one) given the packed
