@@ -633,10 +633,11 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         t_wall1 = clk.mark()
-        # the timed region lasts tens of milliseconds, a few sampling periods: where fewer than three samples fell
-        # inside it, the same steps go on (untimed) for a quarter of a second and their samples are counted too
+        # the timed region lasts tens of milliseconds, a few sampling periods: only where no sample at all fell
+        # inside it do the same steps go on (untimed) for a quarter of a second, and those samples are reported
+        # (a longer run of back-to-back steps draws more power and may show lower clocks than the timed region saw)
         t_wall2 = t_wall1
-        if clk.count(t_wall0, t_wall1) < 3:
+        if clk.count(t_wall0, t_wall1) < 1:
             while time.time() - t_wall1 < 0.25:
                 step()
             torch.cuda.synchronize()
