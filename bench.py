@@ -160,6 +160,11 @@ def _time_ms(fn, warmup, steps):
         fn()
     e1.record()
     torch.cuda.synchronize()
+    # a bounded device-side wait that ran out makes the kernels return early: such a time is not a measurement
+    import race_attention_kernel_b200 as rk
+    code = rk.ops.device_status(torch.device("cuda", torch.cuda.current_device()))
+    if code:
+        raise SystemExit(f"a bounded device-side wait ran out while timing (code {code})")
     return e0.elapsed_time(e1) / steps
 
 

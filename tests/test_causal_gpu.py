@@ -78,6 +78,25 @@ def test_bf16_parity(N, T, L, R, dk):
         assert err <= BF16_TOL, f"{variant}: rel-L2 {err:.3e}"
 
 
+def test_bf16_wide_kernel_under_load():
+    """Config 3's geometry (S = 512, d_k = 128, bf16) with full 2048-token tiles (256 items per CTA) and several
+    waves of CTAs, so that the roles of the wide tensor kernel drift apart the way they do at the bench size:
+    against the CUDA-core kernels on the whole output and against the oracle on the head of one stream."""
+    rk = _ops()
+    N, T, L, R, dk = 40, 8192, 8, 64, 128
+    g = torch.Generator(device="cuda").manual_seed(3)
+    pQ = torch.softmax(torch.randn(N, T, L, R, device="cuda", generator=g), -1).bfloat16()
+    pK = torch.softmax(torch.randn(N, T, L, R, device="cuda", generator=g), -1).bfloat16()
+    V = torch.randn(N, T, dk, device="cuda", generator=g).bfloat16()
+    for _ in range(3):   # the status word is checked after every call (conftest sets RACE_B200_CHECK_STATUS)
+        out = rk.race_causal_prefix(pQ, pK, V, variant="tensor", tile_tokens=2048)
+    ref_simt = rk.race_causal_prefix(pQ, pK, V, variant="simt")
+    assert ro.rel_l2(out, ref_simt) <= BF16_TOL
+    w = 1536
+    ref = _oracle(pQ[:1, :w].cpu(), pK[:1, :w].cpu(), V[:1, :w].cpu())
+    assert ro.rel_l2(out[:1, :w], ref) <= BF16_TOL
+
+
 @pytest.mark.parametrize("tile", [32, 64, 128, 512, 4096])
 def test_forced_tile_lengths_agree(tile):
     rk = _ops()
