@@ -9,16 +9,18 @@
 //     raw(q, k, v)_t = sum_{j <= t} (q_t . k_j) v_j          (reverse: j >= t)
 // which is what the forward's tensor kernels compute when they skip the normalisation: same TMA / TMEM /
 // tcgen05 pipeline, same bf16 hi/lo limbs, the tile totals / scan / output launches with other tensors in the
-// roles of pQ, pK, V.  So the backward is three such passes and two streaming kernels:
-//     1. X  = raw(dO, V, pK)                   state of the pass = B^T, so carry_in enters transposed
-//     2. chunk sums of pK, their scan, then one streaming kernel: A_t (running sum), inv, W, dPQ, g and the
-//        chunk sums of g
+// roles of pQ, pK, V.  So the backward is three such passes and a few streaming kernels:
+//     1. block sums of pK (with the running sum at every 64-token chunk start) and their scan
+//     2. X  = raw(dO, V, pK)                   state of the pass = B^T, so carry_in enters transposed.  X is not
+//        stored: the pass takes A_t = block prefix + chunk prefix + running sum inside the chunk (one more
+//        triangular product over its V operand, which is pK) and writes dPQ = X inv, W = pQ inv and g = -dPQ W
+//        from its epilogue; then the block sums of g
 //     3. dV = raw_reverse(pK, W, dO)           state = sum W^T dO: its carry is the gradient of the final B, its
 //                                              total the gradient of the carried-in B
 //     4. P  = raw_reverse(V, dO, W)            state = the transpose of pass 3's
 //     5. reverse scan of the chunk sums of g (carry: gradient of the final A), then dPK = P + running suffix sum
-// X is written into the dPQ buffer and P into the dPK buffer (same shape and type), so the scratch memory is W
-// and g ([N, T, 64] fp32 each) plus the tile states of the passes.
+// P is written into the dPK buffer (same shape and type), so the scratch memory is W and g ([N, T, 64] fp32 each)
+// plus the block / chunk sums and the tile states of the passes.
 #include <algorithm>
 
 #include "common.cuh"
@@ -85,46 +87,37 @@ bwd_block_scan(float* __restrict__ sums, const float* __restrict__ carry_state, 
     if (total_state) total_state[n * kSF + S * D + c] = run;
 }
 
-// forward streaming kernel: A_t = prefix[block] + running sum of pK; inv = 1/(A_t + eps); W = pQ inv;
-// xdpq holds X on entry and dPQ = X inv on exit; g = -X W inv; gsum[block] = column sums of g
+// sums[n][b][c] as bwd_block_sums, and chunk[n][j][c] = the sum of x over the tokens of chunk j's block that precede
+// chunk j (64-token chunks; a block is kBlk / 64 of them)
 __global__ void __launch_bounds__(kPwThreads)
-bwd_pointwise_fwd(const float* __restrict__ pq, const float* __restrict__ pk, float* __restrict__ xdpq,
-                  const float* __restrict__ aprefix, float* __restrict__ w, float* __restrict__ g,
-                  float* __restrict__ gsum, int64_t T, int64_t nblk, int64_t total_blocks, float eps) {
+bwd_block_chunk_sums(const float* __restrict__ x, float* __restrict__ sums, float* __restrict__ chunk, int64_t T,
+                     int64_t nblk, int64_t nchunk, int64_t total_blocks) {
     const int64_t gb = (int64_t)blockIdx.x * (kPwThreads / 64) + (threadIdx.x >> 6);
     if (gb >= total_blocks) return;
     const int c = threadIdx.x & 63;
     const int64_t n = gb / nblk, b = gb - n * nblk;
     const int64_t t0 = b * kBlk, t1 = min(T, t0 + (int64_t)kBlk);
-    const int64_t base = (n * T + t0) * 64 + c;
-    float a = aprefix[gb * 64 + c], gs = 0.f;
-    int64_t off = base;
-    for (int64_t t = t0; t < t1; t += 4) {
-        float k4[4], q4[4], x4[4];
-        const int cnt = (int)min((int64_t)4, t1 - t);
+    const float* p = x + (n * T + t0) * 64 + c;
+    float* cp = chunk + (n * nchunk + t0 / 64) * 64 + c;
+    float acc = 0.f;
+    for (int64_t t = t0; t < t1; t += 64, cp += 64) {
+        *cp = acc;
+        const int cnt = (int)min((int64_t)64, t1 - t);
+        if (cnt == 64) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (u < cnt) {
-                k4[u] = __ldcs(pk + off + u * 64);
-                q4[u] = __ldcs(pq + off + u * 64);
-                x4[u] = xdpq[off + u * 64];
-            }
+            for (int u8 = 0; u8 < 8; ++u8) {
+                float v[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (u < cnt) {
-                a += k4[u];
-                const float inv = __fdividef(1.f, a + eps);
-                const float wv = q4[u] * inv;
-                const float xi = x4[u] * inv;
-                const float gv = -xi * wv;
-                xdpq[off + u * 64] = xi;
-                w[off + u * 64] = wv;
-                g[off + u * 64] = gv;
-                gs += gv;
+                for (int u = 0; u < 8; ++u) v[u] = __ldg(p + (u8 * 8 + u) * 64);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc += v[u];
             }
-        off += 4 * 64;
+        } else {
+            for (int u = 0; u < cnt; ++u) acc += __ldg(p + u * 64);
+        }
+        p += 64 * 64;
     }
-    gsum[gb * 64 + c] = gs;
+    sums[gb * 64 + c] = acc;
 }
 
 // reverse streaming kernel: dPK_j = P_j + suffix[block] + sum_{t >= j, t in block} g_t (P in pdpk on entry)
@@ -171,7 +164,7 @@ bwd_transpose_state(const float* __restrict__ src, float* __restrict__ dst) {
 }
 
 struct BwdLayout {
-    size_t tiles, tiles2, w, g, asum, gsum, st0, st1, total;
+    size_t tiles, tiles2, w, g, asum, gsum, achunk, st0, st1, total;
 };
 BwdLayout bwd_layout(const Dims& dm, int tile_tokens) {
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
@@ -187,7 +180,8 @@ BwdLayout bwd_layout(const Dims& dm, int tile_tokens) {
     l.g = l.w + tok;
     l.asum = l.g + tok;
     l.gsum = l.asum + blk;
-    l.st0 = l.gsum + blk;
+    l.achunk = l.gsum + blk;
+    l.st0 = l.achunk + align256((size_t)dm.N * ((dm.T + 63) / 64) * 64 * sizeof(float));
     l.st1 = l.st0 + st;
     l.total = l.st1 + st;
     return l;
@@ -231,18 +225,30 @@ cudaError_t causal_bwd_tensor(const void* pq, const void* pk, const void* v, con
     const int64_t nblk = (dm.T + kBlk - 1) / kBlk, total_blocks = dm.N * nblk;
     const unsigned pw_grid = (unsigned)((total_blocks + kPwThreads / 64 - 1) / (kPwThreads / 64));
 
-    // 1. X = raw(dO, V, pK) into the dPQ buffer; the state of this pass is B^T
-    if (carry_in) bwd_transpose_state<<<(unsigned)dm.N, 256, 0, stream>>>(carry_in, st_t);
-    RACE_CK(cudaGetLastError());
-    RACE_CK(causal_raw_tensor(dout, v, pk, dpq, carry_in ? st_t : nullptr, nullptr, ws_tiles, dm, tile_tokens,
-                              /*reverse=*/false, stream, status));
-    // 2. A_t, inv, W, dPQ, g, block sums of g
-    bwd_block_sums<<<pw_grid, kPwThreads, 0, stream>>>((const float*)pk, asum, dm.T, nblk, total_blocks);
+    // 1. sums of pK: per block (then scanned, carry included) and inside the block up to every chunk start
+    float* achunk = (float*)(base + l.achunk);
+    const int64_t nchunk = (dm.T + 63) / 64;
+    bwd_block_chunk_sums<<<pw_grid, kPwThreads, 0, stream>>>((const float*)pk, asum, achunk, dm.T, nblk, nchunk,
+                                                             total_blocks);
     RACE_CK(cudaGetLastError());
     bwd_block_scan<<<(unsigned)dm.N, 64, 0, stream>>>(asum, carry_in, nullptr, nblk, 0);
     RACE_CK(cudaGetLastError());
-    bwd_pointwise_fwd<<<pw_grid, kPwThreads, 0, stream>>>((const float*)pq, (const float*)pk, (float*)dpq, asum, w, g,
-                                                          gsum, dm.T, nblk, total_blocks, dm.eps);
+    // 2. X = raw(dO, V, pK), the state of the pass is B^T; its epilogue writes dPQ, W and g.  Then the block sums of g.
+    if (carry_in) bwd_transpose_state<<<(unsigned)dm.N, 256, 0, stream>>>(carry_in, st_t);
+    RACE_CK(cudaGetLastError());
+    BwdX bx;
+    bx.pq_true = (const float*)pq;
+    bx.ablock = asum;
+    bx.achunk = achunk;
+    bx.w_out = w;
+    bx.g_out = g;
+    bx.nblk = nblk;
+    bx.nchunk = nchunk;
+    bx.block_tokens = kBlk;
+    bx.eps = dm.eps;
+    RACE_CK(causal_raw_tensor(dout, v, pk, dpq, carry_in ? st_t : nullptr, nullptr, ws_tiles, dm, tile_tokens,
+                              /*reverse=*/false, stream, status, kPhaseAll, &bx));
+    bwd_block_sums<<<pw_grid, kPwThreads, 0, stream>>>(g, gsum, dm.T, nblk, total_blocks);
     RACE_CK(cudaGetLastError());
     // 3. dV = raw_reverse(pK, W, dO); state sum W^T dO: carry = gradient of the final B, total = gradient of carry_in's B.
     //    Pass 4 below has the roles of W and dO swapped, so its tile totals are the transposes of this pass's:

@@ -229,15 +229,19 @@ __device__ __forceinline__ void out_phase_init_bars(const Ctx& cx, bool again, u
 // the staged K tile into the pK operand tiles; ptab = the plane fragments in shared memory (build_plane_tab).
 // kWorkerK: the pK operand tile of a chunk is written by the warps of the chunk's own worker group (at the start of
 // their work on the chunk) instead of the converter group, which then only converts V and copies the running B.
-constexpr int kModeBucket = 0, kModeGlobal = 1, kModeRaw = 2;
+// kModeRawX: the plain product with the epilogue of the first backward pass (BwdX in launch.h): after G . V the
+// issuer also runs the triangular running-sum product over the chunk's V operand into the accumulator that G has
+// left, and the worker warps turn X (the product) into dPQ, W and g where they would store it.
+constexpr int kModeBucket = 0, kModeGlobal = 1, kModeRaw = 2, kModeRawX = 3;
 template <int kMode, bool kReverse = false, bool kProj = false, bool kWorkerK = kProj>
 __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, const float* __restrict__ pq,
                                           const CUtensorMap* map_k, const CUtensorMap* map_v,
                                           float* __restrict__ out, const float* __restrict__ slice, int64_t T,
                                           const int64_t t_begin, const int64_t t_end, const int64_t n, float eps,
                                           int heads, int withhold_chunk, const bool l2_last_use = false,
-                                          const uint32_t* ptab = nullptr) {
+                                          const uint32_t* ptab = nullptr, const BwdX* bx = nullptr) {
     constexpr bool kGlobal = kMode == kModeGlobal;
+    constexpr bool kRaw = kMode == kModeRaw || kMode == kModeRawX;   // no running sum, no normalisation in the W stage
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nch = (int)((t_end - t_begin + C - 1) / C);
     // first token of the chunk that is processed c-th
@@ -290,6 +294,59 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
 
         // pQ (kProj: the rows of Q) of chunk c in the accumulator-fragment layout, straight from global memory
         float2 pqv[16];
+        // kModeRawX: X of chunk c (in the O accumulator) and the chunk's running sum of pK (in the accumulator that
+        // held G) -> dPQ, W, g; pqv holds the true query probabilities of the chunk (requested after the W stage)
+        auto store_bwdx = [&](int c) {
+            const int64_t tok0 = chunk_tok0(c);
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+            const float* ab = bx->ablock + (n * bx->nblk + tok0 / bx->block_tokens) * S;
+            const float* ac = bx->achunk + (n * bx->nchunk + tok0 / C) * S;
+            float* w_n = bx->w_out + n * T * S;
+            float* g_n = bx->g_out + n * T * S;
+            tc_fence_after();
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float xv[16], av[16];
+                tmem_ld32(lane_base + tmO(wg) + 32 * half, xv);
+                tmem_ld32(lane_base + tmAG(wg) + 32 * half, av);
+#pragma unroll
+                for (int xx = 0; xx < 4; ++xx) {
+                    const int x = 4 * half + xx, col = 8 * x + 2 * q;
+                    const float2 b2 = __ldg(reinterpret_cast<const float2*>(ab + col));
+                    const float2 c2 = __ldg(reinterpret_cast<const float2*>(ac + col));
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int row = rbase + 8 * h;
+                        if (row < valid) {
+                            const float a0 = (b2.x + c2.x) + av[4 * xx + 2 * h];
+                            const float a1 = (b2.y + c2.y) + av[4 * xx + 2 * h + 1];
+                            const float i0 = __fdividef(1.f, a0 + bx->eps), i1 = __fdividef(1.f, a1 + bx->eps);
+                            const float2 pq2 = pqv[2 * x + h];
+                            const float2 w2 = make_float2(pq2.x * i0, pq2.y * i1);
+                            const float2 d2 = make_float2(xv[4 * xx + 2 * h] * i0, xv[4 * xx + 2 * h + 1] * i1);
+                            const int64_t o = (tok0 + row) * S + col;
+                            __stcs(reinterpret_cast<float2*>(out_n + o), d2);
+                            __stcs(reinterpret_cast<float2*>(w_n + o), w2);
+                            __stcs(reinterpret_cast<float2*>(g_n + o), make_float2(-d2.x * w2.x, -d2.y * w2.y));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+        };
+        auto load_pq_true = [&](int c) {
+            const int64_t tok0 = chunk_tok0(c);
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                const float* prow = bx->pq_true + (n * T + tok0 + row) * S + 2 * q;
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    pqv[2 * x + h] = row < valid ? __ldcs(reinterpret_cast<const float2*>(prow + 8 * x))
+                                                 : make_float2(0.f, 0.f);
+            }
+        };
         auto load_pq = [&](int c) {
             const int64_t tok0 = chunk_tok0(c);
             const int valid = (int)min((int64_t)C, t_end - tok0);
@@ -359,7 +416,7 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             // -- S2: W = pQ / (A + A_loc + eps) ----------------------------------------------------
             // (the plain product needs no running sum: W = pQ goes to the tensor cores as it is)
             float acar[16];
-            if (kMode != kModeRaw) {
+            if (!kRaw) {
             if (!(ok = wait_bar_warp(cx, kAcar + wg, ph, 102))) break;
             {
                 const float* ac = reinterpret_cast<const float*>(cx.sm + oAcar) + wg * 64;
@@ -386,7 +443,7 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     float2 w2;
-                    if (kMode == kModeRaw) {
+                    if (kRaw) {
                         w2 = pqv[2 * x + h];
                         split2(w2.x, w2.y, ohi[2 * x + h], olo[2 * x + h]);
                         continue;
@@ -416,8 +473,9 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(cx.bar(kWReady + wg));
-                if (kMode != kModeRaw && w == 3) mbar_arrive(cx.bar(kAcar + (wg ^ 1)));
+                if (!kRaw && w == 3) mbar_arrive(cx.bar(kAcar + (wg ^ 1)));
             }
+            if (kMode == kModeRawX) load_pq_true(c);   // pqv (the operand of the W stage) is free: for the epilogue
             if (kProj && c + 2 < nch) load_pq(c + 2);
             if (kGlobal) {
                 // a row's 64 buckets are spread over the four lanes of a quad, in a fixed order
@@ -454,7 +512,8 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             // -- S4: O -> global --------------------------------------------------------------------
             if (!(ok = wait_bar_warp(cx, kOReady + wg, ph, 105))) break;
             RACE_TRACE(wg, c, 3);
-            store_out(c);
+            if (kMode == kModeRawX) store_bwdx(c);
+            else store_out(c);
             RACE_TRACE(wg, c, 4);
         }
     } else if (warp < 12) {
@@ -621,7 +680,7 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
                 if (!(ok = wait_bar(cx, kKvReady + wg, ph, 401))) break;
                 tc_fence_after();
                 RACE_TRACE(4, c, 0);
-                if (kMode != kModeRaw) {
+                if (!kRaw) {
                     mma_k64_ta<true, kHiMN, 128>(dAG, a_tril, kt_mn, kIdescBase | kBmn);
                     mma_k64_ta<false, kHiMN, 128>(dAG, a_tril, kt_mn + kLimb, kIdescBase | kBmn);
                     mma_commit(cx.bar(kXReady + wg));
@@ -659,6 +718,13 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
                 mma_k64_ta<false, kHiMN, 128>(dO, a_hi, vt_mn, kIdescBase | kBmn);
                 mma_k64_ta<false, kHiMN, 128>(dO, a_hi, vt_mn + kLimb, kIdescBase | kBmn);
                 mma_k64_ta<false, kHiMN, 128>(dO, a_lo, vt_mn, kIdescBase | kBmn);
+                if (kMode == kModeRawX) {
+                    // running sum of the chunk's V operand (the pK of the backward) into the accumulator G has left:
+                    // the worker warps have read G (their arrival on kGtReady), and the next product into it, G of
+                    // the group's next chunk, is issued only after they have read this one
+                    mma_k64_ta<true, kHiMN, 128>(dAG, a_tril, vt_mn, kIdescBase | kBmn);
+                    mma_k64_ta<false, kHiMN, 128>(dAG, a_tril, vt_mn + kLimb, kIdescBase | kBmn);
+                }
                 mma_commit(cx.bar(kOReady + wg));
                 RACE_TRACE(4, c, 7);
             }
@@ -687,7 +753,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, float* __restrict__ out,
               const float* __restrict__ ws, int64_t T, int tile_tokens, float eps, int heads, int* status,
-              long long wait_cycles, int withhold_chunk, const float* __restrict__ planes) {
+              long long wait_cycles, int withhold_chunk, const float* __restrict__ planes, const BwdX bwdx) {
     extern __shared__ uint8_t smem_raw[];
     Ctx cx;
     cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -718,7 +784,7 @@ causal_out_tc(const float* __restrict__ pq, const __grid_constant__ CUtensorMap 
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     out_phase<kMode, kReverse, kProj, kWorkerK>(cx, tmem, pq, &map_k, &map_v, out, slice, T, t_begin, t_end, n, eps,
-                                                heads, (tile == 0 && n == 0) ? withhold_chunk : -1, false, ptab);
+                                                heads, (tile == 0 && n == 0) ? withhold_chunk : -1, false, ptab, &bwdx);
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) {
@@ -1385,7 +1451,7 @@ static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void*
                                      const float* carry_in, float* state_out, void* ws, bool single_pass,
                                      const Dims& dm, int tile_tokens, cudaStream_t stream, int* status, int phases,
                                      int mode, bool reverse, long long wait_cycles, int withhold_chunk,
-                                     const float* planes = nullptr);
+                                     const float* planes = nullptr, const BwdX* bwdx = nullptr);
 
 cudaError_t causal_fwd_tensor(const void* pq, const void* pk, const void* v, void* out,
                               const float* carry_in, float* state_out, void* ws, bool single_pass, const Dims& dm,
@@ -1418,9 +1484,10 @@ cudaError_t causal_fwd_qkv_tensor(const void* q, const void* k, const void* v, c
 // everywhere: carry[s][c] = sum_j k_j[s] v_j[c] (the A part is carried along and ignored).
 cudaError_t causal_raw_tensor(const void* q, const void* k, const void* v, void* out, const float* carry_in,
                               float* state_out, void* ws, const Dims& dm, int tile_tokens, bool reverse,
-                              cudaStream_t stream, int* status, int phases) {
+                              cudaStream_t stream, int* status, int phases, const BwdX* bwdx) {
+    if (bwdx && (reverse || dm.H != 1)) return cudaErrorInvalidValue;
     return tensor_f32_launch(q, k, v, out, carry_in, state_out, ws, false, dm, tile_tokens, stream, status, phases,
-                             kModeRaw, reverse, 0, -1);
+                             bwdx ? kModeRawX : kModeRaw, reverse, 0, -1, nullptr, bwdx);
 }
 
 // planes != nullptr: pq and pk are Q and K in the layout of V and the kernels form the probabilities (the
@@ -1429,10 +1496,12 @@ static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void*
                                      const float* carry_in, float* state_out, void* ws, bool single_pass,
                                      const Dims& dm, int tile_tokens, cudaStream_t stream, int* status, int phases,
                                      int mode, bool reverse, long long wait_cycles, int withhold_chunk,
-                                     const float* planes) {
+                                     const float* planes, const BwdX* bwdx) {
     const bool global_norm = mode == kModeGlobal;
     const bool proj = planes != nullptr;
-    if (proj && (single_pass || reverse || mode == kModeRaw)) return cudaErrorInvalidValue;
+    const bool raw = mode == kModeRaw || mode == kModeRawX;
+    if (proj && (single_pass || reverse || raw)) return cudaErrorInvalidValue;
+    if ((mode == kModeRawX) != (bwdx != nullptr)) return cudaErrorInvalidValue;
     // Runtime calls first: they bind the device's primary context to the calling host thread,
     // which the driver-level tensor-map encoder needs (a thread that has made no runtime call
     // yet, e.g. an autograd worker, has no current context).
@@ -1494,7 +1563,8 @@ static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void*
     }
     err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, /*write_prefix=*/true, reverse);
     if (err != cudaSuccess) return err;
-    auto kern = mode == kModeRaw
+    auto kern = mode == kModeRawX ? causal_out_tc<kModeRawX, false, false>
+                : mode == kModeRaw
                     ? (reverse ? causal_out_tc<kModeRaw, true, false> : causal_out_tc<kModeRaw, false, false>)
                     : proj ? (global_norm ? causal_out_tc<kModeGlobal, false, true> : causal_out_tc<kModeBucket, false, true>)
                            : (global_norm ? causal_out_tc<kModeGlobal, false, false>
@@ -1502,7 +1572,8 @@ static cudaError_t tensor_f32_launch(const void* pq, const void* pk, const void*
     err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return err;
     kern<<<grid, kThreads, kSmemBytes, stream>>>((const float*)pq, mk, mv, (float*)out, (const float*)ws, dm.T,
-                                                 tile_tokens, dm.eps, dm.H, status, wait_cycles, withhold_chunk, planes);
+                                                 tile_tokens, dm.eps, dm.H, status, wait_cycles, withhold_chunk, planes,
+                                                 bwdx ? *bwdx : BwdX{});
     return cudaGetLastError();
 }
 

@@ -89,9 +89,23 @@ bool tensor_qkv_supported(const Dims& dm, int dtype, int L, int R);
 cudaError_t causal_fwd_qkv_tensor(const void* q, const void* k, const void* v, const float* planes, void* out,
                                   const float* carry_in, float* state_out, void* ws, const Dims& dm, int tile_tokens,
                                   cudaStream_t stream, int* status, int phases, bool global_norm);
+// Epilogue of the first backward pass, run by the forward-direction plain product X = raw(dO, V, pK) where it stores
+// its result: with A_t = ablock[block of t] + achunk[chunk of t] + the running sum of pK inside the chunk (the V
+// operand of that pass; taken with the triangular product the forward uses for its running sum), inv = 1/(A_t + eps):
+//     out <- dPQ = X inv,   w_out <- W = pq_true inv,   g_out <- g = -dPQ W
+struct BwdX {
+    const float* pq_true;   // [N, T, 64] the query probabilities
+    const float* ablock;    // [N, nblk, 64]  sums of pK over the tokens before each block (carry included)
+    const float* achunk;    // [N, nchunk, 64] sums of pK from the start of the block to the start of each chunk
+    float* w_out;           // [N, T, 64]
+    float* g_out;           // [N, T, 64]
+    int64_t nblk, nchunk;
+    int block_tokens;       // tokens per block (a multiple of the 64-token chunk)
+    float eps;
+};
 cudaError_t causal_raw_tensor(const void* q, const void* k, const void* v, void* out, const float* carry_in,
                               float* state_out, void* ws, const Dims& dm, int tile_tokens, bool reverse,
-                              cudaStream_t stream, int* status, int phases = kPhaseAll);
+                              cudaStream_t stream, int* status, int phases = kPhaseAll, const BwdX* bwdx = nullptr);
 
 // ---- causal backward on the tensor kernels (causal_bwd_tc.cu): fp32, S = 64, d_k = 64 ----------
 bool causal_bwd_tensor_supported(const Dims& dm, int dtype);
