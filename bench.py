@@ -56,7 +56,7 @@ def parse():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sub", action="store_true", help="skip the c4 / c3 sub-records")
     ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c4", "c5", "operator", "next"],
+    ap.add_argument("--workload", default="c2", choices=["c2", "sweep", "c3", "c4", "c5", "operator", "next", "bwd"],
                     help="c2 (default): the contract line; the others print extra measurement lines")
     return ap.parse_args()
 
@@ -320,6 +320,78 @@ def sub_c3(rk, ro, dev, rank, world, peak, steps=2, warmup=1):
             "GB_s_per_gpu": gbs, "frac": gbs / peak, "parity_rel_l2": err}
 
 
+def sub_operator(rk, ro, dev, rank, world, peak, steps=5, warmup=2):
+    """The drop-in operator BatchedACE.forward(K, V, Q) on the device (M=B=1, H=8, d_k=64, K=4, L=4, fp32, T=2^20;
+    one replica per rank): with the bucket probabilities formed inside the prefix kernels (the default) and with the
+    producer kernel writing them to device memory first.  Gate: the first 512 tokens of head 0 against the oracle of
+    the whole operator."""
+    import torch.distributed as dist
+    M, B, H, dk, K, L, T = 1, 1, 8, 64, 4, 4, 1 << 20
+    torch.manual_seed(1234)
+    ace = rk.BatchedACE(dk, K, L, M, device=dev)
+    g = torch.Generator(device=dev).manual_seed(4000 + rank)
+    Kh, Vh, Qh = (torch.randn(M, B, T, H, dk, device=dev, generator=g) for _ in range(3))
+    w = 512
+    ref = ro.batched_ace_forward(ace.planes_T.cpu().double(), ace.protos_T.cpu().double(),
+                                 *(t[:, :, :w, :1].cpu().double() for t in (Kh, Vh, Qh)), L, K)
+    res = {}
+    for mode in ("fused", "two_step"):
+        ace.fuse_producer = mode == "fused"
+        with torch.no_grad():
+            err = ro.rel_l2(ace(Kh, Vh, Qh)[:, :, :w, :1], ref)
+            if not err <= 1e-4:
+                raise SystemExit(f"operator parity gate failed ({mode}): rel-L2 {err:.3e}")
+            if world > 1:
+                dist.barrier()
+            ms = _time_ms(lambda: ace(Kh, Vh, Qh), warmup, steps)
+        t = torch.tensor([ms, err], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res[mode] = (t[0].item(), t[1].item())
+    n_tok = M * B * H * T
+    ms_f, ms_t = res["fused"][0], res["two_step"][0]
+    return {"workload": f"BatchedACE.forward f32 M=B=1 H={H} T={T} d_k={dk} K={K} L={L}, one replica per rank",
+            "ranks": world, "ms_per_step": ms_f, "value": world * n_tok / ms_f / 1e3, "unit": "Mtok/s",
+            "frac": n_tok * 4 * dk * 4 / (ms_f * 1e-3) / 1e9 / peak,
+            "algorithmic_bytes_per_token_stream": 4 * dk * 4,
+            "two_step_ms_per_step": ms_t, "steps": steps, "warmup": warmup,
+            "parity_rel_l2": max(res["fused"][1], res["two_step"][1]),
+            "path": "race_b200_causal_fwd_qkv (probabilities formed in-kernel); two_step = "
+                    "race_b200_bucket_probs_streams x2 + race_b200_causal_fwd"}
+
+
+def sub_bwd(rk, ro, dev, rank, world, peak, steps=3, warmup=1):
+    """The causal backward (fp32, N=8 streams per rank, T=2^20, d_k=64, L=4, R=16): dPQ, dPK, dV from pQ, pK, V, dO.
+    Gate: a small case through the same kernels against the oracle's closed form in fp64."""
+    import torch.distributed as dist
+    N, T, L, R, dk = 8, 1 << 20, 4, 16, 64
+    pQ, pK, V = ro.synthetic_probs(2, 4500, L, R, dk, seed=41)
+    dO = torch.randn(2, 4500, dk, generator=torch.Generator().manual_seed(42))
+    ref = ro.causal_backward_closed_form(pQ.double(), pK.double(), V.double(), dO.double())
+    got = rk.race_causal_backward(pQ.to(dev), pK.to(dev), V.to(dev), dO.to(dev))
+    err = max(ro.rel_l2(a, b) for a, b in zip(got[:3], ref[:3]))
+    if not err <= 1e-4:
+        raise SystemExit(f"backward parity gate failed: rel-L2 {err:.3e}")
+    g = torch.Generator(device=dev).manual_seed(5000 + rank)
+    q = _probs_on_device(N, T, L, R, torch.float32, g, dev)
+    k = _probs_on_device(N, T, L, R, torch.float32, g, dev)
+    v = torch.randn(N, T, dk, device=dev, generator=g)
+    do = torch.randn(N, T, dk, device=dev, generator=g)
+    if world > 1:
+        dist.barrier()
+    ms = _time_ms(lambda: rk.race_causal_backward(q, k, v, do), warmup, steps)
+    t = torch.tensor([ms, err], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, err = t[0].item(), t[1].item()
+    bb = N * T * 4 * (4 * L * R + 3 * dk)
+    return {"workload": f"causal backward f32 N={N}/GPU T={T} d_k={dk} L={L} R={R}", "ranks": world,
+            "ms_per_step": ms, "value": world * N * T / ms / 1e3, "unit": "Mtok/s",
+            "GB_s_per_gpu": bb / (ms * 1e-3) / 1e9, "frac": bb / (ms * 1e-3) / 1e9 / peak,
+            "algorithmic_bytes_per_token_stream": 4 * (4 * L * R + 3 * dk), "steps": steps, "warmup": warmup,
+            "parity_rel_l2": err}
+
+
 def workload_c4(args):
     """The sequence-sharded configuration alone (run under torchrun for more than one rank)."""
     import torch.distributed as dist
@@ -498,6 +570,18 @@ def extra_workloads(args):
             print(json.dumps({"workload": "causal_fwd_cuda_cores", "normalization": norm, "N": N, "T": T,
                               "ms": round(ms, 3), "Mtok_s": round(N * T / ms / 1e3, 1),
                               "frac_measured_peak": round(N * T * 1024 / ms / 1e6 / peak, 4)}), flush=True)
+    elif args.workload == "bwd":
+        # the causal backward alone (fp32, N=8, d_k=64, L=4, R=16) at --seq-len: the line of the "next" workload,
+        # as a command of its own for launch lists
+        N, T, L, R, dk = 8, args.seq_len, 4, 16, 64
+        pQ, pK = probs(N, T, L, R, torch.float32, g), probs(N, T, L, R, torch.float32, g)
+        V = torch.randn(N, T, dk, device=dev, generator=g)
+        dO = torch.randn(N, T, dk, device=dev, generator=g)
+        ms = _time_ms(lambda: rk.race_causal_backward(pQ, pK, V, dO), 2, 5)
+        bb = N * T * 4 * (4 * 64 + 3 * 64)
+        print(json.dumps({"workload": "causal_bwd", "dtype": "f32", "N": N, "T": T, "ms": round(ms, 3),
+                          "Mtok_s": round(N * T / ms / 1e3, 1), "GB_s": round(bb / ms / 1e6, 1),
+                          "frac_measured_peak": round(bb / ms / 1e6 / peak, 4)}), flush=True)
     elif args.workload == "operator":
         # the drop-in operator end to end on the device: BatchedACE.forward(K, V, Q); fp32, M=1, B=1, H=8, d_k=64,
         # K=4, L=4 (the reference CPU configuration at longer T).  "fused": the prefix kernels form the bucket
@@ -697,11 +781,15 @@ def main():
     torch.cuda.empty_cache()
 
     # sub-records: the sequence-sharded and the bf16 configuration on the same ranks
-    c4 = c3 = None
+    c4 = c3 = operator = bwd = None
     if not args.no_sub and args.dtype == "f32" and T == (1 << 20):
         c4 = sub_c4(rk, ro, dev, rank, world)
         torch.cuda.empty_cache()
         c3 = sub_c3(rk, ro, dev, rank, world, peak)
+        torch.cuda.empty_cache()
+        operator = sub_operator(rk, ro, dev, rank, world, peak)
+        torch.cuda.empty_cache()
+        bwd = sub_bwd(rk, ro, dev, rank, world, peak)
         torch.cuda.empty_cache()
         code = rk.ops.device_status(dev)
         if code:
@@ -775,6 +863,7 @@ def main():
                            "parity_gate": "first 1024 tokens of stream 0; last 2048 tokens of the last stream vs the "
                                           "oracle with the fp64 carry; final state of every stream vs fp64 totals"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "c4": c4, "c3": c3, "single_pass": single,
+                "operator": operator, "causal_bwd": bwd,
                 "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
         print(json.dumps(line), flush=True)
     if world > 1:
