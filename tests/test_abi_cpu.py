@@ -186,3 +186,31 @@ def test_single_pass_variant_sizes():
     # too small a workspace for the single-pass form is refused, not silently switched
     rc = L.race_b200_causal_fwd(256, 256, 256, 256, None, None, 256, three, ctypes.byref(sh), 1024, 3, None, None)
     assert rc == -4
+
+
+def test_qkv_entry_argument_errors_without_launch():
+    """race_b200_causal_fwd_qkv: supported geometry and the argument errors that come before any launch."""
+    L = _lib.lib()
+    ok = _shape()
+    assert L.race_b200_qkv_is_supported(ctypes.byref(ok), 4) == 1
+    assert L.race_b200_qkv_is_supported(ctypes.byref(_shape(heads=4)), 4) == 1          # the operator's layout
+    assert L.race_b200_qkv_is_supported(ctypes.byref(_shape(L=2)), 4) == 0              # two tables
+    assert L.race_b200_qkv_is_supported(ctypes.byref(_shape(R=8)), 3) == 0              # three planes per table
+    assert L.race_b200_qkv_is_supported(ctypes.byref(_shape(dk=128)), 4) == 0
+    assert L.race_b200_qkv_is_supported(ctypes.byref(_shape(dtype=1)), 4) == 0          # bf16
+    assert L.race_b200_qkv_is_supported(ctypes.byref(ok), 3) == 0                       # R != 2^K
+    buf = ctypes.create_string_buffer(4096 + 16)
+    p = (ctypes.addressof(buf) + 15) & ~15
+
+    def call(shape, q=p, k=p, v=p, planes=p, out=p, ws=p, ws_bytes=1 << 40, n_planes=4, tile=0):
+        return L.race_b200_causal_fwd_qkv(q, k, v, planes, out, None, None, ws, ws_bytes, ctypes.byref(shape),
+                                          n_planes, tile, 0, None, None)
+    assert call(ok, n_planes=3) == -2                    # RACE_ERR_SHAPE: n_buckets != 2^K
+    assert call(_shape(dtype=1)) == -6                   # RACE_ERR_VARIANT: bf16 has no such kernel
+    assert call(_shape(L=2)) == -6
+    assert call(ok, tile=100) == -5                      # RACE_ERR_TILE
+    assert call(ok, q=None) == -1                        # RACE_ERR_NULL
+    assert call(ok, planes=None) == -1
+    assert call(ok, k=p + 4) == -3                       # RACE_ERR_ALIGN
+    assert call(ok, ws_bytes=16) == -4                   # RACE_ERR_WORKSPACE
+    assert call(_shape(N=0)) == 0                        # nothing to do
