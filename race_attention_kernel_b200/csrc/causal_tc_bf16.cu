@@ -496,25 +496,29 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
 // ------------------------------------------------------------------------------------------------
 constexpr int kT1Threads = 10 * 32;
 constexpr int kT1Stages = 4;
-template <int D>
+// GP bucket groups per CTA: they share the V tile of a chunk, which the CTAs of a (stream, tile) otherwise fetch once
+// per group (with GP = 1 and eight groups the kernel moved 3 KB per token-stream from L2 for 1.25 KB of inputs and
+// was bound by that)
+template <int D, int GP>
 struct Lay1 {
-    static constexpr int kTileP = C * 64 * 2, kTileV = C * D * 2, kStage = kTileP + kTileV;
+    static constexpr int kTileP = C * 64 * 2, kTileV = C * D * 2, kStage = GP * kTileP + kTileV;
     static constexpr int oStage = 0;
-    static constexpr int oKt = oStage + kT1Stages * kStage;   // [2]
-    static constexpr int oVt = oKt + 2 * kTileP;              // [2]
-    static constexpr int oRed = oVt + 2 * kTileV;             // [8 warps][4][8] fp32
-    static constexpr int oBars = oRed + 8 * 32 * 4;
+    static constexpr int oKt = oStage + kT1Stages * kStage;   // [2][GP]
+    static constexpr int oVt = oKt + 2 * GP * kTileP;         // [2]
+    static constexpr int oRed = oVt + 2 * kTileV;             // [GP][8 warps][4][8] fp32
+    static constexpr int oBars = oRed + GP * 8 * 32 * 4;
     static constexpr int oMisc = oBars + 16 * 8;
     static constexpr int kSmem = oMisc + 16 + 1024;
 };
 enum Bar1B { b1Full = 0, b1Empty = 4, b1KvReady = 8, b1KvFree = 10, b1Done = 12 };
 
-template <int D>
+template <int D, int GP>
 __global__ void __launch_bounds__(kT1Threads, 1)
 tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     float* __restrict__ ws, int64_t T, int S, int G, int tile_tokens, int* status) {
-    using Ly = Lay1<D>;
+    using Ly = Lay1<D, GP>;
     constexpr int DH = D / 64;
+    static_assert(GP * D <= 512, "one accumulator per group");
     extern __shared__ uint8_t smem_raw[];
     Ctx cx;
     cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -525,14 +529,15 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + Ly::oMisc);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = (int)(blockIdx.x % (unsigned)G);
-    const int64_t tiles = gridDim.x / G, tile = blockIdx.x / G, n = blockIdx.y;
+    const int GC = G / GP;                                   // CTAs per (stream, tile)
+    const int g = (int)(blockIdx.x % (unsigned)GC) * GP;     // first bucket group of this CTA
+    const int64_t tiles = gridDim.x / GC, tile = blockIdx.x / GC, n = blockIdx.y;
     const int64_t t_begin = tile * tile_tokens;
     const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
     const int nch = (int)((t_end - t_begin + C - 1) / C);
     float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
-    float* sliceB = slice + (int64_t)g * SG * D;
-    float* sliceA = slice + (int64_t)S * D + g * SG;
+    float* sliceB = slice + (int64_t)g * SG * D;            // group g + gp: + gp * SG * D
+    float* sliceA = slice + (int64_t)S * D + g * SG;        //               + gp * SG
 
     if (tid == 0) {
         *cx.abort_flag = 0;
@@ -549,7 +554,7 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     }
     if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(cx.sm_u32 + Ly::oMisc), "r"((uint32_t)D) : "memory");
+                     ::"r"(cx.sm_u32 + Ly::oMisc), "r"((uint32_t)(GP * D)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -559,21 +564,26 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 
     if (warp < 8) {
         const int wg = warp >> 2, wtid = tid & 127;
-        float asum[4][8];
+        float asum[GP][4][8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int gp = 0; gp < GP; ++gp)
 #pragma unroll
-            for (int e = 0; e < 8; ++e) asum[i][e] = 0.f;
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) asum[gp][i][e] = 0.f;
         bool ok = true;
         for (int c = wg; c < nch && ok; c += 2) {
             const int st = c % kT1Stages;
             if (!(ok = wait_bar_warp(cx, b1Full + st, (c / kT1Stages) & 1, 111))) break;
             if (c >= 2 && !(ok = wait_bar_warp(cx, b1KvFree + wg, ((c >> 1) - 1) & 1, 112))) break;
             const uint8_t* stage = cx.sm + Ly::oStage + st * Ly::kStage;
-            copy_tile<64, true>(stage, cx.sm + Ly::oKt + wg * Ly::kTileP, 0, wtid, asum);
+#pragma unroll
+            for (int gp = 0; gp < GP; ++gp)
+                copy_tile<64, true>(stage + gp * Ly::kTileP, cx.sm + Ly::oKt + (wg * GP + gp) * Ly::kTileP, 0, wtid,
+                                    asum[gp]);
 #pragma unroll
             for (int dh = 0; dh < DH; ++dh)
-                copy_tile<D, false>(stage + Ly::kTileP + dh * 8192, cx.sm + Ly::oVt + wg * Ly::kTileV, dh * 64,
+                copy_tile<D, false>(stage + GP * Ly::kTileP + dh * 8192, cx.sm + Ly::oVt + wg * Ly::kTileV, dh * 64,
                                     wtid, nullptr);
             fence_proxy_async();
             __syncwarp();
@@ -581,16 +591,19 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
         // column sums: item it of a thread covers columns 8 j .. 8 j + 7 with j = 2 it + (wtid >> 6),
         // lanes of a warp hold different token rows of the same columns
-        float* red = reinterpret_cast<float*>(cx.sm + Ly::oRed) + warp * 32;
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int gp = 0; gp < GP; ++gp) {
+            float* red = reinterpret_cast<float*>(cx.sm + Ly::oRed) + (gp * 8 + warp) * 32;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                float x = asum[i][e];
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
-                if (lane == 0) red[i * 8 + e] = x;
-            }
+                for (int e = 0; e < 8; ++e) {
+                    float x = asum[gp][i][e];
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+                    if (lane == 0) red[i * 8 + e] = x;
+                }
+        }
     } else if (warp == 8) {
         if (lane == 0) {
             int issued = 0;
@@ -601,10 +614,12 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 const uint32_t bar = cx.bar(b1Full + st);
                 const int tok = (int)(t_begin + (int64_t)c * C);
                 mbar_arrive_expect_tx(bar, Ly::kStage);
-                tma_load_4d(dst, &map_k, bar, 0, tok, g, (int)n);
+#pragma unroll
+                for (int gp = 0; gp < GP; ++gp)
+                    tma_load_4d(dst + gp * Ly::kTileP, &map_k, bar, 0, tok, g + gp, (int)n);
 #pragma unroll
                 for (int dh = 0; dh < DH; ++dh)
-                    tma_load_4d(dst + Ly::kTileP + dh * 8192, &map_v, bar, 0, tok, dh, (int)n);
+                    tma_load_4d(dst + GP * Ly::kTileP + dh * 8192, &map_v, bar, 0, tok, dh, (int)n);
                 issued = c + 1;
             }
             if (*cx.abort_flag) {
@@ -624,10 +639,13 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 const int wg = c & 1;
                 if (!(ok = wait_bar(cx, b1KvReady + wg, (c >> 1) & 1, 411))) break;
                 tc_fence_after();
-                const uint32_t kt_mn = lo_mn(smb + Ly::oKt + wg * Ly::kTileP);
                 const uint32_t vt_mn = lo_mn_w(smb + Ly::oVt + wg * Ly::kTileV, Lay<D>::kLboV);
-                if (c == 0) mma_k64<true, kHiMN, 128, kHiMN, Lay<D>::kStepV>(tm, kt_mn, vt_mn, idesc_n(D) | kAmn | kBmn);
-                else mma_k64<false, kHiMN, 128, kHiMN, Lay<D>::kStepV>(tm, kt_mn, vt_mn, idesc_n(D) | kAmn | kBmn);
+#pragma unroll
+                for (int gp = 0; gp < GP; ++gp) {
+                    const uint32_t kt_mn = lo_mn(smb + Ly::oKt + (wg * GP + gp) * Ly::kTileP);
+                    if (c == 0) mma_k64<true, kHiMN, 128, kHiMN, Lay<D>::kStepV>(tm + gp * D, kt_mn, vt_mn, idesc_n(D) | kAmn | kBmn);
+                    else mma_k64<false, kHiMN, 128, kHiMN, Lay<D>::kStepV>(tm + gp * D, kt_mn, vt_mn, idesc_n(D) | kAmn | kBmn);
+                }
                 mma_commit(cx.bar(b1KvFree + wg));
             }
             mma_commit(cx.bar(b1Done));
@@ -639,28 +657,33 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             float v[32];
             const int q = lane & 3, rbase = 16 * warp + (lane >> 2);
 #pragma unroll
-            for (int dh = 0; dh < DH; ++dh) {
-                tc_fence_after();
-                tmem_ld64(((uint32_t)(32 * warp) << 16) + tmem + dh * 64, v);
-                tc_fence_before();
+            for (int gp = 0; gp < GP; ++gp)
 #pragma unroll
-                for (int x = 0; x < 8; ++x)
+                for (int dh = 0; dh < DH; ++dh) {
+                    tc_fence_after();
+                    tmem_ld64(((uint32_t)(32 * warp) << 16) + tmem + gp * D + dh * 64, v);
+                    tc_fence_before();
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
-                        *reinterpret_cast<float2*>(sliceB + (rbase + 8 * h) * D + dh * 64 + 8 * x + 2 * q) =
-                            make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
-            }
+                    for (int x = 0; x < 8; ++x)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            *reinterpret_cast<float2*>(sliceB + ((int64_t)gp * SG + rbase + 8 * h) * D + dh * 64 +
+                                                       8 * x + 2 * q) = make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+                }
             if (tid < 64) {
-                // column s = 8 j + e, j = 2 item + (warp-in-group >> 1): partials of both groups and
+                // column s = 8 j + e, j = 2 item + (warp-in-group >> 1): partials of both converter groups and
                 // both row halves in a fixed order
                 const int j = tid >> 3, e = tid & 7, it = j >> 1, wh = (j & 1) * 2;
-                const float* red = reinterpret_cast<const float*>(cx.sm + Ly::oRed);
-                float a = 0.f;
 #pragma unroll
-                for (int gg = 0; gg < 2; ++gg)
+                for (int gp = 0; gp < GP; ++gp) {
+                    const float* red = reinterpret_cast<const float*>(cx.sm + Ly::oRed) + gp * 8 * 32;
+                    float a = 0.f;
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) a += red[(gg * 4 + wh + half) * 32 + it * 8 + e];
-                sliceA[tid] = a;
+                    for (int gg = 0; gg < 2; ++gg)
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) a += red[(gg * 4 + wh + half) * 32 + it * 8 + e];
+                    sliceA[gp * SG + tid] = a;
+                }
             }
         }
     }
@@ -668,7 +691,7 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     __syncthreads();
     if (warp == 9) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)D) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(GP * D)) : "memory");
     }
 }
 
@@ -1144,10 +1167,13 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
                         int* status, int phases, bool global_norm) {
     const int G = dm.S / SG;
     if (global_norm && G > 1) return cudaErrorInvalidValue;   // the one-group kernel has the global form
-    auto k1 = tile_totals_tc_bf16<D>;
+    // two bucket groups per totals CTA where there are at least two (they share the V tile)
+    const int GP = G >= 2 ? 2 : 1;
+    auto k1 = GP == 2 ? tile_totals_tc_bf16<D, 2> : tile_totals_tc_bf16<D, 1>;
+    const int k1_smem = GP == 2 ? Lay1<D, 2>::kSmem : Lay1<D, 1>::kSmem;
     auto k3 = global_norm ? causal_out_tc_bf16<D, true> : causal_out_tc_bf16<D, false>;
     // runtime call first: binds the primary context to this host thread for the map encoder
-    cudaError_t err = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay1<D>::kSmem);
+    cudaError_t err = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, k1_smem);
     if (err != cudaSuccess) return err;
     CUtensorMap mk, mv;
     if (!make_map_bf16(&mk, pk, dm.N, dm.T, dm.S) || !make_map_bf16(&mv, v, dm.N, dm.T, dm.D))
@@ -1155,7 +1181,8 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     dim3 grid((unsigned)(tiles * G), (unsigned)dm.N);
     if (phases & kPhaseTotals) {
-        k1<<<grid, kT1Threads, Lay1<D>::kSmem, stream>>>(mk, mv, (float*)ws, dm.T, dm.S, G, tile_tokens, status);
+        dim3 grid1((unsigned)(tiles * (G / GP)), (unsigned)dm.N);
+        k1<<<grid1, kT1Threads, k1_smem, stream>>>(mk, mv, (float*)ws, dm.T, dm.S, G, tile_tokens, status);
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
     }
