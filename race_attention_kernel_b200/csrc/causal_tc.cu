@@ -116,7 +116,7 @@ __device__ __forceinline__ void convert_tile(const uint8_t* __restrict__ stage, 
 // TMA unit fills for a probabilities tile.  kSum adds the lane's probabilities into asum[16] (column 16 t + i).
 template <bool kSum>
 __device__ __forceinline__ void produce_tile(const uint8_t* __restrict__ stage, uint8_t* __restrict__ hi,
-                                             uint8_t* __restrict__ lo, const uint32_t* ptab, int w, int lane,
+                                             uint8_t* __restrict__ lo, const PlaneFrags& pf, int w, int lane,
                                              int valid, float (&asum)[16]) {
     const int g = lane >> 2, t = lane & 3;
     float2 raw[16];
@@ -130,8 +130,6 @@ __device__ __forceinline__ void produce_tile(const uint8_t* __restrict__ stage, 
             raw[2 * u + h] = *reinterpret_cast<const float2*>(src + ((unit ^ (r & 7)) << 4) + ((t & 1) << 3));
         }
     }
-    PlaneFrags pf;
-    load_plane_frags_tab(ptab, lane, pf);
     float c[2][4];
     project_rows(raw, pf, c);
     float vals[2][16];
@@ -363,13 +361,13 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
         if (kProj && wg < nch) load_pq(wg);
         // kWorkerK: the pK operand tile of chunk c from the group's stage (convert, or with kProj form the
         // probabilities), into buffer (c >> 1) & 1 of the group, last read by the products of the group's chunk c - 4
-        auto write_kt = [&](int c) {
+        auto write_kt = [&](int c, const PlaneFrags& pf) {
             const int kb = (c >> 1) & 1;
             uint8_t* kt_hi = cx.sm + oKt + (wg * 2 + kb) * 2 * kOpTile;
             const uint8_t* stage = cx.sm + oStage + wg * kStageBytes;
             if (kProj) {
                 float unused[16];
-                produce_tile<false>(stage, kt_hi, kt_hi + kOpTile, ptab, w, lane,
+                produce_tile<false>(stage, kt_hi, kt_hi + kOpTile, pf, w, lane,
                                     (int)min((int64_t)C, t_end - chunk_tok0(c)), unused);
             } else {
                 convert_tile(stage, kt_hi, kt_hi + kOpTile, tid & 127);
@@ -379,10 +377,8 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             if (lane == 0) { mbar_arrive(cx.bar(kKvReady + wg)); mbar_arrive(cx.bar(kEmpty + wg)); }
         };
         // kProj: the rows of Q in pqv -> the probabilities of chunk c, in place (rows past the end stay zero)
-        auto q_to_probs = [&](int c) {
+        auto q_to_probs = [&](int c, const PlaneFrags& pf) {
             const int valid = (int)min((int64_t)C, t_end - chunk_tok0(c));
-            PlaneFrags pf;
-            load_plane_frags_tab(ptab, lane, pf);
             float cp[2][4];
             project_rows(pqv, pf, cp);
             fragment_probs(cp, lane, 0.125f, pqv);
@@ -405,12 +401,14 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             // Both at the start of the chunk, where the group would otherwise idle until the running A of the other
             // group's chunk arrives.  (Done during the waits for this group's own products instead, they delayed the
             // reaction to those products by more than they saved.)
+            PlaneFrags pf;   // one read of the plane fragments serves both tiles of the chunk
+            if (kProj) load_plane_frags_tab(ptab, lane, pf);
             if (kWorkerK) {
                 if (c >= 4 && !(ok = wait_bar_warp(cx, kKtFree + wg * 2 + (int)ph, (uint32_t)(((c >> 2) - 1) & 1), 108))) break;
                 if (!(ok = wait_bar_warp(cx, kFull + wg, ph, 109))) break;
-                write_kt(c);
+                write_kt(c, pf);
             }
-            if (kProj) q_to_probs(c);
+            if (kProj) q_to_probs(c, pf);
             RACE_TRACE(wg, c, 0);
 
             // -- S2: W = pQ / (A + A_loc + eps) ----------------------------------------------------
@@ -591,7 +589,9 @@ __device__ __forceinline__ void out_phase(const Ctx& cx, const uint32_t tmem, co
             if (!kWorkerK) {
                 if (kProj) {
                     float unused[16];
-                    produce_tile<false>(stage, kt_hi, kt_hi + kOpTile, ptab, w, lane,
+                    PlaneFrags pf;
+                    load_plane_frags_tab(ptab, lane, pf);
+                    produce_tile<false>(stage, kt_hi, kt_hi + kOpTile, pf, w, lane,
                                         (int)min((int64_t)C, t_end - chunk_tok0(c)), unused);
                 } else {
                     convert_tile(stage, kt_hi, kt_hi + kOpTile, wtid);
@@ -939,6 +939,8 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
         float psum[16];   // kProj: the lane's table (columns 16 (lane % 4) + i), rows lane / 4 and lane / 4 + 8
 #pragma unroll
         for (int i = 0; i < 16; ++i) psum[i] = 0.f;
+        PlaneFrags pf;    // kProj: the plane fragments stay in registers for the whole tile
+        if (kProj) load_plane_frags_tab(ptab, lane, pf);
         bool ok = true;
         int i = 0;   // the group's i-th chunk
         RACE_PROF_T(tq);
@@ -950,7 +952,7 @@ __device__ __forceinline__ void totals_phase(const Ctx& cx, const uint32_t tmem,
             if (i >= 1 && !(ok = wait_bar_warp(cx, k1KvFree + wg, (uint32_t)((i - 1) & 1), 112))) break;
             if (tid == 0) RACE_PROF_LANE(9, tq);
             if (kProj)
-                produce_tile<true>(stage, kt_hi, kt_hi + kOpTile, ptab, warp & 3, lane,
+                produce_tile<true>(stage, kt_hi, kt_hi + kOpTile, pf, warp & 3, lane,
                                    (int)min((int64_t)C, t_end - (t_begin + (int64_t)c * C)), psum);
             else
                 convert_tile_sum(stage, kt_hi, kt_hi + kOpTile, wtid, asum);
