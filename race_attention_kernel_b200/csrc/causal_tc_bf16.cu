@@ -1119,6 +1119,504 @@ causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Output pass for S > 64 with an even number (>= 4) of bucket groups ("wide, four worker groups").  Same
+// decomposition as causal_out_wide_bf16 (one CTA = stream, tile, 32-column slice of the head dimension, all
+// groups; items = (chunk, group) in order).  What bounds that kernel is the worker group's own sequence per
+// item (wait for A_loc, tcgen05.ld, W, tcgen05.st, arrive: about 3 k clk whatever the arithmetic in it), of
+// which only two run at a time.  Here four worker groups take every fourth item, each with its own A_loc / W
+// buffer.  The columns for two more buffers come from stacking the states of two adjacent groups in one
+// M = 128 accumulator (128 buckets x 32 columns on all 128 lanes of tensor memory: 4 x 32 columns for eight
+// groups instead of 8 x 32); the state update then runs once per pair of groups (M = 128) on a pK tile that is
+// 128 buckets wide, and the auxiliary group reads a pair's state with the 32-lane TMEM load.
+// TMEM (512 columns): pair states 4 x 32 | A_loc / W of the four worker groups 4 x 64 | G 64 | O 2 x 32.
+// ------------------------------------------------------------------------------------------------
+constexpr int kW4Threads = 26 * 32;
+constexpr int kW4ConverterWarp0 = 16, kW4AuxWarp0 = 20, kW4ProducerWarp = 24, kW4MmaWarp = 25;
+constexpr int kW4Stages = 4;      // ring of pK pair tiles (stage and operand buffers)
+struct LayW4 {
+    static constexpr int kTileP = C * 64 * 2;     // 64 x 64 bf16
+    static constexpr int kTileP2 = 2 * kTileP;    // the pK tiles of two adjacent groups: [64 tokens][128 buckets]
+    static constexpr int kTileS = C * DS * 2;     // 64 x 32 bf16
+    static constexpr int oStage = 0;                            // [kW4Stages][kTileP2] staged: two boxes of 64 x 64
+    static constexpr int oVst = oStage + kW4Stages * kTileP2;   // [2][kTileS] staged V slice
+    static constexpr int oKt = oVst + 2 * kTileS;               // [kW4Stages][kTileP2] operand tile, 128 wide
+    static constexpr int oVt = oKt + kW4Stages * kTileP2;       // [2][kTileS]
+    static constexpr int oBt = oVt + 2 * kTileS;                // [4 pairs][128 x 32] state operand tiles
+    static constexpr int oTril = oBt + 8 * kTileS;
+    static constexpr int oAcar = oTril + kTileP;                // [8][64] fp32
+    static constexpr int oBars = oAcar + 8 * 64 * 4;
+    static constexpr int kNumBars = 64;
+    static constexpr int oMisc = oBars + kNumBars * 8;
+    static constexpr int kSmem = oMisc + 16 + 1024;
+    static constexpr uint32_t kLboS = (DS / 8) * 128;           // MN-major [.][32] tile: stride between 8-row groups
+    static constexpr uint32_t kStepS = (2 * kLboS) >> 4;
+    static constexpr uint32_t kLboP2 = (128 / 8) * 128;         // MN-major [64][128] tile: stride between 8-token groups
+    static constexpr uint32_t kStepP2 = (2 * kLboP2) >> 4;
+    static constexpr uint32_t kHiK2 = (kLboP2 >> 4) | (1u << 14);    // K-major use of the 128-wide tile: sbo = 2048
+};
+static_assert(LayW4::kSmem <= 227 * 1024, "shared memory of the four-group wide kernel");
+enum BarW4 {
+    w4Full = 0, w4Empty = w4Full + kW4Stages, w4KReady = w4Empty + kW4Stages, w4KFree = w4KReady + kW4Stages,
+    w4VFull = w4KFree + kW4Stages, w4VEmpty = w4VFull + 2, w4VReady = w4VEmpty + 2, w4VFree = w4VReady + 2,
+    w4XReady = w4VFree + 2,          // [4] A_loc of the worker group's item complete
+    w4WReady = w4XReady + 4,         // [4] W of the item in tensor memory (four warps)
+    w4AcarReady = w4WReady + 4,      // [4] the item's running A written by the warp that owns row 63
+    w4AcarRead = w4AcarReady + 4,    // [4] ... read by the four warps of the worker group
+    w4PairDone = w4AcarRead + 4,     // [4] every product of a pair of groups of the chunk has run
+    w4BtReady = w4PairDone + 4,      // [4] state operand tile of the pair written (four warps)
+    w4GtReady = w4BtReady + 4, w4OReady = w4GtReady + 1, w4OFree = w4OReady + 1, w4Drain = w4OFree + 2,
+    w4NumBars = w4Drain + 1
+};
+static_assert(w4NumBars <= LayW4::kNumBars, "barrier array of the four-group wide kernel");
+
+__device__ __forceinline__ constexpr uint32_t idesc_mn(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// 32 lanes x 32 columns of fp32: thread t of the warp <-> lane (lane of taddr) + t, register j <-> column + j
+__device__ __forceinline__ void tmem_ld_rows32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st_rows32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+        ::"r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])),
+          "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// 16 lanes x 16 columns of packed bf16 pairs (half of tmem_st_pairs: 32 K-values per row).  No wait inside.
+__device__ __forceinline__ void tmem_st_pairs4(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x128b.x4.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr) : "memory");
+}
+
+__global__ void __launch_bounds__(kW4Threads, 1)
+causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_vs, __nv_bfloat16* __restrict__ out,
+                      const float* __restrict__ ws, int64_t T, int S, int D, int G, int tile_tokens, float eps,
+                      int* status) {
+    using Ly = LayW4;
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cx;
+    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cx.sm_u32 = smem_u32(cx.sm);
+    cx.bars = Ly::oBars;
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + Ly::oMisc + 4);
+    cx.status = status;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + Ly::oMisc);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int NS = D / DS;                                   // slices of the head dimension
+    const int P = G / 2;                                     // pairs of bucket groups
+    const int js = (int)(blockIdx.x % (unsigned)NS);
+    const int64_t tiles = gridDim.x / NS;
+    const int64_t tile = blockIdx.x / NS, n = blockIdx.y;
+    const int64_t t_begin = tile * tile_tokens;
+    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
+    const int nch = (int)((t_end - t_begin + C - 1) / C);
+    const int nitems = nch * G;                              // an item = (chunk, group); a pair item = two of them
+    const int npairs = nch * P;
+    const float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+
+    if (tid == 0) {
+        *cx.abort_flag = 0;
+        for (int i = 0; i < kW4Stages; ++i) {
+            mbar_init(cx.bar(w4Full + i), 1);
+            mbar_init(cx.bar(w4Empty + i), 4);
+            mbar_init(cx.bar(w4KReady + i), 4);
+            mbar_init(cx.bar(w4KFree + i), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(cx.bar(w4VFull + i), 1);
+            mbar_init(cx.bar(w4VEmpty + i), 4);
+            mbar_init(cx.bar(w4VReady + i), 4);
+            mbar_init(cx.bar(w4VFree + i), 1);
+            mbar_init(cx.bar(w4OFree + i), 4);
+        }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(cx.bar(w4XReady + i), 1);
+            mbar_init(cx.bar(w4WReady + i), 4);
+            mbar_init(cx.bar(w4AcarReady + i), 1);
+            mbar_init(cx.bar(w4AcarRead + i), 4);
+            mbar_init(cx.bar(w4PairDone + i), 1);
+            mbar_init(cx.bar(w4BtReady + i), 4);
+        }
+        mbar_init(cx.bar(w4GtReady), 4);
+        mbar_init(cx.bar(w4OReady), 1);
+        mbar_init(cx.bar(w4Drain), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kW4MmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(cx.sm_u32 + Ly::oMisc), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    for (int i = tid; i < C * 8; i += kW4Threads) {   // tril[t][j] = (j <= t)
+        const int t = i >> 3, jg = i & 7;
+        uint32_t w[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int j0 = jg * 8 + 2 * p;
+            w[p] = (j0 <= t ? 0x3F80u : 0u) | (j0 + 1 <= t ? 0x3F800000u : 0u);
+        }
+        *reinterpret_cast<uint4*>(cx.sm + Ly::oTril + off_w<64>(t, jg * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    for (int i = tid; i < G * 64; i += kW4Threads)   // running A of every group: the carry-in
+        reinterpret_cast<float*>(cx.sm + Ly::oAcar)[i] = slice[(int64_t)S * D + i];
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    auto tmBp = [&](int p) { return tmem + p * DS; };                 // [0, 128): pair states, all 128 lanes
+    auto tmX = [&](int wg) { return tmem + 128 + wg * 64; };          // A_loc of the group's item, then W (32 columns)
+    const uint32_t tmG = tmem + 384;                                  // G, then masked G (32 columns of pairs)
+    auto tmO = [&](int c) { return tmem + 448 + (c & 1) * DS; };
+
+    if (warp < 16) {
+        // =========================== four worker groups: W of every fourth item =====================
+        // The number of groups is a multiple of four or equal to... G = 4 or 8: item i belongs to worker group
+        // i & 3, so a bucket group always stays with one worker group (its running A has one owner).
+        const int wg = warp >> 2, w = warp & 3;
+        const int q = lane & 3, rbase = 16 * w + (lane >> 2);
+        const uint32_t lane_base = (uint32_t)(32 * w) << 16;
+        bool ok = true;
+        // pQ of an item in the accumulator-fragment layout (pairs of bf16), loaded one item of this worker group ahead
+        auto load_pq = [&](int i, uint32_t (&f)[16]) {
+            const int c = i / G, g = i - c * G;
+            const int64_t tok0 = t_begin + (int64_t)c * C;
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                const __nv_bfloat16* prow = pq + (n * T + tok0 + row) * S + g * SG + 2 * q;
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    f[2 * x + h] = row < valid ? __ldg(reinterpret_cast<const unsigned int*>(prow + 8 * x)) : 0u;
+            }
+        };
+        uint32_t pq_next[16];
+        if (wg < nitems) load_pq(wg, pq_next);
+        for (int i = wg, k = 0; i < nitems && ok; i += 4, ++k) {
+            const int c = i / G, g = i - c * G;
+            uint32_t pqv[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) pqv[j] = pq_next[j];
+            if (i + 4 < nitems) load_pq(i + 4, pq_next);
+            // running A of the group: written at the end of the previous item of this worker group (which is the
+            // same bucket group when G = 4)
+            if (!(ok = wait_bar_warp(cx, w4AcarReady + wg, (uint32_t)((k & 1) ^ 1), 101))) break;
+            float* ac = reinterpret_cast<float*>(cx.sm + Ly::oAcar) + g * 64;
+            float acar[16];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                const float2 a2 = *reinterpret_cast<const float2*>(ac + 8 * x + 2 * q);
+                acar[2 * x] = a2.x; acar[2 * x + 1] = a2.y;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(w4AcarRead + wg));
+            // the warp that owns row 63 overwrites the values below: all four warps must hold them first
+            if (w == 3 && !(ok = wait_bar_warp(cx, w4AcarRead + wg, (uint32_t)(k & 1), 102))) break;
+            if (!(ok = wait_bar_warp(cx, w4XReady + wg, (uint32_t)(k & 1), 103))) break;
+            tc_fence_after();
+            // two halves of 32 buckets, to stay inside the registers 26 warps leave a thread: the W pairs of a half
+            // go over columns of A_loc this warp has already loaded (half 0: columns 0..15 of its 0..31; half 1:
+            // columns 16..31, loaded with half 0)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                float v[16];
+                tmem_ld32(lane_base + tmX(wg) + 32 * hf, v);
+                uint32_t wv[8];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const float2 pq2 = unpack_bf16(pqv[2 * (4 * hf + x) + h]);
+                        const float a0 = acar[2 * (4 * hf + x)] + v[4 * x + 2 * h];
+                        const float a1 = acar[2 * (4 * hf + x) + 1] + v[4 * x + 2 * h + 1];
+                        wv[2 * x + h] = pack_bf16(__fdividef(pq2.x, a0 + eps), __fdividef(pq2.y, a1 + eps));
+                        if (h == 1 && w == 3 && (lane >> 2) == 7)    // row 63: the running A after this chunk
+                            *reinterpret_cast<float2*>(ac + 8 * (4 * hf + x) + 2 * q) = make_float2(a0, a1);
+                    }
+                }
+                tmem_st_pairs4(lane_base + tmX(wg) + 16 * hf, wv);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(cx.bar(w4WReady + wg));
+                if (w == 3) mbar_arrive(cx.bar(w4AcarReady + wg));   // the new running A is in place
+            }
+        }
+    } else if (warp < kW4AuxWarp0) {
+        // =========================== converter warpgroup ==========================================
+        const int wtid = tid & 127;
+        bool ok = true;
+        for (int j = 0; j < npairs && ok; ++j) {
+            const int c = j / P, p = j - c * P, st = j % kW4Stages;
+            const uint32_t rp = (uint32_t)((j / kW4Stages) & 1);
+            if (j >= kW4Stages && !(ok = wait_bar_warp(cx, w4KFree + st, rp ^ 1, 203))) break;
+            if (!(ok = wait_bar_warp(cx, w4Full + st, rp, 201))) break;
+            // two staged 64 x 64 boxes -> one [64 tokens][128 buckets] operand tile
+#pragma unroll
+            for (int hb = 0; hb < 2; ++hb)
+                copy_tile<128, false>(cx.sm + Ly::oStage + st * Ly::kTileP2 + hb * Ly::kTileP,
+                                      cx.sm + Ly::oKt + st * Ly::kTileP2, 64 * hb, wtid, nullptr);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(w4KReady + st)); mbar_arrive(cx.bar(w4Empty + st)); }
+            if (p == 0) {
+                // V slice of the chunk: [64 tokens][32 values], staged without swizzle
+                const int vb = c & 1;
+                const uint32_t vp = (uint32_t)((c >> 1) & 1);
+                if (c >= 2 && !(ok = wait_bar_warp(cx, w4VFree + vb, vp ^ 1, 205))) break;
+                if (!(ok = wait_bar_warp(cx, w4VFull + vb, vp, 206))) break;
+                const uint8_t* src = cx.sm + Ly::oVst + vb * Ly::kTileS;
+                uint8_t* dst = cx.sm + Ly::oVt + vb * Ly::kTileS;
+#pragma unroll
+                for (int it = 0; it < 2; ++it) {
+                    const int idx = it * 128 + wtid;          // 256 items of 16 bytes
+                    const int r = idx >> 2, jj = idx & 3;
+                    *reinterpret_cast<uint4*>(dst + off_w<DS>(r, 8 * jj)) =
+                        *reinterpret_cast<const uint4*>(src + r * 64 + jj * 16);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(cx.bar(w4VReady + vb)); mbar_arrive(cx.bar(w4VEmpty + vb)); }
+            }
+        }
+    } else if (warp < kW4ProducerWarp) {
+        // =========================== auxiliary warpgroup: state operands, mask, output ============
+        const int w = warp & 3, q = lane & 3, rbase = 16 * w + (lane >> 2);
+        const uint32_t lane_base = (uint32_t)(32 * w) << 16;
+        // a pair's state: thread <-> bucket row 32 w + lane of the pair (128 rows over the four warps), 32 columns
+        const int prow = 32 * w + lane;
+        float b[32];
+        auto write_bt = [&](int p) {
+            uint8_t* bt = cx.sm + Ly::oBt + p * 2 * Ly::kTileS;   // [128][32] bf16, 8x8 core matrices
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 x4;
+                x4.x = pack_bf16(b[8 * j], b[8 * j + 1]);
+                x4.y = pack_bf16(b[8 * j + 2], b[8 * j + 3]);
+                x4.z = pack_bf16(b[8 * j + 4], b[8 * j + 5]);
+                x4.w = pack_bf16(b[8 * j + 6], b[8 * j + 7]);
+                *reinterpret_cast<uint4*>(bt + off_w<DS>(prow, 8 * j)) = x4;
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(w4BtReady + p));
+        };
+        // carry-in of every pair: accumulator and operand tile
+        for (int p = 0; p < P; ++p) {
+            const float* srow = slice + (int64_t)(p * 2 * SG + prow) * D + js * DS;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 f = *reinterpret_cast<const float4*>(srow + 4 * j);
+                b[4 * j] = f.x; b[4 * j + 1] = f.y; b[4 * j + 2] = f.z; b[4 * j + 3] = f.w;
+            }
+            tmem_st_rows32(lane_base + tmBp(p), b);
+            tc_fence_before();
+            write_bt(p);
+        }
+        bool ok = true;
+        for (int c = 0; c < nch && ok; ++c) {
+            const uint32_t cp = (uint32_t)(c & 1);
+            const int64_t tok0 = t_begin + (int64_t)c * C;
+            const int valid = (int)min((int64_t)C, t_end - tok0);
+            auto carry = [&](int p) {   // state of pair p after this chunk -> operand tile for the next chunk
+                tc_fence_after();
+                tmem_ld_rows32(lane_base + tmBp(p), b);
+                tc_fence_before();
+                write_bt(p);   // its arrival also tells the issuer that the accumulator has been read
+            };
+            for (int p = 0; p < P - 1 && ok; ++p) {
+                if (!(ok = wait_bar_warp(cx, w4PairDone + p, cp, 501))) break;
+                if (c + 1 < nch) carry(p);
+            }
+            if (!ok) break;
+            // all groups have accumulated into G: causal mask -> bf16 pairs over G's first 32 columns
+            if (!(ok = wait_bar_warp(cx, w4PairDone + P - 1, cp, 502))) break;
+            {
+                float v[32];
+                uint32_t gv[16];
+                tc_fence_after();
+                tmem_ld64(lane_base + tmG, v);
+                tc_fence_before();
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int row = rbase + 8 * h, col = 8 * x + 2 * q;
+                        gv[2 * x + h] = pack_bf16(col <= row ? v[4 * x + 2 * h] : 0.f,
+                                                  col + 1 <= row ? v[4 * x + 2 * h + 1] : 0.f);
+                    }
+                tmem_st_pairs(lane_base + tmG, gv);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(cx.bar(w4GtReady));
+            }
+            if (c + 1 < nch) carry(P - 1);
+            // O of the chunk (this CTA's 32 columns)
+            if (!(ok = wait_bar_warp(cx, w4OReady, cp, 503))) break;
+            float o[16];
+            tc_fence_after();
+            tmem_ld32(lane_base + tmO(c), o);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(w4OFree + (c & 1)));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rbase + 8 * h;
+                if (row < valid) {
+                    __nv_bfloat16* orow = out + (n * T + tok0 + row) * D + js * DS + 2 * q;
+#pragma unroll
+                    for (int x = 0; x < 4; ++x)
+                        *reinterpret_cast<uint32_t*>(orow + 8 * x) = pack_bf16(o[4 * x + 2 * h], o[4 * x + 2 * h + 1]);
+                }
+            }
+        }
+    } else if (warp == kW4ProducerWarp) {
+        // =========================== TMA producer ==================================================
+        if (lane == 0) {
+            int issued = 0, v_issued = 0;
+            for (int j = 0; j < npairs; ++j) {
+                const int c = j / P, p = j - c * P, st = j % kW4Stages;
+                const int tok = (int)(t_begin + (int64_t)c * C);
+                if (j >= kW4Stages && !wait_bar(cx, w4Empty + st, (uint32_t)(((j / kW4Stages) - 1) & 1), 301)) break;
+                mbar_arrive_expect_tx(cx.bar(w4Full + st), Ly::kTileP2);
+                tma_load_4d(cx.sm_u32 + Ly::oStage + st * Ly::kTileP2, &map_k, cx.bar(w4Full + st), 0, tok, 2 * p, (int)n);
+                tma_load_4d(cx.sm_u32 + Ly::oStage + st * Ly::kTileP2 + Ly::kTileP, &map_k, cx.bar(w4Full + st), 0, tok,
+                            2 * p + 1, (int)n);
+                issued = j + 1;
+                if (p == 0) {
+                    const int vb = c & 1;
+                    if (c >= 2 && !wait_bar(cx, w4VEmpty + vb, (uint32_t)(((c >> 1) - 1) & 1), 302)) break;
+                    mbar_arrive_expect_tx(cx.bar(w4VFull + vb), Ly::kTileS);
+                    tma_load_4d(cx.sm_u32 + Ly::oVst + vb * Ly::kTileS, &map_vs, cx.bar(w4VFull + vb), 0, tok, js, (int)n);
+                    v_issued = c + 1;
+                }
+            }
+            if (*cx.abort_flag) {   // copies in flight must land before the CTA may exit
+                for (int j = max(0, issued - kW4Stages); j < issued; ++j) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(w4Full + j % kW4Stages), (uint32_t)((j / kW4Stages) & 1)) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
+                for (int c = max(0, v_issued - 2); c < v_issued; ++c) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(w4VFull + (c & 1)), (uint32_t)((c >> 1) & 1)) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
+            }
+        }
+    } else {
+        // =========================== MMA issuer ======================================================
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
+        const int Gu = __shfl_sync(0xffffffffu, G, 0);
+        const uint32_t tril_lo = lo_k(smb + Ly::oTril);
+        constexpr uint32_t kI64 = idesc_n(64), kIS = idesc_n(DS);
+        constexpr uint32_t kIM128S = idesc_mn(128, DS);
+        if (elect_one()) {
+            bool ok = true;
+            // A_loc of item i = tril . pK_g: the group's 64 buckets are half (i & 1) of its pair's 128-wide tile
+            auto cumsum = [&](int i) -> bool {
+                const int j = i >> 1, st = j % kW4Stages, half = i & 1;
+                if (half == 0 && !wait_bar(cx, w4KReady + st, (uint32_t)((j / kW4Stages) & 1), 401)) return false;
+                tc_fence_after();
+                mma_k64<true, kHiK, 16, kHiMN, Ly::kStepP2>(
+                    tm + 128 + (i & 3) * 64, tril_lo,
+                    lo_mn_w(smb + Ly::oKt + st * Ly::kTileP2 + half * 1024, Ly::kLboP2), kI64 | kBmn);
+                mma_commit(cx.bar(w4XReady + (i & 3)));
+                return true;
+            };
+            auto gv = [&](int c) -> bool {       // O += masked G . V, once per chunk
+                if (!wait_bar(cx, w4GtReady, (uint32_t)(c & 1), 406)) return false;
+                tc_fence_after();
+                mma_k64_ta<false, kHiMN, Ly::kStepS>(tm + 448 + (c & 1) * DS, tm + 384,
+                                                     lo_mn_w(smb + Ly::oVt + (c & 1) * Ly::kTileS, Ly::kLboS), kIS | kBmn);
+                mma_commit(cx.bar(w4OReady));
+                mma_commit(cx.bar(w4VFree + (c & 1)));
+                return true;
+            };
+            for (int i = 0; i < 3 && i < nitems && ok; ++i) ok = cumsum(i);
+            int c = 0, g = 0;
+            for (int i = 0; i < nitems && ok; ++i) {
+                const int p = g >> 1, half = g & 1, j = i >> 1, st = j % kW4Stages, wg = i & 3;
+                // three items ahead: its buffer held W of item i - 1, whose products were issued in the previous turn
+                if (i + 3 < nitems && !(ok = cumsum(i + 3))) break;
+                if (g == 0 && c >= 1 && !(ok = gv(c - 1))) break;        // frees G for this chunk
+                // W of the item in tensor memory; state operand of the pair written (which also means that the
+                // pair's accumulator has been read out after the previous chunk)
+                if (!(ok = wait_bar2(cx, w4WReady + wg, (uint32_t)((i >> 2) & 1), w4BtReady + p, (uint32_t)(c & 1), 404))) break;
+                if (g == 0) {
+                    if (c >= 2 && !(ok = wait_bar(cx, w4OFree + (c & 1), (uint32_t)(((c >> 1) - 1) & 1), 408))) break;
+                    if (!(ok = wait_bar(cx, w4VReady + (c & 1), (uint32_t)((c >> 1) & 1), 407))) break;
+                }
+                tc_fence_after();
+                const uint32_t a_w = tm + 128 + wg * 64;
+                const uint32_t kt = smb + Ly::oKt + st * Ly::kTileP2;
+                const uint32_t kt_k = lo_k(kt + half * 1024);       // K-major: the group's buckets start 8 column groups in
+                const uint32_t bt_mn = lo_mn_w(smb + Ly::oBt + p * 2 * Ly::kTileS + half * Ly::kTileS, Ly::kLboS);
+                const uint32_t dO = tm + 448 + (c & 1) * DS;
+                if (g == 0) {
+                    mma_k64_ta<true, Ly::kHiK2, 16>(tm + 384, a_w, kt_k, kI64);               // G  = W . pK^T
+                    mma_k64_ta<true, kHiMN, Ly::kStepS>(dO, a_w, bt_mn, kIS | kBmn);          // O  = W . B_g
+                } else {
+                    mma_k64_ta<false, Ly::kHiK2, 16>(tm + 384, a_w, kt_k, kI64);              // G += ...
+                    mma_k64_ta<false, kHiMN, Ly::kStepS>(dO, a_w, bt_mn, kIS | kBmn);         // O += ...
+                }
+                if (half == 1) {
+                    // B_pair += [pK_a | pK_b]^T . V : M = 128, once per pair
+                    const uint32_t vt_mn = lo_mn_w(smb + Ly::oVt + (c & 1) * Ly::kTileS, Ly::kLboS);
+                    mma_k64<false, kHiMN, Ly::kStepP2, kHiMN, Ly::kStepS>(tm + p * DS, lo_mn_w(kt, Ly::kLboP2), vt_mn,
+                                                                          kIM128S | kAmn | kBmn);
+                    mma_commit(cx.bar(w4PairDone + p));
+                    mma_commit(cx.bar(w4KFree + st));
+                }
+                if (++g == Gu) { g = 0; ++c; }
+            }
+            if (ok && nch > 0) ok = gv(nch - 1);
+            mma_commit(cx.bar(w4Drain));
+            const long long t0 = clock64();
+            while (!mbar_try_wait(cx.bar(w4Drain), 0) && clock64() - t0 < cx.limit) {}
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kW4MmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn_bf16() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -1196,9 +1694,18 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
         // all bucket groups in one CTA, the head dimension in slices of 32 columns
         CUtensorMap mvs;
         if (!make_map_bf16_slice(&mvs, v, dm.N, dm.T, dm.D)) return cudaErrorInvalidValue;
+        dim3 wgrid((unsigned)(tiles * (D / DS)), (unsigned)dm.N);
+        if (G >= 4) {
+            // four worker groups, the states of two adjacent groups stacked in M = 128 accumulators
+            err = cudaFuncSetAttribute(causal_out_wide4_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, LayW4::kSmem);
+            if (err != cudaSuccess) return err;
+            causal_out_wide4_bf16<<<wgrid, kW4Threads, LayW4::kSmem, stream>>>(
+                (const __nv_bfloat16*)pq, mk, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
+                dm.eps, status);
+            return cudaGetLastError();
+        }
         err = cudaFuncSetAttribute(causal_out_wide_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, LayW::kSmem);
         if (err != cudaSuccess) return err;
-        dim3 wgrid((unsigned)(tiles * (D / DS)), (unsigned)dm.N);
         causal_out_wide_bf16<<<wgrid, kWThreads, LayW::kSmem, stream>>>(
             (const __nv_bfloat16*)pq, mk, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
             dm.eps, status);
