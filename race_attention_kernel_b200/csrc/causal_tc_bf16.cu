@@ -1120,45 +1120,58 @@ causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------------------
-// Output pass for S > 64 with an even number (>= 4) of bucket groups ("wide, four worker groups").  Same
-// decomposition as causal_out_wide_bf16 (one CTA = stream, tile, 32-column slice of the head dimension, all
-// groups; items = (chunk, group) in order).  What bounds that kernel is the worker group's own sequence per
-// item (wait for A_loc, tcgen05.ld, W, tcgen05.st, arrive: about 3 k clk whatever the arithmetic in it), of
-// which only two run at a time.  Here four worker groups take every fourth item, each with its own A_loc / W
-// buffer.  The columns for two more buffers come from stacking the states of two adjacent groups in one
-// M = 128 accumulator (128 buckets x 32 columns on all 128 lanes of tensor memory: 4 x 32 columns for eight
-// groups instead of 8 x 32); the state update then runs once per pair of groups (M = 128) on a pK tile that is
-// 128 buckets wide, and the auxiliary group reads a pair's state with the 32-lane TMEM load.
-// TMEM (512 columns): pair states 4 x 32 | A_loc / W of the four worker groups 4 x 64 | G 64 | O 2 x 32.
+// Output pass for S > 64 with an even number (>= 4) of bucket groups.  Same decomposition as causal_out_wide_bf16
+// (one CTA = stream, tile, DSX-column slice of the head dimension, all groups; items = (chunk, group) in order),
+// with the states of two adjacent groups stacked in one M = 128 accumulator (128 buckets x DSX columns on all 128
+// lanes of tensor memory); the state update then runs once per pair of groups (M = 128) on a pK tile that is 128
+// buckets wide, and the auxiliary group reads a pair's state with the 32-lane TMEM load.  NWG worker groups take
+// every NWG-th item, each with its own A_loc / W buffer.
+// What runs is DSX = 64, NWG = 2 (TMEM, 512 columns: pair states 4 x 64 | A_loc / W 2 x 64 | G 64 | O 64): the CTAs of
+// the d_k / DSX slices each form W and G for themselves, so slices twice as wide halve that repeated work, which
+// outweighs having two instead of four W stages in flight (DSX = 32, NWG = 4: pair states 4 x 32 | A_loc / W 4 x 64
+// | G 64 | O 2 x 32).  pQ reaches the worker warps through shared memory: one TMA tile per item (full 128-byte
+// rows), read in the accumulator-fragment layout with 4-byte loads that the 128B swizzle spreads over all banks;
+// the same 4-byte loads straight from global memory touched eight rows per instruction and bound the pass.
 // ------------------------------------------------------------------------------------------------
-constexpr int kW4Threads = 26 * 32;
-constexpr int kW4ConverterWarp0 = 16, kW4AuxWarp0 = 20, kW4ProducerWarp = 24, kW4MmaWarp = 25;
-constexpr int kW4Stages = 4;      // ring of pK pair tiles (stage and operand buffers)
+constexpr int kW4MaxStages = 4;
+// DSX: columns of the head dimension a CTA owns; NWG: worker groups (A_loc / W buffers in flight); NST: ring of pK
+// pair tiles (stage and operand buffers)
+template <int DSX, int NWG, int NST>
 struct LayW4 {
+    static constexpr int kWarps = 4 * NWG + 10;
+    static constexpr int kThreads = kWarps * 32;
+    static constexpr int kConverterWarp0 = 4 * NWG, kAuxWarp0 = kConverterWarp0 + 4, kProducerWarp = kAuxWarp0 + 4,
+                         kMmaWarp = kProducerWarp + 1;
+    static constexpr int kOBufs = DSX == 32 ? 2 : 1;
+    // tensor memory columns: pair states | A_loc / W per worker group | G | O
+    static constexpr int kTmX = 4 * DSX, kTmG = kTmX + NWG * 64, kTmO = kTmG + 64;
+    static_assert(kTmO + kOBufs * DSX <= 512, "tensor memory columns");
+    static_assert(NST <= kW4MaxStages && NWG <= 4, "barrier array");
     static constexpr int kTileP = C * 64 * 2;     // 64 x 64 bf16
     static constexpr int kTileP2 = 2 * kTileP;    // the pK tiles of two adjacent groups: [64 tokens][128 buckets]
-    static constexpr int kTileS = C * DS * 2;     // 64 x 32 bf16
-    static constexpr int oStage = 0;                            // [kW4Stages][kTileP2] staged: two boxes of 64 x 64
-    static constexpr int oVst = oStage + kW4Stages * kTileP2;   // [2][kTileS] staged V slice
-    static constexpr int oKt = oVst + 2 * kTileS;               // [kW4Stages][kTileP2] operand tile, 128 wide
-    static constexpr int oVt = oKt + kW4Stages * kTileP2;       // [2][kTileS]
-    static constexpr int oBt = oVt + 2 * kTileS;                // [4 pairs][128 x 32] state operand tiles
+    static constexpr int kTileS = C * DSX * 2;    // 64 x DSX bf16
+    static constexpr int oPq = 0;                         // [NWG][kTileP] pQ of a worker group's next item (swizzled)
+    static constexpr int oStage = oPq + NWG * kTileP;     // [NST][kTileP2] staged: two boxes of 64 x 64
+    static constexpr int oVst = oStage + NST * kTileP2;   // [2][kTileS] staged V slice
+    static constexpr int oKt = oVst + 2 * kTileS;         // [NST][kTileP2] operand tile, 128 wide
+    static constexpr int oVt = oKt + NST * kTileP2;       // [2][kTileS]
+    static constexpr int oBt = oVt + 2 * kTileS;          // [4 pairs][128 x DSX] state operand tiles
     static constexpr int oTril = oBt + 8 * kTileS;
     static constexpr int oAcar = oTril + kTileP;                // [8][64] fp32
     static constexpr int oBars = oAcar + 8 * 64 * 4;
     static constexpr int kNumBars = 64;
     static constexpr int oMisc = oBars + kNumBars * 8;
     static constexpr int kSmem = oMisc + 16 + 1024;
-    static constexpr uint32_t kLboS = (DS / 8) * 128;           // MN-major [.][32] tile: stride between 8-row groups
+    static constexpr uint32_t kLboS = (DSX / 8) * 128;          // MN-major [.][DSX] tile: stride between 8-row groups
     static constexpr uint32_t kStepS = (2 * kLboS) >> 4;
     static constexpr uint32_t kLboP2 = (128 / 8) * 128;         // MN-major [64][128] tile: stride between 8-token groups
     static constexpr uint32_t kStepP2 = (2 * kLboP2) >> 4;
     static constexpr uint32_t kHiK2 = (kLboP2 >> 4) | (1u << 14);    // K-major use of the 128-wide tile: sbo = 2048
 };
-static_assert(LayW4::kSmem <= 227 * 1024, "shared memory of the four-group wide kernel");
+static_assert(LayW4<64, 2, 3>::kSmem <= 227 * 1024, "shared memory of the wide kernel");
 enum BarW4 {
-    w4Full = 0, w4Empty = w4Full + kW4Stages, w4KReady = w4Empty + kW4Stages, w4KFree = w4KReady + kW4Stages,
-    w4VFull = w4KFree + kW4Stages, w4VEmpty = w4VFull + 2, w4VReady = w4VEmpty + 2, w4VFree = w4VReady + 2,
+    w4Full = 0, w4Empty = w4Full + kW4MaxStages, w4KReady = w4Empty + kW4MaxStages, w4KFree = w4KReady + kW4MaxStages,
+    w4VFull = w4KFree + kW4MaxStages, w4VEmpty = w4VFull + 2, w4VReady = w4VEmpty + 2, w4VFree = w4VReady + 2,
     w4XReady = w4VFree + 2,          // [4] A_loc of the worker group's item complete
     w4WReady = w4XReady + 4,         // [4] W of the item in tensor memory (four warps)
     w4AcarReady = w4WReady + 4,      // [4] the item's running A written by the warp that owns row 63
@@ -1166,9 +1179,11 @@ enum BarW4 {
     w4PairDone = w4AcarRead + 4,     // [4] every product of a pair of groups of the chunk has run
     w4BtReady = w4PairDone + 4,      // [4] state operand tile of the pair written (four warps)
     w4GtReady = w4BtReady + 4, w4OReady = w4GtReady + 1, w4OFree = w4OReady + 1, w4Drain = w4OFree + 2,
-    w4NumBars = w4Drain + 1
+    w4PqFull = w4Drain + 1,          // [4] pQ tile of the worker group's next item has landed
+    w4PqEmpty = w4PqFull + 4,        // [4] ... copied to registers by the four warps
+    w4NumBars = w4PqEmpty + 4
 };
-static_assert(w4NumBars <= LayW4::kNumBars, "barrier array of the four-group wide kernel");
+static_assert(w4NumBars <= LayW4<64, 2, 3>::kNumBars, "barrier array of the wide kernel");
 
 __device__ __forceinline__ constexpr uint32_t idesc_mn(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
@@ -1213,12 +1228,13 @@ __device__ __forceinline__ void tmem_st_pairs4(uint32_t taddr, const uint32_t (&
         ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr) : "memory");
 }
 
-__global__ void __launch_bounds__(kW4Threads, 1)
-causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
+template <int DSX, int NWG, int NST>
+__global__ void __launch_bounds__((LayW4<DSX, NWG, NST>::kThreads), 1)
+causal_out_wide4_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_vs, __nv_bfloat16* __restrict__ out,
                       const float* __restrict__ ws, int64_t T, int S, int D, int G, int tile_tokens, float eps,
                       int* status) {
-    using Ly = LayW4;
+    using Ly = LayW4<DSX, NWG, NST>;
     extern __shared__ uint8_t smem_raw[];
     Ctx cx;
     cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -1229,7 +1245,7 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + Ly::oMisc);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int NS = D / DS;                                   // slices of the head dimension
+    const int NS = D / DSX;                                  // slices of the head dimension
     const int P = G / 2;                                     // pairs of bucket groups
     const int js = (int)(blockIdx.x % (unsigned)NS);
     const int64_t tiles = gridDim.x / NS;
@@ -1243,7 +1259,7 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
 
     if (tid == 0) {
         *cx.abort_flag = 0;
-        for (int i = 0; i < kW4Stages; ++i) {
+        for (int i = 0; i < NST; ++i) {
             mbar_init(cx.bar(w4Full + i), 1);
             mbar_init(cx.bar(w4Empty + i), 4);
             mbar_init(cx.bar(w4KReady + i), 4);
@@ -1263,18 +1279,20 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
             mbar_init(cx.bar(w4AcarRead + i), 4);
             mbar_init(cx.bar(w4PairDone + i), 1);
             mbar_init(cx.bar(w4BtReady + i), 4);
+            mbar_init(cx.bar(w4PqFull + i), 1);
+            mbar_init(cx.bar(w4PqEmpty + i), 4);
         }
         mbar_init(cx.bar(w4GtReady), 4);
         mbar_init(cx.bar(w4OReady), 1);
         mbar_init(cx.bar(w4Drain), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kW4MmaWarp) {
+    if (warp == Ly::kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(cx.sm_u32 + Ly::oMisc), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int i = tid; i < C * 8; i += kW4Threads) {   // tril[t][j] = (j <= t)
+    for (int i = tid; i < C * 8; i += Ly::kThreads) {   // tril[t][j] = (j <= t)
         const int t = i >> 3, jg = i & 7;
         uint32_t w[4];
 #pragma unroll
@@ -1284,48 +1302,51 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
         }
         *reinterpret_cast<uint4*>(cx.sm + Ly::oTril + off_w<64>(t, jg * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    for (int i = tid; i < G * 64; i += kW4Threads)   // running A of every group: the carry-in
+    for (int i = tid; i < G * 64; i += Ly::kThreads)   // running A of every group: the carry-in
         reinterpret_cast<float*>(cx.sm + Ly::oAcar)[i] = slice[(int64_t)S * D + i];
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    auto tmBp = [&](int p) { return tmem + p * DS; };                 // [0, 128): pair states, all 128 lanes
-    auto tmX = [&](int wg) { return tmem + 128 + wg * 64; };          // A_loc of the group's item, then W (32 columns)
-    const uint32_t tmG = tmem + 384;                                  // G, then masked G (32 columns of pairs)
-    auto tmO = [&](int c) { return tmem + 448 + (c & 1) * DS; };
+    auto tmBp = [&](int p) { return tmem + p * DSX; };                // pair states, all 128 lanes
+    auto tmX = [&](int wg) { return tmem + Ly::kTmX + wg * 64; };          // A_loc of the group's item, then W (32 columns)
+    const uint32_t tmG = tmem + Ly::kTmG;                                 // G, then masked G (32 columns of pairs)
+    auto tmO = [&](int c) { return tmem + Ly::kTmO + (c % Ly::kOBufs) * DSX; };
 
-    if (warp < 16) {
-        // =========================== four worker groups: W of every fourth item =====================
-        // The number of groups is a multiple of four or equal to... G = 4 or 8: item i belongs to worker group
-        // i & 3, so a bucket group always stays with one worker group (its running A has one owner).
+    if (warp < 4 * NWG) {
+        // =========================== NWG worker groups: W of every NWG-th item ======================
+        // G = 4 or 8 is a multiple of NWG: item i belongs to worker group i % NWG, so a bucket group always stays
+        // with one worker group (its running A has one owner).
         const int wg = warp >> 2, w = warp & 3;
         const int q = lane & 3, rbase = 16 * w + (lane >> 2);
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
         bool ok = true;
-        // pQ of an item in the accumulator-fragment layout (pairs of bf16), loaded one item of this worker group ahead
-        auto load_pq = [&](int i, uint32_t (&f)[16]) {
-            const int c = i / G, g = i - c * G;
-            const int64_t tok0 = t_begin + (int64_t)c * C;
-            const int valid = (int)min((int64_t)C, t_end - tok0);
+        // pQ of the group's next item: a TMA-staged [64 tokens][64 buckets] tile (128-byte rows, 128B swizzle; rows past
+        // the end of the sequence are zero) read in the accumulator-fragment layout (pairs of bf16), one item of this
+        // worker group ahead.  Lanes of a warp instruction read eight rows, whose 16-byte pieces the swizzle spreads
+        // over all banks.
+        const uint8_t* pq_tile = cx.sm + Ly::oPq + wg * Ly::kTileP;
+        auto take_pq = [&](int k, uint32_t (&f)[16]) -> bool {
+            if (!wait_bar_warp(cx, w4PqFull + wg, (uint32_t)(k & 1), 104)) return false;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int row = rbase + 8 * h;
-                const __nv_bfloat16* prow = pq + (n * T + tok0 + row) * S + g * SG + 2 * q;
 #pragma unroll
                 for (int x = 0; x < 8; ++x)
-                    f[2 * x + h] = row < valid ? __ldg(reinterpret_cast<const unsigned int*>(prow + 8 * x)) : 0u;
+                    f[2 * x + h] = *reinterpret_cast<const uint32_t*>(pq_tile + row * 128 + ((x ^ (row & 7)) << 4) + 4 * q);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(w4PqEmpty + wg));
+            return true;
         };
         uint32_t pq_next[16];
-        if (wg < nitems) load_pq(wg, pq_next);
-        for (int i = wg, k = 0; i < nitems && ok; i += 4, ++k) {
+        if (wg < nitems) ok = take_pq(0, pq_next);
+        for (int i = wg, k = 0; i < nitems && ok; i += NWG, ++k) {
             const int c = i / G, g = i - c * G;
             uint32_t pqv[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) pqv[j] = pq_next[j];
-            if (i + 4 < nitems) load_pq(i + 4, pq_next);
             // running A of the group: written at the end of the previous item of this worker group (which is the
             // same bucket group when G = 4)
             if (!(ok = wait_bar_warp(cx, w4AcarReady + wg, (uint32_t)((k & 1) ^ 1), 101))) break;
@@ -1342,7 +1363,7 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
             if (w == 3 && !(ok = wait_bar_warp(cx, w4AcarRead + wg, (uint32_t)(k & 1), 102))) break;
             if (!(ok = wait_bar_warp(cx, w4XReady + wg, (uint32_t)(k & 1), 103))) break;
             tc_fence_after();
-            // two halves of 32 buckets, to stay inside the registers 26 warps leave a thread: the W pairs of a half
+            // two halves of 32 buckets, to stay inside the registers a thread has: the W pairs of a half
             // go over columns of A_loc this warp has already loaded (half 0: columns 0..15 of its 0..31; half 1:
             // columns 16..31, loaded with half 0)
 #pragma unroll
@@ -1371,15 +1392,16 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
                 mbar_arrive(cx.bar(w4WReady + wg));
                 if (w == 3) mbar_arrive(cx.bar(w4AcarReady + wg));   // the new running A is in place
             }
+            if (i + NWG < nitems && !(ok = take_pq(k + 1, pq_next))) break;
         }
-    } else if (warp < kW4AuxWarp0) {
+    } else if (warp < Ly::kAuxWarp0) {
         // =========================== converter warpgroup ==========================================
         const int wtid = tid & 127;
         bool ok = true;
         for (int j = 0; j < npairs && ok; ++j) {
-            const int c = j / P, p = j - c * P, st = j % kW4Stages;
-            const uint32_t rp = (uint32_t)((j / kW4Stages) & 1);
-            if (j >= kW4Stages && !(ok = wait_bar_warp(cx, w4KFree + st, rp ^ 1, 203))) break;
+            const int c = j / P, p = j - c * P, st = j % NST;
+            const uint32_t rp = (uint32_t)((j / NST) & 1);
+            if (j >= NST && !(ok = wait_bar_warp(cx, w4KFree + st, rp ^ 1, 203))) break;
             if (!(ok = wait_bar_warp(cx, w4Full + st, rp, 201))) break;
             // two staged 64 x 64 boxes -> one [64 tokens][128 buckets] operand tile
 #pragma unroll
@@ -1398,34 +1420,34 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
                 const uint8_t* src = cx.sm + Ly::oVst + vb * Ly::kTileS;
                 uint8_t* dst = cx.sm + Ly::oVt + vb * Ly::kTileS;
 #pragma unroll
-                for (int it = 0; it < 2; ++it) {
-                    const int idx = it * 128 + wtid;          // 256 items of 16 bytes
-                    const int r = idx >> 2, jj = idx & 3;
-                    *reinterpret_cast<uint4*>(dst + off_w<DS>(r, 8 * jj)) =
-                        *reinterpret_cast<const uint4*>(src + r * 64 + jj * 16);
+                for (int it = 0; it < DSX / 16; ++it) {
+                    const int idx = it * 128 + wtid;          // 64 rows of DSX / 8 pieces of 16 bytes
+                    const int r = idx / (DSX / 8), jj = idx % (DSX / 8);
+                    *reinterpret_cast<uint4*>(dst + off_w<DSX>(r, 8 * jj)) =
+                        *reinterpret_cast<const uint4*>(src + r * (DSX * 2) + jj * 16);
                 }
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(cx.bar(w4VReady + vb)); mbar_arrive(cx.bar(w4VEmpty + vb)); }
             }
         }
-    } else if (warp < kW4ProducerWarp) {
+    } else if (warp < Ly::kProducerWarp) {
         // =========================== auxiliary warpgroup: state operands, mask, output ============
         const int w = warp & 3, q = lane & 3, rbase = 16 * w + (lane >> 2);
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
         // a pair's state: thread <-> bucket row 32 w + lane of the pair (128 rows over the four warps), 32 columns
         const int prow = 32 * w + lane;
-        float b[32];
+        float b[DSX];
         auto write_bt = [&](int p) {
             uint8_t* bt = cx.sm + Ly::oBt + p * 2 * Ly::kTileS;   // [128][32] bf16, 8x8 core matrices
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < DSX / 8; ++j) {
                 uint4 x4;
                 x4.x = pack_bf16(b[8 * j], b[8 * j + 1]);
                 x4.y = pack_bf16(b[8 * j + 2], b[8 * j + 3]);
                 x4.z = pack_bf16(b[8 * j + 4], b[8 * j + 5]);
                 x4.w = pack_bf16(b[8 * j + 6], b[8 * j + 7]);
-                *reinterpret_cast<uint4*>(bt + off_w<DS>(prow, 8 * j)) = x4;
+                *reinterpret_cast<uint4*>(bt + off_w<DSX>(prow, 8 * j)) = x4;
             }
             fence_proxy_async();
             __syncwarp();
@@ -1433,13 +1455,15 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
         };
         // carry-in of every pair: accumulator and operand tile
         for (int p = 0; p < P; ++p) {
-            const float* srow = slice + (int64_t)(p * 2 * SG + prow) * D + js * DS;
+            const float* srow = slice + (int64_t)(p * 2 * SG + prow) * D + js * DSX;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < DSX / 4; ++j) {
                 const float4 f = *reinterpret_cast<const float4*>(srow + 4 * j);
                 b[4 * j] = f.x; b[4 * j + 1] = f.y; b[4 * j + 2] = f.z; b[4 * j + 3] = f.w;
             }
-            tmem_st_rows32(lane_base + tmBp(p), b);
+#pragma unroll
+            for (int hb = 0; hb < DSX / 32; ++hb)
+                tmem_st_rows32(lane_base + tmBp(p) + 32 * hb, *reinterpret_cast<const float(*)[32]>(b + 32 * hb));
             tc_fence_before();
             write_bt(p);
         }
@@ -1450,7 +1474,9 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
             const int valid = (int)min((int64_t)C, t_end - tok0);
             auto carry = [&](int p) {   // state of pair p after this chunk -> operand tile for the next chunk
                 tc_fence_after();
-                tmem_ld_rows32(lane_base + tmBp(p), b);
+#pragma unroll
+                for (int hb = 0; hb < DSX / 32; ++hb)
+                    tmem_ld_rows32(lane_base + tmBp(p) + 32 * hb, *reinterpret_cast<float(*)[32]>(b + 32 * hb));
                 tc_fence_before();
                 write_bt(p);   // its arrival also tells the issuer that the accumulator has been read
             };
@@ -1484,31 +1510,44 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
             if (c + 1 < nch) carry(P - 1);
             // O of the chunk (this CTA's 32 columns)
             if (!(ok = wait_bar_warp(cx, w4OReady, cp, 503))) break;
-            float o[16];
+            float o[DSX / 32][16];
             tc_fence_after();
-            tmem_ld32(lane_base + tmO(c), o);
+#pragma unroll
+            for (int hb = 0; hb < DSX / 32; ++hb) tmem_ld32(lane_base + tmO(c) + 32 * hb, o[hb]);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(cx.bar(w4OFree + (c & 1)));
+            if (lane == 0) mbar_arrive(cx.bar(w4OFree + (c % Ly::kOBufs)));
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int row = rbase + 8 * h;
                 if (row < valid) {
-                    __nv_bfloat16* orow = out + (n * T + tok0 + row) * D + js * DS + 2 * q;
+                    __nv_bfloat16* orow = out + (n * T + tok0 + row) * D + js * DSX + 2 * q;
 #pragma unroll
-                    for (int x = 0; x < 4; ++x)
-                        *reinterpret_cast<uint32_t*>(orow + 8 * x) = pack_bf16(o[4 * x + 2 * h], o[4 * x + 2 * h + 1]);
+                    for (int hb = 0; hb < DSX / 32; ++hb)
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+                            *reinterpret_cast<uint32_t*>(orow + 32 * hb + 8 * x) =
+                                pack_bf16(o[hb][4 * x + 2 * h], o[hb][4 * x + 2 * h + 1]);
                 }
             }
         }
-    } else if (warp == kW4ProducerWarp) {
+    } else if (warp == Ly::kProducerWarp) {
         // =========================== TMA producer ==================================================
         if (lane == 0) {
-            int issued = 0, v_issued = 0;
+            int issued = 0, v_issued = 0, q_issued = 0;
+            bool pok = true;
             for (int j = 0; j < npairs; ++j) {
-                const int c = j / P, p = j - c * P, st = j % kW4Stages;
+                const int c = j / P, p = j - c * P, st = j % NST;
                 const int tok = (int)(t_begin + (int64_t)c * C);
-                if (j >= kW4Stages && !wait_bar(cx, w4Empty + st, (uint32_t)(((j / kW4Stages) - 1) & 1), 301)) break;
+                for (int i = 2 * j; i < 2 * j + 2 && pok; ++i) {       // pQ of the pair's two items
+                    const int qs = i % NWG, qu = i / NWG;
+                    if (qu >= 1 && !(pok = wait_bar(cx, w4PqEmpty + qs, (uint32_t)((qu - 1) & 1), 303))) break;
+                    mbar_arrive_expect_tx(cx.bar(w4PqFull + qs), Ly::kTileP);
+                    tma_load_4d(cx.sm_u32 + Ly::oPq + qs * Ly::kTileP, &map_q, cx.bar(w4PqFull + qs), 0, tok, i - c * G, (int)n);
+                    q_issued = i + 1;
+                }
+                if (!pok) break;
+                if (j >= NST && !wait_bar(cx, w4Empty + st, (uint32_t)(((j / NST) - 1) & 1), 301)) break;
                 mbar_arrive_expect_tx(cx.bar(w4Full + st), Ly::kTileP2);
                 tma_load_4d(cx.sm_u32 + Ly::oStage + st * Ly::kTileP2, &map_k, cx.bar(w4Full + st), 0, tok, 2 * p, (int)n);
                 tma_load_4d(cx.sm_u32 + Ly::oStage + st * Ly::kTileP2 + Ly::kTileP, &map_k, cx.bar(w4Full + st), 0, tok,
@@ -1523,14 +1562,19 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
                 }
             }
             if (*cx.abort_flag) {   // copies in flight must land before the CTA may exit
-                for (int j = max(0, issued - kW4Stages); j < issued; ++j) {
+                for (int j = max(0, issued - NST); j < issued; ++j) {
                     const long long t0 = clock64();
-                    while (!mbar_try_wait(cx.bar(w4Full + j % kW4Stages), (uint32_t)((j / kW4Stages) & 1)) &&
+                    while (!mbar_try_wait(cx.bar(w4Full + j % NST), (uint32_t)((j / NST) & 1)) &&
                            clock64() - t0 < (1ll << 24)) {}
                 }
                 for (int c = max(0, v_issued - 2); c < v_issued; ++c) {
                     const long long t0 = clock64();
                     while (!mbar_try_wait(cx.bar(w4VFull + (c & 1)), (uint32_t)((c >> 1) & 1)) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
+                for (int i = max(0, q_issued - NWG); i < q_issued; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(w4PqFull + i % NWG), (uint32_t)((i / NWG) & 1)) &&
                            clock64() - t0 < (1ll << 24)) {}
                 }
             }
@@ -1541,61 +1585,62 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
         const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
         const int Gu = __shfl_sync(0xffffffffu, G, 0);
         const uint32_t tril_lo = lo_k(smb + Ly::oTril);
-        constexpr uint32_t kI64 = idesc_n(64), kIS = idesc_n(DS);
-        constexpr uint32_t kIM128S = idesc_mn(128, DS);
+        constexpr uint32_t kI64 = idesc_n(64), kIS = idesc_n(DSX);
+        constexpr uint32_t kIM128S = idesc_mn(128, DSX);
         if (elect_one()) {
             bool ok = true;
             // A_loc of item i = tril . pK_g: the group's 64 buckets are half (i & 1) of its pair's 128-wide tile
             auto cumsum = [&](int i) -> bool {
-                const int j = i >> 1, st = j % kW4Stages, half = i & 1;
-                if (half == 0 && !wait_bar(cx, w4KReady + st, (uint32_t)((j / kW4Stages) & 1), 401)) return false;
+                const int j = i >> 1, st = j % NST, half = i & 1;
+                if (half == 0 && !wait_bar(cx, w4KReady + st, (uint32_t)((j / NST) & 1), 401)) return false;
                 tc_fence_after();
                 mma_k64<true, kHiK, 16, kHiMN, Ly::kStepP2>(
-                    tm + 128 + (i & 3) * 64, tril_lo,
+                    tm + Ly::kTmX + (i % NWG) * 64, tril_lo,
                     lo_mn_w(smb + Ly::oKt + st * Ly::kTileP2 + half * 1024, Ly::kLboP2), kI64 | kBmn);
-                mma_commit(cx.bar(w4XReady + (i & 3)));
+                mma_commit(cx.bar(w4XReady + (i % NWG)));
                 return true;
             };
             auto gv = [&](int c) -> bool {       // O += masked G . V, once per chunk
                 if (!wait_bar(cx, w4GtReady, (uint32_t)(c & 1), 406)) return false;
                 tc_fence_after();
-                mma_k64_ta<false, kHiMN, Ly::kStepS>(tm + 448 + (c & 1) * DS, tm + 384,
+                mma_k64_ta<false, kHiMN, Ly::kStepS>(tm + Ly::kTmO + (c % Ly::kOBufs) * DSX, tm + Ly::kTmG,
                                                      lo_mn_w(smb + Ly::oVt + (c & 1) * Ly::kTileS, Ly::kLboS), kIS | kBmn);
                 mma_commit(cx.bar(w4OReady));
                 mma_commit(cx.bar(w4VFree + (c & 1)));
                 return true;
             };
-            for (int i = 0; i < 3 && i < nitems && ok; ++i) ok = cumsum(i);
+            for (int i = 0; i < NWG - 1 && i < nitems && ok; ++i) ok = cumsum(i);
             int c = 0, g = 0;
             for (int i = 0; i < nitems && ok; ++i) {
-                const int p = g >> 1, half = g & 1, j = i >> 1, st = j % kW4Stages, wg = i & 3;
+                const int p = g >> 1, half = g & 1, j = i >> 1, st = j % NST, wg = i % NWG;
                 // three items ahead: its buffer held W of item i - 1, whose products were issued in the previous turn
-                if (i + 3 < nitems && !(ok = cumsum(i + 3))) break;
+                if (i + NWG - 1 < nitems && !(ok = cumsum(i + NWG - 1))) break;
                 if (g == 0 && c >= 1 && !(ok = gv(c - 1))) break;        // frees G for this chunk
                 // W of the item in tensor memory; state operand of the pair written (which also means that the
                 // pair's accumulator has been read out after the previous chunk)
-                if (!(ok = wait_bar2(cx, w4WReady + wg, (uint32_t)((i >> 2) & 1), w4BtReady + p, (uint32_t)(c & 1), 404))) break;
+                if (!(ok = wait_bar2(cx, w4WReady + wg, (uint32_t)((i / NWG) & 1), w4BtReady + p, (uint32_t)(c & 1), 404))) break;
                 if (g == 0) {
-                    if (c >= 2 && !(ok = wait_bar(cx, w4OFree + (c & 1), (uint32_t)(((c >> 1) - 1) & 1), 408))) break;
+                    const int ob = c % Ly::kOBufs, ou = c / Ly::kOBufs;    // the chunk's O buffer and its use count
+                    if (ou >= 1 && !(ok = wait_bar(cx, w4OFree + ob, (uint32_t)((ou - 1) & 1), 408))) break;
                     if (!(ok = wait_bar(cx, w4VReady + (c & 1), (uint32_t)((c >> 1) & 1), 407))) break;
                 }
                 tc_fence_after();
-                const uint32_t a_w = tm + 128 + wg * 64;
+                const uint32_t a_w = tm + Ly::kTmX + wg * 64;
                 const uint32_t kt = smb + Ly::oKt + st * Ly::kTileP2;
                 const uint32_t kt_k = lo_k(kt + half * 1024);       // K-major: the group's buckets start 8 column groups in
                 const uint32_t bt_mn = lo_mn_w(smb + Ly::oBt + p * 2 * Ly::kTileS + half * Ly::kTileS, Ly::kLboS);
-                const uint32_t dO = tm + 448 + (c & 1) * DS;
+                const uint32_t dO = tm + Ly::kTmO + (c % Ly::kOBufs) * DSX;
                 if (g == 0) {
-                    mma_k64_ta<true, Ly::kHiK2, 16>(tm + 384, a_w, kt_k, kI64);               // G  = W . pK^T
+                    mma_k64_ta<true, Ly::kHiK2, 16>(tm + Ly::kTmG, a_w, kt_k, kI64);               // G  = W . pK^T
                     mma_k64_ta<true, kHiMN, Ly::kStepS>(dO, a_w, bt_mn, kIS | kBmn);          // O  = W . B_g
                 } else {
-                    mma_k64_ta<false, Ly::kHiK2, 16>(tm + 384, a_w, kt_k, kI64);              // G += ...
+                    mma_k64_ta<false, Ly::kHiK2, 16>(tm + Ly::kTmG, a_w, kt_k, kI64);              // G += ...
                     mma_k64_ta<false, kHiMN, Ly::kStepS>(dO, a_w, bt_mn, kIS | kBmn);         // O += ...
                 }
                 if (half == 1) {
                     // B_pair += [pK_a | pK_b]^T . V : M = 128, once per pair
                     const uint32_t vt_mn = lo_mn_w(smb + Ly::oVt + (c & 1) * Ly::kTileS, Ly::kLboS);
-                    mma_k64<false, kHiMN, Ly::kStepP2, kHiMN, Ly::kStepS>(tm + p * DS, lo_mn_w(kt, Ly::kLboP2), vt_mn,
+                    mma_k64<false, kHiMN, Ly::kStepP2, kHiMN, Ly::kStepS>(tm + p * DSX, lo_mn_w(kt, Ly::kLboP2), vt_mn,
                                                                           kIM128S | kAmn | kBmn);
                     mma_commit(cx.bar(w4PairDone + p));
                     mma_commit(cx.bar(w4KFree + st));
@@ -1611,7 +1656,7 @@ causal_out_wide4_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constan
 
     tc_fence_before();
     __syncthreads();
-    if (warp == kW4MmaWarp) {
+    if (warp == Ly::kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
@@ -1645,14 +1690,14 @@ bool make_map_bf16(CUtensorMap* map, const void* base, int64_t N, int64_t T, int
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// V [N][T][width] bf16 viewed as (32 values, T tokens, width/32 column blocks, N streams); one box =
-// 32 values x 64 tokens (64-byte rows, no swizzle); tokens past T read as zero
-bool make_map_bf16_slice(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width) {
+// V [N][T][width] bf16 viewed as (ds values, T tokens, width/ds column blocks, N streams); one box =
+// ds values x 64 tokens (rows of 2 ds bytes, no swizzle); tokens past T read as zero
+bool make_map_bf16_slice(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width, int ds) {
     auto fn = encode_fn_bf16();
     if (!fn) return false;
-    cuuint64_t dims[4] = {DS, (cuuint64_t)T, (cuuint64_t)(width / DS), (cuuint64_t)N};
-    cuuint64_t strides[3] = {(cuuint64_t)width * 2, DS * 2, (cuuint64_t)T * width * 2};
-    cuuint32_t box[4] = {DS, (cuuint32_t)C, 1, 1};
+    cuuint64_t dims[4] = {(cuuint64_t)ds, (cuuint64_t)T, (cuuint64_t)(width / ds), (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)width * 2, (cuuint64_t)ds * 2, (cuuint64_t)T * width * 2};
+    cuuint32_t box[4] = {(cuuint32_t)ds, (cuuint32_t)C, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1691,19 +1736,27 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
     err = causal_scan_tiles((float*)ws, carry_in, state_out, dm, tile_tokens, stream, true);
     if (err != cudaSuccess) return err;
     if (G > 1) {
-        // all bucket groups in one CTA, the head dimension in slices of 32 columns
+        // all bucket groups in one CTA, the head dimension in slices
         CUtensorMap mvs;
-        if (!make_map_bf16_slice(&mvs, v, dm.N, dm.T, dm.D)) return cudaErrorInvalidValue;
-        dim3 wgrid((unsigned)(tiles * (D / DS)), (unsigned)dm.N);
         if (G >= 4) {
-            // four worker groups, the states of two adjacent groups stacked in M = 128 accumulators
-            err = cudaFuncSetAttribute(causal_out_wide4_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, LayW4::kSmem);
+            // 64-column slices, two worker groups: the states of the pairs take 256 columns of tensor memory, which
+            // leaves two A_loc / W buffers
+            using LyW = LayW4<64, 2, 3>;
+            auto kw = causal_out_wide4_bf16<64, 2, 3>;
+            constexpr int ds = 64;
+            CUtensorMap mq;
+            if (!make_map_bf16_slice(&mvs, v, dm.N, dm.T, dm.D, ds) || !make_map_bf16(&mq, pq, dm.N, dm.T, dm.S))
+                return cudaErrorInvalidValue;
+            err = cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, LyW::kSmem);
             if (err != cudaSuccess) return err;
-            causal_out_wide4_bf16<<<wgrid, kW4Threads, LayW4::kSmem, stream>>>(
-                (const __nv_bfloat16*)pq, mk, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
+            dim3 wgrid4((unsigned)(tiles * (D / ds)), (unsigned)dm.N);
+            kw<<<wgrid4, LyW::kThreads, LyW::kSmem, stream>>>(
+                mq, mk, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
                 dm.eps, status);
             return cudaGetLastError();
         }
+        if (!make_map_bf16_slice(&mvs, v, dm.N, dm.T, dm.D, DS)) return cudaErrorInvalidValue;
+        dim3 wgrid((unsigned)(tiles * (D / DS)), (unsigned)dm.N);
         err = cudaFuncSetAttribute(causal_out_wide_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, LayW::kSmem);
         if (err != cudaSuccess) return err;
         causal_out_wide_bf16<<<wgrid, kWThreads, LayW::kSmem, stream>>>(
