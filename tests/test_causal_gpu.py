@@ -65,7 +65,8 @@ def test_fp32_parity(N, T, L, R, dk):
 @pytest.mark.parametrize("N,T,L,R,dk", [(8, 4096, 4, 16, 64), (2, 333, 4, 16, 64),
                                         (2, 300, 8, 64, 128), (2, 257, 4, 16, 128),
                                         (2, 300, 1, 32, 64), (2, 1000, 2, 64, 64), (2, 700, 4, 64, 128),
-                                        (3, 5000, 8, 64, 128), (1, 65, 8, 64, 128)])
+                                        (3, 5000, 8, 64, 128), (1, 65, 8, 64, 128),
+                                        (2, 500, 4, 64, 64), (1, 2177, 8, 64, 64)])
 def test_bf16_parity(N, T, L, R, dk):
     rk = _ops()
     pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=7 + T)
@@ -95,6 +96,27 @@ def test_bf16_wide_kernel_under_load():
     w = 1536
     ref = _oracle(pQ[:1, :w].cpu(), pK[:1, :w].cpu(), V[:1, :w].cpu())
     assert ro.rel_l2(out[:1, :w], ref) <= BF16_TOL
+
+
+@pytest.mark.parametrize("L,R,dk", [(8, 64, 128), (4, 64, 64), (2, 64, 128)])
+def test_bf16_wide_carry_and_short_tiles(L, R, dk):
+    """The wide bf16 tensor kernels (2, 4 and 8 bucket groups) with a carried-in state (the chunked form of
+    src/race_chunked.py:54-63) and with tiles of two chunks, so that every tile starts from a scanned carry."""
+    rk = _ops()
+    N, T = 2, 900
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=77)
+    pQ, pK, V = pQ.bfloat16(), pK.bfloat16(), V.bfloat16()
+    ref, A_ref, B_ref = _oracle(pQ, pK, V, return_state=True)
+    q, k, v = pQ.cuda(), pK.cuda(), V.cuda()
+    cut = 385
+    o1, A1, B1 = rk.race_causal_prefix(q[:, :cut].contiguous(), k[:, :cut].contiguous(), v[:, :cut].contiguous(),
+                                       return_state=True, variant="tensor")
+    o2, A2, B2 = rk.race_causal_prefix(q[:, cut:].contiguous(), k[:, cut:].contiguous(), v[:, cut:].contiguous(),
+                                       carry_in=(A1, B1), return_state=True, variant="tensor")
+    assert ro.rel_l2(torch.cat([o1, o2], dim=1), ref) <= BF16_TOL
+    assert ro.rel_l2(A2, A_ref) <= 1e-3 and ro.rel_l2(B2, B_ref) <= 1e-3
+    short = rk.race_causal_prefix(q, k, v, variant="tensor", tile_tokens=128)
+    assert ro.rel_l2(short, ref) <= BF16_TOL
 
 
 @pytest.mark.parametrize("tile", [32, 64, 128, 512, 4096])
