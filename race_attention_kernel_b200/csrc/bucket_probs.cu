@@ -250,6 +250,216 @@ bucket_probs_mma_d64_l4k4(const float* __restrict__ x, const float* __restrict__
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Tensor-core producer for wider geometries (what the bf16 multi-head configuration uses: d_k = 128, L = 8,
+// K = 6): the L K projections of a row are a [rows x D] . [D x L K] product on warp-level mma.sync (m16n8k16).
+// A warp takes 16 rows at a time; the plane fragments (hi and lo bf16 limbs) live in shared memory as one 16-byte
+// item per (plane block, k-step, lane); bf16 rows are exact A operands (two products: x.hi + x.lo), fp32 rows are
+// split into limbs (three products).  Two index permutations keep everything in registers without shuffles:
+//   * K side: lane t of a quad loads the 16-byte (bf16) or 32-byte (fp32) piece [32 m + 8 t, +8) of its rows and
+//     uses it for the k-steps 2 m and 2 m + 1, i.e. "k index" (j, half, 2 t + e) stands for feature
+//     32 (j / 2) + 8 t + 4 (j % 2) + 2 half + e; the plane fragments are built with the same map.
+//   * N side: after the product lane t holds the columns 8 nt + 2 t + e of its two rows, 2 NT = L K / 4 of them, and
+//     the planes are assigned to columns so that these are exactly the K planes of L / 4 whole tables
+//     (column slot s = 2 nt + e of lane t = plane s % K of table (L / 4) t + s / K).
+// Each lane then forms the R probabilities of its (row, table) pairs by doubling, in bucket order.  The R values
+// of a (row, table) are contiguous in the output but the lanes of a warp hold 32 different such pieces, so they go
+// through an 8 KB staging buffer of the warp (16-byte pieces XOR-swizzled inside every 128 bytes: writes and reads
+// take the minimum number of shared-memory wavefronts) and leave as 512-byte contiguous warp stores.
+// ------------------------------------------------------------------------------------------------
+template <int D, int L, int K>
+struct WideProbs {
+    static constexpr int NT = L * K / 8, NJ = D / 16, R = 1 << K, TPL = L / 4;
+    static constexpr int kTabBytes = NT * NJ * 32 * 16;
+    static constexpr int kStageBytes = 8192;       // per warp
+    static_assert(D % 32 == 0 && L % 4 == 0 && (L * K) % 8 == 0, "geometry of the tensor-core producer");
+};
+constexpr int kWideThreads = 128;
+
+template <int D, int L, int K, typename Tx, typename Tp>
+__global__ void __launch_bounds__(kWideThreads, (sizeof(Tx) == 4 ? 3 : 4))
+bucket_probs_mma_wide(const Tx* __restrict__ x, const float* __restrict__ planes, Tp* __restrict__ probs,
+                      int64_t rows, int64_t T, int heads) {
+    using W = WideProbs<D, L, K>;
+    constexpr int NT = W::NT, NJ = W::NJ, R = W::R, TPL = W::TPL;
+    constexpr bool kX32 = sizeof(Tx) == 4;
+    extern __shared__ __align__(16) uint8_t wide_smem[];
+    uint4* tab = reinterpret_cast<uint4*>(wide_smem);          // [(nt NJ + j) 32 + lane] = {b0 hi, b1 hi, b0 lo, b1 lo}
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    // staging: PB bytes per (row, table); a flush covers 8 rows x kTPF tables = 8 KB, i.e. kPPF passes over tb
+    constexpr int PB = R * (int)sizeof(Tp), kTPF = W::kStageBytes / (8 * PB), kPPF = kTPF / 4;
+    static_assert(kPPF >= 1 && TPL % kPPF == 0 && PB % 128 == 0, "staging geometry");
+    uint8_t* stage = wide_smem + W::kTabBytes + (threadIdx.x >> 5) * W::kStageBytes;
+    auto swz = [](int off) {   // 16-byte piece (off >> 4) & 7 of 128-byte block b = off >> 7, XOR (b / 8 + 2 (b % 8)) % 8
+        const int b = off >> 7;
+        return (b << 7) | (((((off >> 4) & 7) ^ ((b >> 3) + 2 * (b & 7))) & 7) << 4);
+    };
+    for (int i = threadIdx.x; i < NT * NJ * 32; i += kWideThreads) {
+        const int ln = i & 31, f = i >> 5, j = f % NJ, nt = f / NJ;
+        const int fg = ln >> 2, ft = ln & 3;                    // the fragment's lane: column 8 nt + fg, k pairs of ft
+        const int slot = 2 * nt + (fg & 1), owner = fg >> 1;   // column 8 nt + 2 owner + e
+        const int plane = (TPL * owner + slot / K) * K + slot % K;
+        const float* src = planes + (int64_t)plane * D + 32 * (j >> 1) + 8 * ft + 4 * (j & 1);
+        const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+        uint4 w;
+        split_pair(v.x, v.y, w.x, w.z);
+        split_pair(v.z, v.w, w.y, w.w);
+        tab[i] = w;
+    }
+    __syncthreads();
+    const float inv_scale = rsqrtf((float)D);
+    const int64_t blocks = (rows + 15) / 16;
+    const int64_t warp_global = (int64_t)blockIdx.x * (kWideThreads / 32) + (threadIdx.x >> 5);
+    const int64_t warps_total = (int64_t)gridDim.x * (kWideThreads / 32);
+    for (int64_t blk = warp_global; blk < blocks; blk += warps_total) {
+        const int64_t r0 = blk * 16;
+        bool live[2];
+        const Tx* src[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t row = r0 + g + 8 * h;
+            live[h] = row < rows;
+            const int64_t rr = live[h] ? row : 0;
+            const int64_t n = rr / T, tok = rr - n * T;
+            const int64_t mb = n / heads, hd = n - mb * heads;
+            src[h] = x + ((mb * T + tok) * heads + hd) * D + 8 * t;
+        }
+        float acc[kX32 ? 3 : 2][NT][4];
+#pragma unroll
+        for (int p = 0; p < (kX32 ? 3 : 2); ++p)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[p][nt][i] = 0.f;
+#pragma unroll
+        for (int m = 0; m < D / 32; ++m) {
+            // the lane's eight features [32 m + 8 t, +8) of both rows: words {k-step 2m: a0|a2, k-step 2m+1: a0|a2}
+            uint32_t hi[2][4], lo[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (kX32) {
+                    float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+                    if (live[h]) {
+                        v0 = __ldcs(reinterpret_cast<const float4*>(src[h] + 32 * m));
+                        v1 = __ldcs(reinterpret_cast<const float4*>(src[h] + 32 * m) + 1);
+                    }
+                    split_pair(v0.x, v0.y, hi[h][0], lo[h][0]);
+                    split_pair(v0.z, v0.w, hi[h][1], lo[h][1]);
+                    split_pair(v1.x, v1.y, hi[h][2], lo[h][2]);
+                    split_pair(v1.z, v1.w, hi[h][3], lo[h][3]);
+                } else {
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (live[h]) v = __ldcs(reinterpret_cast<const uint4*>(src[h] + 32 * m));
+                    hi[h][0] = v.x; hi[h][1] = v.y; hi[h][2] = v.z; hi[h][3] = v.w;
+                }
+            }
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+                const int j = 2 * m + jj;
+                const uint32_t ahi[4] = {hi[0][2 * jj], hi[1][2 * jj], hi[0][2 * jj + 1], hi[1][2 * jj + 1]};
+                uint32_t alo[4] = {0u, 0u, 0u, 0u};
+                if (kX32) {
+                    alo[0] = lo[0][2 * jj]; alo[1] = lo[1][2 * jj]; alo[2] = lo[0][2 * jj + 1]; alo[3] = lo[1][2 * jj + 1];
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const uint4 b = tab[(nt * NJ + j) * 32 + lane];
+                    mma_bf16_16816(acc[0][nt], ahi, b.x, b.y);
+                    mma_bf16_16816(acc[1][nt], ahi, b.z, b.w);
+                    if (kX32) mma_bf16_16816(acc[2][nt], alo, b.x, b.y);
+                }
+            }
+        }
+        // the lane's (row, table) pairs, one at a time
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int tb = 0; tb < TPL; ++tb) {
+                float p0[K], p1[K];
+#pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    const int s = tb * K + k, nt = s >> 1, i = 2 * h + (s & 1);
+                    float pr = acc[0][nt][i] + acc[1][nt][i];
+                    if (kX32) pr = acc[0][nt][i] + (acc[1][nt][i] + acc[2][nt][i]);
+                    const float e = __expf(-2.f * fabsf(pr));
+                    const float th = copysignf(__fdividef(1.f - e, 1.f + e), pr) * inv_scale;
+                    const float sq = th * th;
+                    const float poly = fmaf(sq, fmaf(sq, fmaf(sq, -17.f / 315.f, 2.f / 15.f), -1.f / 3.f), 1.f);
+                    const float half = 0.5f * th * poly;
+                    p1[k] = 0.5f + half;
+                    p0[k] = 0.5f - half;
+                }
+                float vals[R];
+                vals[0] = p0[0];
+                vals[1] = p1[0];
+#pragma unroll
+                for (int k = 1; k < K; ++k) {
+#pragma unroll
+                    for (int i = R / 2 - 1; i >= 0; --i) {     // constant bounds: every index is known at compile time
+                        if (i < (1 << k)) {
+                            const float b = vals[i];
+                            vals[2 * i] = b * p0[k];
+                            vals[2 * i + 1] = b * p1[k];
+                        }
+                    }
+                }
+                // stage the piece: local table kPPF t + (tb % kPPF) of row g
+                const int base = g * (kTPF * PB) + (kPPF * t + tb % kPPF) * PB;
+                if (sizeof(Tp) == 4) {
+#pragma unroll
+                    for (int i = 0; i < R; i += 4)
+                        *reinterpret_cast<float4*>(stage + swz(base + 4 * i)) =
+                            make_float4(vals[i], vals[i + 1], vals[i + 2], vals[i + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < R; i += 8) {
+                        uint4 w;
+                        __nv_bfloat162 a = __floats2bfloat162_rn(vals[i], vals[i + 1]);
+                        __nv_bfloat162 b = __floats2bfloat162_rn(vals[i + 2], vals[i + 3]);
+                        __nv_bfloat162 c = __floats2bfloat162_rn(vals[i + 4], vals[i + 5]);
+                        __nv_bfloat162 d = __floats2bfloat162_rn(vals[i + 6], vals[i + 7]);
+                        w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&b);
+                        w.z = *reinterpret_cast<uint32_t*>(&c); w.w = *reinterpret_cast<uint32_t*>(&d);
+                        *reinterpret_cast<uint4*>(stage + swz(base + 2 * i)) = w;
+                    }
+                }
+                if (tb % kPPF == kPPF - 1) {
+                    // flush: 16 warp stores of 512 contiguous staged bytes; PB-byte pieces are contiguous in the output
+                    const int tb0 = tb - (kPPF - 1);
+                    __syncwarp();
+#pragma unroll
+                    for (int qq = 0; qq < W::kStageBytes / 512; ++qq) {
+                        const int off = qq * 512 + lane * 16;
+                        const int gr = off / (kTPF * PB), rem = off % (kTPF * PB), lt = rem / PB, inner = rem % PB;
+                        const int table = TPL * (lt / kPPF) + tb0 + lt % kPPF;
+                        const int64_t row = r0 + gr + 8 * h;
+                        const uint4 w = *reinterpret_cast<const uint4*>(stage + swz(off));
+                        if (row < rows)
+                            __stcs(reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(probs) +
+                                                            (row * L + table) * (int64_t)PB + inner), w);
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    }
+}
+
+template <int D, int L, int K, typename Tx, typename Tp>
+cudaError_t launch_probs_wide(const void* x, const float* planes, void* probs, int64_t rows, int64_t T, int heads,
+                              cudaStream_t stream) {
+    auto kern = bucket_probs_mma_wide<D, L, K, Tx, Tp>;
+    constexpr int smem = WideProbs<D, L, K>::kTabBytes + (kWideThreads / 32) * WideProbs<D, L, K>::kStageBytes;
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return err;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t want = (rows + 63) / 64;   // 64 rows per CTA and pass
+    const unsigned blocks = (unsigned)std::min<int64_t>(want, (int64_t)(sms > 0 ? sms : 148) * 12);
+    kern<<<blocks, kWideThreads, smem, stream>>>((const Tx*)x, planes, (Tp*)probs, rows, T, heads);
+    return cudaGetLastError();
+}
+
 template <typename Tx, typename Tp, int K>
 cudaError_t launch_probs_k(const void* x, const float* planes, void* probs, int64_t rows, int64_t T, int heads,
                            int d, int L, cudaStream_t stream) {
@@ -301,6 +511,16 @@ cudaError_t bucket_probs(const void* x, const float* planes, void* probs, int64_
         bucket_probs_mma_d64_l4k4<<<blocks, kFastThreads, 0, stream>>>((const float*)x, planes, (float*)probs, rows, T,
                                                                        heads);
         return cudaGetLastError();
+    }
+    if (d == 128 && L == 8 && K == 6) {
+        if (dtype_x == RACE_DTYPE_BF16 && dtype_probs == RACE_DTYPE_BF16)
+            return launch_probs_wide<128, 8, 6, __nv_bfloat16, __nv_bfloat16>(x, planes, probs, rows, T, heads, stream);
+        if (dtype_x == RACE_DTYPE_F32 && dtype_probs == RACE_DTYPE_F32)
+            return launch_probs_wide<128, 8, 6, float, float>(x, planes, probs, rows, T, heads, stream);
+        if (dtype_x == RACE_DTYPE_F32 && dtype_probs == RACE_DTYPE_BF16)
+            return launch_probs_wide<128, 8, 6, float, __nv_bfloat16>(x, planes, probs, rows, T, heads, stream);
+        if (dtype_x == RACE_DTYPE_BF16 && dtype_probs == RACE_DTYPE_F32)
+            return launch_probs_wide<128, 8, 6, __nv_bfloat16, float>(x, planes, probs, rows, T, heads, stream);
     }
     if (dtype_x == RACE_DTYPE_F32 && dtype_probs == RACE_DTYPE_F32)
         return launch_probs<float, float>(x, planes, probs, rows, T, heads, d, L, K, stream);

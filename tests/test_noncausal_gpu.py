@@ -77,7 +77,7 @@ def test_last_causal_token_equals_noncausal():
 
 
 @pytest.mark.parametrize("dk,K,L,rows", [(64, 4, 4, 1000), (64, 2, 2, 77), (64, 5, 1, 64),
-                                         (128, 6, 8, 130), (32, 3, 2, 1), (64, 1, 3, 50)])
+                                         (128, 6, 8, 130), (32, 3, 2, 1), (64, 1, 3, 50), (128, 6, 8, 20007)])
 def test_bucket_probs(dk, K, L, rows):
     rk = _rk()
     torch.manual_seed(1234)
