@@ -590,30 +590,38 @@ def extra_workloads(args):
         # algorithmic bytes as the probabilities-level path); "two_step": producer kernel writes the
         # probabilities to HBM, the prefix kernels read them back.  A parity gate against the oracle of the
         # whole operator (first 512 tokens of stream 0) runs before the timing.
+        # --dtype bf16: the operator at the geometry of the bf16 multi-head configuration (H=32 streams, d_k=128, K=6,
+        # L=8, T=65536 unless --seq-len says otherwise): producer kernel, then the wide bf16 prefix kernels.
         from oracle import race_oracle as ro
-        M, B, H, dk, K, L = 1, 1, 8, 64, 4, 4
+        wide = args.dtype == "bf16"
+        M, B, H, dk, K, L = (1, 1, 32, 128, 6, 8) if wide else (1, 1, 8, 64, 4, 4)
+        dt, elt, tol = (torch.bfloat16, 2, 2e-2) if wide else (torch.float32, 4, 1e-4)
+        default_T = (65536,) if wide else (4096, 131072, 1048576)
         # --seq-len other than the default picks that one length (small captures under a profiler)
-        for T in ((4096, 131072, 1048576) if args.seq_len == 1 << 20 else (args.seq_len,)):
+        for T in (default_T if args.seq_len == 1 << 20 else (args.seq_len,)):
             torch.manual_seed(1234)
             ace = rk.BatchedACE(dk, K, L, M, device=dev)
-            Kh, Vh, Qh = (torch.randn(M, B, T, H, dk, device=dev, generator=g) for _ in range(3))
+            Kh, Vh, Qh = (torch.randn(M, B, T, H, dk, device=dev, generator=g).to(dt) for _ in range(3))
             n_tok = M * B * H * T
-            w = min(T, 512)
+            w = min(T, 256 if wide else 512)
             ref = ro.batched_ace_forward(ace.planes_T.cpu().double(), ace.protos_T.cpu().double(),
                                          *(t[:, :, :w, :1].cpu().double() for t in (Kh, Vh, Qh)), L, K)
-            for mode in ("fused", "two_step"):
+            for mode in (("two_step",) if wide else ("fused", "two_step")):
                 ace.fuse_producer = mode == "fused"
                 with torch.no_grad():
                     err = ro.rel_l2(ace(Kh, Vh, Qh)[:, :, :w, :1], ref)
-                    if not err <= 1e-4:
+                    if not err <= tol:
                         raise SystemExit(f"operator parity gate failed ({mode}): rel-L2 {err:.3e}")
                     ms = _time_ms(lambda: ace(Kh, Vh, Qh), 3, 10)
-                print(json.dumps({"workload": "operator", "mode": mode, "M,B,H": [M, B, H], "T": T,
-                                  "ms": round(ms, 4), "Mtok_s": round(n_tok / ms / 1e3, 1),
-                                  "qkvo_GB_s": round(n_tok * 4 * dk * 4 / ms / 1e6, 1),
-                                  "frac_measured_peak": round(n_tok * 4 * dk * 4 / ms / 1e6 / peak, 4),
-                                  "parity_rel_l2": err,
-                                  "peak_GiB": round(torch.cuda.max_memory_allocated() / 2**30, 2)}), flush=True)
+                    ms_prod = _time_ms(lambda: ace.bucket_probs(Kh.view(M * B * T, H, dk)), 3, 10) if wide else None
+                rec = {"workload": "operator", "mode": mode, "dtype": args.dtype, "M,B,H": [M, B, H], "T": T,
+                       "d_k,K,L": [dk, K, L], "ms": round(ms, 4), "Mtok_s": round(n_tok / ms / 1e3, 1),
+                       "qkvo_GB_s": round(n_tok * 4 * dk * elt / ms / 1e6, 1),
+                       "frac_measured_peak": round(n_tok * 4 * dk * elt / ms / 1e6 / peak, 4),
+                       "parity_rel_l2": err, "peak_GiB": round(torch.cuda.max_memory_allocated() / 2**30, 2)}
+                if ms_prod is not None:
+                    rec["producer_ms_per_tensor"] = round(ms_prod, 4)
+                print(json.dumps(rec), flush=True)
             del Kh, Vh, Qh
             torch.cuda.empty_cache()
 
