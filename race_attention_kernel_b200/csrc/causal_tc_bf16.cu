@@ -1539,14 +1539,6 @@ causal_out_wide4_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int j = 0; j < npairs; ++j) {
                 const int c = j / P, p = j - c * P, st = j % NST;
                 const int tok = (int)(t_begin + (int64_t)c * C);
-                for (int i = 2 * j; i < 2 * j + 2 && pok; ++i) {       // pQ of the pair's two items
-                    const int qs = i % NWG, qu = i / NWG;
-                    if (qu >= 1 && !(pok = wait_bar(cx, w4PqEmpty + qs, (uint32_t)((qu - 1) & 1), 303))) break;
-                    mbar_arrive_expect_tx(cx.bar(w4PqFull + qs), Ly::kTileP);
-                    tma_load_4d(cx.sm_u32 + Ly::oPq + qs * Ly::kTileP, &map_q, cx.bar(w4PqFull + qs), 0, tok, i - c * G, (int)n);
-                    q_issued = i + 1;
-                }
-                if (!pok) break;
                 if (j >= NST && !wait_bar(cx, w4Empty + st, (uint32_t)(((j / NST) - 1) & 1), 301)) break;
                 mbar_arrive_expect_tx(cx.bar(w4Full + st), Ly::kTileP2);
                 tma_load_4d(cx.sm_u32 + Ly::oStage + st * Ly::kTileP2, &map_k, cx.bar(w4Full + st), 0, tok, 2 * p, (int)n);
@@ -1560,6 +1552,15 @@ causal_out_wide4_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     tma_load_4d(cx.sm_u32 + Ly::oVst + vb * Ly::kTileS, &map_vs, cx.bar(w4VFull + vb), 0, tok, js, (int)n);
                     v_issued = c + 1;
                 }
+                // pQ of the pair's two items last: their slots free up later than the pK stage does
+                for (int i = 2 * j; i < 2 * j + 2 && pok; ++i) {       // pQ of the pair's two items
+                    const int qs = i % NWG, qu = i / NWG;
+                    if (qu >= 1 && !(pok = wait_bar(cx, w4PqEmpty + qs, (uint32_t)((qu - 1) & 1), 303))) break;
+                    mbar_arrive_expect_tx(cx.bar(w4PqFull + qs), Ly::kTileP);
+                    tma_load_4d(cx.sm_u32 + Ly::oPq + qs * Ly::kTileP, &map_q, cx.bar(w4PqFull + qs), 0, tok, i - c * G, (int)n);
+                    q_issued = i + 1;
+                }
+                if (!pok) break;
             }
             if (*cx.abort_flag) {   // copies in flight must land before the CTA may exit
                 for (int j = max(0, issued - NST); j < issued; ++j) {
