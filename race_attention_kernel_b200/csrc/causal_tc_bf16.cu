@@ -417,9 +417,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                 const int tok = (int)(t_begin + (int64_t)c * C);
                 mbar_arrive_expect_tx(bar, Ly::kStage);
                 tma_load_4d(dst, &map_k, bar, 0, tok, g, (int)n);
-#pragma unroll
-                for (int dh = 0; dh < DH; ++dh)
-                    tma_load_4d(dst + Ly::kTileP + dh * 8192, &map_v, bar, 0, tok, dh, (int)n);
+                tma_load_4d(dst + Ly::kTileP, &map_v, bar, 0, tok, 0, (int)n);   // one box: all D / 64 column blocks
                 issued = c + 1;
             }
             if (*cx.abort_flag) {
@@ -614,12 +612,8 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 const uint32_t bar = cx.bar(b1Full + st);
                 const int tok = (int)(t_begin + (int64_t)c * C);
                 mbar_arrive_expect_tx(bar, Ly::kStage);
-#pragma unroll
-                for (int gp = 0; gp < GP; ++gp)
-                    tma_load_4d(dst + gp * Ly::kTileP, &map_k, bar, 0, tok, g + gp, (int)n);
-#pragma unroll
-                for (int dh = 0; dh < DH; ++dh)
-                    tma_load_4d(dst + GP * Ly::kTileP + dh * 8192, &map_v, bar, 0, tok, dh, (int)n);
+                tma_load_4d(dst, &map_k, bar, 0, tok, g, (int)n);                    // one box: GP column blocks
+                tma_load_4d(dst + GP * Ly::kTileP, &map_v, bar, 0, tok, 0, (int)n);  // one box: all D / 64 blocks
                 issued = c + 1;
             }
             if (*cx.abort_flag) {
@@ -1541,9 +1535,8 @@ causal_out_wide4_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const int tok = (int)(t_begin + (int64_t)c * C);
                 if (j >= NST && !wait_bar(cx, w4Empty + st, (uint32_t)(((j / NST) - 1) & 1), 301)) break;
                 mbar_arrive_expect_tx(cx.bar(w4Full + st), Ly::kTileP2);
+                // one box: the two column blocks of the pair, landing as two consecutive 64 x 64 tiles
                 tma_load_4d(cx.sm_u32 + Ly::oStage + st * Ly::kTileP2, &map_k, cx.bar(w4Full + st), 0, tok, 2 * p, (int)n);
-                tma_load_4d(cx.sm_u32 + Ly::oStage + st * Ly::kTileP2 + Ly::kTileP, &map_k, cx.bar(w4Full + st), 0, tok,
-                            2 * p + 1, (int)n);
                 issued = j + 1;
                 if (p == 0) {
                     const int vb = c & 1;
@@ -1678,13 +1671,15 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn_bf16() {
 }
 
 // [N][T][width] bf16 viewed as (64 values, T tokens, width/64 column blocks, N streams); one box =
-// 64 values x 64 tokens (128-byte rows, 128B swizzle); tokens past T read as zero
-bool make_map_bf16(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width) {
+// `blocks` adjacent column blocks of 64 values x 64 tokens (128-byte rows, 128B swizzle), which land as consecutive
+// 8 KB tiles: one TMA instruction instead of `blocks` (an elected thread needs about 0.3 k clk for each); tokens past
+// T read as zero
+bool make_map_bf16(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width, int blocks = 1) {
     auto fn = encode_fn_bf16();
     if (!fn) return false;
     cuuint64_t dims[4] = {64, (cuuint64_t)T, (cuuint64_t)(width / 64), (cuuint64_t)N};
     cuuint64_t strides[3] = {(cuuint64_t)width * 2, 128, (cuuint64_t)T * width * 2};
-    cuuint32_t box[4] = {64, (cuuint32_t)C, 1, 1};
+    cuuint32_t box[4] = {64, (cuuint32_t)C, (cuuint32_t)blocks, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1719,14 +1714,16 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
     // runtime call first: binds the primary context to this host thread for the map encoder
     cudaError_t err = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, k1_smem);
     if (err != cudaSuccess) return err;
-    CUtensorMap mk, mv;
-    if (!make_map_bf16(&mk, pk, dm.N, dm.T, dm.S) || !make_map_bf16(&mv, v, dm.N, dm.T, dm.D))
+    // mk: one pK column block per box; mk2: two (a pair of bucket groups); mv: all of V's column blocks in one box
+    CUtensorMap mk, mk2, mv;
+    if (!make_map_bf16(&mk, pk, dm.N, dm.T, dm.S) || !make_map_bf16(&mk2, pk, dm.N, dm.T, dm.S, GP) ||
+        !make_map_bf16(&mv, v, dm.N, dm.T, dm.D, D / 64))
         return cudaErrorInvalidValue;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     dim3 grid((unsigned)(tiles * G), (unsigned)dm.N);
     if (phases & kPhaseTotals) {
         dim3 grid1((unsigned)(tiles * (G / GP)), (unsigned)dm.N);
-        k1<<<grid1, kT1Threads, k1_smem, stream>>>(mk, mv, (float*)ws, dm.T, dm.S, G, tile_tokens, status);
+        k1<<<grid1, kT1Threads, k1_smem, stream>>>(mk2, mv, (float*)ws, dm.T, dm.S, G, tile_tokens, status);
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
     }
@@ -1752,7 +1749,7 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
             if (err != cudaSuccess) return err;
             dim3 wgrid4((unsigned)(tiles * (D / ds)), (unsigned)dm.N);
             kw<<<wgrid4, LyW::kThreads, LyW::kSmem, stream>>>(
-                mq, mk, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
+                mq, mk2, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
                 dm.eps, status);
             return cudaGetLastError();
         }
