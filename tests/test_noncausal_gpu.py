@@ -93,6 +93,25 @@ def test_bucket_probs(dk, K, L, rows):
     assert got16.dtype == torch.bfloat16 and ro.rel_l2(got16, ref16) <= 1e-2
 
 
+def test_bucket_probs_wide_geometry_mixed_dtypes():
+    """The tensor-core producer of the d_k = 128, L = 8, K = 6 geometry: fp32 rows to bf16 probabilities and bf16
+    rows to fp32 probabilities, a row count that is no multiple of the 16-row blocks, and rows past one grid pass."""
+    rk = _rk()
+    dk, K, L, rows = 128, 6, 8, 70003
+    torch.manual_seed(1234)
+    planes_T, protos_T = ro.make_planes(dk, K, L), ro.make_protos(K)
+    planes = planes_T.T.contiguous().cuda()
+    x = torch.randn(1, rows, dk, generator=torch.Generator().manual_seed(3))
+    ref = ro.bucket_probs(x[:, -3000:].double(), planes_T.double(), protos_T.double(), L, K)
+    got = rk.bucket_probs(x.cuda(), planes, L, K, out_dtype=torch.bfloat16)
+    assert got.dtype == torch.bfloat16 and ro.rel_l2(got[:, -3000:], ref) <= 1e-2
+    xb = x.bfloat16()
+    refb = ro.bucket_probs(xb[:, -3000:].double(), planes_T.double(), protos_T.double(), L, K)
+    gotb = rk.bucket_probs(xb.cuda(), planes, L, K, out_dtype=torch.float32)
+    assert gotb.dtype == torch.float32 and ro.rel_l2(gotb[:, -3000:], refb) <= 1e-5
+    assert torch.allclose(gotb.sum(-1).cpu(), torch.ones(1, rows, L), atol=1e-5)
+
+
 @pytest.mark.parametrize("M,B,T,H,dk,K,L", [(1, 1, 300, 8, 64, 4, 4), (2, 2, 37, 3, 32, 3, 2), (1, 2, 130, 2, 128, 6, 8),
                                             (1, 1, 257, 1, 64, 1, 3), (2, 1, 1, 4, 64, 2, 2)])
 def test_bucket_probs_streams(M, B, T, H, dk, K, L):
