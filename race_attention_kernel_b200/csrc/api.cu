@@ -48,14 +48,14 @@ inline int family(int variant) { return is_single_pass(variant) ? RACE_VARIANT_T
 
 int resolve_variant(const Dims& dm, int dtype, int variant) {
     if (variant == RACE_VARIANT_AUTO)
-        return (tensor_supported(dm, dtype) && (dm.H == 1 || dtype == RACE_DTYPE_F32)) ? RACE_VARIANT_TENSOR
-                                                                                   : RACE_VARIANT_SIMT;
+        return tensor_supported(dm, dtype) ? RACE_VARIANT_TENSOR : RACE_VARIANT_SIMT;
     return variant;
 }
 
 bool variant_supported(const Dims& dm, int dtype, int variant) {
-    // the heads layout of V / out is read by the fp32 tensor kernels only
-    if (dm.H > 1 && !(family(variant) == RACE_VARIANT_TENSOR && dtype == RACE_DTYPE_F32)) return false;
+    // the heads layout of V / out is read by tensor kernels only: fp32 (S = 64, d_k = 64) and bf16 with four or eight
+    // bucket groups (tensor_supported says which); the single-pass form is fp32
+    if (dm.H > 1 && family(variant) != RACE_VARIANT_TENSOR) return false;
     if (variant == RACE_VARIANT_SIMT) return simt_supported(dm);
     if (variant == RACE_VARIANT_TENSOR) return tensor_supported(dm, dtype);
     if (is_single_pass(variant)) return dtype == RACE_DTYPE_F32 && tensor_supported(dm, dtype);

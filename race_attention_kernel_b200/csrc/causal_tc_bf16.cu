@@ -510,10 +510,11 @@ struct Lay1 {
 };
 enum Bar1B { b1Full = 0, b1Empty = 4, b1KvReady = 8, b1KvFree = 10, b1Done = 12 };
 
+// heads > 1: V is laid out [N / heads][T][heads][D] and map_v is the 5-D map of that layout
 template <int D, int GP>
 __global__ void __launch_bounds__(kT1Threads, 1)
 tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                    float* __restrict__ ws, int64_t T, int S, int G, int tile_tokens, int* status) {
+                    float* __restrict__ ws, int64_t T, int S, int G, int tile_tokens, int heads, int* status) {
     using Ly = Lay1<D, GP>;
     constexpr int DH = D / 64;
     static_assert(GP * D <= 512, "one accumulator per group");
@@ -613,7 +614,9 @@ tile_totals_tc_bf16(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 const int tok = (int)(t_begin + (int64_t)c * C);
                 mbar_arrive_expect_tx(bar, Ly::kStage);
                 tma_load_4d(dst, &map_k, bar, 0, tok, g, (int)n);                    // one box: GP column blocks
-                tma_load_4d(dst + GP * Ly::kTileP, &map_v, bar, 0, tok, 0, (int)n);  // one box: all D / 64 blocks
+                // one box: all D / 64 blocks
+                if (heads > 1) tma_load_5d(dst + GP * Ly::kTileP, &map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                else tma_load_4d(dst + GP * Ly::kTileP, &map_v, bar, 0, tok, 0, (int)n);
                 issued = c + 1;
             }
             if (*cx.abort_flag) {
@@ -1227,7 +1230,7 @@ __global__ void __launch_bounds__((LayW4<DSX, NWG, NST>::kThreads), 1)
 causal_out_wide4_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_vs, __nv_bfloat16* __restrict__ out,
                       const float* __restrict__ ws, int64_t T, int S, int D, int G, int tile_tokens, float eps,
-                      int* status) {
+                      int heads, int* status) {
     using Ly = LayW4<DSX, NWG, NST>;
     extern __shared__ uint8_t smem_raw[];
     Ctx cx;
@@ -1330,6 +1333,10 @@ causal_out_wide4_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 for (int x = 0; x < 8; ++x)
                     f[2 * x + h] = *reinterpret_cast<const uint32_t*>(pq_tile + row * 128 + ((x ^ (row & 7)) << 4) + 4 * q);
             }
+            // the slot goes back to the TMA thread: these generic-proxy reads are ordered before the async-proxy write
+            // of the next tile only through a proxy fence by the reading threads (without it a few 16-byte pieces of the
+            // tile were now and then those of the next tile: outputs differed from run to run within the bf16 tolerance)
+            fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(cx.bar(w4PqEmpty + wg));
             return true;
@@ -1515,7 +1522,9 @@ causal_out_wide4_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int h = 0; h < 2; ++h) {
                 const int row = rbase + 8 * h;
                 if (row < valid) {
-                    __nv_bfloat16* orow = out + (n * T + tok0 + row) * D + js * DSX + 2 * q;
+                    // out in the layout of V: [N][T][D], or [N / heads][T][heads][D]
+                    const int64_t orow_idx = heads > 1 ? (((n / heads) * T + tok0 + row) * heads + n % heads) : (n * T + tok0 + row);
+                    __nv_bfloat16* orow = out + orow_idx * D + js * DSX + 2 * q;
 #pragma unroll
                     for (int hb = 0; hb < DSX / 32; ++hb)
 #pragma unroll
@@ -1542,7 +1551,12 @@ causal_out_wide4_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     const int vb = c & 1;
                     if (c >= 2 && !wait_bar(cx, w4VEmpty + vb, (uint32_t)(((c >> 1) - 1) & 1), 302)) break;
                     mbar_arrive_expect_tx(cx.bar(w4VFull + vb), Ly::kTileS);
-                    tma_load_4d(cx.sm_u32 + Ly::oVst + vb * Ly::kTileS, &map_vs, cx.bar(w4VFull + vb), 0, tok, js, (int)n);
+                    // heads > 1: V is [N / heads][T][heads][D] behind a 5-D map
+                    if (heads > 1)
+                        tma_load_5d(cx.sm_u32 + Ly::oVst + vb * Ly::kTileS, &map_vs, cx.bar(w4VFull + vb), 0, tok, js,
+                                    (int)(n % heads), (int)(n / heads));
+                    else
+                        tma_load_4d(cx.sm_u32 + Ly::oVst + vb * Ly::kTileS, &map_vs, cx.bar(w4VFull + vb), 0, tok, js, (int)n);
                     v_issued = c + 1;
                 }
                 // pQ of the pair's two items last: their slots free up later than the pK stage does
@@ -1674,9 +1688,19 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn_bf16() {
 // `blocks` adjacent column blocks of 64 values x 64 tokens (128-byte rows, 128B swizzle), which land as consecutive
 // 8 KB tiles: one TMA instruction instead of `blocks` (an elected thread needs about 0.3 k clk for each); tokens past
 // T read as zero
-bool make_map_bf16(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width, int blocks = 1) {
+bool make_map_bf16(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width, int blocks = 1, int heads = 1) {
     auto fn = encode_fn_bf16();
     if (!fn) return false;
+    if (heads > 1) {   // [N / heads][T][heads][width]: (64 values, T tokens, column blocks, heads, outer)
+        cuuint64_t dims5[5] = {64, (cuuint64_t)T, (cuuint64_t)(width / 64), (cuuint64_t)heads, (cuuint64_t)(N / heads)};
+        cuuint64_t strides5[4] = {(cuuint64_t)heads * width * 2, 128, (cuuint64_t)width * 2,
+                                  (cuuint64_t)T * heads * width * 2};
+        cuuint32_t box5[5] = {64, (cuuint32_t)C, (cuuint32_t)blocks, 1, 1};
+        cuuint32_t estr5[5] = {1, 1, 1, 1, 1};
+        return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims5, strides5, box5, estr5,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
     cuuint64_t dims[4] = {64, (cuuint64_t)T, (cuuint64_t)(width / 64), (cuuint64_t)N};
     cuuint64_t strides[3] = {(cuuint64_t)width * 2, 128, (cuuint64_t)T * width * 2};
     cuuint32_t box[4] = {64, (cuuint32_t)C, (cuuint32_t)blocks, 1};
@@ -1688,9 +1712,20 @@ bool make_map_bf16(CUtensorMap* map, const void* base, int64_t N, int64_t T, int
 
 // V [N][T][width] bf16 viewed as (ds values, T tokens, width/ds column blocks, N streams); one box =
 // ds values x 64 tokens (rows of 2 ds bytes, no swizzle); tokens past T read as zero
-bool make_map_bf16_slice(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width, int ds) {
+bool make_map_bf16_slice(CUtensorMap* map, const void* base, int64_t N, int64_t T, int width, int ds, int heads = 1) {
     auto fn = encode_fn_bf16();
     if (!fn) return false;
+    if (heads > 1) {   // [N / heads][T][heads][width]
+        cuuint64_t dims5[5] = {(cuuint64_t)ds, (cuuint64_t)T, (cuuint64_t)(width / ds), (cuuint64_t)heads,
+                               (cuuint64_t)(N / heads)};
+        cuuint64_t strides5[4] = {(cuuint64_t)heads * width * 2, (cuuint64_t)ds * 2, (cuuint64_t)width * 2,
+                                  (cuuint64_t)T * heads * width * 2};
+        cuuint32_t box5[5] = {(cuuint32_t)ds, (cuuint32_t)C, 1, 1, 1};
+        cuuint32_t estr5[5] = {1, 1, 1, 1, 1};
+        return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims5, strides5, box5, estr5,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
     cuuint64_t dims[4] = {(cuuint64_t)ds, (cuuint64_t)T, (cuuint64_t)(width / ds), (cuuint64_t)N};
     cuuint64_t strides[3] = {(cuuint64_t)width * 2, (cuuint64_t)ds * 2, (cuuint64_t)T * width * 2};
     cuuint32_t box[4] = {(cuuint32_t)ds, (cuuint32_t)C, 1, 1};
@@ -1706,6 +1741,7 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
                         int* status, int phases, bool global_norm) {
     const int G = dm.S / SG;
     if (global_norm && G > 1) return cudaErrorInvalidValue;   // the one-group kernel has the global form
+    if (dm.H > 1 && G < 4) return cudaErrorInvalidValue;      // the heads layout of V / out: the wide kernel below
     // two bucket groups per totals CTA where there are at least two (they share the V tile)
     const int GP = G >= 2 ? 2 : 1;
     auto k1 = GP == 2 ? tile_totals_tc_bf16<D, 2> : tile_totals_tc_bf16<D, 1>;
@@ -1717,13 +1753,13 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
     // mk: one pK column block per box; mk2: two (a pair of bucket groups); mv: all of V's column blocks in one box
     CUtensorMap mk, mk2, mv;
     if (!make_map_bf16(&mk, pk, dm.N, dm.T, dm.S) || !make_map_bf16(&mk2, pk, dm.N, dm.T, dm.S, GP) ||
-        !make_map_bf16(&mv, v, dm.N, dm.T, dm.D, D / 64))
+        !make_map_bf16(&mv, v, dm.N, dm.T, dm.D, D / 64, dm.H))
         return cudaErrorInvalidValue;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     dim3 grid((unsigned)(tiles * G), (unsigned)dm.N);
     if (phases & kPhaseTotals) {
         dim3 grid1((unsigned)(tiles * (G / GP)), (unsigned)dm.N);
-        k1<<<grid1, kT1Threads, k1_smem, stream>>>(mk2, mv, (float*)ws, dm.T, dm.S, G, tile_tokens, status);
+        k1<<<grid1, kT1Threads, k1_smem, stream>>>(mk2, mv, (float*)ws, dm.T, dm.S, G, tile_tokens, dm.H, status);
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
     }
@@ -1743,14 +1779,14 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
             auto kw = causal_out_wide4_bf16<64, 2, 3>;
             constexpr int ds = 64;
             CUtensorMap mq;
-            if (!make_map_bf16_slice(&mvs, v, dm.N, dm.T, dm.D, ds) || !make_map_bf16(&mq, pq, dm.N, dm.T, dm.S))
+            if (!make_map_bf16_slice(&mvs, v, dm.N, dm.T, dm.D, ds, dm.H) || !make_map_bf16(&mq, pq, dm.N, dm.T, dm.S))
                 return cudaErrorInvalidValue;
             err = cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, LyW::kSmem);
             if (err != cudaSuccess) return err;
             dim3 wgrid4((unsigned)(tiles * (D / ds)), (unsigned)dm.N);
             kw<<<wgrid4, LyW::kThreads, LyW::kSmem, stream>>>(
                 mq, mk2, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
-                dm.eps, status);
+                dm.eps, dm.H, status);
             return cudaGetLastError();
         }
         if (!make_map_bf16_slice(&mvs, v, dm.N, dm.T, dm.D, DS)) return cudaErrorInvalidValue;
@@ -1773,8 +1809,9 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
 
 bool tensor_bf16_supported(const Dims& dm) {
     const int G = dm.S / SG;
+    // the heads layout of V / out ([N / H][T][H][D]) is read by the kernel of four and eight bucket groups
     return dm.S % SG == 0 && (G == 1 || G == 2 || G == 4 || G == 8) && (dm.D == 64 || dm.D == 128) &&
-           dm.N >= 0 && dm.N <= 65535 && dm.T < (1ll << 31);
+           dm.N >= 0 && dm.N <= 65535 && dm.T < (1ll << 31) && (dm.H == 1 || (G >= 4 && dm.N % dm.H == 0));
 }
 
 cudaError_t causal_fwd_tensor_bf16(const void* pq, const void* pk, const void* v, void* out,

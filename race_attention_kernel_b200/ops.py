@@ -148,7 +148,7 @@ def race_causal_prefix(probsQ, probsK, V, eps: float = 1e-6, *, carry_in=None,
 
     V may also be given in the operator's layout [M,B,T,H,d_k] (stream n = (m*B+b)*H + h, the order of
     src/race_baseline.py:35-40); the output then has that layout too and no flattened copy is made
-    (fp32, S = 64, d_k = 64 only: see ``is_supported(..., heads=H)``).
+    (fp32 with S = 64, d_k = 64, and bf16 with 256 or 512 buckets: see ``is_supported(..., heads=H)``).
 
     carry_in: None, a packed state [N, S*d_k+S] or a tuple (A [N,L,R], B [N,L,R,d_k]) holding the
     sums over tokens before this call's first token.  return_state=True also returns (A, B)

@@ -119,6 +119,25 @@ def test_bf16_wide_carry_and_short_tiles(L, R, dk):
     assert ro.rel_l2(short, ref) <= BF16_TOL
 
 
+@pytest.mark.parametrize("tile", [64, 256])
+def test_bf16_wide_kernel_is_bitwise_reproducible(tile):
+    """Run-to-run bitwise equality of the wide bf16 tensor kernel with short tiles: every CTA then starts cold and reads
+    its first pQ tiles the moment they land, which is where a slot handed back to the TMA thread too early showed."""
+    rk = _ops()
+    N, T, L, R, dk = 4, 4200, 8, 64, 128
+    pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=2 + T)
+    q, k, v = pQ.bfloat16().cuda(), pK.bfloat16().cuda(), V.bfloat16().cuda()
+    first = None
+    for i in range(10):
+        junk = torch.full((16 << 20,), float(i), device="cuda")   # the allocations of a run reuse dirtied memory
+        del junk
+        out = rk.race_causal_prefix(q, k, v, variant="tensor", tile_tokens=tile)
+        if first is None:
+            first = out.clone()
+        else:
+            assert torch.equal(out, first), f"run {i} differs in {int((out != first).sum())} values"
+
+
 @pytest.mark.parametrize("tile", [32, 64, 128, 512, 4096])
 def test_forced_tile_lengths_agree(tile):
     rk = _ops()
@@ -351,9 +370,29 @@ def test_heads_layout_equals_flattened_streams(M, B, T, H):
     assert ro.rel_l2(flat, ref) <= 1e-4
 
 
+@pytest.mark.parametrize("M,B,T,H,L,R,dk", [(1, 1, 1000, 4, 8, 64, 128), (2, 1, 257, 3, 4, 64, 64), (1, 2, 4200, 2, 8, 64, 128)])
+def test_heads_layout_bf16_wide_equals_flattened_streams(M, B, T, H, L, R, dk):
+    """The same for the bf16 tensor kernels of four and eight bucket groups: V and out as [M,B,T,H,d_k]."""
+    rk = _ops()
+    N = M * B * H
+    pQ, pK, V2 = ro.synthetic_probs(N, T, L, R, dk, seed=H + T)
+    pQ, pK, V2 = pQ.bfloat16(), pK.bfloat16(), V2.bfloat16()
+    V5 = V2.view(M, B, H, T, dk).permute(0, 1, 3, 2, 4).contiguous()      # [M,B,T,H,d_k]
+    q, k = pQ.cuda(), pK.cuda()
+    assert rk.is_supported(N, T, L, R, dk, torch.bfloat16, "auto", heads=H)
+    flat, A0, B0 = rk.race_causal_prefix(q, k, V2.cuda(), return_state=True)
+    got, A1, B1 = rk.race_causal_prefix(q, k, V5.cuda(), return_state=True)
+    assert got.shape == (M, B, T, H, dk)
+    assert torch.equal(got.permute(0, 1, 3, 2, 4).reshape(N, T, dk), flat)
+    assert torch.equal(A0, A1) and torch.equal(B0, B1)
+    ref = ro.causal_prefix(pQ.double(), pK.double(), V2.double())
+    assert ro.rel_l2(flat, ref) <= BF16_TOL
+
+
 def test_heads_layout_rejected_where_not_built():
     rk = _ops()
-    assert not rk.is_supported(8, 256, 4, 16, 64, torch.bfloat16, "auto", heads=4)   # bf16 path
+    assert not rk.is_supported(8, 256, 4, 16, 64, torch.bfloat16, "auto", heads=4)   # bf16 path, one bucket group
+    assert not rk.is_supported(8, 256, 2, 64, 64, torch.bfloat16, "auto", heads=4)   # bf16 path, two bucket groups
     assert not rk.is_supported(8, 256, 4, 16, 64, torch.float32, "simt", heads=4)    # CUDA-core path
     assert not rk.is_supported(8, 256, 8, 64, 128, torch.float32, "auto", heads=4)   # no tensor path: S=512 fp32
     assert not rk.is_supported(8, 256, 4, 16, 64, torch.float32, "auto", heads=3)    # 8 streams / 3 heads
