@@ -119,12 +119,14 @@ def test_bf16_wide_carry_and_short_tiles(L, R, dk):
     assert ro.rel_l2(short, ref) <= BF16_TOL
 
 
-@pytest.mark.parametrize("tile", [64, 256])
-def test_bf16_wide_kernel_is_bitwise_reproducible(tile):
-    """Run-to-run bitwise equality of the wide bf16 tensor kernel with short tiles: every CTA then starts cold and reads
-    its first pQ tiles the moment they land, which is where a slot handed back to the TMA thread too early showed."""
+@pytest.mark.parametrize("tile,L,R,dk", [(64, 8, 64, 128), (256, 8, 64, 128), (256, 4, 64, 64), (128, 2, 64, 128),
+                                         (128, 4, 16, 64), (128, 4, 16, 128)])
+def test_bf16_tensor_kernels_are_bitwise_reproducible(tile, L, R, dk):
+    """Run-to-run bitwise equality of the bf16 tensor kernels (one, two, four and eight bucket groups) with short tiles:
+    every CTA then starts cold and reads its first tiles the moment they land, which is where a pQ slot handed back to
+    the TMA thread without a proxy fence showed in the kernel of four and eight groups."""
     rk = _ops()
-    N, T, L, R, dk = 4, 4200, 8, 64, 128
+    N, T = 4, 4200
     pQ, pK, V = ro.synthetic_probs(N, T, L, R, dk, seed=2 + T)
     q, k, v = pQ.bfloat16().cuda(), pK.bfloat16().cuda(), V.bfloat16().cuda()
     first = None
@@ -136,6 +138,33 @@ def test_bf16_wide_kernel_is_bitwise_reproducible(tile):
             first = out.clone()
         else:
             assert torch.equal(out, first), f"run {i} differs in {int((out != first).sum())} values"
+
+
+def test_fp32_tensor_paths_are_bitwise_reproducible():
+    """The same for the fp32 tensor paths: the forward with one-chunk tiles, the forward that forms the probabilities
+    itself, the single-pass form and the backward, each run several times on dirtied memory."""
+    rk = _ops()
+    N, T, L, R, dk = 4, 4200, 4, 16, 64
+    pQ, pK, V = (t.cuda() for t in ro.synthetic_probs(N, T, L, R, dk, seed=5))
+    g = torch.Generator().manual_seed(9)
+    Q, Kx = torch.randn(N, T, dk, generator=g).cuda(), torch.randn(N, T, dk, generator=g).cuda()
+    planes, dO = torch.randn(L * 4, dk, generator=g).cuda(), torch.randn(N, T, dk, generator=g).cuda()
+    calls = {
+        "forward, tile 64": lambda: (rk.race_causal_prefix(pQ, pK, V, variant="tensor", tile_tokens=64),),
+        "forward, single pass": lambda: (rk.race_causal_prefix(pQ, pK, V, variant="tensor_single_pass", tile_tokens=128),),
+        "forward from Q, K": lambda: (rk.ops.race_causal_qkv(Q, Kx, V, planes, L, 4, tile_tokens=64),),
+        "backward": lambda: rk.race_causal_backward(pQ, pK, V, dO),
+    }
+    for name, fn in calls.items():
+        first = None
+        for i in range(6):
+            junk = torch.full((16 << 20,), float(i), device="cuda")
+            del junk
+            outs = [o.clone() for o in fn()]
+            if first is None:
+                first = outs
+            else:
+                assert all(torch.equal(a, b) for a, b in zip(outs, first)), f"{name}: run {i} differs"
 
 
 @pytest.mark.parametrize("tile", [32, 64, 128, 512, 4096])
