@@ -21,9 +21,10 @@
  * With RaceShape.heads = H > 1 the causal entry points read V and write out in the operator's own
  * layout [N/H, T, H, d_k] (stream n = outer*H + h), so that neither the flattened copy of V nor the
  * permuted view of the output (src/race_baseline.py:40,52) is needed; the probabilities stay
- * [N, T, L, R].  Supported by the fp32 tensor variant (S = 64, d_k = 64) of race_b200_causal_fwd,
- * race_b200_tile_totals and race_b200_causal_fwd_resume; every other entry point and variant
- * rejects heads > 1 with RACE_ERR_SHAPE / reports it as unsupported.
+ * [N, T, L, R].  Supported by the tensor variant of race_b200_causal_fwd, race_b200_tile_totals and
+ * race_b200_causal_fwd_resume for fp32 (S = 64, d_k = 64) and for bf16 with S = 256 or 512 (d_k = 64 or
+ * 128); every other entry point, shape and variant rejects heads > 1 with RACE_ERR_SHAPE / reports
+ * it as unsupported.
  */
 #ifndef RACE_B200_H_
 #define RACE_B200_H_
