@@ -17,6 +17,12 @@ One step = one forward over all streams.  Metric: M tokens/s = streams*T / secon
             over the ranks, carry chain over NCCL send/recv) and the bf16 configuration (256 streams,
             T=262,144, S=512, d_k=128, split over the ranks, walked in batches of 32 streams)
 
+  operator, causal_bwd   sub-records: BatchedACE.forward at T=2^20 (probabilities formed in-kernel, the two-step
+            time beside it) and the causal backward at N=8, T=2^20
+Other workloads (--workload): sweep (lengths up to what fits, each with its parity figure), c3, c4, c5, bwd, next
+(incremental step, global form, backward) and operator (--dtype bf16: the operator at the bf16 multi-head geometry,
+H=32, d_k=128, K=6, L=8, T=65,536).
+
 With N > 1 (torchrun) every rank runs its own N=8 streams: streams are independent, so ranks
 share nothing on the data path ("weak" scaling); only timing uses a collective.
 
