@@ -1670,6 +1670,195 @@ causal_out_wide4_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Tile totals for four or eight bucket groups: FOUR groups per CTA (the CTAs of a (stream, tile) then fetch
+// the chunk's V tile twice instead of four times: the pass is bound by what the memory system delivers, L2 hits
+// included).  The states of two adjacent groups are one M = 128 accumulator, as in the output pass above (A operand:
+// the [64 tokens][128 buckets] pair tile, MN-major), and the column sums of pK come out of the same products: the V
+// operand tile is 32 columns wider than d_k, column d_k holds ones, so accumulator column d_k is sum_t pK[t][bucket]
+// (bf16 values times 1.0, summed in fp32 by the tensor core in a fixed order).
+// TMEM: 2 pairs x (D + 32) columns.  Roles as in tile_totals_tc_bf16: two converter groups on alternate chunks
+// (a stage always belongs to one group: the ring has two stages), TMA thread, issuing thread.
+// ------------------------------------------------------------------------------------------------
+constexpr int kT4Stages = 2;
+template <int D>
+struct Lay4 {
+    static constexpr int DX = D + 32;                              // V operand tile: d_k columns, a ones column, padding
+    static constexpr int kTileP = C * 64 * 2, kTileP2 = 2 * kTileP, kTileV = C * D * 2, kTileVx = C * DX * 2;
+    static constexpr int kStage = 4 * kTileP + kTileV;
+    static constexpr int oStage = 0;                               // [kT4Stages][4 pK tiles | V]
+    static constexpr int oKt = oStage + kT4Stages * kStage;        // [2 groups][2 pairs][kTileP2]
+    static constexpr int oVt = oKt + 2 * 2 * kTileP2;              // [2 groups][kTileVx]
+    static constexpr int oBars = oVt + 2 * kTileVx;
+    static constexpr int oMisc = oBars + 16 * 8;
+    static constexpr int kSmem = oMisc + 16 + 1024;
+    static constexpr uint32_t kLboVx = (DX / 8) * 128, kStepVx = (2 * kLboVx) >> 4;
+    static constexpr uint32_t kLboP2 = (128 / 8) * 128, kStepP2 = (2 * kLboP2) >> 4;
+    static_assert(2 * DX <= 512 && DX % 32 == 0, "tensor memory columns of the four-group totals kernel");
+};
+static_assert(Lay4<128>::kSmem <= 227 * 1024 && Lay4<64>::kSmem <= 227 * 1024, "shared memory of the four-group totals kernel");
+
+template <int D>
+__global__ void __launch_bounds__(kT1Threads, 1)
+tile_totals4_tc_bf16(const __grid_constant__ CUtensorMap map_k4, const __grid_constant__ CUtensorMap map_v,
+                     float* __restrict__ ws, int64_t T, int S, int G, int tile_tokens, int heads, int* status) {
+    using Ly = Lay4<D>;
+    constexpr int DX = Ly::DX;
+    extern __shared__ uint8_t smem_raw[];
+    Ctx cx;
+    cx.sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    cx.sm_u32 = smem_u32(cx.sm);
+    cx.bars = Ly::oBars;
+    cx.abort_flag = reinterpret_cast<volatile int*>(cx.sm + Ly::oMisc + 4);
+    cx.status = status;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(cx.sm + Ly::oMisc);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int GC = G / 4;                                    // CTAs per (stream, tile)
+    const int g = (int)(blockIdx.x % (unsigned)GC) * 4;      // first bucket group of this CTA
+    const int64_t tiles = gridDim.x / GC, tile = blockIdx.x / GC, n = blockIdx.y;
+    const int64_t t_begin = tile * tile_tokens;
+    const int64_t t_end = min(T, t_begin + (int64_t)tile_tokens);
+    const int nch = (int)((t_end - t_begin + C - 1) / C);
+    float* slice = ws + (n * tiles + tile) * (int64_t)(S * (D + 1));
+    float* sliceB = slice + (int64_t)g * SG * D;
+    float* sliceA = slice + (int64_t)S * D + g * SG;
+
+    if (tid == 0) {
+        *cx.abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(cx.bar(b1Full + i), 1);
+            mbar_init(cx.bar(b1Empty + i), 4);
+            mbar_init(cx.bar(b1KvReady + i), 4);
+            mbar_init(cx.bar(b1KvFree + i), 1);
+        }
+        mbar_init(cx.bar(b1Done), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(cx.sm_u32 + Ly::oMisc), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // the constant columns d_k .. d_k + 31 of both V operand tiles: ones in column d_k, zeros after it
+    for (int i = tid; i < 2 * C * 4; i += kT1Threads) {
+        const int buf = i / (C * 4), r = (i / 4) % C, jj = i % 4;
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (jj == 0) w.x = 0x3F80u;                          // bf16 1.0 in column d_k
+        *reinterpret_cast<uint4*>(cx.sm + Ly::oVt + buf * Ly::kTileVx + off_w<DX>(r, D + 8 * jj)) = w;
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        const int wg = warp >> 2, wtid = tid & 127;
+        bool ok = true;
+        for (int c = wg; c < nch && ok; c += 2) {
+            const int st = c % kT4Stages;                    // = wg: a stage always belongs to one group
+            if (!(ok = wait_bar_warp(cx, b1Full + st, (c / kT4Stages) & 1, 111))) break;
+            if (c >= 2 && !(ok = wait_bar_warp(cx, b1KvFree + wg, ((c >> 1) - 1) & 1, 112))) break;
+            const uint8_t* stage = cx.sm + Ly::oStage + st * Ly::kStage;
+#pragma unroll
+            for (int t4 = 0; t4 < 4; ++t4)    // four staged 64 x 64 boxes -> two [64 tokens][128 buckets] pair tiles
+                copy_tile<128, false>(stage + t4 * Ly::kTileP, cx.sm + Ly::oKt + (wg * 2 + (t4 >> 1)) * Ly::kTileP2,
+                                      64 * (t4 & 1), wtid, nullptr);
+#pragma unroll
+            for (int dh = 0; dh < D / 64; ++dh)
+                copy_tile<DX, false>(stage + 4 * Ly::kTileP + dh * 8192, cx.sm + Ly::oVt + wg * Ly::kTileVx, dh * 64,
+                                     wtid, nullptr);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(cx.bar(b1KvReady + wg)); mbar_arrive(cx.bar(b1Empty + st)); }
+        }
+    } else if (warp == 8) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int c = 0; c < nch; ++c) {
+                const int st = c % kT4Stages;
+                if (c >= kT4Stages && !wait_bar(cx, b1Empty + st, ((c / kT4Stages) - 1) & 1, 311)) break;
+                const uint32_t dst = cx.sm_u32 + Ly::oStage + st * Ly::kStage;
+                const uint32_t bar = cx.bar(b1Full + st);
+                const int tok = (int)(t_begin + (int64_t)c * C);
+                mbar_arrive_expect_tx(bar, Ly::kStage);
+                tma_load_4d(dst, &map_k4, bar, 0, tok, g, (int)n);                     // one box: four column blocks
+                if (heads > 1) tma_load_5d(dst + 4 * Ly::kTileP, &map_v, bar, 0, tok, 0, (int)(n % heads), (int)(n / heads));
+                else tma_load_4d(dst + 4 * Ly::kTileP, &map_v, bar, 0, tok, 0, (int)n);
+                issued = c + 1;
+            }
+            if (*cx.abort_flag) {
+                for (int c = max(0, issued - kT4Stages); c < issued; ++c) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(b1Full + c % kT4Stages), (c / kT4Stages) & 1) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
+            }
+        }
+    } else {
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        const uint32_t smb = __shfl_sync(0xffffffffu, cx.sm_u32, 0);
+        constexpr uint32_t kI = idesc_mn(128, DX) | kAmn | kBmn;
+        if (elect_one()) {
+            bool ok = true;
+            for (int c = 0; c < nch && ok; ++c) {
+                const int wg = c & 1;
+                if (!(ok = wait_bar(cx, b1KvReady + wg, (c >> 1) & 1, 411))) break;
+                tc_fence_after();
+                const uint32_t vt_mn = lo_mn_w(smb + Ly::oVt + wg * Ly::kTileVx, Ly::kLboVx);
+#pragma unroll
+                for (int t2 = 0; t2 < 2; ++t2) {
+                    const uint32_t kt_mn = lo_mn_w(smb + Ly::oKt + (wg * 2 + t2) * Ly::kTileP2, Ly::kLboP2);
+                    if (c == 0) mma_k64<true, kHiMN, Ly::kStepP2, kHiMN, Ly::kStepVx>(tm + t2 * DX, kt_mn, vt_mn, kI);
+                    else mma_k64<false, kHiMN, Ly::kStepP2, kHiMN, Ly::kStepVx>(tm + t2 * DX, kt_mn, vt_mn, kI);
+                }
+                mma_commit(cx.bar(b1KvFree + wg));
+            }
+            mma_commit(cx.bar(b1Done));
+        }
+    }
+    __syncthreads();
+    if (warp < 4) {
+        if (wait_bar_warp(cx, b1Done, 0, 113)) {
+            const int q = lane & 3;
+            float v[32];
+#pragma unroll
+            for (int t2 = 0; t2 < 2; ++t2) {
+                // rows of the pair's accumulator = its 128 buckets on the 128 lanes; this warp reads lanes 32 w .. 32 w + 31
+                // as two 16-lane fragments
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    const int r0 = 32 * warp + 16 * h2 + (lane >> 2);            // bucket row of register half h = 0
+#pragma unroll
+                    for (int dh = 0; dh < D / 64; ++dh) {
+                        tc_fence_after();
+                        tmem_ld64(((uint32_t)(32 * warp + 16 * h2) << 16) + tmem + t2 * DX + dh * 64, v);
+                        tc_fence_before();
+#pragma unroll
+                        for (int x = 0; x < 8; ++x)
+#pragma unroll
+                            for (int h = 0; h < 2; ++h)
+                                *reinterpret_cast<float2*>(sliceB + ((int64_t)t2 * 128 + r0 + 8 * h) * D + dh * 64 + 8 * x +
+                                                           2 * q) = make_float2(v[4 * x + 2 * h], v[4 * x + 2 * h + 1]);
+                    }
+                }
+                // column d_k of the accumulator: the column sums of pK (thread = bucket row)
+                tc_fence_after();
+                tmem_ld_rows32(((uint32_t)(32 * warp) << 16) + tmem + t2 * DX + D, v);
+                tc_fence_before();
+                sliceA[t2 * 128 + 32 * warp + lane] = v[0];
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn_bf16() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -1757,7 +1946,18 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
         return cudaErrorInvalidValue;
     const int64_t tiles = (dm.T + tile_tokens - 1) / tile_tokens;
     dim3 grid((unsigned)(tiles * G), (unsigned)dm.N);
-    if (phases & kPhaseTotals) {
+    if ((phases & kPhaseTotals) && G >= 4) {
+        // four bucket groups per CTA, pair-stacked accumulators, column sums by the tensor core
+        CUtensorMap mk4;
+        if (!make_map_bf16(&mk4, pk, dm.N, dm.T, dm.S, 4)) return cudaErrorInvalidValue;
+        auto k4 = tile_totals4_tc_bf16<D>;
+        err = cudaFuncSetAttribute(k4, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay4<D>::kSmem);
+        if (err != cudaSuccess) return err;
+        dim3 grid4((unsigned)(tiles * (G / 4)), (unsigned)dm.N);
+        k4<<<grid4, kT1Threads, Lay4<D>::kSmem, stream>>>(mk4, mv, (float*)ws, dm.T, dm.S, G, tile_tokens, dm.H, status);
+        err = cudaGetLastError();
+        if (err != cudaSuccess) return err;
+    } else if (phases & kPhaseTotals) {
         dim3 grid1((unsigned)(tiles * (G / GP)), (unsigned)dm.N);
         k1<<<grid1, kT1Threads, k1_smem, stream>>>(mk2, mv, (float*)ws, dm.T, dm.S, G, tile_tokens, dm.H, status);
         err = cudaGetLastError();
