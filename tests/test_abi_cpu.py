@@ -52,6 +52,14 @@ def test_state_floats_and_support():
     assert L.race_b200_is_supported(ctypes.byref(_shape(dk=128)), 2) == 0                       # fp32 d_k=128
     assert L.race_b200_is_supported(ctypes.byref(_shape(dtype=7)), 0) == 0
     assert L.race_b200_is_supported(ctypes.byref(_shape(heads=3)), 0) == 0
+    # the heads layout of V / out: fp32 tensor kernels, bf16 tensor kernels with four or eight bucket groups
+    assert L.race_b200_is_supported(ctypes.byref(_shape(heads=4)), 0) == 1
+    assert L.race_b200_is_supported(ctypes.byref(_shape(heads=4)), 1) == 0                                   # CUDA-core path
+    assert L.race_b200_is_supported(ctypes.byref(_shape(L=8, R=64, dk=128, dtype=1, heads=4)), 0) == 1
+    assert L.race_b200_is_supported(ctypes.byref(_shape(L=4, R=64, dk=64, dtype=1, heads=2)), 2) == 1
+    assert L.race_b200_is_supported(ctypes.byref(_shape(L=2, R=64, dk=64, dtype=1, heads=2)), 0) == 0        # two groups
+    assert L.race_b200_is_supported(ctypes.byref(_shape(dtype=1, heads=2)), 0) == 0                          # one group
+    assert L.race_b200_is_supported(ctypes.byref(_shape(N=9, L=8, R=64, dk=128, dtype=1, heads=4)), 0) == 0  # 9 streams / 4
 
 
 @pytest.mark.parametrize("kw,code", [
