@@ -39,7 +39,8 @@ struct Lay {
     static constexpr int oBt = oWt + 2 * kTileP;        // [2]
     static constexpr int oTril = oBt + 2 * kTileV;
     static constexpr int oAcar = oTril + kTileP;        // [2][64] fp32
-    static constexpr int oBars = oAcar + 2 * 64 * 4;
+    static constexpr int oPq = (oAcar + 2 * 64 * 4 + 1023) / 1024 * 1024;   // [2 wg][kTileP] pQ of the group's next chunk
+    static constexpr int oBars = oPq + 2 * kTileP;
     static constexpr int kNumBars = 36;
     static constexpr int oMisc = oBars + kNumBars * 8;
     static constexpr int kSmem = oMisc + 16 + 1024;
@@ -51,7 +52,9 @@ struct Lay {
 enum BarB {
     bFull = 0, bEmpty = 2, bKReady = 4, bVReady = 6, bXReady = 8, bWReady = 10, bGReady = 12,
     bGtReady = 14, bOReady = 16, bAcar = 18, bAcarFree = 20, bBupdDone = 22, bBaccFree = 23,
-    bBtReady = 25, bDrain = 27
+    bBtReady = 25, bDrain = 27,
+    bPqFull = 29,    // [2] pQ tile of the worker group's next chunk has landed
+    bPqEmpty = 31    // [2] ... copied to registers by the four warps
 };
 
 __device__ __forceinline__ uint32_t lo_mn_w(uint32_t addr, uint32_t lbo) {
@@ -100,7 +103,7 @@ __device__ __forceinline__ void copy_tile(const uint8_t* stage, uint8_t* dst, in
 // den_t = pQ_t . A_t (a zero denominator gives a row of zeros).
 template <int D, bool kGlobal>
 __global__ void __launch_bounds__(kThreads, 1)
-causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
+causal_out_tc_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                    const float* __restrict__ ws, int64_t T, int S, int G, int tile_tokens, float eps,
                    int* status) {
@@ -143,6 +146,8 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
             mbar_init(cx.bar(bBaccFree + i), 4);
             mbar_init(cx.bar(bBtReady + i), 4);
             mbar_init(cx.bar(bDrain + i), 1);
+            mbar_init(cx.bar(bPqFull + i), 1);
+            mbar_init(cx.bar(bPqEmpty + i), 4);
         }
         mbar_init(cx.bar(bBupdDone), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -183,7 +188,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
         uint8_t* wt = cx.sm + Ly::oWt + wg * Ly::kTileP;
         __nv_bfloat16* out_n = out + n * T * D;
-        const __nv_bfloat16* pq_n = pq + n * T * S + g * SG;
+        const uint8_t* pq_tile = cx.sm + Ly::oPq + wg * Ly::kTileP;
         float v[32];
         uint32_t ov[16];   // W / masked G pairs on their way to tensor memory (d_k = 64)
         float den[2] = {1.f, 1.f};   // global form: denominators of rows rbase, rbase + 8 of the chunk
@@ -192,17 +197,23 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
         for (int c = wg; c < nch && ok; c += 2, ph ^= 1) {
             const int64_t tok0 = t_begin + (int64_t)c * C;
             const int valid = (int)min((int64_t)C, t_end - tok0);
-            // pQ in the accumulator-fragment layout (pairs of bf16), issued first
+            // pQ in the accumulator-fragment layout (pairs of bf16) from the group's TMA-staged tile ([64 tokens][64
+            // buckets], 128-byte rows, 128B swizzle: the eight rows a warp instruction reads fall on different banks; rows
+            // past the end of the sequence are zero).  The 4-byte global loads this replaces touched eight rows each.
             RACE_TRACE(wg, c >> 1, 0);
             uint32_t pqv[16];
+            if (!(ok = wait_bar_warp(cx, bPqFull + wg, ph, 105))) break;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int row = rbase + 8 * h;
-                const __nv_bfloat16* prow = pq_n + (tok0 + row) * S + 2 * q;
 #pragma unroll
                 for (int x = 0; x < 8; ++x)
-                    pqv[2 * x + h] = row < valid ? __ldg(reinterpret_cast<const unsigned int*>(prow + 8 * x)) : 0u;
+                    pqv[2 * x + h] = *reinterpret_cast<const uint32_t*>(pq_tile + row * 128 + ((x ^ (row & 7)) << 4) + 4 * q);
             }
+            // generic-proxy reads before the async-proxy write of the next tile: proxy fence, then the slot goes back
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(bPqEmpty + wg));
             // ---- W = pQ / (A + A_loc + eps) --------------------------------------------------------
             if (!(ok = wait_bar_warp(cx, bAcar + wg, ph, 102))) break;
             float acar[16];
@@ -408,7 +419,7 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
     } else if (warp == kProducerWarp) {
         // =========================== TMA producer ==============================================
         if (lane == 0) {
-            int issued = 0;
+            int issued = 0, q_issued = 0;
             for (int c = 0; c < nch; ++c) {
                 const int st = c & 1;
                 if (c >= 2 && !wait_bar(cx, bEmpty + st, ((c >> 1) - 1) & 1, 301)) break;
@@ -419,11 +430,20 @@ causal_out_tc_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__
                 tma_load_4d(dst, &map_k, bar, 0, tok, g, (int)n);
                 tma_load_4d(dst + Ly::kTileP, &map_v, bar, 0, tok, 0, (int)n);   // one box: all D / 64 column blocks
                 issued = c + 1;
+                // pQ of the chunk into the slot of its worker group (c & 1), once the group has taken chunk c - 2
+                if (c >= 2 && !wait_bar(cx, bPqEmpty + st, ((c >> 1) - 1) & 1, 302)) break;
+                mbar_arrive_expect_tx(cx.bar(bPqFull + st), Ly::kTileP);
+                tma_load_4d(cx.sm_u32 + Ly::oPq + st * Ly::kTileP, &map_q, cx.bar(bPqFull + st), 0, tok, g, (int)n);
+                q_issued = c + 1;
             }
             if (*cx.abort_flag) {
                 for (int c = max(0, issued - 2); c < issued; ++c) {
                     const long long t0 = clock64();
                     while (!mbar_try_wait(cx.bar(bFull + (c & 1)), (c >> 1) & 1) && clock64() - t0 < (1ll << 24)) {}
+                }
+                for (int c = max(0, q_issued - 2); c < q_issued; ++c) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(bPqFull + (c & 1)), (c >> 1) & 1) && clock64() - t0 < (1ll << 24)) {}
                 }
             }
         }
@@ -2000,7 +2020,9 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
     }
     err = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<D>::kSmem);
     if (err != cudaSuccess) return err;
-    k3<<<grid, kThreads, Lay<D>::kSmem, stream>>>((const __nv_bfloat16*)pq, mk, mv, (__nv_bfloat16*)out,
+    CUtensorMap mq1;
+    if (!make_map_bf16(&mq1, pq, dm.N, dm.T, dm.S)) return cudaErrorInvalidValue;
+    k3<<<grid, kThreads, Lay<D>::kSmem, stream>>>(mq1, mk, mv, (__nv_bfloat16*)out,
                                                   (const float*)ws, dm.T, dm.S, G, tile_tokens, dm.eps, status);
     return cudaGetLastError();
 }
