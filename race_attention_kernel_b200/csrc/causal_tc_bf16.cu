@@ -735,7 +735,8 @@ constexpr int DS = 32;            // head-dim slice of a CTA
 struct LayW {
     static constexpr int kTileP = C * 64 * 2;    // 64 x 64 bf16
     static constexpr int kTileS = C * DS * 2;    // 64 x 32 bf16
-    static constexpr int oStage = 0;                          // [kWStages][kTileP] staged pK
+    static constexpr int oPq = 0;                             // [2 wg][kTileP] pQ of a worker group's next item (swizzled)
+    static constexpr int oStage = oPq + 2 * kTileP;           // [kWStages][kTileP] staged pK
     static constexpr int oVst = oStage + kWStages * kTileP;   // [2][kTileS] staged V slice
     static constexpr int oKt = oVst + 2 * kTileS;             // [kWStages][kTileP]
     static constexpr int oVt = oKt + kWStages * kTileP;       // [2][kTileS]
@@ -743,7 +744,7 @@ struct LayW {
     static constexpr int oTril = oBt + 8 * kTileS;
     static constexpr int oAcar = oTril + kTileP;              // [8][64] fp32
     static constexpr int oBars = oAcar + 8 * 64 * 4;
-    static constexpr int kNumBars = 62;
+    static constexpr int kNumBars = 66;
     static constexpr int oMisc = oBars + kNumBars * 8;
     static constexpr int kSmem = oMisc + 16 + 1024;
     static constexpr uint32_t kLboS = (DS / 8) * 128;         // MN-major [64][32] tile: K-direction stride
@@ -754,11 +755,13 @@ enum BarW {
     wXReady = 24, wWReady = 26, wItemDone = 28, wBtReady = 44, wGtReady = 52, wOReady = 53,
     wOFree = 54, wDrain = 56,
     wAcarReady = 57,   // [2] the group's running A written by the warp that owns row 63
-    wAcarRead = 59     // [2] ... read by the four warps of the worker group
+    wAcarRead = 59,    // [2] ... read by the four warps of the worker group
+    wPqFull = 61,      // [2] pQ tile of the worker group's next item has landed
+    wPqEmpty = 63      // [2] ... copied to registers by the four warps
 };
 
 __global__ void __launch_bounds__(kWThreads, 1)
-causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant__ CUtensorMap map_k,
+causal_out_wide_bf16(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_vs, __nv_bfloat16* __restrict__ out,
                      const float* __restrict__ ws, int64_t T, int S, int D, int G, int tile_tokens, float eps,
                      int* status) {
@@ -801,6 +804,8 @@ causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant
             mbar_init(cx.bar(wOFree + i), 4);
             mbar_init(cx.bar(wAcarReady + i), 1);
             mbar_init(cx.bar(wAcarRead + i), 4);
+            mbar_init(cx.bar(wPqFull + i), 1);
+            mbar_init(cx.bar(wPqEmpty + i), 4);
         }
         for (int i = 0; i < 8; ++i) {
             mbar_init(cx.bar(wItemDone + i), 1);
@@ -845,29 +850,32 @@ causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
         float v[32];
         bool ok = true;
-        // pQ of an item in the accumulator-fragment layout (pairs of bf16), loaded one item of this worker
-        // group ahead: an item lasts about as long as a load from HBM takes
-        auto load_pq = [&](int i, uint32_t (&f)[16]) {
-            const int c = i / G, g = i - c * G;
-            const int64_t tok0 = t_begin + (int64_t)c * C;
-            const int valid = (int)min((int64_t)C, t_end - tok0);
+        // pQ of the group's next item: a TMA-staged [64 tokens][64 buckets] tile (128-byte rows, 128B swizzle; rows past
+        // the end of the sequence are zero) read in the accumulator-fragment layout (pairs of bf16), one item of this
+        // worker group ahead; the eight rows a warp instruction reads fall on different banks
+        const uint8_t* pq_tile = cx.sm + Ly::oPq + wg * Ly::kTileP;
+        auto take_pq = [&](int k, uint32_t (&f)[16]) -> bool {
+            if (!wait_bar_warp(cx, wPqFull + wg, (uint32_t)(k & 1), 104)) return false;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int row = rbase + 8 * h;
-                const __nv_bfloat16* prow = pq + (n * T + tok0 + row) * S + g * SG + 2 * q;
 #pragma unroll
                 for (int x = 0; x < 8; ++x)
-                    f[2 * x + h] = row < valid ? __ldg(reinterpret_cast<const unsigned int*>(prow + 8 * x)) : 0u;
+                    f[2 * x + h] = *reinterpret_cast<const uint32_t*>(pq_tile + row * 128 + ((x ^ (row & 7)) << 4) + 4 * q);
             }
+            // generic-proxy reads before the async-proxy write of the next tile: proxy fence, then the slot goes back
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cx.bar(wPqEmpty + wg));
+            return true;
         };
         uint32_t pq_next[16];
-        if (wg < nitems) load_pq(wg, pq_next);
+        if (wg < nitems) ok = take_pq(0, pq_next);
         for (int i = wg, k = 0; i < nitems && ok; i += 2, ++k) {
             const int c = i / G, g = i - c * G;
             uint32_t pqv[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) pqv[j] = pq_next[j];
-            if (i + 2 < nitems) load_pq(i + 2, pq_next);
             // running A of the group: written at the end of the previous item of this worker group
             // (which is the same bucket group when G = 2)
             if (!(ok = wait_bar_warp(cx, wAcarReady + wg, (uint32_t)((k & 1) ^ 1), 101))) break;
@@ -911,6 +919,7 @@ causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant
                 if (w == 3) mbar_arrive(cx.bar(wAcarReady + wg));   // the new running A is in place
             }
             if (w == 0) RACE_TRACE(wg, i - 64, 3);
+            if (i + 2 < nitems && !(ok = take_pq(k + 1, pq_next))) break;
         }
     } else if (warp < 12) {
         // =========================== converter warpgroup ==========================================
@@ -1036,7 +1045,7 @@ causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant
     } else if (warp == kWProducerWarp) {
         // =========================== TMA producer ==================================================
         if (lane == 0) {
-            int issued = 0, v_issued = 0;
+            int issued = 0, v_issued = 0, q_issued = 0;
             for (int i = 0; i < nitems; ++i) {
                 const int c = i / G, g = i - c * G, st = i % kWStages;
                 const int tok = (int)(t_begin + (int64_t)c * C);
@@ -1051,8 +1060,20 @@ causal_out_wide_bf16(const __nv_bfloat16* __restrict__ pq, const __grid_constant
                     tma_load_4d(cx.sm_u32 + Ly::oVst + vb * Ly::kTileS, &map_vs, cx.bar(wVFull + vb), 0, tok, js, (int)n);
                     v_issued = c + 1;
                 }
+                {   // pQ of the item into the slot of its worker group, once the group has taken the tile before it
+                    const int qs = i & 1, qu = i >> 1;
+                    if (qu >= 1 && !wait_bar(cx, wPqEmpty + qs, (uint32_t)((qu - 1) & 1), 303)) break;
+                    mbar_arrive_expect_tx(cx.bar(wPqFull + qs), Ly::kTileP);
+                    tma_load_4d(cx.sm_u32 + Ly::oPq + qs * Ly::kTileP, &map_q, cx.bar(wPqFull + qs), 0, tok, g, (int)n);
+                    q_issued = i + 1;
+                }
             }
             if (*cx.abort_flag) {   // copies in flight must land before the CTA may exit
+                for (int i = max(0, q_issued - 2); i < q_issued; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(cx.bar(wPqFull + (i & 1)), (uint32_t)((i >> 1) & 1)) &&
+                           clock64() - t0 < (1ll << 24)) {}
+                }
                 for (int i = max(0, issued - kWStages); i < issued; ++i) {
                     const long long t0 = clock64();
                     while (!mbar_try_wait(cx.bar(wFull + i % kWStages), (uint32_t)((i / kWStages) & 1)) &&
@@ -2013,8 +2034,10 @@ cudaError_t launch_bf16(const void* pq, const void* pk, const void* v, void* out
         dim3 wgrid((unsigned)(tiles * (D / DS)), (unsigned)dm.N);
         err = cudaFuncSetAttribute(causal_out_wide_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, LayW::kSmem);
         if (err != cudaSuccess) return err;
+        CUtensorMap mq2;
+        if (!make_map_bf16(&mq2, pq, dm.N, dm.T, dm.S)) return cudaErrorInvalidValue;
         causal_out_wide_bf16<<<wgrid, kWThreads, LayW::kSmem, stream>>>(
-            (const __nv_bfloat16*)pq, mk, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
+            mq2, mk, mvs, (__nv_bfloat16*)out, (const float*)ws, dm.T, dm.S, D, G, tile_tokens,
             dm.eps, status);
         return cudaGetLastError();
     }
